@@ -1,0 +1,151 @@
+// Embedding lookup, residual add + RMSNorm, SwiGLU product, finite check and
+// the counter-based normal fill used for random weights.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// x[n, :] = float(table[ids[n], :]); the residual stream is 32-bit in every mode.
+template <typename TW>
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
+                                    int n_tokens, int width, int vocab, int* __restrict__ status) {
+    const int n = blockIdx.x;
+    if (n >= n_tokens) return;
+    int id = ids[n];
+    if (id < 0 || id >= vocab) {       // never read outside the table
+        if (threadIdx.x == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+        id = 0;
+    }
+    const TW* row = table + (size_t)id * width;
+    float* out = x + (size_t)n * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_f32(row[i]);
+}
+
+ESP_API int esp_embed_gather(const void* table, int table_is_bf16, const int* ids, float* x, int n_tokens, int width,
+                             int vocab, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (table_is_bf16)
+        embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>((const bf16*)table, ids, x, n_tokens, width, vocab, status);
+    else
+        embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, x, n_tokens, width, vocab, status);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- add + RMSNorm
+// Row r works on source row s = rows ? rows[r] : r.
+//   v = x[s] + (y ? y[s] : 0);  if (write_x) x[s] = v;
+//   h[r] = v * (1 / sqrt(mean(v^2) + eps)) * gamma       (all in 32-bit)
+// The sum of squares is taken per thread in index order and combined by a
+// fixed tree, so a row's result does not depend on the rest of the batch.
+template <typename TH>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma,
+                                   const int* __restrict__ rows, TH* __restrict__ h, int width, float eps, int write_x) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = x + s * width;
+    const float* yr = y ? y + s * width : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = xr[i];
+        if (yr) {
+            v += yr[i];
+            if (write_x) xr[i] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    TH* hr = h + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = xr[i];
+        if (yr && !write_x) v += yr[i];
+        hr[i] = from_f32<TH>(v * inv * gamma[i]);
+    }
+}
+
+ESP_API int esp_add_rmsnorm(float* x, const float* y, const float* gamma, const int* rows, void* h, int h_is_bf16,
+                            int n_rows, int width, float eps, int write_x, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (h_is_bf16)
+        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (bf16*)h, width, eps, write_x);
+    else
+        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (float*)h, width, eps, write_x);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- SwiGLU product
+// act[m, i] = silu(gu[m, i]) * gu[m, inter + i], gu being [rows, 2*inter] in 32-bit.
+template <typename TO>
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ act, long long rows, int inter) {
+    const long long total = rows * inter;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long m = idx / inter;
+        const int i = (int)(idx - m * inter);
+        const float g = gu[m * 2 * inter + i];
+        const float u = gu[m * 2 * inter + inter + i];
+        act[idx] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+ESP_API int esp_swiglu(const float* gu, void* act, int act_is_bf16, long long rows, int inter, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const long long total = rows * inter;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    if (act_is_bf16)
+        swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>(gu, (bf16*)act, rows, inter);
+    else
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gu, (float*)act, rows, inter);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- finite check
+__global__ void finite_check_kernel(const float* __restrict__ v, long long count, int* __restrict__ status) {
+    bool bad = false;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+        bad |= !isfinite(v[i]);
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, ESP_STATUS_LOGITS_NONFINITE);
+}
+
+ESP_API int esp_finite_check(const float* v, long long count, int* status, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    finite_check_kernel<<<(int)blocks, 256, 0, stream>>>(v, count, status);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- random normal fill
+// value(i) = mean + std * z(i), z from a counter-based generator: two 64-bit
+// mixes of (key + i) give two uniforms, Box-Muller gives the normal.  The value
+// of an element depends on (key, i) only, not on the launch shape.
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void normal_fill_kernel(T* __restrict__ out, long long count, unsigned long long key, float mean, float stddev) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        const unsigned long long a = mix64(key + 2ull * (unsigned long long)i);
+        const unsigned long long b = mix64(key + 2ull * (unsigned long long)i + 1ull);
+        const float u1 = ((float)(a >> 40) + 1.0f) * (1.0f / 16777216.0f);   // (0, 1]
+        const float u2 = (float)(b >> 40) * (1.0f / 16777216.0f);            // [0, 1)
+        const float z = sqrtf(-2.0f * logf(u1)) * cosf(6.283185307179586f * u2);
+        out[i] = from_f32<T>(mean + stddev * z);
+    }
+}
+
+ESP_API int esp_normal_fill(void* out, int out_is_bf16, long long count, unsigned long long key, float mean, float stddev,
+                            cudaStream_t stream) {
+    if (count <= 0) return 0;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (out_is_bf16)
+        normal_fill_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((bf16*)out, count, key, mean, stddev);
+    else
+        normal_fill_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, count, key, mean, stddev);
+    return esp_launch_status();
+}

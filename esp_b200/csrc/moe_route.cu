@@ -1,0 +1,209 @@
+// Routing for the sparse feed-forward block: router logits, softmax, top-k and
+// the shared expert's sigmoid gate in 32-bit; the permutation of (token, rank)
+// pairs into expert order; and the ordered sum that brings expert outputs back
+// to token order.  Nothing here returns to the host.
+#include "common.cuh"
+
+namespace {
+constexpr int ROUTER_THREADS = 256;
+constexpr int MAX_TOPK = 32;
+
+// One block per token.  logits[e] = sum_k h[k] * Wr[e][k]: a warp per expert,
+// lanes stride over k, partial sums combined by the fixed warp butterfly.
+// p = softmax(logits) over all experts; the k largest p win, ties to the lower
+// id; weights are p / (sum of the chosen p) if norm_topk else p.
+// gate[n] = sigmoid(h . w_gate) when w_gate is given.
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, const TW* __restrict__ w_gate,
+                   int* __restrict__ topk_ids, float* __restrict__ topk_w, float* __restrict__ gate,
+                   float* __restrict__ probs_out, int width, int n_experts, int top_k, int norm_topk,
+                   int* __restrict__ status) {
+    extern __shared__ float smem[];
+    float* hs = smem;                    // [width]
+    float* ps = smem + width;            // [n_experts]
+    __shared__ float scratch[33];
+    __shared__ int chosen[MAX_TOPK];
+    __shared__ float chosen_p[MAX_TOPK];
+    const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = ROUTER_THREADS / 32;
+    const TH* hr = h + (size_t)n * width;
+    for (int i = tid; i < width; i += ROUTER_THREADS) hs[i] = to_f32(hr[i]);
+    __syncthreads();
+    for (int e = warp; e < n_experts + (w_gate ? 1 : 0); e += nwarp) {
+        const TW* wr = e < n_experts ? w_router + (size_t)e * width : w_gate;
+        float s = 0.f;
+        for (int i = lane; i < width; i += 32) s = fmaf(hs[i], to_f32(wr[i]), s);
+        s = warp_sum(s);
+        if (lane == 0) {
+            if (e < n_experts) ps[e] = s;
+            else gate[n] = 1.0f / (1.0f + expf(-s));
+        }
+    }
+    __syncthreads();
+    float lm = -INFINITY;
+    for (int e = tid; e < n_experts; e += ROUTER_THREADS) lm = fmaxf(lm, ps[e]);
+    const float mx = block_max(lm, scratch);
+    float ls = 0.f;
+    for (int e = tid; e < n_experts; e += ROUTER_THREADS) {
+        const float p = expf(ps[e] - mx);
+        ps[e] = p;
+        ls += p;
+    }
+    const float total = block_sum(ls, scratch);
+    for (int e = tid; e < n_experts; e += ROUTER_THREADS) {
+        const float p = ps[e] / total;
+        ps[e] = p;
+        if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
+    }
+    __syncthreads();
+    // top-k by repeated arg-max in warp 0 (k and E are small); ties go to the lower id
+    if (warp == 0) {
+        bool bad = false;
+        float mass = 0.f;
+        for (int r = 0; r < top_k; r++) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+            for (int e = lane; e < n_experts; e += 32) {
+                const float p = ps[e];
+                if (!(p == p) || isinf(p)) bad = true;
+                if (p > best) { best = p; best_e = e; }   // ascending e per lane: the first maximum is the lowest id
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+            }
+            if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
+            if (lane == 0) {
+                chosen[r] = best_e;
+                chosen_p[r] = best;
+                ps[best_e] = -1.0f;           // probabilities are >= 0: taken out of the running
+            }
+            mass += best;
+            __syncwarp();
+        }
+        const float denom = norm_topk ? mass : 1.0f;
+        if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
+            if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
+        }
+        for (int r = lane; r < top_k; r += 32) {
+            topk_ids[(size_t)n * top_k + r] = chosen[r];
+            topk_w[(size_t)n * top_k + r] = chosen_p[r] / denom;
+        }
+    }
+}
+
+// One block.  counts -> exclusive offsets -> placement of every (token, rank)
+// pair into its expert's range.  Which row of its expert's range a pair lands
+// in is left to the atomics; a row's arithmetic never depends on where it sits.
+__global__ void __launch_bounds__(1024)
+moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ topk_w, int n_pairs, int n_experts,
+                   int* __restrict__ offsets, int* __restrict__ perm_token, float* __restrict__ perm_weight,
+                   int* __restrict__ inverse, int top_k, int* __restrict__ status) {
+    extern __shared__ int sm[];
+    int* counts = sm;                      // [n_experts]
+    int* cursor = sm + n_experts;          // [n_experts + 1]
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = topk_ids[i];
+        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+        else atomicOr(status, ESP_STATUS_BAD_INDEX);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_experts; e++) {
+            cursor[e] = run;
+            offsets[e] = run;
+            run += counts[e];
+        }
+        cursor[n_experts] = run;
+        offsets[n_experts] = run;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = topk_ids[i];
+        if (e < 0 || e >= n_experts) { inverse[i] = -1; continue; }
+        const int row = atomicAdd(&cursor[e], 1);
+        perm_token[row] = i / top_k;
+        perm_weight[row] = topk_w[i];
+        inverse[i] = row;
+    }
+}
+
+// y[t, :] = sum over the token's chosen experts, in ascending expert id, of
+// expert_out[inverse[t, r], :] (already scaled by the routing weight), then
+// + gate[t] * shared[t, :].
+__global__ void moe_combine_kernel(const float* __restrict__ expert_out, const int* __restrict__ topk_ids,
+                                   const int* __restrict__ inverse, const float* __restrict__ gate,
+                                   const float* __restrict__ shared, float* __restrict__ y, int width, int top_k) {
+    __shared__ int order[MAX_TOPK];
+    const int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        int ids[MAX_TOPK];
+        for (int r = 0; r < top_k; r++) { ids[r] = topk_ids[(size_t)t * top_k + r]; order[r] = r; }
+        for (int a = 1; a < top_k; a++) {          // insertion sort of ranks by expert id
+            const int oa = order[a], ia = ids[oa];
+            int b = a - 1;
+            while (b >= 0 && ids[order[b]] > ia) { order[b + 1] = order[b]; b--; }
+            order[b + 1] = oa;
+        }
+        for (int r = 0; r < top_k; r++) order[r] = inverse[(size_t)t * top_k + order[r]];
+    }
+    __syncthreads();
+    const float g = gate ? gate[t] : 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float acc = 0.f;
+        for (int r = 0; r < top_k; r++) {
+            const int row = order[r];
+            if (row >= 0) acc += expert_out[(size_t)row * width + i];
+        }
+        if (shared) acc += g * shared[(size_t)t * width + i];
+        y[(size_t)t * width + i] = acc;
+    }
+}
+}  // namespace
+
+ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, const void* w_gate, int w_is_bf16,
+                            int* topk_ids, float* topk_w, float* gate, float* probs_out, int n_tokens, int width,
+                            int n_experts, int top_k, int norm_topk, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)(width + n_experts) * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+#define ESP_ROUTER(TH, TW)                                                                                          \
+    do {                                                                                                            \
+        if (smem > 48 * 1024)                                                                                       \
+            cudaFuncSetAttribute(router_topk_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        router_topk_kernel<TH, TW><<<n_tokens, ROUTER_THREADS, smem, stream>>>(                                      \
+            (const TH*)h, (const TW*)w_router, (const TW*)w_gate, topk_ids, topk_w, gate, probs_out, width,         \
+            n_experts, top_k, norm_topk, status);                                                                   \
+    } while (0)
+    if (h_is_bf16 && w_is_bf16) ESP_ROUTER(bf16, bf16);
+    else if (h_is_bf16) ESP_ROUTER(bf16, float);
+    else if (w_is_bf16) ESP_ROUTER(float, bf16);
+    else ESP_ROUTER(float, float);
+#undef ESP_ROUTER
+    return esp_launch_status();
+}
+
+ESP_API int esp_moe_permute(const int* topk_ids, const float* topk_w, int n_tokens, int top_k, int n_experts,
+                            int* offsets, int* perm_token, float* perm_weight, int* inverse, int* status,
+                            cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    moe_permute_kernel<<<1, 1024, smem, stream>>>(topk_ids, topk_w, n_tokens * top_k, n_experts, offsets, perm_token,
+                                                  perm_weight, inverse, top_k, status);
+    return esp_launch_status();
+}
+
+ESP_API int esp_moe_combine(const float* expert_out, const int* topk_ids, const int* inverse, const float* gate,
+                            const float* shared, float* y, int n_tokens, int width, int top_k, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top_k > MAX_TOPK) return (int)cudaErrorInvalidValue;
+    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(expert_out, topk_ids, inverse, gate, shared, y, width, top_k);
+    return esp_launch_status();
+}

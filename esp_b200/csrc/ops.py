@@ -1,0 +1,216 @@
+"""Python faces of the compiled kernels.
+
+Every function here checks what it is given (device, dtype, contiguity, the
+sizes the kernel takes), launches on torch's current stream and raises
+``Backend`` if the launch is refused.  There is no other implementation behind
+these functions: without the compiled library they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from ..errors import Backend
+from .build import load_library
+
+P = c_void_p
+
+_SIGNATURES = {
+    "esp_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, P, P],
+    "esp_add_rmsnorm": [P, P, P, P, P, c_int, c_int, c_int, c_float, c_int, P],
+    "esp_swiglu": [P, P, c_int, c_longlong, c_int, P],
+    "esp_finite_check": [P, c_longlong, P, P],
+    "esp_normal_fill": [P, c_int, c_longlong, c_ulonglong, c_float, c_float, P],
+    "esp_gemm_simt": [P, c_int, P, P, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, P],
+    "esp_rope_kvwrite": [P, P, P, P, P, P, c_int, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                         c_int, c_int, P, P],
+    "esp_attn_simt": [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P],
+    "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
+    "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
+}
+
+_bound: dict = {}
+
+
+def _fn(library: str, name: str):
+    f = _bound.get(name)
+    if f is None:
+        lib = load_library(library)
+        try:
+            f = getattr(lib, name)
+        except AttributeError:
+            raise Backend(f"the compiled library '{library}' has no entry point {name}") from None
+        f.argtypes = _SIGNATURES[name]
+        f.restype = c_int
+        _bound[name] = f
+    return f
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise Backend(f"{what}: the launch was refused with CUDA error {code} "
+                      f"(invalid value means a size this kernel does not take)")
+
+
+def _ptr(t, dtype=None, what="tensor"):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise Backend(f"{what} must live on the GPU; this library has no CPU path")
+    if not t.is_contiguous():
+        raise Backend(f"{what} must be contiguous")
+    if dtype is not None and t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+        raise Backend(f"{what} has dtype {t.dtype}, expected {dtype}")
+    return t.data_ptr()
+
+
+FLOATS = (torch.float32, torch.bfloat16)
+
+
+def _is_bf16(t) -> int:
+    return 1 if t.dtype == torch.bfloat16 else 0
+
+
+# ---------------------------------------------------------------------------
+
+def embed_gather(table, ids, x, status):
+    """x[n] = float(table[ids[n]]); ids int32 [N], x float32 [N, H]."""
+    n, width = x.shape
+    _check(_fn("core", "esp_embed_gather")(
+        _ptr(table, FLOATS, "embedding table"), _is_bf16(table), _ptr(ids, torch.int32, "ids"),
+        _ptr(x, torch.float32, "x"), n, width, table.shape[0], _ptr(status, torch.int32), _stream()), "embed_gather")
+
+
+def add_rmsnorm(x, y, gamma, h, eps, rows=None, write_x=True):
+    """h = rmsnorm(x + y) * gamma with x (+= y when write_x) float32, gamma
+    float32, h float32 or bfloat16.  ``rows`` (int32) selects source rows."""
+    n_rows = h.shape[0]
+    width = h.shape[1]
+    if x.shape[1] != width or gamma.shape[0] != width:
+        raise Backend("add_rmsnorm: widths disagree")
+    _check(_fn("core", "esp_add_rmsnorm")(
+        _ptr(x, torch.float32, "x"), _ptr(y, torch.float32, "y"), _ptr(gamma, torch.float32, "gamma"),
+        _ptr(rows, torch.int32, "rows"), _ptr(h, FLOATS, "h"), _is_bf16(h), n_rows, width, float(eps),
+        1 if write_x else 0, _stream()), "add_rmsnorm")
+
+
+def swiglu(gu, act):
+    """act[m, i] = silu(gu[m, i]) * gu[m, I + i]; gu float32 [M, 2I]."""
+    rows, inter = act.shape
+    if gu.shape[0] < rows or gu.shape[1] != 2 * inter:
+        raise Backend("swiglu: gu must be [rows, 2 * intermediate]")
+    _check(_fn("core", "esp_swiglu")(_ptr(gu, torch.float32, "gu"), _ptr(act, FLOATS, "act"), _is_bf16(act), rows,
+                                     inter, _stream()), "swiglu")
+
+
+def finite_check(values, status):
+    _check(_fn("core", "esp_finite_check")(_ptr(values, torch.float32, "values"), values.numel(),
+                                           _ptr(status, torch.int32), _stream()), "finite_check")
+
+
+def normal_fill(out, key: int, mean: float, std: float):
+    """out[i] = mean + std * z(key, i), z standard normal, counter-based."""
+    _check(_fn("core", "esp_normal_fill")(_ptr(out, FLOATS, "out"), _is_bf16(out), out.numel(),
+                                          key & 0xFFFFFFFFFFFFFFFF, float(mean), float(std), _stream()), "normal_fill")
+
+
+def gemm_simt(a, w, c, bias=None, row_scale=None, a_rows=None, group_offsets=None, rows=None):
+    """c[m, :] = (a[a_rows[m] or m, :] @ w[g].T + bias) * row_scale[m] with true
+    32-bit multiply-adds.  ``w`` is [N, K] or, grouped, [G, N, K] with
+    ``group_offsets`` int32 [G+1] over the rows.  ``rows``: how many rows of c to
+    compute (default: all of c)."""
+    grouped = group_offsets is not None
+    if grouped:
+        groups, n, k = w.shape
+    else:
+        groups = 1
+        n, k = w.shape
+    m = c.shape[0] if rows is None else rows
+    if a.shape[-1] != k or c.shape[-1] != n:
+        raise Backend(f"gemm: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, c {tuple(c.shape)}")
+    if a.stride(-1) != 1 or c.stride(-1) != 1 or not w.is_contiguous():
+        raise Backend("gemm: operands must be row-major")
+    code = _fn("core", "esp_gemm_simt")(
+        a.data_ptr(), _is_bf16(a), _ptr(a_rows, torch.int32, "a_rows"), w.data_ptr(), _is_bf16(w),
+        _ptr(bias, torch.float32, "bias"), _ptr(row_scale, torch.float32, "row_scale"), c.data_ptr(), _is_bf16(c),
+        _ptr(group_offsets, torch.int32, "group_offsets"), groups, m, n, k, a.stride(0), c.stride(0), _stream())
+    _check(code, "gemm_simt")
+
+
+def rope_kvwrite(qkv, bias, tok_seq, tok_pos, cos, sin, rot, q_out, k_cache, v_cache, block_table, page, nh, nkv, hd,
+                 write_kv, status):
+    """Add the bias, rotate queries and keys (split-half, 32-bit) and store keys
+    and values in the paged cache.  k_cache/v_cache: [pages, nkv, page, hd]."""
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * hd:
+        raise Backend("rope_kvwrite: qkv width disagrees with the head counts")
+    n_pages = k_cache.shape[0] if k_cache is not None else 0
+    _check(_fn("core", "esp_rope_kvwrite")(
+        _ptr(qkv, torch.float32, "qkv"), _ptr(bias, torch.float32, "bias"), _ptr(tok_seq, torch.int32),
+        _ptr(tok_pos, torch.int32), _ptr(cos, torch.float32), _ptr(sin, torch.float32), rot, cos.shape[0] if cos is not None else (1 << 30),
+        _ptr(q_out, FLOATS, "q_out"), _ptr(k_cache, FLOATS), _ptr(v_cache, FLOATS), _is_bf16(q_out),
+        _ptr(block_table, torch.int32), block_table.shape[1] if block_table is not None else 0, n_pages, page, n,
+        nh, nkv, hd, 1 if write_kv else 0, _ptr(status, torch.int32), _stream()), "rope_kvwrite")
+
+
+def attn_simt(q, k_cache, v_cache, out, tok_seq, tok_pos, block_table, page, nh, nkv, hd, window, status):
+    """Attention of every token over its sequence's cached keys (32-bit arithmetic)."""
+    if hd > 256:
+        raise Backend(f"attention: head size {hd} is beyond the 256 this kernel takes")
+    _check(_fn("core", "esp_attn_simt")(
+        _ptr(q, FLOATS, "q"), _ptr(k_cache, FLOATS), _ptr(v_cache, FLOATS), _ptr(out, FLOATS), _is_bf16(q),
+        _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
+        k_cache.shape[0], page, q.shape[0], nh, nkv, hd, int(window or 0), _ptr(status, torch.int32), _stream()),
+        "attn_simt")
+
+
+def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, status, probs_out=None):
+    n, width = h.shape
+    n_experts = w_router.shape[0]
+    if top_k > 32:
+        raise Backend(f"router: top-k {top_k} is beyond the 32 this kernel takes")
+    if (width + n_experts) * 4 > 200 * 1024:
+        raise Backend(f"router: width {width} + experts {n_experts} do not fit the kernel's shared memory")
+    if w_gate is not None and w_gate.dtype != w_router.dtype:
+        raise Backend("router: router and shared-gate weights must share a dtype")
+    _check(_fn("core", "esp_router_topk")(
+        _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(w_router, FLOATS), _ptr(w_gate, FLOATS), _is_bf16(w_router),
+        _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32), _ptr(gate, torch.float32),
+        _ptr(probs_out, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
+        _ptr(status, torch.int32), _stream()), "router_topk")
+
+
+def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, inverse, status):
+    n, top_k = topk_ids.shape
+    if (2 * n_experts + 1) * 4 > 48 * 1024:
+        raise Backend(f"moe_permute: {n_experts} experts are beyond what this kernel takes")
+    _check(_fn("core", "esp_moe_permute")(
+        _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32), n, top_k, n_experts, _ptr(offsets, torch.int32),
+        _ptr(perm_token, torch.int32), _ptr(perm_weight, torch.float32), _ptr(inverse, torch.int32),
+        _ptr(status, torch.int32), _stream()), "moe_permute")
+
+
+def moe_combine(expert_out, topk_ids, inverse, gate, shared, y):
+    n, width = y.shape
+    _check(_fn("core", "esp_moe_combine")(
+        _ptr(expert_out, torch.float32), _ptr(topk_ids, torch.int32), _ptr(inverse, torch.int32),
+        _ptr(gate, torch.float32), _ptr(shared, torch.float32), _ptr(y, torch.float32), n, width, topk_ids.shape[1],
+        _stream()), "moe_combine")
+
+
+def pick_tokens(logits, temperature, top_p, rng_state, row_slot, tokens):
+    """tokens[r] = arg-max of row r when temperature[r] == 0 (or temperature is
+    None), else a draw from the row's own splitmix64 stream rng_state[row_slot[r]]
+    (int64 storage read as unsigned)."""
+    n, vocab = logits.shape
+    _check(_fn("core", "esp_pick_tokens")(
+        _ptr(logits, torch.float32, "logits"), n, vocab, _ptr(temperature, torch.float32), _ptr(top_p, torch.float32),
+        _ptr(rng_state, torch.int64), _ptr(row_slot, torch.int32), _ptr(tokens, torch.int32), _stream()), "pick_tokens")

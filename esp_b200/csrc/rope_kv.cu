@@ -1,0 +1,87 @@
+// Rotary position encoding (split-half) of the new queries and keys in 32-bit,
+// and the write of the new keys and values into the paged cache.
+//
+// qkv: [n_tokens, (nh + 2*nkv) * hd] float; ``bias`` (same width, may be null) is
+// added first.  Head h of the
+// query block is columns [h*hd, (h+1)*hd); keys follow the queries, values the
+// keys.  For i < rot/2 and the token's absolute position p:
+//   o[i]         = x[i] * cos[p][i] - x[i + rot/2] * sin[p][i]
+//   o[i + rot/2] = x[i + rot/2] * cos[p][i] + x[i] * sin[p][i]
+// Columns at or beyond ``rot`` pass through (rot = 0: no rotation at all).
+// Keys are cached after rotation.  A page holds PAGE consecutive positions of
+// one sequence: K/V are [pages, nkv, PAGE, hd]; the page of position p is
+// block_table[seq * table_stride + p / PAGE].
+#include "common.cuh"
+
+template <typename T>
+__global__ void rope_kvwrite_kernel(const float* __restrict__ qkv, const float* __restrict__ bias,
+                                    const int* __restrict__ tok_seq,
+                                    const int* __restrict__ tok_pos, const float* __restrict__ cos_t,
+                                    const float* __restrict__ sin_t, int rot, int max_pos, T* __restrict__ q_out,
+                                    T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ block_table,
+                                    int table_stride, int n_pages, int page, int nh, int nkv, int hd, int write_kv,
+                                    int* __restrict__ status) {
+    const int n = blockIdx.x;
+    const int pos = tok_pos[n];
+    const int seq = tok_seq[n];
+    const int half = rot / 2;
+    const int width = (nh + 2 * nkv) * hd;
+    const float* src = qkv + (size_t)n * width;
+    if (pos < 0 || pos >= max_pos) {
+        if (threadIdx.x == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+        return;
+    }
+    const float* cs = cos_t + (size_t)pos * half;
+    const float* sn = sin_t + (size_t)pos * half;
+    int page_id = -1;
+    if (write_kv) {
+        page_id = block_table[(size_t)seq * table_stride + pos / page];
+        if (page_id < 0 || page_id >= n_pages) {
+            if (threadIdx.x == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+            page_id = -1;
+        }
+    }
+    const int in_page = pos % page;
+    const int heads = nh + 2 * nkv;
+    for (int idx = threadIdx.x; idx < heads * hd; idx += blockDim.x) {
+        const int head = idx / hd, i = idx - head * hd;
+        const float* x = src + (size_t)head * hd;
+        const float* b = bias ? bias + (size_t)head * hd : nullptr;
+        float v = x[i] + (b ? b[i] : 0.f);
+        if (head < nh + nkv && i < rot) {          // queries and keys rotate, values do not
+            if (i < half) {
+                const float other = x[i + half] + (b ? b[i + half] : 0.f);
+                v = v * cs[i] - other * sn[i];
+            } else {
+                const float other = x[i - half] + (b ? b[i - half] : 0.f);
+                v = v * cs[i - half] + other * sn[i - half];
+            }
+        }
+        if (head < nh) {
+            q_out[(size_t)n * nh * hd + idx] = from_f32<T>(v);
+        } else if (page_id >= 0) {
+            const bool is_k = head < nh + nkv;
+            const int kvh = is_k ? head - nh : head - nh - nkv;
+            T* dst = (is_k ? k_cache : v_cache) + (((size_t)page_id * nkv + kvh) * page + in_page) * hd + i;
+            *dst = from_f32<T>(v);
+        }
+    }
+}
+
+ESP_API int esp_rope_kvwrite(const float* qkv, const float* bias, const int* tok_seq, const int* tok_pos, const float* cos_t,
+                             const float* sin_t, int rot, int max_pos, void* q_out, void* k_cache, void* v_cache,
+                             int is_bf16, const int* block_table, int table_stride, int n_pages, int page, int n_tokens,
+                             int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (rot < 0 || rot > hd || (rot & 1)) return (int)cudaErrorInvalidValue;
+    if (is_bf16)
+        rope_kvwrite_kernel<bf16><<<n_tokens, 256, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
+                                                               (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, block_table,
+                                                               table_stride, n_pages, page, nh, nkv, hd, write_kv, status);
+    else
+        rope_kvwrite_kernel<float><<<n_tokens, 256, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
+                                                                (float*)q_out, (float*)k_cache, (float*)v_cache,
+                                                                block_table, table_stride, n_pages, page, nh, nkv, hd,
+                                                                write_kv, status);
+    return esp_launch_status();
+}

@@ -1,0 +1,190 @@
+"""The engine: a model, its cache and the one step function.
+
+``step`` takes a batch of sequences, each with the tokens it brings now (a
+whole prompt, one decoded token, or any run in between), runs exactly those
+tokens as one packed batch from what the cache holds, appends their keys and
+values, and returns the logits at the places asked for.  There is no padding:
+token rows are packed back to back and every kernel works on rows.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..cache import Cache
+from ..config import config_from_json
+from ..errors import Backend, InvalidRequest
+from ..parts import Runtime, StepContext
+from ..weights import FolderSource, InitSpec, RandomSource, load_into
+from .model import DecoderModel
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        return name
+    if name not in DTYPES:
+        raise InvalidRequest(f"dtype must be one of {sorted(DTYPES)}, got {name!r}")
+    return DTYPES[name]
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: list
+    want: list = field(default_factory=list)     # places among ``tokens`` whose logits are wanted
+
+
+class Engine:
+    def __init__(self, config, source_factory, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
+                 max_slots: Optional[int] = None):
+        """``source_factory(specs) -> source``: gives the loader its tensors."""
+        self.config = config
+        self.plan = config.plan()
+        self.dtype = parse_dtype(dtype)
+        if not torch.cuda.is_available():
+            raise Backend("no CUDA device is visible; esp_b200 has no CPU path")
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+        self.rt = Runtime(device, self.dtype)
+        with torch.cuda.device(self.rt.device):
+            self.model = DecoderModel(self.plan, self.rt)
+            specs = [s for part in self.model.all_parts() for s in part.param_specs()]
+            load_into(self.model, source_factory(specs), self.rt)
+            n_pages = (max_tokens + 63) // 64
+            if max_slots is None:
+                max_slots = max(1, min(n_pages, 4096))
+            self.max_slots = max_slots
+            self.cache = Cache(self.model.cache_requests(), max_tokens, max_slots, self.plan.max_positions,
+                               self.dtype, self.rt.device)
+        self._pinned = None
+        self._pinned_event = None
+        self._meta_dev = None
+        self.steps_run = 0
+
+    # -- construction ---------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder, **kw) -> "Engine":
+        folder = Path(folder)
+        config = config_from_json(folder)
+        return cls(config, lambda specs: FolderSource(folder), **kw)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, init: InitSpec = InitSpec(), stored_dtype=None, **kw) -> "Engine":
+        dt = parse_dtype(kw.get("dtype", "bfloat16")) if stored_dtype is None else parse_dtype(stored_dtype)
+        return cls(config, lambda specs: RandomSource(specs, seed, init, dt), **kw)
+
+    # -- slots -----------------------------------------------------------------
+    def open(self) -> int:
+        with torch.cuda.device(self.rt.device):
+            return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.book.length(slot)
+
+    # -- the step ----------------------------------------------------------------
+    def _stage(self, arrays: list):
+        """Packs int32 arrays into one pinned buffer, copies it to the device in
+        one transfer and returns device views in the same order."""
+        offsets, total = [], 0
+        for a in arrays:
+            offsets.append(total)
+            total += (a.size + 3) // 4 * 4          # keep every section 16-byte aligned
+        total = max(total, 4)
+        if self._pinned is None or self._pinned.numel() < total:
+            cap = max(total, 1 << 16)
+            self._pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.rt.device)
+            self._pinned_event = None
+        if self._pinned_event is not None:
+            self._pinned_event.synchronize()         # the last copy out of the pinned buffer is done
+        host = self._pinned.numpy()
+        for a, off in zip(arrays, offsets):
+            host[off:off + a.size] = a.reshape(-1)
+        self._meta_dev[:total].copy_(self._pinned[:total], non_blocking=True)
+        self._pinned_event = torch.cuda.Event()
+        self._pinned_event.record()
+        return [self._meta_dev[off:off + a.size].view(a.shape) for a, off in zip(arrays, offsets)]
+
+    def plan_step(self, entries: list):
+        """Validates a step against the cache without changing anything and
+        returns the host-side arrays."""
+        if not entries:
+            raise InvalidRequest("a step needs at least one entry")
+        book = self.cache.book
+        slots = [e.slot for e in entries]
+        if len(set(slots)) != len(slots):
+            raise InvalidRequest("a slot appears twice in one step")
+        vocab = self.plan.vocab
+        news, pasts, want_rows = [], [], []
+        start = 0
+        starts = [0]
+        for e in entries:
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.ndim != 1 or toks.size == 0:
+                raise InvalidRequest(f"slot {e.slot}: a step entry needs at least one token")
+            if toks.min() < 0 or toks.max() >= vocab:
+                raise InvalidRequest(f"slot {e.slot}: token ids must lie in [0, {vocab})")
+            for w in e.want:
+                if not 0 <= int(w) < toks.size:
+                    raise InvalidRequest(f"slot {e.slot}: wanted place {w} is outside its {toks.size} tokens")
+                want_rows.append(start + int(w))
+            news.append(int(toks.size))
+            pasts.append(book.length(e.slot))
+            start += int(toks.size)
+            starts.append(start)
+        growth = dict(zip(slots, news))
+        book.check_step(growth)
+        return slots, news, pasts, starts, want_rows, growth
+
+    def step(self, entries: list, aux: Optional[dict] = None) -> torch.Tensor:
+        """Runs the entries' tokens as one batch; returns float32 logits
+        [number of wanted places, vocab] in the order of the entries and of
+        their ``want`` lists.  On a validation error nothing is changed."""
+        with torch.cuda.device(self.rt.device):
+            slots, news, pasts, starts, want_rows, growth = self.plan_step(entries)
+            book = self.cache.book
+            book.reserve(growth)
+            b, n = len(entries), starts[-1]
+            tok_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+            tok_seq = np.repeat(np.arange(b, dtype=np.int32), news)
+            tok_pos = np.concatenate([np.arange(p, p + t, dtype=np.int32) for p, t in zip(pasts, news)])
+            stride = self.cache.max_table_stride(slots, growth)
+            tables = [np.asarray(g.table_rows(slots, stride), dtype=np.int32).reshape(b, stride)
+                      for g in book.groups]
+            arrays = [tok_ids, tok_seq, tok_pos, np.asarray(slots, dtype=np.int32),
+                      np.asarray(starts, dtype=np.int32), np.asarray(pasts, dtype=np.int32),
+                      np.asarray(want_rows, dtype=np.int32), *tables]
+            dev = self._stage(arrays)
+            ctx = StepContext(
+                n_tokens=n, n_seqs=b, max_new=max(news), max_len=max(p + t for p, t in zip(pasts, news)),
+                tok_ids=dev[0], tok_seq=dev[1], tok_pos=dev[2], seq_slot=dev[3], seq_start=dev[4], seq_past=dev[5],
+                want_rows=dev[6], block_tables=list(dev[7:]),
+                host={"slots": slots, "news": news, "pasts": pasts, "starts": starts, "want_rows": want_rows},
+                aux=aux if aux is not None else {})
+            logits = self.model.forward(ctx, self.cache)
+            book.commit(growth)
+            self.steps_run += 1
+            return logits
+
+    def read_status(self) -> int:
+        """The device status word (0: nothing went wrong); reading it waits
+        for the device."""
+        return int(self.rt.status.item())
+
+    def raise_on_status(self) -> None:
+        code = self.read_status()
+        if code:
+            names = {1: "non-finite router probabilities", 2: "non-finite logits", 4: "a bounded wait ran out",
+                     8: "an index on the device was out of range"}
+            what = ", ".join(v for k, v in names.items() if code & k)
+            self.rt.status.zero_()
+            raise Backend(f"the device reported: {what}")

@@ -1,0 +1,165 @@
+"""What every part of a layer has in common: its parameters, the registries
+that map a spec's ``kind`` to a builder, and the runtime that parts run in.
+
+A part never learns which model it is in.  It is built from its spec (sizes
+and constants) and a ``Runtime``; it names its tensors, says where each one is
+to be stored, and then runs on packed token rows.
+
+Interfaces (all tensors live on the GPU; N = tokens of the step, H = width):
+
+* norm:      ``forward(x, delta, h, rows=None, write_x=True)``: x [N,H] float32 is the residual stream;
+             ``delta`` (float32 [N,H] or None) is added to it first; h receives the normed rows in the
+             activation dtype.
+* mixer:     ``forward(h, ctx, layer) -> delta`` float32 [N,H]; ``kv_layout()`` and ``state_spec()`` say
+             what it keeps per sequence (``layer`` is a ``cache.LayerCache``).
+* ffn:       ``forward(h, ctx) -> delta`` float32 [N,H].
+* position:  ``rotate_and_store(qkv, bias, ctx, q_out, layer, nh, nkv, hd)``: encodes the new queries and
+             keys (float32 in ``qkv``) and stores keys and values in the cache.
+* block:     ``forward(x, pending, ctx, layer) -> pending``: runs its parts in its arrangement.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+
+from ..errors import Backend, InvalidConfig
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    name: str                 # tensor name in the checkpoint
+    shape: tuple
+    role: str                 # "matrix" | "bias" | "norm_scale"
+    optional: bool = False
+
+
+class Part:
+    """Base of every part.  ``params`` maps tensor name -> the view the loader
+    fills; it exists after ``allocate``."""
+
+    def param_specs(self) -> list:
+        return []
+
+    def allocate(self, stored: dict, rt: "Runtime") -> dict:
+        """``stored``: tensor name -> dtype in the checkpoint (only names that
+        are present).  Returns tensor name -> destination view."""
+        return {}
+
+    def finalize(self) -> None:
+        """Called once every view has been filled; device-side tables are built
+        here, never in the constructor.  Must be harmless when called twice."""
+
+    def children(self) -> list:
+        return []
+
+
+def walk(part: Part):
+    yield part
+    for c in part.children():
+        yield from walk(c)
+
+
+# ---------------------------------------------------------------------------
+# registries: spec.kind -> builder(spec, rt) -> part
+# ---------------------------------------------------------------------------
+_REGISTRIES: dict = {"mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}}
+
+
+def register(family: str, kind: str, builder: Callable) -> None:
+    if family not in _REGISTRIES:
+        raise InvalidConfig(f"no part family {family!r}; families: {sorted(_REGISTRIES)}")
+    _REGISTRIES[family][kind] = builder
+
+
+def build(family: str, spec, rt: "Runtime"):
+    if spec is None:
+        return None
+    kind = getattr(spec, "kind", None)
+    builder = _REGISTRIES[family].get(kind)
+    if builder is None:
+        raise InvalidConfig(f"no {family} is registered under {kind!r}; registered: {sorted(_REGISTRIES[family])}")
+    return builder(spec, rt)
+
+
+# ---------------------------------------------------------------------------
+# runtime
+# ---------------------------------------------------------------------------
+class Workspace:
+    """Named scratch buffers that live as long as the runtime.  A buffer only
+    grows; while ``frozen`` (a CUDA graph holds the addresses) growth is an error."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: dict = {}
+        self.frozen = False
+
+    def get(self, name: str, shape: tuple, dtype) -> torch.Tensor:
+        count = 1
+        for s in shape:
+            count *= int(s)
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < count:
+            if self.frozen:
+                raise Backend(f"workspace buffer {name} would have to grow while a captured graph holds it")
+            buf = torch.empty(max(count, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:count].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+class Runtime:
+    """Device, activation dtype, scratch and the device status word."""
+
+    def __init__(self, device, dtype: torch.dtype, ffn_chunk_tokens: int = 16384):
+        """``device`` None gives a runtime that can only enumerate parts and
+        their parameters (used to write model folders without a GPU)."""
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise InvalidConfig(f"dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        self.shared_parts: dict = {}
+        self.device = None
+        if device is not None:
+            self.device = torch.device(device)
+            if self.device.type != "cuda":
+                raise Backend("esp_b200 runs on a CUDA device only; there is no CPU path")
+            self.ws = Workspace(self.device)
+            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.ffn_chunk_tokens = ffn_chunk_tokens
+        self.record_routing = False       # debugging aid: MoE parts put their choices into ctx.aux
+
+    @property
+    def full_precision(self) -> bool:
+        return self.dtype == torch.float32
+
+    def matrix_dtype(self, stored_dtypes) -> torch.dtype:
+        """Dtype a (packed) weight matrix is kept in: in the 32-bit engine
+        everything is widened to float32 (exact); otherwise bfloat16 stays
+        bfloat16 and anything stored wider stays 32-bit."""
+        if self.full_precision:
+            return torch.float32
+        return torch.bfloat16 if all(d == torch.bfloat16 for d in stored_dtypes) else torch.float32
+
+
+@dataclass
+class StepContext:
+    """Everything about one step that parts may need.  All index tensors are
+    int32 on the device."""
+    n_tokens: int
+    n_seqs: int
+    max_new: int                     # longest run of new tokens of one sequence
+    max_len: int                     # longest sequence after the step
+    tok_ids: torch.Tensor            # [N]
+    tok_seq: torch.Tensor            # [N] index of the token's sequence within the step
+    tok_pos: torch.Tensor            # [N] absolute position of the token in its sequence
+    seq_slot: torch.Tensor           # [B] cache slot of each sequence
+    seq_start: torch.Tensor          # [B+1] offsets of the sequences in the token rows
+    seq_past: torch.Tensor           # [B] cached length before the step
+    want_rows: torch.Tensor          # [R] token rows whose logits are wanted
+    block_tables: list               # per layer group: [B, stride] page ids
+    host: dict                       # the same lists on the host (slots, starts, pasts, news)
+    aux: dict

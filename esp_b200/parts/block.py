@@ -1,0 +1,33 @@
+"""How the parts of one layer are arranged."""
+from __future__ import annotations
+
+from .base import Part, build, register
+
+
+class PreNormResidualBlock(Part):
+    """x += mixer(norm(x)); x += ffn(norm(x))
+    (crates/esp/src/infer/decoder/layer.rs:115-153).  The residual adds are
+    folded into the norm that follows them: a part's output travels as
+    ``pending`` until the next norm adds it to the 32-bit residual stream."""
+
+    def __init__(self, spec, rt):
+        self.spec = spec
+        self.rt = rt
+        self.mixer_norm = build("norm", spec.mixer_norm, rt)
+        self.mixer = build("mixer", spec.mixer, rt)
+        self.ffn_norm = build("norm", spec.ffn_norm, rt)
+        self.ffn = build("ffn", spec.ffn, rt)
+
+    def children(self):
+        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def forward(self, x, pending, ctx, layer):
+        rt = self.rt
+        h = rt.ws.get("block_h", tuple(x.shape), rt.dtype)
+        self.mixer_norm.forward(x, pending, h)
+        delta = self.mixer.forward(h, ctx, layer)
+        self.ffn_norm.forward(x, delta, h)
+        return self.ffn.forward(h, ctx)
+
+
+register("block", "prenorm_residual", PreNormResidualBlock)

@@ -1,0 +1,160 @@
+"""Feed-forward parts: a dense SwiGLU MLP and the sparse block with routed
+experts and a gated shared expert."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import ParamSpec, Part, register
+from .linear import grouped_linear, linear
+
+
+def _swiglu_mlp(rt, h, w_gate_up, w_down, out, tag):
+    """out = down(silu(gate h) * (up h)); w_gate_up is [2I, H], gate rows first."""
+    n = h.shape[0]
+    inter = w_gate_up.shape[0] // 2
+    gu = rt.ws.get(tag + "_gu", (n, 2 * inter), torch.float32)
+    linear(rt, h, w_gate_up, gu)
+    act = rt.ws.get(tag + "_act", (n, inter), rt.dtype)
+    ops.swiglu(gu, act)
+    linear(rt, act, w_down, out)
+    return out
+
+
+class DenseSwiGlu(Part):
+    """y = W_d(silu(W_g h) * (W_u h)), no biases
+    (crates/esp/src/infer/decoder/moe.rs:87-89, :143-148)."""
+
+    def __init__(self, spec, rt):
+        self.spec = spec
+        self.rt = rt
+        self.w_gate_up = self.w_down = None
+
+    def param_specs(self):
+        s, p = self.spec, self.spec.prefix
+        return [ParamSpec(p + "gate_proj.weight", (s.intermediate, s.hidden), "matrix"),
+                ParamSpec(p + "up_proj.weight", (s.intermediate, s.hidden), "matrix"),
+                ParamSpec(p + "down_proj.weight", (s.hidden, s.intermediate), "matrix")]
+
+    def allocate(self, stored, rt):
+        s, p = self.spec, self.spec.prefix
+        dt = rt.matrix_dtype([stored[p + "gate_proj.weight"], stored[p + "up_proj.weight"]])
+        self.w_gate_up = torch.empty((2 * s.intermediate, s.hidden), dtype=dt, device=rt.device)
+        self.w_down = torch.empty((s.hidden, s.intermediate), dtype=rt.matrix_dtype([stored[p + "down_proj.weight"]]),
+                                  device=rt.device)
+        return {p + "gate_proj.weight": self.w_gate_up[:s.intermediate],
+                p + "up_proj.weight": self.w_gate_up[s.intermediate:], p + "down_proj.weight": self.w_down}
+
+    def forward(self, h, ctx):
+        rt = self.rt
+        n = h.shape[0]
+        y = rt.ws.get("ffn_out", (n, self.spec.hidden), torch.float32)
+        step = rt.ffn_chunk_tokens
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            _swiglu_mlp(rt, h[a:b], self.w_gate_up, self.w_down, y[a:b], "dense")
+        return y
+
+
+class MoeSwiGluShared(Part):
+    """Router (32-bit softmax over all experts, top-k, ties to the lower id,
+    optional renormalisation), routed SwiGLU experts whose outputs are scaled
+    by their routing weight and summed in ascending expert id, plus a shared
+    SwiGLU expert scaled by sigmoid(h . w_shared_gate)
+    (crates/esp/src/infer/decoder/moe.rs:135-256)."""
+
+    def __init__(self, spec, rt):
+        self.spec = spec
+        self.rt = rt
+        self.w_router = self.w_shared_gate = None
+        self.w_gate_up = self.w_down = None            # [E, 2Im, H], [E, H, Im]
+        self.w_shared_gate_up = self.w_shared_down = None
+
+    def param_specs(self):
+        s, p = self.spec, self.spec.prefix
+        specs = [ParamSpec(p + "gate.weight", (s.num_experts, s.hidden), "matrix"),
+                 ParamSpec(p + "shared_expert_gate.weight", (1, s.hidden), "matrix"),
+                 ParamSpec(p + "shared_expert.gate_proj.weight", (s.shared_intermediate, s.hidden), "matrix"),
+                 ParamSpec(p + "shared_expert.up_proj.weight", (s.shared_intermediate, s.hidden), "matrix"),
+                 ParamSpec(p + "shared_expert.down_proj.weight", (s.hidden, s.shared_intermediate), "matrix")]
+        for e in range(s.num_experts):
+            q = f"{p}experts.{e}."
+            specs += [ParamSpec(q + "gate_proj.weight", (s.expert_intermediate, s.hidden), "matrix"),
+                      ParamSpec(q + "up_proj.weight", (s.expert_intermediate, s.hidden), "matrix"),
+                      ParamSpec(q + "down_proj.weight", (s.hidden, s.expert_intermediate), "matrix")]
+        return specs
+
+    def allocate(self, stored, rt):
+        s, p = self.spec, self.spec.prefix
+        dev = rt.device
+        E, Im, Is, H = s.num_experts, s.expert_intermediate, s.shared_intermediate, s.hidden
+        rdt = rt.matrix_dtype([stored[p + "gate.weight"], stored[p + "shared_expert_gate.weight"]])
+        self.w_router = torch.empty((E, H), dtype=rdt, device=dev)
+        self.w_shared_gate = torch.empty((1, H), dtype=rdt, device=dev)
+        gu_names = [f"{p}experts.{e}.{k}_proj.weight" for e in range(E) for k in ("gate", "up")]
+        self.w_gate_up = torch.empty((E, 2 * Im, H), dtype=rt.matrix_dtype([stored[n] for n in gu_names]), device=dev)
+        d_names = [f"{p}experts.{e}.down_proj.weight" for e in range(E)]
+        self.w_down = torch.empty((E, H, Im), dtype=rt.matrix_dtype([stored[n] for n in d_names]), device=dev)
+        sdt = rt.matrix_dtype([stored[p + "shared_expert.gate_proj.weight"], stored[p + "shared_expert.up_proj.weight"]])
+        self.w_shared_gate_up = torch.empty((2 * Is, H), dtype=sdt, device=dev)
+        self.w_shared_down = torch.empty((H, Is), dtype=rt.matrix_dtype([stored[p + "shared_expert.down_proj.weight"]]),
+                                         device=dev)
+        views = {p + "gate.weight": self.w_router, p + "shared_expert_gate.weight": self.w_shared_gate,
+                 p + "shared_expert.gate_proj.weight": self.w_shared_gate_up[:Is],
+                 p + "shared_expert.up_proj.weight": self.w_shared_gate_up[Is:],
+                 p + "shared_expert.down_proj.weight": self.w_shared_down}
+        for e in range(E):
+            q = f"{p}experts.{e}."
+            views[q + "gate_proj.weight"] = self.w_gate_up[e, :Im]
+            views[q + "up_proj.weight"] = self.w_gate_up[e, Im:]
+            views[q + "down_proj.weight"] = self.w_down[e]
+        return views
+
+    def forward(self, h, ctx):
+        rt = self.rt
+        n = h.shape[0]
+        y = rt.ws.get("ffn_out", (n, self.spec.hidden), torch.float32)
+        step = rt.ffn_chunk_tokens
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            self._forward_rows(h[a:b], y[a:b], ctx, a)
+        return y
+
+    def _forward_rows(self, h, y, ctx, row0):
+        s, rt = self.spec, self.rt
+        n, k, E, Im, H = h.shape[0], s.top_k, s.num_experts, s.expert_intermediate, s.hidden
+        ws = rt.ws
+        ids = ws.get("moe_ids", (n, k), torch.int32)
+        wts = ws.get("moe_w", (n, k), torch.float32)
+        gate = ws.get("moe_gate", (n,), torch.float32)
+        probs = None
+        if rt.record_routing:
+            probs = torch.empty((n, E), dtype=torch.float32, device=rt.device)
+        ops.router_topk(h, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status, probs)
+        if rt.record_routing:
+            ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
+        offsets = ws.get("moe_offsets", (E + 1,), torch.int32)
+        perm_token = ws.get("moe_perm_token", (n * k,), torch.int32)
+        perm_weight = ws.get("moe_perm_weight", (n * k,), torch.float32)
+        inverse = ws.get("moe_inverse", (n, k), torch.int32)
+        ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status)
+        expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k)
+        shared = ws.get("moe_shared_out", (n, H), torch.float32)
+        _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
+        ops.moe_combine(expert_out, ids, inverse, gate, shared, y)
+
+    def experts(self, h, offsets, perm_token, perm_weight, rows):
+        """expert_out[r] = weight[r] * down_e(silu(gate_e x) * (up_e x)) for every
+        permuted row r, x = h[perm_token[r]], e the expert whose range holds r."""
+        s, rt = self.spec, self.rt
+        gu = rt.ws.get("moe_gu", (rows, 2 * s.expert_intermediate), torch.float32)
+        grouped_linear(rt, h, self.w_gate_up, gu, offsets, a_rows=perm_token, rows=rows)
+        act = rt.ws.get("moe_act", (rows, s.expert_intermediate), rt.dtype)
+        ops.swiglu(gu, act)
+        out = rt.ws.get("moe_expert_out", (rows, s.hidden), torch.float32)
+        grouped_linear(rt, act, self.w_down, out, offsets, row_scale=perm_weight, rows=rows)
+        return out
+
+
+register("ffn", "swiglu", DenseSwiGlu)
+register("ffn", "moe_swiglu_shared", MoeSwiGluShared)

@@ -1,0 +1,59 @@
+"""The plain implementation against the outputs that the reference project
+records for its two Qwen2-MoE checkpoints (tests/golden/README.md)."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import plain_qwen2_moe as plain
+
+GOLDEN = Path(__file__).parent / "golden"
+CASES = {c["name"]: c for c in json.loads((GOLDEN / "recorded_outputs.json").read_text())["cases"]}
+
+
+@pytest.mark.parametrize("name", ["qwen2_moe", "qwen2_moe_normalized"])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_recorded_logits_and_greedy_ids(name, dtype):
+    case = CASES[name]
+    c, w = plain.load_model(GOLDEN / name)
+    logits = plain.forward_logits(c, w, case["input_ids"], dtype)
+    err = np.abs(logits[-1] - np.asarray(case["last_logits"], dtype=np.float32)).max()
+    # the reference's own acceptance is 2e-5 (architecture_tests.rs:237-247)
+    assert err < (2e-6 if dtype is np.float32 else 5e-7), err
+    ids = plain.generate(c, w, case["input_ids"], len(case["generated_ids"]), dtype=dtype)
+    assert ids == case["generated_ids"]
+
+
+def test_splitmix64_known_values():
+    # first outputs of splitmix64 from seed 0 (public test vector of the generator)
+    r = plain.SplitMix64(0)
+    assert r.next_u64() == 0xE220A8397B1DCDAF
+    assert r.next_u64() == 0x6E789E6AA1B965F4
+    a = plain.SplitMix64(7)
+    b = plain.SplitMix64(7)
+    for _ in range(5):
+        a.next_u64()
+    b.skip(5)
+    assert a.next_u64() == b.next_u64()
+
+
+def test_sampler_low_temperature_is_greedy_and_top_p_small_is_argmax():
+    rng = np.random.default_rng(0)
+    row = rng.normal(size=50).astype(np.float32)
+    assert plain.sample_row(row, 1e-4, None, plain.SplitMix64(1)) == int(np.argmax(row))
+    assert plain.sample_row(row, 1.0, 1e-6, plain.SplitMix64(2)) == int(np.argmax(row))
+
+
+def test_window_masks_far_keys():
+    c, w = plain.load_model(GOLDEN / "qwen2_moe")
+    x = np.random.default_rng(0).normal(size=(12, c["hidden_size"])).astype(np.float32)
+    full = plain.attention(c, w, "model.layers.0.self_attn.", x, None)
+    win = plain.attention(c, w, "model.layers.0.self_attn.", x, 4)
+    assert np.allclose(full[:4], win[:4], atol=1e-6)
+    assert not np.allclose(full[8:], win[8:], atol=1e-6)
+    # a query sees itself and window-1 predecessors: changing token 0 leaves row 4 unchanged
+    x2 = x.copy(); x2[0] += 1.0
+    win2 = plain.attention(c, w, "model.layers.0.self_attn.", x2, 4)
+    assert np.allclose(win[4:], win2[4:], atol=1e-6)
+    assert not np.allclose(win[3], win2[3], atol=1e-6)
