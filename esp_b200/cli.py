@@ -1,0 +1,90 @@
+"""Command line: ``python -m esp_b200 <command>``.
+
+The reference has no generation command; the options here carry the names and
+meanings of its request (crates/esp/src/infer/provider.rs:91-117):
+``--max-tokens``, ``--temperature`` (0 = greedy), ``--top-p``, ``--seed``,
+``--stop``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+
+def _ids(text: str) -> list:
+    return [int(t) for t in text.replace(",", " ").split()]
+
+
+def cmd_generate(a) -> int:
+    from .provider import DecoderProvider, GenerationRequest
+    prov = DecoderProvider.load(a.model, dtype=a.dtype, device=a.device, max_batch=a.max_batch,
+                                max_context=a.max_context)
+    reqs = []
+    for ids in a.prompt_ids or []:
+        reqs.append(GenerationRequest(prompt_ids=_ids(ids), max_tokens=a.max_tokens, temperature=a.temperature,
+                                      top_p=a.top_p, seed=a.seed, stop=a.stop or [], stop_token_ids=a.stop_token_id or []))
+    for text in a.prompt or []:
+        reqs.append(GenerationRequest(prompt=text, max_tokens=a.max_tokens, temperature=a.temperature, top_p=a.top_p,
+                                      seed=a.seed, stop=a.stop or [], stop_token_ids=a.stop_token_id or []))
+    if not reqs:
+        print("give at least one --prompt-ids or --prompt", file=sys.stderr)
+        return 2
+    for i, g in enumerate(prov.generate(reqs)):
+        print(json.dumps({"request": i, "token_ids": g.token_ids, "text": g.text, "finish_reason": g.finish_reason,
+                          "prompt_tokens": g.prompt_tokens, "seed": g.seed}))
+    return 0
+
+
+def cmd_random_model(a) -> int:
+    from .config import config_from_json
+    from .weights import InitSpec, write_model_folder
+    cfg = config_from_json(a.config)
+    write_model_folder(cfg, a.weights_seed, a.out, a.store_dtype, InitSpec(a.weight_std, a.bias_std, a.norm_std))
+    print(a.out)
+    return 0
+
+
+def cmd_build(a) -> int:
+    from .csrc.build import build_all
+    for p in build_all():
+        print(p)
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="esp_b200", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="command", required=True)
+    g = sub.add_parser("generate", help="generate tokens for one or more prompts")
+    g.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--device", default="cuda:0")
+    g.add_argument("--prompt-ids", action="append", help="token ids, comma or space separated; repeat for a batch")
+    g.add_argument("--prompt", action="append", help="text prompt (needs tokenizer.json); repeat for a batch")
+    g.add_argument("--max-tokens", type=int, default=256)
+    g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-p", type=float, default=None)
+    g.add_argument("--seed", type=int, default=None)
+    g.add_argument("--stop", action="append", help="stop string (text level)")
+    g.add_argument("--stop-token-id", type=int, action="append")
+    g.add_argument("--max-batch", type=int, default=64)
+    g.add_argument("--max-context", type=int, default=None)
+    g.set_defaults(fn=cmd_generate)
+    r = sub.add_parser("random-model", help="write a model folder with random weights from a config.json and a seed")
+    r.add_argument("--config", required=True)
+    r.add_argument("--weights-seed", type=int, default=0)
+    r.add_argument("--out", required=True)
+    r.add_argument("--store-dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.add_argument("--weight-std", type=float, default=0.02)
+    r.add_argument("--bias-std", type=float, default=0.0)
+    r.add_argument("--norm-std", type=float, default=0.0)
+    r.set_defaults(fn=cmd_random_model)
+    b = sub.add_parser("build", help="compile every kernel library now")
+    b.set_defaults(fn=cmd_build)
+    a = ap.parse_args(argv)
+    from .errors import InferError
+    try:
+        return a.fn(a)
+    except InferError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1

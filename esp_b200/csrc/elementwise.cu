@@ -33,11 +33,14 @@ ESP_API int esp_embed_gather(const void* table, int table_is_bf16, const int* id
 // Row r works on source row s = rows ? rows[r] : r.
 //   v = x[s] + (y ? y[s] : 0);  if (write_x) x[s] = v;
 //   h[r] = v * (1 / sqrt(mean(v^2) + eps)) * gamma       (all in 32-bit)
+// ``h32`` (may be null) receives the same rows unrounded, for consumers that
+// must work from 32-bit values whatever the activation dtype (the router).
 // The sum of squares is taken per thread in index order and combined by a
 // fixed tree, so a row's result does not depend on the rest of the batch.
 template <typename TH>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma,
-                                   const int* __restrict__ rows, TH* __restrict__ h, int width, float eps, int write_x) {
+                                   const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
+                                   float eps, int write_x) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
@@ -55,21 +58,24 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     const float total = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / (float)width + eps);
     TH* hr = h + (size_t)r * width;
+    float* h32r = h32 ? h32 + (size_t)r * width : nullptr;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = xr[i];
         if (yr && !write_x) v += yr[i];
-        hr[i] = from_f32<TH>(v * inv * gamma[i]);
+        const float o = v * inv * gamma[i];
+        hr[i] = from_f32<TH>(o);
+        if (h32r) h32r[i] = o;
     }
 }
 
 ESP_API int esp_add_rmsnorm(float* x, const float* y, const float* gamma, const int* rows, void* h, int h_is_bf16,
-                            int n_rows, int width, float eps, int write_x, cudaStream_t stream) {
+                            float* h32, int n_rows, int width, float eps, int write_x, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (h_is_bf16)
-        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (bf16*)h, width, eps, write_x);
+        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
     else
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (float*)h, width, eps, write_x);
+        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (float*)h, h32, width, eps, write_x);
     return esp_launch_status();
 }
 

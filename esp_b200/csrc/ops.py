@@ -19,7 +19,7 @@ P = c_void_p
 
 _SIGNATURES = {
     "esp_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, P, P],
-    "esp_add_rmsnorm": [P, P, P, P, P, c_int, c_int, c_int, c_float, c_int, P],
+    "esp_add_rmsnorm": [P, P, P, P, P, c_int, P, c_int, c_int, c_float, c_int, P],
     "esp_swiglu": [P, P, c_int, c_longlong, c_int, P],
     "esp_finite_check": [P, c_longlong, P, P],
     "esp_normal_fill": [P, c_int, c_longlong, c_ulonglong, c_float, c_float, P],
@@ -89,16 +89,18 @@ def embed_gather(table, ids, x, status):
         _ptr(x, torch.float32, "x"), n, width, table.shape[0], _ptr(status, torch.int32), _stream()), "embed_gather")
 
 
-def add_rmsnorm(x, y, gamma, h, eps, rows=None, write_x=True):
+def add_rmsnorm(x, y, gamma, h, eps, rows=None, write_x=True, h32=None):
     """h = rmsnorm(x + y) * gamma with x (+= y when write_x) float32, gamma
-    float32, h float32 or bfloat16.  ``rows`` (int32) selects source rows."""
+    float32, h float32 or bfloat16.  ``rows`` (int32) selects source rows;
+    ``h32`` (float32, same shape as h) receives the unrounded rows."""
     n_rows = h.shape[0]
     width = h.shape[1]
     if x.shape[1] != width or gamma.shape[0] != width:
         raise Backend("add_rmsnorm: widths disagree")
     _check(_fn("core", "esp_add_rmsnorm")(
         _ptr(x, torch.float32, "x"), _ptr(y, torch.float32, "y"), _ptr(gamma, torch.float32, "gamma"),
-        _ptr(rows, torch.int32, "rows"), _ptr(h, FLOATS, "h"), _is_bf16(h), n_rows, width, float(eps),
+        _ptr(rows, torch.int32, "rows"), _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(h32, torch.float32, "h32"), n_rows,
+        width, float(eps),
         1 if write_x else 0, _stream()), "add_rmsnorm")
 
 

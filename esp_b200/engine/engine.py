@@ -16,6 +16,9 @@ import numpy as np
 import torch
 
 from ..cache import Cache
+from ..cache.storage import STATE_RNG, STATE_WORDS
+from ..csrc import ops
+from ..sampling import as_signed64
 from ..config import config_from_json
 from ..errors import Backend, InvalidRequest
 from ..parts import Runtime, StepContext
@@ -149,6 +152,36 @@ class Engine:
         """Runs the entries' tokens as one batch; returns float32 logits
         [number of wanted places, vocab] in the order of the entries and of
         their ``want`` lists.  On a validation error nothing is changed."""
+        logits, _ = self._run(entries, aux, [])
+        return logits
+
+    def step_and_pick(self, entries: list, temperatures: list, top_ps: list, aux: Optional[dict] = None):
+        """One step that ends with the choice of the next token of every entry
+        (each entry must want exactly one place).  ``temperatures[i] == 0``
+        chooses the arg-max, otherwise a draw from the slot's own stream;
+        ``top_ps[i]`` None means no nucleus cut.  Returns (tokens, logits):
+        tokens is an int32 device tensor [B + 1] whose last element is the
+        device status word."""
+        if any(len(e.want) != 1 for e in entries):
+            raise InvalidRequest("step_and_pick needs exactly one wanted place per entry")
+        temps = np.asarray(temperatures, dtype=np.float32)
+        tops = np.asarray([-1.0 if t is None else t for t in top_ps], dtype=np.float32)
+        rows = np.asarray([e.slot * STATE_WORDS + STATE_RNG for e in entries], dtype=np.int32)
+        logits, extra = self._run(entries, aux, [temps.view(np.int32), tops.view(np.int32), rows])
+        with torch.cuda.device(self.rt.device):
+            b = len(entries)
+            out = self.rt.ws.get("picked_tokens", (b + 1,), torch.int32)
+            ops.finite_check(logits, self.rt.status)
+            ops.pick_tokens(logits, extra[0].view(torch.float32), extra[1].view(torch.float32),
+                            self.cache.engine_state.view(-1), extra[2], out)
+            out[b:].copy_(self.rt.status)
+        return out, logits
+
+    def seed_slot(self, slot: int, seed: int) -> None:
+        """Starts the slot's sampling stream from ``seed``."""
+        self.cache.engine_state[slot, STATE_RNG] = as_signed64(seed)
+
+    def _run(self, entries: list, aux, extra_arrays: list):
         with torch.cuda.device(self.rt.device):
             slots, news, pasts, starts, want_rows, growth = self.plan_step(entries)
             book = self.cache.book
@@ -162,18 +195,19 @@ class Engine:
                       for g in book.groups]
             arrays = [tok_ids, tok_seq, tok_pos, np.asarray(slots, dtype=np.int32),
                       np.asarray(starts, dtype=np.int32), np.asarray(pasts, dtype=np.int32),
-                      np.asarray(want_rows, dtype=np.int32), *tables]
+                      np.asarray(want_rows, dtype=np.int32), *tables, *extra_arrays]
             dev = self._stage(arrays)
+            nt = 7 + len(tables)
             ctx = StepContext(
                 n_tokens=n, n_seqs=b, max_new=max(news), max_len=max(p + t for p, t in zip(pasts, news)),
                 tok_ids=dev[0], tok_seq=dev[1], tok_pos=dev[2], seq_slot=dev[3], seq_start=dev[4], seq_past=dev[5],
-                want_rows=dev[6], block_tables=list(dev[7:]),
+                want_rows=dev[6], block_tables=list(dev[7:nt]),
                 host={"slots": slots, "news": news, "pasts": pasts, "starts": starts, "want_rows": want_rows},
                 aux=aux if aux is not None else {})
             logits = self.model.forward(ctx, self.cache)
             book.commit(growth)
             self.steps_run += 1
-            return logits
+            return logits, dev[nt:]
 
     def read_status(self) -> int:
         """The device status word (0: nothing went wrong); reading it waits

@@ -1,0 +1,147 @@
+"""The generation loop above the step function.
+
+Rules taken from the reference's loop
+(crates/esp/src/infer/decoder/generate.rs:134-170,
+crates/esp/src/infer/decoder/provider.rs:474-517): an empty prompt and
+``max_tokens == 0`` are errors; a prompt as long as the context window is too
+long; ``max_new = min(max_tokens, window - prompt)``; a stop token ends the
+sequence, is not emitted and still costs its draw; after a token is kept the
+callback may stop the sequence; the forward pass after the last token is
+skipped.
+
+What the reference does not have: batches.  Requests are packed into batches
+that start together; prompts of unequal lengths run in one step, then every
+live sequence advances by one token per step; a sequence that ends leaves the
+batch and gives its slot back at once; batches follow one another until every
+request is served.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+from ..cache.book import PAGE
+from ..errors import InvalidRequest, PromptTooLong
+from ..sampling import SamplingParams
+
+
+@dataclass
+class SequenceRequest:
+    """One request at the token seam."""
+    prompt_ids: list
+    max_tokens: int = 256
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    stop_token_ids: tuple = ()
+
+
+@dataclass
+class SequenceResult:
+    token_ids: list
+    finish_reason: str            # "stop" (stop token), "length" (budget) or "cancelled" (callback)
+    prompt_tokens: int
+    seed: Optional[int] = None    # the seed the stream was started from (sampled requests)
+
+
+def budget(prompt_len: int, max_tokens: int, window: int) -> int:
+    """Tokens a request may generate; raises as the reference does."""
+    if prompt_len == 0:
+        raise InvalidRequest("the prompt is empty")
+    if max_tokens <= 0:
+        raise InvalidRequest("max_tokens must be positive")
+    if prompt_len >= window:
+        raise PromptTooLong(prompt_len, window)
+    return min(max_tokens, window - prompt_len)
+
+
+def reserved_tokens(prompt_len: int, max_new: int) -> int:
+    """Cache tokens a sequence can come to hold, rounded up to whole pages.  The
+    last generated token is never fed back, so it needs no room."""
+    held = prompt_len + max_new - 1
+    return (max(held, 1) + PAGE - 1) // PAGE * PAGE
+
+
+def form_batches(lengths: list, max_batch: int, max_tokens: int) -> list:
+    """Splits requests, in order, into batches of at most ``max_batch``
+    sequences whose reserved tokens fit ``max_tokens``.  ``lengths``: one
+    (prompt_len, max_new) per request.  Returns lists of request indices."""
+    batches, cur, used = [], [], 0
+    for i, (p, m) in enumerate(lengths):
+        need = reserved_tokens(p, m)
+        if need > max_tokens:
+            raise InvalidRequest(f"request {i} needs room for {need} tokens, the cache holds {max_tokens}")
+        if cur and (len(cur) >= max_batch or used + need > max_tokens):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+class GenerationLoop:
+    """Drives a backend with four calls:
+
+    ``open(sampling, seed) -> slot``, ``close(slot)``,
+    ``prefill(slots, prompts) -> tokens`` (one chosen token per sequence) and
+    ``decode(slots, tokens) -> tokens``.  The backend chooses tokens on the
+    device with each slot's own sampling options; this class only decides what
+    runs next and what is kept."""
+
+    def __init__(self, backend, window: int, max_batch: int, max_tokens: int, default_stop_ids=()):
+        self.backend = backend
+        self.window = window
+        self.max_batch = max_batch
+        self.max_tokens = max_tokens
+        self.default_stop_ids = tuple(default_stop_ids)
+
+    def run(self, requests: list, on_token: Optional[Callable] = None) -> list:
+        """``on_token(request_index, token) -> bool``: a true return value
+        stops that sequence after the token is kept."""
+        budgets = []
+        for r in requests:
+            r.sampling.validate()
+            budgets.append(budget(len(r.prompt_ids), r.max_tokens, self.window))
+        results = [None] * len(requests)
+        lengths = [(len(r.prompt_ids), b) for r, b in zip(requests, budgets)]
+        for batch in form_batches(lengths, self.max_batch, self.max_tokens):
+            self._run_batch(batch, requests, budgets, results, on_token)
+        return results
+
+    def _run_batch(self, batch, requests, budgets, results, on_token):
+        slots, seeds, outs = {}, {}, {}
+        live = []
+        try:
+            for i in batch:
+                seed = None if requests[i].sampling.greedy else requests[i].sampling.resolved_seed()
+                seeds[i] = seed
+                slots[i] = self.backend.open(requests[i].sampling, seed)
+                outs[i] = []
+                live.append(i)
+            tokens = self.backend.prefill([slots[i] for i in live], [list(requests[i].prompt_ids) for i in live])
+            while live:
+                nxt, feed = [], []
+                for i, tok in zip(live, tokens):
+                    tok = int(tok)
+                    stops = self.default_stop_ids + tuple(requests[i].stop_token_ids)
+                    reason = None
+                    if tok in stops:
+                        reason = "stop"
+                    else:
+                        outs[i].append(tok)
+                        if on_token is not None and on_token(i, tok):
+                            reason = "cancelled"
+                        elif len(outs[i]) == budgets[i]:
+                            reason = "length"
+                    if reason is None:
+                        nxt.append(i)
+                        feed.append(tok)
+                    else:
+                        results[i] = SequenceResult(outs[i], reason, len(requests[i].prompt_ids), seeds[i])
+                        self.backend.close(slots.pop(i))
+                live = nxt
+                if live:
+                    tokens = self.backend.decode([slots[i] for i in live], feed)
+        finally:
+            for s in slots.values():      # only reached with slots left over when something raised
+                self.backend.close(s)

@@ -7,12 +7,13 @@ to be stored, and then runs on packed token rows.
 
 Interfaces (all tensors live on the GPU; N = tokens of the step, H = width):
 
-* norm:      ``forward(x, delta, h, rows=None, write_x=True)``: x [N,H] float32 is the residual stream;
+* norm:      ``forward(x, delta, h, rows=None, write_x=True, h32=None)``: x [N,H] float32 is the residual stream;
              ``delta`` (float32 [N,H] or None) is added to it first; h receives the normed rows in the
              activation dtype.
 * mixer:     ``forward(h, ctx, layer) -> delta`` float32 [N,H]; ``kv_layout()`` and ``state_spec()`` say
              what it keeps per sequence (``layer`` is a ``cache.LayerCache``).
-* ffn:       ``forward(h, ctx) -> delta`` float32 [N,H].
+* ffn:       ``forward(h, ctx, h32=None) -> delta`` float32 [N,H]; a part with ``wants_f32_input = True``
+             also gets the normed rows unrounded (float32) when the activation dtype is narrower.
 * position:  ``rotate_and_store(qkv, bias, ctx, q_out, layer, nh, nkv, hd)``: encodes the new queries and
              keys (float32 in ``qkv``) and stores keys and values in the cache.
 * block:     ``forward(x, pending, ctx, layer) -> pending``: runs its parts in its arrangement.

@@ -1,6 +1,8 @@
 """How the parts of one layer are arranged."""
 from __future__ import annotations
 
+import torch
+
 from .base import Part, build, register
 
 
@@ -26,8 +28,11 @@ class PreNormResidualBlock(Part):
         h = rt.ws.get("block_h", tuple(x.shape), rt.dtype)
         self.mixer_norm.forward(x, pending, h)
         delta = self.mixer.forward(h, ctx, layer)
-        self.ffn_norm.forward(x, delta, h)
-        return self.ffn.forward(h, ctx)
+        h32 = None
+        if rt.dtype != torch.float32 and getattr(self.ffn, "wants_f32_input", False):
+            h32 = rt.ws.get("block_h32", tuple(x.shape), torch.float32)
+        self.ffn_norm.forward(x, delta, h, h32=h32)
+        return self.ffn.forward(h, ctx, h32=h32)
 
 
 register("block", "prenorm_residual", PreNormResidualBlock)

@@ -45,7 +45,7 @@ class DenseSwiGlu(Part):
         return {p + "gate_proj.weight": self.w_gate_up[:s.intermediate],
                 p + "up_proj.weight": self.w_gate_up[s.intermediate:], p + "down_proj.weight": self.w_down}
 
-    def forward(self, h, ctx):
+    def forward(self, h, ctx, h32=None):
         rt = self.rt
         n = h.shape[0]
         y = rt.ws.get("ffn_out", (n, self.spec.hidden), torch.float32)
@@ -110,17 +110,19 @@ class MoeSwiGluShared(Part):
             views[q + "down_proj.weight"] = self.w_down[e]
         return views
 
-    def forward(self, h, ctx):
+    wants_f32_input = True      # the router works from unrounded rows
+
+    def forward(self, h, ctx, h32=None):
         rt = self.rt
         n = h.shape[0]
         y = rt.ws.get("ffn_out", (n, self.spec.hidden), torch.float32)
         step = rt.ffn_chunk_tokens
         for a in range(0, n, step):
             b = min(n, a + step)
-            self._forward_rows(h[a:b], y[a:b], ctx, a)
+            self._forward_rows(h[a:b], y[a:b], ctx, a, h32[a:b] if h32 is not None else h[a:b])
         return y
 
-    def _forward_rows(self, h, y, ctx, row0):
+    def _forward_rows(self, h, y, ctx, row0, router_in):
         s, rt = self.spec, self.rt
         n, k, E, Im, H = h.shape[0], s.top_k, s.num_experts, s.expert_intermediate, s.hidden
         ws = rt.ws
@@ -130,7 +132,7 @@ class MoeSwiGluShared(Part):
         probs = None
         if rt.record_routing:
             probs = torch.empty((n, E), dtype=torch.float32, device=rt.device)
-        ops.router_topk(h, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status, probs)
+        ops.router_topk(router_in, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status, probs)
         if rt.record_routing:
             ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
         offsets = ws.get("moe_offsets", (E + 1,), torch.int32)

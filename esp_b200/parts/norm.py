@@ -23,8 +23,8 @@ class RmsNorm(Part):
         self.weight = torch.empty(self.spec.width, dtype=torch.float32, device=rt.device)
         return {self.spec.weight: self.weight}
 
-    def forward(self, x, delta, h, rows=None, write_x=True):
-        ops.add_rmsnorm(x, delta, self.weight, h, self.spec.eps, rows=rows, write_x=write_x)
+    def forward(self, x, delta, h, rows=None, write_x=True, h32=None):
+        ops.add_rmsnorm(x, delta, self.weight, h, self.spec.eps, rows=rows, write_x=write_x, h32=h32)
         return h
 
 

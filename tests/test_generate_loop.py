@@ -1,0 +1,157 @@
+"""The generation loop's decisions, driven with a scripted backend (no GPU):
+budgets, stop tokens, sequences that end earlier, slot hand-back, batches one
+after another (rules: crates/esp/src/infer/decoder/generate.rs:134-170,
+crates/esp/src/infer/decoder/provider.rs:474-517)."""
+import pytest
+
+from esp_b200.engine.generate import (GenerationLoop, SequenceRequest, budget, form_batches, reserved_tokens)
+from esp_b200.errors import InvalidRequest, PromptTooLong
+from esp_b200.sampling import SamplingParams, skip_draws, splitmix64_next
+
+
+class ScriptedBackend:
+    """Every sequence emits prompt[0], prompt[0]+1, ... ; records all calls."""
+
+    def __init__(self, n_slots=4):
+        self.free = list(range(n_slots))[::-1]
+        self.held = {}
+        self.calls = []
+        self.max_live = 0
+
+    def open(self, sampling, seed):
+        s = self.free.pop()
+        self.held[s] = None
+        self.max_live = max(self.max_live, len(self.held))
+        self.calls.append(("open", s, seed))
+        return s
+
+    def close(self, slot):
+        assert slot in self.held, "closed twice"
+        del self.held[slot]
+        self.free.append(slot)
+        self.calls.append(("close", slot))
+
+    def prefill(self, slots, prompts):
+        self.calls.append(("prefill", tuple(slots), tuple(len(p) for p in prompts)))
+        for s, p in zip(slots, prompts):
+            self.held[s] = p[0]
+        return [self.held[s] for s in slots]
+
+    def decode(self, slots, tokens):
+        self.calls.append(("decode", tuple(slots), tuple(tokens)))
+        for s, t in zip(slots, tokens):
+            assert self.held[s] == t, "the loop fed back a token it was not given"
+            self.held[s] = t + 1
+        return [self.held[s] for s in slots]
+
+
+def loop(backend, **kw):
+    args = dict(window=64, max_batch=4, max_tokens=64 * 64, default_stop_ids=())
+    args.update(kw)
+    return GenerationLoop(backend, **args)
+
+
+def test_budget_rules():
+    assert budget(5, 256, 64) == 59 and budget(5, 10, 64) == 10
+    with pytest.raises(InvalidRequest):
+        budget(0, 10, 64)
+    with pytest.raises(InvalidRequest):
+        budget(5, 0, 64)
+    with pytest.raises(PromptTooLong) as e:
+        budget(64, 10, 64)            # a prompt of exactly the window is already too long
+    assert (e.value.length, e.value.limit) == (64, 64)
+
+
+def test_length_stop_and_skipped_last_forward():
+    be = ScriptedBackend()
+    (r,) = loop(be).run([SequenceRequest([10, 0, 0], max_tokens=3)])
+    assert r.token_ids == [10, 11, 12] and r.finish_reason == "length" and r.prompt_tokens == 3
+    # two decode steps only: the forward after the last token is skipped
+    assert [c[0] for c in be.calls] == ["open", "prefill", "decode", "decode", "close"]
+
+
+def test_stop_token_is_not_emitted_and_sequences_leave_early():
+    be = ScriptedBackend()
+    reqs = [SequenceRequest([10], max_tokens=8, stop_token_ids=(12,)),
+            SequenceRequest([20, 1], max_tokens=5),
+            SequenceRequest([12], max_tokens=5, stop_token_ids=(12,))]
+    res = loop(be).run(reqs)
+    assert res[0].token_ids == [10, 11] and res[0].finish_reason == "stop"
+    assert res[1].token_ids == [20, 21, 22, 23, 24] and res[1].finish_reason == "length"
+    assert res[2].token_ids == [] and res[2].finish_reason == "stop"
+    decodes = [c for c in be.calls if c[0] == "decode"]
+    assert [len(c[1]) for c in decodes] == [2, 2, 1, 1]           # the batch shrinks as sequences end
+    closes = [i for i, c in enumerate(be.calls) if c[0] == "close"]
+    first_decode = next(i for i, c in enumerate(be.calls) if c[0] == "decode")
+    assert closes[0] < first_decode                                # a finished sequence gives its slot back at once
+    assert not be.held
+
+
+def test_default_stop_ids_and_callback_cancel():
+    be = ScriptedBackend()
+    seen = []
+
+    def on_token(i, tok):
+        seen.append((i, tok))
+        return i == 1 and tok == 31
+    res = loop(be, default_stop_ids=(13,)).run(
+        [SequenceRequest([10], max_tokens=9), SequenceRequest([30], max_tokens=9)], on_token)
+    assert res[0].token_ids == [10, 11, 12] and res[0].finish_reason == "stop"
+    assert res[1].token_ids == [30, 31] and res[1].finish_reason == "cancelled"
+    assert (1, 31) in seen and (0, 13) not in seen
+
+
+def test_batches_follow_one_another_and_slots_are_used_again():
+    be = ScriptedBackend(n_slots=2)
+    reqs = [SequenceRequest([10 * i], max_tokens=2 + i % 3) for i in range(1, 8)]
+    res = loop(be, max_batch=2).run(reqs)
+    assert [r.token_ids[0] for r in res] == [10 * i for i in range(1, 8)]
+    assert [len(r.token_ids) for r in res] == [2 + i % 3 for i in range(1, 8)]
+    assert be.max_live == 2 and not be.held
+    assert sum(c[0] == "prefill" for c in be.calls) == 4
+    # no request joins a batch that has started: every prefill comes after the previous batch's last close
+    opens = [c for c in be.calls if c[0] == "open"]
+    assert len(opens) == 7
+
+
+def test_batches_respect_the_cache_size():
+    assert reserved_tokens(5, 1) == 64 and reserved_tokens(60, 6) == 128 and reserved_tokens(64, 1) == 64
+    assert form_batches([(60, 6), (10, 10), (100, 100)], max_batch=8, max_tokens=256) == [[0, 1], [2]]
+    with pytest.raises(InvalidRequest):
+        form_batches([(300, 10)], 8, 256)
+
+
+def test_requests_are_validated_before_anything_runs():
+    be = ScriptedBackend()
+    with pytest.raises(InvalidRequest):
+        loop(be).run([SequenceRequest([1], 4), SequenceRequest([1], 4, SamplingParams(temperature=-1.0))])
+    with pytest.raises(InvalidRequest):
+        loop(be).run([SequenceRequest([1], 4, SamplingParams(temperature=float("nan")))])
+    with pytest.raises(PromptTooLong):
+        loop(be).run([SequenceRequest([1] * 64, 4)])
+    assert be.calls == []
+
+
+def test_seeds():
+    be = ScriptedBackend()
+    res = loop(be).run([SequenceRequest([1], 2, SamplingParams(0.8, None, 42)), SequenceRequest([1], 2),
+                        SequenceRequest([1], 2, SamplingParams(0.8))])
+    assert res[0].seed == 42 and res[1].seed is None and isinstance(res[2].seed, int)
+    opens = [c for c in be.calls if c[0] == "open"]
+    assert opens[0][2] == 42 and opens[1][2] is None
+    s, a = splitmix64_next(0)
+    assert a == 0xE220A8397B1DCDAF
+    s2 = skip_draws(0, 3)
+    for _ in range(3):
+        s, _ = splitmix64_next(s) if _ else (s, None)
+    assert skip_draws(0, 1) == splitmix64_next(0)[0] and s2 == splitmix64_next(splitmix64_next(splitmix64_next(0)[0])[0])[0]
+
+
+def test_slots_are_closed_when_the_backend_fails():
+    class Failing(ScriptedBackend):
+        def decode(self, slots, tokens):
+            raise RuntimeError("device lost")
+    be = Failing()
+    with pytest.raises(RuntimeError):
+        loop(be).run([SequenceRequest([1], 4), SequenceRequest([2], 4)])
+    assert not be.held

@@ -1,0 +1,53 @@
+"""The two tiny configurations of the test suite.  They differ in every size
+and option: head counts and grouping, head size, widths that are no power of
+two, number of layers, vocabulary, eps, rope base, window, experts, top-k,
+renormalisation, dense layers, tying, initialisation."""
+import json
+import os
+from pathlib import Path
+
+import numpy as np
+
+TINY_A = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "hidden_act": "silu",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+    "vocab_size": 256, "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 128,
+    "intermediate_size": 96, "num_experts": 4, "num_experts_per_tok": 2, "norm_topk_prob": False,
+    "moe_intermediate_size": 32, "shared_expert_intermediate_size": 64, "decoder_sparse_step": 1,
+    "mlp_only_layers": [], "use_sliding_window": False, "sliding_window": None, "tie_word_embeddings": False,
+}
+INIT_A = dict(weight_std=0.02, bias_std=0.02, norm_std=0.01)
+PROMPTS_A = (5, 11, 17)
+
+TINY_B = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "hidden_act": "silu",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 24,
+    "vocab_size": 384, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 256,
+    "intermediate_size": 128, "num_experts": 6, "num_experts_per_tok": 3, "norm_topk_prob": True,
+    "moe_intermediate_size": 48, "shared_expert_intermediate_size": 80, "decoder_sparse_step": 2,
+    "mlp_only_layers": [0], "use_sliding_window": True, "sliding_window": 16, "max_window_layers": 1,
+    "tie_word_embeddings": True,
+}
+INIT_B = dict(weight_std=0.05, bias_std=0.0, norm_std=0.0)
+PROMPTS_B = (1, 7, 23, 40)
+
+CASES = {"A": (TINY_A, INIT_A), "B": (TINY_B, INIT_B)}
+
+
+def make_folder(tmp: Path, case: str, seed: int = 1234, store: str = "bfloat16", **overrides) -> Path:
+    """Writes config.json and model.safetensors of a tiny case into ``tmp``."""
+    from esp_b200.config import config_from_dict
+    from esp_b200.weights import InitSpec, write_model_folder
+    raw, init = CASES[case]
+    raw = {**raw, **overrides}
+    folder = Path(tmp) / f"tiny_{case}_{store}"
+    write_model_folder(config_from_dict(raw), seed, folder, store, InitSpec(**init))
+    return folder
+
+
+def random_ids(rng: np.random.Generator, n: int, vocab: int) -> list:
+    return [int(t) for t in rng.integers(0, vocab, size=n)]
+
+
+def repo_root() -> Path:
+    return Path(__file__).resolve().parent.parent
