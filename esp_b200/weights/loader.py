@@ -70,12 +70,15 @@ def check_names_and_shapes(specs: list, source, tolerated_suffixes=()) -> None:
     raise InvalidWeights("\n".join(lines))
 
 
-def load_into(model, source, rt) -> None:
-    """Checks the source against the model's parameters, lets every part
-    allocate its storage and fills it."""
-    parts = model.all_parts()
+def load_into(root, source, rt, tolerated_suffixes=None) -> None:
+    """Checks the source against the parameters of ``root`` (a model, or any
+    part with its children), lets every part allocate its storage and fills it."""
+    from ..parts import walk
+    parts = list(walk(root))
     specs = [s for part in parts for s in part.param_specs()]
-    check_names_and_shapes(specs, source, model.plan.tolerated_suffixes)
+    if tolerated_suffixes is None:
+        tolerated_suffixes = getattr(getattr(root, "plan", None), "tolerated_suffixes", ())
+    check_names_and_shapes(specs, source, tolerated_suffixes)
     have = set(source.names())
     stored = {s.name: source.dtype(s.name) for s in specs if s.name in have}
     views = {}

@@ -1,0 +1,116 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy and seeded sampling, unequal prompts in one batch, stop tokens,
+sequences that end earlier, batches that follow one another."""
+import numpy as np
+import pytest
+
+import plain_qwen2_moe as plain
+from esp_b200.provider import DecoderProvider, GenerationRequest
+from tiny import CASES, PROMPTS_A, PROMPTS_B, make_folder, random_ids
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("gen")
+    return {case: make_folder(tmp, case) for case in CASES}
+
+
+def prompts(case, lengths, seed=5):
+    rng = np.random.default_rng(seed)
+    return [random_ids(rng, n, CASES[case][0]["vocab_size"]) for n in lengths]
+
+
+def test_greedy_batch_of_unequal_prompts_float32(folders):
+    """Tiny A: prompts of 5/11/17 tokens, 8 greedy tokens each, token by token."""
+    prov = DecoderProvider.load(folders["A"], dtype="float32", max_batch=4)
+    ps = prompts("A", PROMPTS_A)
+    outs = prov.generate([GenerationRequest(prompt_ids=p, max_tokens=8) for p in ps])
+    c, w = plain.load_model(folders["A"])
+    for p, o in zip(ps, outs):
+        assert o.token_ids == plain.generate(c, w, p, 8) and o.finish_reason == "length" and o.prompt_tokens == len(p)
+    # the same requests one batch after another (two at a time): same tokens, slots used again
+    prov.max_batch = 2
+    again = prov.generate([GenerationRequest(prompt_ids=p, max_tokens=8) for p in ps])
+    assert [o.token_ids for o in again] == [o.token_ids for o in outs]
+    assert prov.engine.cache.book.slots.available == prov.engine.max_slots
+
+
+def test_seeded_sampling_batch_float32(folders):
+    """Tiny B: prompts of 1/7/23/40 tokens, 12 tokens at temperature 0.8."""
+    prov = DecoderProvider.load(folders["B"], dtype="float32", max_batch=4)
+    ps = prompts("B", PROMPTS_B)
+    reqs = [GenerationRequest(prompt_ids=p, max_tokens=12, temperature=0.8, seed=100 + i) for i, p in enumerate(ps)]
+    outs = prov.generate(reqs)
+    c, w = plain.load_model(folders["B"])
+    for i, (p, o) in enumerate(zip(ps, outs)):
+        assert o.token_ids == plain.generate(c, w, p, 12, temperature=0.8, seed=100 + i), i
+        assert o.seed == 100 + i
+    assert [o.token_ids for o in prov.generate(reqs)] == [o.token_ids for o in outs], "same seed, same tokens"
+    nucleus = prov.generate(GenerationRequest(prompt_ids=ps[2], max_tokens=12, temperature=0.8, top_p=0.3, seed=9))
+    assert nucleus.token_ids == plain.generate(c, w, ps[2], 12, temperature=0.8, top_p=0.3, seed=9)
+    unseeded = prov.generate(GenerationRequest(prompt_ids=ps[1], max_tokens=4, temperature=0.8))
+    assert isinstance(unseeded.seed, int) and len(unseeded.token_ids) == 4
+    assert unseeded.token_ids == plain.generate(c, w, ps[1], 4, temperature=0.8, seed=unseeded.seed)
+
+
+def test_stop_tokens_and_early_ends(folders):
+    prov = DecoderProvider.load(folders["A"], dtype="float32", max_batch=4)
+    ps = prompts("A", PROMPTS_A, seed=8)
+    c, w = plain.load_model(folders["A"])
+    free = [plain.generate(c, w, p, 10) for p in ps]
+    stop = free[1][3]                       # what request 1 would say fourth
+    outs = prov.generate([GenerationRequest(prompt_ids=p, max_tokens=10, stop_token_ids=[stop] if i == 1 else [])
+                          for i, p in enumerate(ps)])
+    cut = free[1].index(stop)
+    assert outs[1].token_ids == free[1][:cut] and outs[1].finish_reason == "stop"
+    assert outs[0].token_ids == free[0] and outs[2].token_ids == free[2]      # the others are not disturbed
+    short = prov.generate([GenerationRequest(prompt_ids=ps[0], max_tokens=2), GenerationRequest(prompt_ids=ps[2], max_tokens=9)])
+    assert short[0].token_ids == free[0][:2] and short[1].token_ids == free[2][:9]
+    seen = []
+    streamed = prov.generate_streaming(GenerationRequest(prompt_ids=ps[0], max_tokens=10), lambda t: seen.append(t) or len(seen) == 3)
+    assert streamed.token_ids == free[0][:3] == seen and streamed.finish_reason == "cancelled"
+
+
+@pytest.mark.parametrize("case", ["A", "B"])
+def test_greedy_bfloat16_follows_the_plain_logits(folders, case):
+    """In bfloat16 a near tie between two logits may fall the other way, so each
+    chosen token is checked against the plain logits for the engine's own
+    prefix: it must be the best token up to the bfloat16 bound."""
+    prov = DecoderProvider.load(folders[case], dtype="bfloat16", max_batch=4)
+    ps = prompts(case, PROMPTS_A if case == "A" else PROMPTS_B)
+    outs = prov.generate([GenerationRequest(prompt_ids=p, max_tokens=8) for p in ps])
+    c, w = plain.load_model(folders[case])
+    exact = 0
+    for p, o in zip(ps, outs):
+        assert len(o.token_ids) == 8
+        ids = list(p)
+        for tok in o.token_ids:
+            row = plain.forward_logits(c, w, ids)[-1]
+            assert row[tok] >= row.max() - 2 * 4 * 2.0 ** -8 * np.abs(row).max(), "not the best token within rounding"
+            exact += int(tok == int(row.argmax()))
+            ids.append(tok)
+    assert exact >= 0.9 * 8 * len(ps)
+
+
+def test_next_token_logits_and_capability(folders):
+    prov = DecoderProvider.load(folders["B"], dtype="float32")
+    p = prompts("B", [9])[0]
+    c, w = plain.load_model(folders["B"])
+    ref = plain.forward_logits(c, w, p)[-1]
+    assert np.abs(prov.next_token_logits(p).cpu().numpy() - ref).max() < 2e-5 * max(1.0, np.abs(ref).max())
+    cap = prov.capability
+    assert (cap.context_window, cap.vocab_size, cap.architecture) == (256, 384, "Qwen2MoeForCausalLM")
+
+
+def test_command_line_generates(folders, capsys):
+    import json
+    from esp_b200.cli import main
+    p = prompts("A", [6])[0]
+    rc = main(["generate", "--model", str(folders["A"]), "--dtype", "float32", "--prompt-ids", ",".join(map(str, p)),
+               "--max-tokens", "5"])
+    assert rc == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    c, w = plain.load_model(folders["A"])
+    assert out["token_ids"] == plain.generate(c, w, p, 5) and out["finish_reason"] == "length"

@@ -1,0 +1,387 @@
+"""Each kernel alone against a plain PyTorch reference of the same operation in
+float32/float64, at sizes other than the models' (widths and vocabularies that
+are no power of two, odd row counts, empty groups), with inputs made so that a
+fault shows: one score that stands out at a far key, at the window's edge, at
+a page boundary, in another sequence's pages."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2_moe as plain
+from esp_b200.csrc import ops
+from esp_b200.weights.random_init import normal_values
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, ref, dtype, what=""):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    tol = 2e-6 if dtype == torch.float32 else 2.0 ** -7
+    scale = max(1e-9, float(ref.abs().max()))
+    err = float((got - ref).abs().max())
+    assert err <= tol * scale, f"{what}: max error {err:.3e} on scale {scale:.3e} (bound {tol * scale:.3e})"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(dtype):
+    table = rnd(1000, 200, dtype=dtype)
+    ids = torch.tensor([0, 999, 17, 17, 500], dtype=torch.int32, device=DEV)
+    x = torch.empty(5, 200, device=DEV)
+    st = status()
+    ops.embed_gather(table, ids, x, st)
+    assert torch.equal(x, table.float()[ids.long()]) and st.item() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [200, 2072])
+def test_add_rmsnorm(dtype, width):
+    x = rnd(9, width)
+    y = rnd(9, width, seed=1)
+    gamma = 1 + 0.1 * rnd(width, seed=2)
+    eps = 1e-5
+    ref_x = x + y
+    ref = ref_x.double() / torch.sqrt((ref_x.double() ** 2).mean(-1, keepdim=True) + eps) * gamma.double()
+    x1, h, h32 = x.clone(), torch.empty(9, width, dtype=dtype, device=DEV), torch.empty(9, width, device=DEV)
+    ops.add_rmsnorm(x1, y, gamma, h, eps, h32=h32)
+    assert torch.equal(x1, ref_x)
+    close(h, ref, dtype, "normed rows")
+    close(h32, ref, torch.float32, "unrounded rows")
+    # selected rows, residual left alone
+    rows = torch.tensor([7, 0, 7], dtype=torch.int32, device=DEV)
+    x2, h2 = x.clone(), torch.empty(3, width, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(x2, y, gamma, h2, eps, rows=rows, write_x=False)
+    assert torch.equal(x2, x)
+    close(h2, ref[rows.long()], dtype, "selected rows")
+    # no addend
+    x3, h3 = x.clone(), torch.empty(9, width, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(x3, None, gamma, h3, eps)
+    close(h3, x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * gamma.double(), dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    gu = rnd(13, 2 * 37, scale=3.0)
+    act = torch.empty(13, 37, dtype=dtype, device=DEV)
+    ops.swiglu(gu, act)
+    g, u = gu[:, :37].double(), gu[:, 37:].double()
+    close(act, g / (1 + torch.exp(-g)) * u, dtype)
+
+
+@pytest.mark.parametrize("a_dt, w_dt, c_dt", [(torch.float32, torch.float32, torch.float32),
+                                               (torch.bfloat16, torch.bfloat16, torch.float32),
+                                               (torch.bfloat16, torch.float32, torch.float32),
+                                               (torch.float32, torch.bfloat16, torch.bfloat16)])
+def test_gemm_simt_dense(a_dt, w_dt, c_dt):
+    m, n, k = 77, 130, 150
+    a, w = rnd(m, k, dtype=a_dt), rnd(n, k, dtype=w_dt, seed=1)
+    bias, scale = rnd(n, seed=2), rnd(m, seed=3)
+    c = torch.empty(m, n, dtype=c_dt, device=DEV)
+    ops.gemm_simt(a, w, c, bias=bias, row_scale=scale)
+    ref = (a.double() @ w.double().t() + bias.double()) * scale.double()[:, None]
+    close(c, ref, c_dt, "dense")
+    # a single row gives the same bits as that row inside the larger product
+    c1 = torch.empty(1, n, dtype=c_dt, device=DEV)
+    ops.gemm_simt(a[5:6], w, c1, bias=bias, row_scale=scale[5:6].contiguous())
+    assert torch.equal(c1[0], c[5])
+
+
+def test_gemm_simt_grouped_with_gather_and_empty_groups():
+    g, n, k = 5, 70, 90
+    counts = [3, 0, 66, 1, 0]
+    offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+    total = sum(counts)
+    src = rnd(40, k)
+    a_rows = torch.tensor(np.random.default_rng(0).integers(0, 40, total), dtype=torch.int32, device=DEV)
+    w = rnd(g, n, k, seed=1)
+    scale = rnd(total, seed=2)
+    c = torch.full((total + 3, n), 7.0, device=DEV)
+    ops.gemm_simt(src, w, c, a_rows=a_rows, row_scale=scale, group_offsets=offsets, rows=total)
+    row = 0
+    for e, cnt in enumerate(counts):
+        for _ in range(cnt):
+            ref = (src[a_rows[row].long()].double() @ w[e].double().t()) * scale[row].double()
+            close(c[row], ref, torch.float32, f"group {e} row {row}")
+            row += 1
+    assert torch.all(c[total:] == 7.0), "rows beyond the groups were written"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd, rot", [(24, 24), (128, 128), (40, 16)])
+def test_rope_kvwrite(dtype, hd, rot):
+    nh, nkv, page, n_pages = 3, 1, 64, 6
+    # two sequences: 70 new tokens from position 60, and one token at position 129
+    pos = list(range(60, 130)) + [129]
+    seq = [0] * 70 + [1]
+    n = len(pos)
+    table = torch.tensor([[4, 0, 2], [1, 5, 3]], dtype=torch.int32, device=DEV)
+    qkv = rnd(n, (nh + 2 * nkv) * hd)
+    bias = rnd((nh + 2 * nkv) * hd, seed=5)
+    theta = 10000.0
+    cos_np, sin_np = plain.rope_angles(np.arange(200), rot, theta)
+    cos, sin = torch.from_numpy(cos_np).to(DEV), torch.from_numpy(sin_np).to(DEV)
+    q_out = torch.empty(n, nh * hd, dtype=dtype, device=DEV)
+    kc = torch.zeros(n_pages, nkv, page, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    st = status()
+    ops.rope_kvwrite(qkv, bias, torch.tensor(seq, dtype=torch.int32, device=DEV),
+                     torch.tensor(pos, dtype=torch.int32, device=DEV), cos, sin, rot, q_out, kc, vc, table, page,
+                     nh, nkv, hd, True, st)
+    assert st.item() == 0
+    x = (qkv + bias).cpu().numpy().reshape(n, nh + 2 * nkv, hd)
+    rotated = x.copy()
+    rotated[:, :nh + nkv, :rot] = plain.apply_rope(x[:, :nh + nkv, :rot], cos_np[pos], sin_np[pos])
+    close(q_out.view(n, nh, hd), torch.from_numpy(rotated[:, :nh]), dtype, "queries")
+    tbl = table.cpu().numpy()
+    for i in range(n):
+        pg = tbl[seq[i], pos[i] // page]
+        close(kc[pg, 0, pos[i] % page], torch.from_numpy(rotated[i, nh]), dtype, f"key of token {i}")
+        close(vc[pg, 0, pos[i] % page], torch.from_numpy(x[i, nh + 1]), dtype, f"value of token {i}")
+    written = {(tbl[seq[i], pos[i] // page], pos[i] % page) for i in range(n)}
+    mask = torch.ones(n_pages, page, dtype=torch.bool)
+    for pg, ip in written:
+        mask[pg, ip] = False
+    assert torch.all(kc[:, 0][mask.to(DEV)] == 0), "a cache row that no token owns was written"
+
+
+def paged(seqs_k, seqs_v, tables, n_pages, nkv, hd, dtype, page=64):
+    kc = torch.zeros(n_pages, nkv, page, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    for s, (k, v) in enumerate(zip(seqs_k, seqs_v)):
+        for p in range(k.shape[0]):
+            pg = tables[s][p // page]
+            kc[pg, :, p % page] = k[p].to(dtype)
+            vc[pg, :, p % page] = v[p].to(dtype)
+    return kc, vc
+
+
+def attention_reference(q, k, v, pos, window, group):
+    """q [nh, hd] at absolute position pos over k, v [len, nkv, hd] in float64."""
+    nh, hd = q.shape
+    out = torch.zeros(nh, hd, dtype=torch.float64)
+    lo = 0 if not window else max(0, pos - window + 1)
+    for h in range(nh):
+        kk, vv = k[lo:pos + 1, h // group].double(), v[lo:pos + 1, h // group].double()
+        s = (kk @ q[h].double()) / np.sqrt(hd)
+        out[h] = torch.softmax(s, 0) @ vv
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, nkv, hd, window", [(6, 2, 40, None), (4, 1, 128, 100), (2, 2, 256, None), (8, 4, 16, 65)])
+def test_attention_finds_the_key_that_matters(dtype, nh, nkv, hd, window):
+    """Three sequences in interleaved pages.  In each, one key is made to carry
+    almost all of a query's weight: a far key among hundreds, the oldest key a
+    window still shows, the key just outside it, keys on both sides of a page
+    boundary.  Dropping, shifting or misplacing any of them changes the output
+    by far more than rounding."""
+    torch.manual_seed(1)
+    lens = [700, 130, 65]
+    group = nh // nkv
+    tables = [[3 * i + s for i in range(12)] for s in range(3)]        # interleaved pages
+    ks = [torch.randn(n, nkv, hd) * 0.3 for n in lens]
+    vs = [torch.randn(n, nkv, hd) for n in lens]
+    queries = []   # (sequence, position, target key)
+    last = lens[0] - 1
+    w = window or 10 ** 9
+    for target in {3, 63, 64, 65, 127, 128, max(0, last - w + 1), max(0, last - w), last}:
+        queries.append((0, last, target))
+    queries += [(1, 129, 64), (1, 100, 0), (2, 64, 63), (2, 0, 0), (2, 1, 0)]
+    q = torch.randn(len(queries), nh, hd) * 0.3
+    for i, (s, p, target) in enumerate(queries):
+        for h in range(nh):
+            # align the query with the target key and give the pair a large norm
+            ks[s][target, h // group] = ks[s][target, h // group] / ks[s][target, h // group].norm() * 6.0
+            q[i, h] = ks[s][target, h // group] * (np.sqrt(hd) * 3.0 / 6.0)
+    # (a later query may re-scale an earlier target; keys are final now, so references below are consistent)
+    qd = q.to(dtype)
+    kc, vc = paged(ks, vs, tables, 36, nkv, hd, dtype)
+    table = torch.tensor([t + [-1] * 0 for t in tables], dtype=torch.int32, device=DEV)
+    out = torch.empty(len(queries), nh * hd, dtype=dtype, device=DEV)
+    st = status()
+    ops.attn_simt(qd.reshape(len(queries), nh * hd).to(DEV), kc, vc, out,
+                  torch.tensor([s for s, _, _ in queries], dtype=torch.int32, device=DEV),
+                  torch.tensor([p for _, p, _ in queries], dtype=torch.int32, device=DEV), table, 64, nh, nkv, hd,
+                  window, st)
+    assert st.item() == 0
+    for i, (s, p, target) in enumerate(queries):
+        ref = attention_reference(qd[i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(), p, window, group)
+        close(out[i].view(nh, hd), ref, dtype, f"query {i} (sequence {s}, position {p}, target key {target})")
+
+
+@pytest.mark.parametrize("h_dt, w_dt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("norm", [False, True])
+def test_router_topk(h_dt, w_dt, norm):
+    n, width, e, k = 11, 150, 10, 3
+    h = rnd(n, width, dtype=h_dt)
+    wr = rnd(e, width, dtype=w_dt, seed=1, scale=0.2)
+    wr[7] = wr[2]                      # experts 2 and 7 always tie: the lower id must win
+    wg = rnd(1, width, dtype=w_dt, seed=2, scale=0.2)
+    ids = torch.empty(n, k, dtype=torch.int32, device=DEV)
+    wts = torch.empty(n, k, device=DEV)
+    gate = torch.empty(n, device=DEV)
+    probs = torch.empty(n, e, device=DEV)
+    st = status()
+    ops.router_topk(h, wr, wg, ids, wts, gate, k, norm, st, probs)
+    assert st.item() == 0
+    p = torch.softmax(h.double() @ wr.double().t(), -1)
+    close(probs, p, torch.float32, "probabilities")
+    close(gate, torch.sigmoid(h.double() @ wg.double().t())[:, 0], torch.float32, "shared gate")
+    order = np.argsort(-p.cpu().numpy(), axis=1, kind="stable")[:, :k]
+    got = ids.cpu().numpy()
+    for t in range(n):
+        assert list(got[t]) == list(order[t]), (t, got[t], order[t])
+        assert not (7 in got[t] and 2 not in got[t])
+        chosen = p[t, got[t]]
+        close(wts[t], chosen / chosen.sum() if norm else chosen, torch.float32, "weights")
+
+
+def test_moe_permute_and_combine():
+    n, k, e, width = 37, 3, 6, 50
+    rng = np.random.default_rng(0)
+    ids_np = np.stack([rng.permutation(e)[:k] for _ in range(n)]).astype(np.int32)
+    ids_np[:, :] = np.where(ids_np == 4, 5, ids_np) if False else ids_np
+    ids = torch.tensor(ids_np, device=DEV)
+    wts = rnd(n, k).abs()
+    offsets = torch.empty(e + 1, dtype=torch.int32, device=DEV)
+    perm_token = torch.empty(n * k, dtype=torch.int32, device=DEV)
+    perm_weight = torch.empty(n * k, device=DEV)
+    inverse = torch.empty(n, k, dtype=torch.int32, device=DEV)
+    st = status()
+    ops.moe_permute(ids, wts, e, offsets, perm_token, perm_weight, inverse, st)
+    assert st.item() == 0
+    off = offsets.cpu().numpy()
+    assert list(off) == list(np.concatenate([[0], np.cumsum(np.bincount(ids_np.reshape(-1), minlength=e))]))
+    inv, pt, pw = inverse.cpu().numpy(), perm_token.cpu().numpy(), perm_weight.cpu().numpy()
+    assert sorted(inv.reshape(-1)) == list(range(n * k)), "a permuted row is used twice or not at all"
+    for t in range(n):
+        for r in range(k):
+            row = inv[t, r]
+            assert off[ids_np[t, r]] <= row < off[ids_np[t, r] + 1] and pt[row] == t
+            assert pw[row] == wts[t, r].item()
+    expert_out = rnd(n * k, width, seed=3)
+    shared, gate = rnd(n, width, seed=4), rnd(n, seed=5).abs()
+    y = torch.empty(n, width, device=DEV)
+    ops.moe_combine(expert_out, ids, inverse, gate, shared, y)
+    eo = expert_out.cpu().numpy()
+    for t in range(n):
+        acc = np.zeros(width, dtype=np.float32)
+        for r in np.argsort(ids_np[t], kind="stable"):          # ascending expert id, float32 adds in that order
+            acc = acc + eo[inv[t, r]]
+        acc = acc + gate[t].item() * shared[t].cpu().numpy()
+        assert np.allclose(y[t].cpu().numpy(), acc, rtol=0, atol=1e-6), t
+
+
+def test_argmax_takes_the_lower_id_on_ties():
+    logits = rnd(4, 1000)
+    logits[0, 900] = logits[0, 17] = 50.0
+    logits[1, 999] = 60.0
+    logits[2, 0] = 60.0
+    tokens = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.pick_tokens(logits, None, None, torch.zeros(4, dtype=torch.int64, device=DEV),
+                    torch.arange(4, dtype=torch.int32, device=DEV), tokens)
+    assert tokens.tolist() == [17, 999, 0, int(logits[3].argmax())]
+
+
+def _draw_setup(rows, vocab):
+    logits = rnd(rows, vocab, scale=2.0)
+    temps = [0.8 if r % 3 else 1.5 for r in range(rows)]
+    temps[5] = 0.0
+    top_ps = [None if r % 2 else [0.9, 0.5, 0.05][r % 3] for r in range(rows)]
+    seeds = [1000 + 7 * r for r in range(rows)]
+    state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    tokens = torch.empty(rows, dtype=torch.int32, device=DEV)
+    args = (logits, torch.tensor(temps, device=DEV), torch.tensor([-1.0 if t is None else t for t in top_ps], device=DEV),
+            state, torch.arange(rows, dtype=torch.int32, device=DEV), tokens)
+    return logits, temps, top_ps, seeds, state, tokens, args
+
+
+def test_sampling_matches_the_plain_sampler():
+    """Same seed, same logits: the device picks what the plain sampler picks,
+    with and without a nucleus cut, and advances its stream by one draw."""
+    rows, vocab = 48, 1000
+    logits, temps, top_ps, seeds, state, tokens, args = _draw_setup(rows, vocab)
+    ops.pick_tokens(*args)
+    first = tokens.tolist()
+    ops.pick_tokens(*args)
+    second = tokens.tolist()
+    lg = logits.cpu().numpy()
+    for r in range(rows):
+        rng = plain.SplitMix64(seeds[r])
+        if temps[r] == 0.0:
+            assert first[r] == second[r] == int(lg[r].argmax())
+            assert state[r].item() == seeds[r], "a greedy row must not draw"
+            continue
+        assert first[r] == plain.sample_row(lg[r], temps[r], top_ps[r], rng), f"row {r}, first draw"
+        assert second[r] == plain.sample_row(lg[r], temps[r], top_ps[r], rng), f"row {r}, second draw"
+        assert (state[r].item() & ((1 << 64) - 1)) == rng.state
+
+
+def test_sampling_at_a_large_flat_vocabulary_picks_the_token_under_the_draw():
+    """With 151,936 nearly equal weights the plain sampler's running float32
+    sums drift by more than one token's mass, so equality with it is not a
+    property of a correct sampler.  What is: the chosen token's interval of
+    cumulative mass (ranking by descending weight, ties by id; sums in
+    float64) holds the draw u * (kept mass), up to the rounding of u."""
+    rows, vocab = 24, 151936
+    logits, temps, top_ps, seeds, state, tokens, args = _draw_setup(rows, vocab)
+    ops.pick_tokens(*args)
+    picked = tokens.tolist()
+    lg = logits.cpu().numpy()
+    for r in range(rows):
+        if temps[r] == 0.0:
+            assert picked[r] == int(lg[r].argmax())
+            continue
+        u = np.float32(plain.SplitMix64(seeds[r]).next_f64())
+        w = np.exp((lg[r] - lg[r].max()) * (np.float32(1.0) / np.float32(temps[r]))).astype(np.float32)
+        order = np.lexsort((np.arange(vocab), -w))
+        cum = np.cumsum(w[order].astype(np.float64))
+        kept = cum[-1]
+        if top_ps[r] is not None:
+            keep = int(np.argmax(cum >= kept * top_ps[r]))
+            kept = cum[keep]
+            assert np.nonzero(order == picked[r])[0][0] <= keep, f"row {r}: picked outside the nucleus"
+        rank = int(np.nonzero(order == picked[r])[0][0])
+        thr, tol = float(u) * kept, 1e-6 * kept
+        assert cum[rank] >= thr - tol and (rank == 0 or cum[rank - 1] <= thr + tol), (
+            f"row {r}: draw {thr:.6f} is outside [{cum[rank - 1] if rank else 0:.6f}, {cum[rank]:.6f}]")
+
+
+def test_sampling_follows_the_distribution():
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5]], device=DEV).repeat(4096, 1).contiguous()
+    state = torch.arange(4096, dtype=torch.int64, device=DEV) * 7919 + 3
+    tokens = torch.empty(4096, dtype=torch.int32, device=DEV)
+    ops.pick_tokens(logits, torch.ones(4096, device=DEV), None, state, torch.arange(4096, dtype=torch.int32, device=DEV),
+                    tokens)
+    freq = np.bincount(tokens.cpu().numpy(), minlength=5) / 4096
+    p = torch.softmax(logits[0].double(), 0).cpu().numpy()
+    assert np.abs(freq - p).max() < 0.03
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_normal_fill_matches_the_host_generator(dtype):
+    out = torch.empty(5000, dtype=dtype, device=DEV)
+    ops.normal_fill(out, 0x1234567890ABCDEF, 1.0, 0.5)
+    host = torch.from_numpy(normal_values(0x1234567890ABCDEF, 5000, 1.0, 0.5)).to(dtype)
+    diff = (out.cpu().float() - host.float()).abs()
+    assert diff.max() <= (1e-5 if dtype == torch.float32 else 2.0 ** -7 * 3)
+    assert abs(out.float().mean().item() - 1.0) < 0.03 and abs(out.float().std().item() - 0.5) < 0.03
+
+
+def test_finite_check_sets_the_status_word():
+    st = status()
+    v = rnd(3, 1000)
+    ops.finite_check(v, st)
+    assert st.item() == 0
+    v[1, 500] = float("nan")
+    ops.finite_check(v, st)
+    assert st.item() == 2
