@@ -54,7 +54,17 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches made through this module since the process started."""
+    return _launches
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if code != 0:
         raise Backend(f"{what}: the launch was refused with CUDA error {code} "
                       f"(invalid value means a size this kernel does not take)")
