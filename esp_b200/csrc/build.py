@@ -30,6 +30,8 @@ CSRC = Path(__file__).resolve().parent
 # library name -> its sources.  Headers (*.cuh) are shared by all of them.
 LIBRARIES = {
     "core": ["elementwise.cu", "gemm_simt.cu", "rope_kv.cu", "attn_simt.cu", "moe_route.cu", "sampling.cu"],
+    # bfloat16 only: loaded when a model runs in bfloat16
+    "bf16": ["gemm_skinny.cu", "attn_decode.cu"],
 }
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

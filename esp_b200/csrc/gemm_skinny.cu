@@ -1,0 +1,211 @@
+// Weight-streaming matrix product for a handful of rows (decode):
+//   C[m, n] = scale[m] * sum_k A[row(m), k] * W[g][n, k]          (PLAIN)
+//   act[m, j] = silu(A W_gate[j]) * (A W_up[j])                   (SWIGLU; W = [gate rows; up rows])
+// bfloat16 operands, float accumulation on the tensor cores (mma.sync
+// m16n8k16 with the weight rows as the 16-row operand and up to 8 tokens as the
+// 8-column operand, so a step with few rows wastes no tensor work and every
+// weight byte is read from HBM exactly once).  The kernel is bound by the
+// weight stream: each lane loads 16 contiguous bytes of a weight row straight
+// into its fragment registers (no shared-memory staging), with a permutation
+// of k inside each group of 32 that the activation fragment mirrors.
+//
+// One block = one tile of 16 weight rows (PLAIN) or 8 gate + 8 up rows
+// (SWIGLU) and, in the grouped form, one group (expert).  Its 8 warps split K
+// into 8 slices and their partial sums are added in warp order, so a result
+// does not depend on anything but its own row and weights.  Activation rows of
+// the block's group are staged in shared memory (gathered through ``a_rows``),
+// 8 * NBLK rows at a time.
+#include "common.cuh"
+
+namespace {
+constexpr int WARPS = 8;
+constexpr int UNROLL = 4;
+
+struct SkinnyParams {
+    const bf16* W;
+    long long w_group_stride;       // elements between groups
+    const bf16* A;
+    long long lda;
+    const int* a_rows;
+    const int* group_offsets;
+    const float* row_scale;
+    void* C;
+    long long ldc;
+    int M, N, K;
+};
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                         unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load_stream(const bf16* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+
+template <int NBLK, bool SWIGLU, typename TC>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_kernel(SkinnyParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int K = p.K;
+    const int a_stride = K + 32;                                    // elements; 64 bytes of padding per row
+    bf16* a_s = reinterpret_cast<bf16*>(smem_raw);                   // [8*NBLK][a_stride]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)8 * NBLK * a_stride * sizeof(bf16));   // [WARPS][NBLK][32][4]
+
+    int m_begin = 0, m_end = p.M;
+    const bf16* W = p.W;
+    if (p.group_offsets) {
+        m_begin = p.group_offsets[blockIdx.y];
+        m_end = p.group_offsets[blockIdx.y + 1];
+        W += (size_t)blockIdx.y * p.w_group_stride;
+    }
+    if (m_begin >= m_end) return;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
+    // the two weight rows this lane streams
+    int row_a, row_b;
+    bool ok_a, ok_b;
+    if (SWIGLU) {
+        const int j = blockIdx.x * 8 + g;
+        ok_a = ok_b = j < p.N;
+        row_a = j;
+        row_b = p.N + j;
+    } else {
+        row_a = blockIdx.x * 16 + g;
+        row_b = row_a + 8;
+        ok_a = row_a < p.N;
+        ok_b = row_b < p.N;
+    }
+    const bf16* wa_ptr = W + (size_t)(ok_a ? row_a : 0) * K;
+    const bf16* wb_ptr = W + (size_t)(ok_b ? row_b : 0) * K;
+    // K slice of this warp, in whole groups of 32
+    const int groups32 = (K + 31) / 32;
+    const int per_warp = (groups32 + WARPS - 1) / WARPS;
+    const int k_lo = warp * per_warp * 32;
+    const int k_hi = min(K, (warp + 1) * per_warp * 32);
+
+    for (int m0 = m_begin; m0 < m_end; m0 += 8 * NBLK) {
+        const int cnt = min(8 * NBLK, m_end - m0);
+        __syncthreads();                                              // the previous chunk's readers are done
+        // stage the activation rows (16-byte pieces), zero rows beyond cnt
+        const int pieces = K / 8;
+        for (int idx = tid; idx < 8 * NBLK * pieces; idx += WARPS * 32) {
+            const int r = idx / pieces, q = idx - r * pieces;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < cnt) {
+                const int src = p.a_rows ? p.a_rows[m0 + r] : (m0 + r);
+                v = *reinterpret_cast<const uint4*>(p.A + (size_t)src * p.lda + q * 8);
+            }
+            *reinterpret_cast<uint4*>(a_s + (size_t)r * a_stride + q * 8) = v;
+        }
+        __syncthreads();
+
+        float acc[NBLK][4];
+#pragma unroll
+        for (int nb = 0; nb < NBLK; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[nb][i] = 0.f;
+
+        for (int k0 = k_lo; k0 < k_hi; k0 += 32 * UNROLL) {
+            uint4 wa[UNROLL], wb[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const int k = k0 + u * 32 + tg * 8;
+                const bool in = k < k_hi;                             // K is a multiple of 8: a piece is whole or absent
+                wa[u] = (in && ok_a) ? load_stream(wa_ptr + k) : make_uint4(0, 0, 0, 0);
+                wb[u] = (in && ok_b) ? load_stream(wb_ptr + k) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const int k = k0 + u * 32 + tg * 8;
+                if (k0 + u * 32 >= k_hi) break;
+#pragma unroll
+                for (int nb = 0; nb < NBLK; nb++) {
+                    if (nb * 8 >= cnt) break;
+                    uint4 av = make_uint4(0, 0, 0, 0);
+                    if (k < k_hi) av = *reinterpret_cast<const uint4*>(a_s + (size_t)(nb * 8 + g) * a_stride + k);
+                    mma_bf16(acc[nb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, av.x, av.y);
+                    mma_bf16(acc[nb], wa[u].z, wb[u].z, wa[u].w, wb[u].w, av.z, av.w);
+                }
+            }
+        }
+        // partial sums of the 8 warps, added in warp order
+#pragma unroll
+        for (int nb = 0; nb < NBLK; nb++)
+            *reinterpret_cast<float4*>(red + (((size_t)warp * NBLK + nb) * 32 + lane) * 4) =
+                make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
+        __syncthreads();
+        if (SWIGLU) {
+            for (int e = tid; e < NBLK * 64; e += WARPS * 32) {
+                const int nb = e / 64, ln = (e % 64) / 2, i = e & 1;
+                float gate = 0.f, up = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; w++) {
+                    gate += red[(((size_t)w * NBLK + nb) * 32 + ln) * 4 + i];
+                    up += red[(((size_t)w * NBLK + nb) * 32 + ln) * 4 + 2 + i];
+                }
+                const int tok = nb * 8 + (ln & 3) * 2 + i, j = blockIdx.x * 8 + (ln >> 2);
+                if (tok < cnt && j < p.N) {
+                    const float v = gate / (1.0f + expf(-gate)) * up;
+                    reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + j] = from_f32<TC>(v);
+                }
+            }
+        } else {
+            for (int e = tid; e < NBLK * 128; e += WARPS * 32) {
+                const int nb = e / 128, ln = (e % 128) / 4, i = e & 3;
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; w++) v += red[(((size_t)w * NBLK + nb) * 32 + ln) * 4 + i];
+                const int tok = nb * 8 + (ln & 3) * 2 + (i & 1), n = blockIdx.x * 16 + (ln >> 2) + (i >= 2 ? 8 : 0);
+                if (tok < cnt && n < p.N) {
+                    if (p.row_scale) v *= p.row_scale[m0 + tok];
+                    reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n] = from_f32<TC>(v);
+                }
+            }
+        }
+    }
+}
+
+template <int NBLK, bool SWIGLU, typename TC>
+int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
+    const size_t smem = (size_t)8 * NBLK * (p.K + 32) * sizeof(bf16) + (size_t)WARPS * NBLK * 32 * 4 * sizeof(float);
+    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    static bool raised = false;        // per instantiation
+    if (smem > 48 * 1024 && !raised) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NBLK, SWIGLU, TC>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    const int tiles = SWIGLU ? (p.N + 7) / 8 : (p.N + 15) / 16;
+    dim3 grid(tiles, groups);
+    gemm_skinny_kernel<NBLK, SWIGLU, TC><<<grid, WARPS * 32, smem, stream>>>(p);
+    return esp_launch_status();
+}
+}  // namespace
+
+// ``max_rows``: an upper bound of the rows of any one group (of M when dense); it
+// selects how many rows are staged at a time.  swiglu: N is the intermediate
+// size and W holds 2N rows per group.  c_dtype: 0 float, 1 bfloat16.
+ESP_API int esp_gemm_skinny(const void* A, long long lda, const int* a_rows, const void* W, long long w_group_stride,
+                            const float* row_scale, void* C, int c_dtype, long long ldc, const int* group_offsets,
+                            int groups, int M, int N, int K, int max_rows, int swiglu, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K % 8 != 0 || lda % 8 != 0 || groups > 65535) return (int)cudaErrorInvalidValue;
+    SkinnyParams p{(const bf16*)W, w_group_stride, (const bf16*)A, lda, a_rows, group_offsets, row_scale, C, ldc, M, N, K};
+    const int g = group_offsets ? groups : 1;
+    const bool two = max_rows > 8 && (size_t)16 * (K + 32) * 2 + WARPS * 2 * 512 <= 227 * 1024;
+#define ESP_GO(NB, SW, TC) return launch<NB, SW, TC>(p, g, stream)
+    if (swiglu) {
+        if (c_dtype == 1) { if (two) ESP_GO(2, true, bf16); else ESP_GO(1, true, bf16); }
+        else { if (two) ESP_GO(2, true, float); else ESP_GO(1, true, float); }
+    } else {
+        if (c_dtype == 1) { if (two) ESP_GO(2, false, bf16); else ESP_GO(1, false, bf16); }
+        else { if (two) ESP_GO(2, false, float); else ESP_GO(1, false, float); }
+    }
+#undef ESP_GO
+    return (int)cudaErrorInvalidValue;
+}

@@ -31,6 +31,9 @@ _SIGNATURES = {
     "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P],
     "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
+    "esp_gemm_skinny": [P, c_longlong, P, P, c_longlong, P, P, c_int, c_longlong, P, c_int, c_int, c_int, c_int, c_int,
+                        c_int, P],
+    "esp_attn_decode": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
 }
 
 _bound: dict = {}
@@ -226,3 +229,62 @@ def pick_tokens(logits, temperature, top_p, rng_state, row_slot, tokens):
     _check(_fn("core", "esp_pick_tokens")(
         _ptr(logits, torch.float32, "logits"), n, vocab, _ptr(temperature, torch.float32), _ptr(top_p, torch.float32),
         _ptr(rng_state, torch.int64), _ptr(row_slot, torch.int32), _ptr(tokens, torch.int32), _stream()), "pick_tokens")
+
+
+# ---------------------------------------------------------------------------
+# bfloat16 kernels (library "bf16")
+# ---------------------------------------------------------------------------
+SKINNY_MAX_SMEM = 227 * 1024
+
+
+def skinny_fits(k: int) -> bool:
+    """Whether gemm_skinny can stage eight activation rows of width k."""
+    return k % 8 == 0 and 8 * (k + 32) * 2 + 8 * 512 <= SKINNY_MAX_SMEM
+
+
+def gemm_skinny(a, w, c, swiglu=False, row_scale=None, a_rows=None, group_offsets=None, rows=None, max_rows=None):
+    """Weight-streaming product for few rows; bfloat16 a and w.  Plain: c[m] =
+    scale[m] * a[row(m)] @ w[g].T with w [N,K] or [G,N,K].  swiglu: w holds
+    [gate rows; up rows] ([2I,K] or [G,2I,K]) and c[m, j] = silu(gate_j) * up_j
+    ([rows, I]).  ``max_rows``: upper bound of the rows of one group."""
+    grouped = group_offsets is not None
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise Backend("gemm_skinny takes bfloat16 operands")
+    if grouped:
+        groups, wn, k = w.shape
+    else:
+        groups = 1
+        wn, k = w.shape
+    n = wn // 2 if swiglu else wn
+    m = c.shape[0] if rows is None else rows
+    if a.shape[-1] != k or c.shape[-1] != n or a.stride(-1) != 1 or c.stride(-1) != 1 or not w.is_contiguous():
+        raise Backend(f"gemm_skinny: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, c {tuple(c.shape)}")
+    if k % 8 != 0 or a.stride(0) % 8 != 0 or a.data_ptr() % 16 != 0:
+        raise Backend(f"gemm_skinny: width {k} (and the row stride) must be a multiple of 8")
+    if max_rows is None:
+        max_rows = m
+    code = _fn("bf16", "esp_gemm_skinny")(
+        a.data_ptr(), a.stride(0), _ptr(a_rows, torch.int32, "a_rows"), w.data_ptr(), wn * k,
+        _ptr(row_scale, torch.float32, "row_scale"), c.data_ptr(), _is_bf16(c), c.stride(0),
+        _ptr(group_offsets, torch.int32, "group_offsets"), groups, m, n, k, max_rows, 1 if swiglu else 0, _stream())
+    _check(code, "gemm_skinny")
+
+
+ATTN_DECODE_SPLIT = 256
+
+
+def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, tok_seq, tok_pos, block_table, page, nh, nkv, hd, window,
+                n_splits, status):
+    """Split-key attention for few token rows (bfloat16; head sizes 64, 128, 192, 256).
+    part_o float32 [N, nh, n_splits, hd] and part_ml float32 [N, nh, n_splits, 2] are scratch."""
+    if hd not in (64, 128, 192, 256):
+        raise Backend(f"attn_decode: head size {hd} is not one of 64, 128, 192, 256")
+    n = q.shape[0]
+    if part_o.numel() < n * nh * n_splits * hd or part_ml.numel() < n * nh * n_splits * 2:
+        raise Backend("attn_decode: scratch is too small")
+    _check(_fn("bf16", "esp_attn_decode")(
+        _ptr(q, torch.bfloat16, "q"), _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
+        _ptr(out, torch.bfloat16), _ptr(part_o, torch.float32), _ptr(part_ml, torch.float32),
+        _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
+        k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), n_splits, _ptr(status, torch.int32), _stream()),
+        "attn_decode")

@@ -11,6 +11,9 @@ from .linear import linear
 from .position import NoPosition
 
 
+DECODE_ROWS = 128      # steps with at most this many token rows use the split-key kernel
+
+
 class Attention(Part):
     """q/k/v projection (+bias), position encoding of q and k, cache write,
     causal (optionally windowed) softmax attention, output projection
@@ -98,9 +101,19 @@ class Attention(Part):
         return y
 
     def attend(self, q, o, ctx, layer):
-        s = self.spec
-        ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, ctx.block_tables[layer.group], layer.page,
-                      s.num_heads, s.num_kv_heads, s.head_dim, s.window, self.rt.status)
+        s, rt = self.spec, self.rt
+        table = ctx.block_tables[layer.group]
+        n = q.shape[0]
+        if rt.dtype == torch.bfloat16 and s.head_dim in (64, 128, 192, 256) and n <= DECODE_ROWS:
+            # few rows: split the keys over blocks so that the cache streams at full width
+            n_splits = (table.shape[1] * layer.page + ops.ATTN_DECODE_SPLIT - 1) // ops.ATTN_DECODE_SPLIT
+            part_o = rt.ws.get("attn_part_o", (n, s.num_heads, n_splits, s.head_dim), torch.float32)
+            part_ml = rt.ws.get("attn_part_ml", (n, s.num_heads, n_splits, 2), torch.float32)
+            ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, ctx.tok_seq, ctx.tok_pos, table, layer.page,
+                            s.num_heads, s.num_kv_heads, s.head_dim, s.window, n_splits, rt.status)
+            return
+        ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, table, layer.page, s.num_heads,
+                      s.num_kv_heads, s.head_dim, s.window, rt.status)
 
 
 register("mixer", "attention", Attention)

@@ -6,17 +6,15 @@ import torch
 
 from ..csrc import ops
 from .base import ParamSpec, Part, register
-from .linear import grouped_linear, linear
+from .linear import grouped_linear, grouped_swiglu_linear, linear, swiglu_linear
 
 
 def _swiglu_mlp(rt, h, w_gate_up, w_down, out, tag):
     """out = down(silu(gate h) * (up h)); w_gate_up is [2I, H], gate rows first."""
     n = h.shape[0]
     inter = w_gate_up.shape[0] // 2
-    gu = rt.ws.get(tag + "_gu", (n, 2 * inter), torch.float32)
-    linear(rt, h, w_gate_up, gu)
     act = rt.ws.get(tag + "_act", (n, inter), rt.dtype)
-    ops.swiglu(gu, act)
+    swiglu_linear(rt, h, w_gate_up, act, tag)
     linear(rt, act, w_down, out)
     return out
 
@@ -140,21 +138,20 @@ class MoeSwiGluShared(Part):
         perm_weight = ws.get("moe_perm_weight", (n * k,), torch.float32)
         inverse = ws.get("moe_inverse", (n, k), torch.int32)
         ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status)
-        expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k)
+        expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n)
         shared = ws.get("moe_shared_out", (n, H), torch.float32)
         _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
         ops.moe_combine(expert_out, ids, inverse, gate, shared, y)
 
-    def experts(self, h, offsets, perm_token, perm_weight, rows):
+    def experts(self, h, offsets, perm_token, perm_weight, rows, max_rows):
         """expert_out[r] = weight[r] * down_e(silu(gate_e x) * (up_e x)) for every
-        permuted row r, x = h[perm_token[r]], e the expert whose range holds r."""
+        permuted row r, x = h[perm_token[r]], e the expert whose range holds r.
+        ``max_rows``: no expert has more rows than this (a token names an expert once)."""
         s, rt = self.spec, self.rt
-        gu = rt.ws.get("moe_gu", (rows, 2 * s.expert_intermediate), torch.float32)
-        grouped_linear(rt, h, self.w_gate_up, gu, offsets, a_rows=perm_token, rows=rows)
         act = rt.ws.get("moe_act", (rows, s.expert_intermediate), rt.dtype)
-        ops.swiglu(gu, act)
+        grouped_swiglu_linear(rt, h, self.w_gate_up, act, offsets, perm_token, rows, max_rows, "moe")
         out = rt.ws.get("moe_expert_out", (rows, s.hidden), torch.float32)
-        grouped_linear(rt, act, self.w_down, out, offsets, row_scale=perm_weight, rows=rows)
+        grouped_linear(rt, act, self.w_down, out, offsets, perm_weight, rows, max_rows)
         return out
 
 

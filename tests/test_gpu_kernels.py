@@ -385,3 +385,105 @@ def test_finite_check_sets_the_status_word():
     v[1, 500] = float("nan")
     ops.finite_check(v, st)
     assert st.item() == 2
+
+
+# ---------------------------------------------------------------------------
+# bfloat16 kernels
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16, 40])
+@pytest.mark.parametrize("n, k", [(70, 96), (130, 200), (48, 2048), (33, 5632)])
+def test_gemm_skinny_dense(m, n, k):
+    a, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1)
+    scale = rnd(m, seed=2)
+    c = torch.full((m + 2, n), 7.0, device=DEV)
+    ops.gemm_skinny(a, w, c, row_scale=scale, rows=m)
+    close(c[:m], (a.double() @ w.double().t()) * scale.double()[:, None], torch.float32, "skinny dense")
+    assert torch.all(c[m:] == 7.0)
+    # a row's bits do not depend on the rows beside it
+    c1 = torch.empty(1, n, device=DEV)
+    ops.gemm_skinny(a[m - 1:m], w, c1, row_scale=scale[m - 1:m].contiguous())
+    assert torch.equal(c1[0], c[m - 1])
+
+
+@pytest.mark.parametrize("m, inter, k", [(3, 44, 96), (16, 100, 2048), (9, 8, 64)])
+def test_gemm_skinny_swiglu(m, inter, k):
+    a, w = rnd(m, k, dtype=torch.bfloat16), rnd(2 * inter, k, dtype=torch.bfloat16, seed=1, scale=0.2)
+    act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(a, w, act, swiglu=True)
+    g, u = a.double() @ w[:inter].double().t(), a.double() @ w[inter:].double().t()
+    close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "skinny swiglu")
+
+
+def test_gemm_skinny_grouped_gather_scale_and_chunks():
+    g, n, k = 6, 40, 136
+    counts = [2, 0, 37, 1, 0, 9]                      # 37 rows: more than one staging chunk
+    offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+    total = sum(counts)
+    src = rnd(20, k, dtype=torch.bfloat16)
+    a_rows = torch.tensor(np.random.default_rng(1).integers(0, 20, total), dtype=torch.int32, device=DEV)
+    w = rnd(g, n, k, dtype=torch.bfloat16, seed=1)
+    scale = rnd(total, seed=2)
+    c = torch.full((total + 1, n), 7.0, device=DEV)
+    ops.gemm_skinny(src, w, c, a_rows=a_rows, row_scale=scale, group_offsets=offsets, rows=total, max_rows=20)
+    row = 0
+    for e, cnt in enumerate(counts):
+        for _ in range(cnt):
+            ref = (src[a_rows[row].long()].double() @ w[e].double().t()) * scale[row].double()
+            close(c[row], ref, torch.float32, f"group {e} row {row}")
+            row += 1
+    assert torch.all(c[total:] == 7.0)
+    # grouped swiglu, rows in place (no gather)
+    inter = 24
+    w2 = rnd(g, 2 * inter, k, dtype=torch.bfloat16, seed=3, scale=0.3)
+    a2 = rnd(total, k, dtype=torch.bfloat16, seed=4)
+    act = torch.empty(total, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(a2, w2, act, swiglu=True, group_offsets=offsets, rows=total, max_rows=37)
+    row = 0
+    for e, cnt in enumerate(counts):
+        for _ in range(cnt):
+            gg, uu = a2[row].double() @ w2[e, :inter].double().t(), a2[row].double() @ w2[e, inter:].double().t()
+            close(act[row], gg / (1 + torch.exp(-gg)) * uu, torch.bfloat16, f"swiglu group {e} row {row}")
+            row += 1
+
+
+@pytest.mark.parametrize("nh, nkv, hd, window", [(4, 4, 128, None), (6, 2, 64, None), (7, 1, 128, 100), (8, 1, 192, None),
+                                                 (4, 2, 256, 300), (16, 16, 128, 65)])
+def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window):
+    """The split-key kernel on the same kind of made-up cache as the plain one:
+    far keys, keys at the window's edges, at page and split boundaries, other
+    sequences in interleaved pages."""
+    torch.manual_seed(2)
+    dtype = torch.bfloat16
+    lens = [700, 300, 65]
+    group = nh // nkv
+    tables = [[3 * i + s for i in range(12)] for s in range(3)]
+    ks = [torch.randn(n, nkv, hd) * 0.3 for n in lens]
+    vs = [torch.randn(n, nkv, hd) for n in lens]
+    queries = []
+    last = lens[0] - 1
+    w = window or 10 ** 9
+    for target in {3, 63, 64, 255, 256, 257, 511, 512, max(0, last - w + 1), max(0, last - w), last}:
+        queries.append((0, last, target))
+    queries += [(1, 299, 256), (1, 256, 255), (1, 255, 0), (2, 64, 63), (2, 0, 0), (2, 1, 0)]
+    q = torch.randn(len(queries), nh, hd) * 0.3
+    for i, (s, p, target) in enumerate(queries):
+        for h in range(nh):
+            ks[s][target, h // group] = ks[s][target, h // group] / ks[s][target, h // group].norm() * 6.0
+            q[i, h] = ks[s][target, h // group] * (np.sqrt(hd) * 3.0 / 6.0)
+    qd = q.to(dtype)
+    kc, vc = paged(ks, vs, tables, 36, nkv, hd, dtype)
+    table = torch.tensor(tables, dtype=torch.int32, device=DEV)
+    n = len(queries)
+    out = torch.empty(n, nh * hd, dtype=dtype, device=DEV)
+    n_splits = 3
+    part_o = torch.full((n, nh, n_splits, hd), float("nan"), device=DEV)
+    part_ml = torch.full((n, nh, n_splits, 2), float("nan"), device=DEV)
+    st = status()
+    ops.attn_decode(qd.reshape(n, nh * hd).to(DEV), kc, vc, out, part_o, part_ml,
+                    torch.tensor([s for s, _, _ in queries], dtype=torch.int32, device=DEV),
+                    torch.tensor([p for _, p, _ in queries], dtype=torch.int32, device=DEV), table, 64, nh, nkv, hd,
+                    window, n_splits, st)
+    assert st.item() == 0
+    for i, (s, p, target) in enumerate(queries):
+        ref = attention_reference(qd[i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(), p, window, group)
+        close(out[i].view(nh, hd), ref, dtype, f"query {i} (sequence {s}, position {p}, target key {target})")
