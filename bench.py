@@ -170,6 +170,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement (for profiling decode)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -209,10 +210,12 @@ def main() -> int:
         engine.step([StepEntry(s, rng.integers(0, vocab, T).tolist(), [T - 1])])
         engine.close(s)
 
-    ms_prefill = timed_steps(torch, prefill_once, 3, 5)
-    prefill_flops = nums["flops_token"] * T + nums["attn_flops_per_key"] * T * (T + 1) / 2 + nums["head_flops_row"]
-    prefill = {"value": round(T / ms_prefill * 1e3, 1), "tokens": T, "ms": round(ms_prefill, 3),
-               "frac": round(prefill_flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    prefill = None
+    if not a.no_prefill:
+        ms_prefill = timed_steps(torch, prefill_once, 3, 5)
+        prefill_flops = nums["flops_token"] * T + nums["attn_flops_per_key"] * T * (T + 1) / 2 + nums["head_flops_row"]
+        prefill = {"value": round(T / ms_prefill * 1e3, 1), "tokens": T, "ms": round(ms_prefill, 3),
+                   "frac": round(prefill_flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode at the headline batch ---------------------------------------------
     launches_before = ops.launch_count()

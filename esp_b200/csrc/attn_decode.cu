@@ -68,32 +68,47 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     // ---- scores: 8 lanes per key, 16 keys in flight per pass --------------------
     const float root = sqrtf((float)HD);
     const int sub = tid & 7, slot = tid >> 3;      // lane within the key group, key slot 0..15
-    for (int t = slot; t < SPLIT; t += THREADS / 8) {
-        float dot[GT];
+    constexpr int KB = 4;                          // keys whose loads are in flight together, per thread
+    for (int t0 = slot; t0 < SPLIT; t0 += KB * (THREADS / 8)) {
+        uint4 kraw[KB][PER_LANE];
+        bool live[KB];
 #pragma unroll
-        for (int g = 0; g < GT; g++) dot[g] = 0.f;
-        const bool live = t < count && pg_s[t] >= 0;
-        if (live) {
-            const int j = j0 + t;
-            const bf16* krow = k_cache + (((size_t)pg_s[t] * nkv + kvh) * page + j % page) * HD;
+        for (int b = 0; b < KB; b++) {
+            const int t = t0 + b * (THREADS / 8);
+            live[b] = t < count && pg_s[t] >= 0;
+            if (live[b]) {
+                const int j = j0 + t;
+                const bf16* krow = k_cache + (((size_t)pg_s[t] * nkv + kvh) * page + j % page) * HD;
 #pragma unroll
-            for (int i = 0; i < PER_LANE; i++) {
-                const int piece = sub + 8 * i;
-                float kf[8];
-                unpack8(*reinterpret_cast<const uint4*>(krow + piece * 8), kf);
-#pragma unroll
-                for (int g = 0; g < GT; g++)
-#pragma unroll
-                    for (int e = 0; e < 8; e++) dot[g] = fmaf(q_s[g][piece * 8 + e], kf[e], dot[g]);
+                for (int i = 0; i < PER_LANE; i++) kraw[b][i] = *reinterpret_cast<const uint4*>(krow + (sub + 8 * i) * 8);
             }
         }
 #pragma unroll
-        for (int g = 0; g < GT; g++) {
-            float v = dot[g];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            v += __shfl_xor_sync(0xffffffffu, v, 4);
-            if (sub == 0 && t < SPLIT) s_s[g][t] = live ? v / root : -INFINITY;
+        for (int b = 0; b < KB; b++) {
+            const int t = t0 + b * (THREADS / 8);
+            float dot[GT];
+#pragma unroll
+            for (int g = 0; g < GT; g++) dot[g] = 0.f;
+            if (live[b]) {
+#pragma unroll
+                for (int i = 0; i < PER_LANE; i++) {
+                    const int piece = sub + 8 * i;
+                    float kf[8];
+                    unpack8(kraw[b][i], kf);
+#pragma unroll
+                    for (int g = 0; g < GT; g++)
+#pragma unroll
+                        for (int e = 0; e < 8; e++) dot[g] = fmaf(q_s[g][piece * 8 + e], kf[e], dot[g]);
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < GT; g++) {
+                float v = dot[g];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (sub == 0 && t < SPLIT) s_s[g][t] = live[b] ? v / root : -INFINITY;
+            }
         }
     }
     __syncthreads();
@@ -131,16 +146,30 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     for (int g = 0; g < GT; g++)
 #pragma unroll
         for (int e = 0; e < 8; e++) acc[g][e] = 0.f;
-    for (int t = kg; t < count && kg < KG; t += KG) {
-        if (pg_s[t] < 0) continue;
-        const int j = j0 + t;
-        float vf[8];
-        unpack8(*reinterpret_cast<const uint4*>(v_cache + (((size_t)pg_s[t] * nkv + kvh) * page + j % page) * HD + piece * 8), vf);
+    for (int t0 = kg; t0 < count && kg < KG; t0 += KB * KG) {
+        uint4 vraw[KB];
+        bool live[KB];
 #pragma unroll
-        for (int g = 0; g < GT; g++) {
-            const float pw = s_s[g][t];
+        for (int b = 0; b < KB; b++) {
+            const int t = t0 + b * KG;
+            live[b] = t < count && pg_s[t] >= 0;
+            if (live[b]) {
+                const int j = j0 + t;
+                vraw[b] = *reinterpret_cast<const uint4*>(v_cache + (((size_t)pg_s[t] * nkv + kvh) * page + j % page) * HD + piece * 8);
+            }
+        }
 #pragma unroll
-            for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pw, vf[e], acc[g][e]);
+        for (int b = 0; b < KB; b++) {
+            if (!live[b]) continue;
+            const int t = t0 + b * KG;
+            float vf[8];
+            unpack8(vraw[b], vf);
+#pragma unroll
+            for (int g = 0; g < GT; g++) {
+                const float pw = s_s[g][t];
+#pragma unroll
+                for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pw, vf[e], acc[g][e]);
+            }
         }
     }
     if (kg < KG) {

@@ -68,9 +68,65 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     }
 }
 
+// Same operation for rows whose width is a multiple of 4 and at most 4 * 4 * 1024: each thread keeps up
+// to four float4 pieces of the row in registers, so x and y are read once and nothing is read back.
+// The sum of squares is taken per thread in piece order and combined by the same fixed tree.
+template <typename TH>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma,
+                        const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width, float eps,
+                        int write_x) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    const int pieces = width / 4;
+    float4* xr = reinterpret_cast<float4*>(x + s * width);
+    const float4* yr = y ? reinterpret_cast<const float4*>(y + s * width) : nullptr;
+    float4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < pieces) {
+            v[i] = xr[q];
+            if (yr) {
+                const float4 a = yr[q];
+                v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+                if (write_x) xr[q] = v[i];
+            }
+            ss = fmaf(v[i].x, v[i].x, ss);
+            ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss);
+            ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < pieces) {
+            const float4 gm = reinterpret_cast<const float4*>(gamma)[q];
+            const float o0 = v[i].x * inv * gm.x, o1 = v[i].y * inv * gm.y, o2 = v[i].z * inv * gm.z, o3 = v[i].w * inv * gm.w;
+            TH* hr = h + (size_t)r * width + 4 * q;
+            hr[0] = from_f32<TH>(o0); hr[1] = from_f32<TH>(o1); hr[2] = from_f32<TH>(o2); hr[3] = from_f32<TH>(o3);
+            if (h32) reinterpret_cast<float4*>(h32 + (size_t)r * width)[q] = make_float4(o0, o1, o2, o3);
+        }
+    }
+}
+
 ESP_API int esp_add_rmsnorm(float* x, const float* y, const float* gamma, const int* rows, void* h, int h_is_bf16,
                             float* h32, int n_rows, int width, float eps, int write_x, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (width % 4 == 0 && width <= 16384) {
+        int threads = ((width / 4 + 3) / 4 + 31) / 32 * 32;       // up to four pieces per thread
+        if (width / 4 <= 1024) threads = (width / 4 + 31) / 32 * 32;   // one piece per thread while a block can hold them
+        if (h_is_bf16)
+            add_rmsnorm_rows_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
+        else
+            add_rmsnorm_rows_kernel<float><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (float*)h, h32, width, eps, write_x);
+        return esp_launch_status();
+    }
     const int threads = width >= 1024 ? 256 : 128;
     if (h_is_bf16)
         add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);

@@ -47,7 +47,7 @@ __device__ __forceinline__ uint4 load_stream(const bf16* p) {
 }
 
 template <int NBLK, bool SWIGLU, typename TC>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 3)
 gemm_skinny_kernel(SkinnyParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K = p.K;

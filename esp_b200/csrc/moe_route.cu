@@ -5,8 +5,42 @@
 #include "common.cuh"
 
 namespace {
-constexpr int ROUTER_THREADS = 256;
+constexpr int ROUTER_THREADS = 512;
 constexpr int MAX_TOPK = 32;
+
+// A lane's share of dot(hs, w): 8 consecutive elements at a time (16-byte loads
+// of bfloat16, 32-byte of float), lanes interleaved, several loads in flight.
+// The order of a lane's additions depends on the width alone.
+__device__ __forceinline__ float lane_dot(const float* __restrict__ hs, const bf16* __restrict__ w, int width, int lane) {
+    float s = 0.f;
+    const int vec_end = (width % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) ? width : 0;
+#pragma unroll 4
+    for (int i = lane * 8; i < vec_end; i += 256) {
+        const uint4 v = *reinterpret_cast<const uint4*>(w + i);
+        const unsigned u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            s = fmaf(hs[i + 2 * j], __uint_as_float(u[j] << 16), s);
+            s = fmaf(hs[i + 2 * j + 1], __uint_as_float(u[j] & 0xffff0000u), s);
+        }
+    }
+    for (int i = vec_end + lane; i < width; i += 32) s = fmaf(hs[i], __bfloat162float(w[i]), s);
+    return s;
+}
+__device__ __forceinline__ float lane_dot(const float* __restrict__ hs, const float* __restrict__ w, int width, int lane) {
+    float s = 0.f;
+    const int vec_end = (width % 4 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) ? width : 0;
+#pragma unroll 4
+    for (int i = lane * 4; i < vec_end; i += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(w + i);
+        s = fmaf(hs[i], v.x, s);
+        s = fmaf(hs[i + 1], v.y, s);
+        s = fmaf(hs[i + 2], v.z, s);
+        s = fmaf(hs[i + 3], v.w, s);
+    }
+    for (int i = vec_end + lane; i < width; i += 32) s = fmaf(hs[i], w[i], s);
+    return s;
+}
 
 // One block per token.  logits[e] = sum_k h[k] * Wr[e][k]: a warp per expert,
 // lanes stride over k, partial sums combined by the fixed warp butterfly.
@@ -31,8 +65,7 @@ router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, co
     __syncthreads();
     for (int e = warp; e < n_experts + (w_gate ? 1 : 0); e += nwarp) {
         const TW* wr = e < n_experts ? w_router + (size_t)e * width : w_gate;
-        float s = 0.f;
-        for (int i = lane; i < width; i += 32) s = fmaf(hs[i], to_f32(wr[i]), s);
+        float s = lane_dot(hs, wr, width, lane);
         s = warp_sum(s);
         if (lane == 0) {
             if (e < n_experts) ps[e] = s;

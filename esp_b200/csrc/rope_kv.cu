@@ -21,7 +21,7 @@ __global__ void rope_kvwrite_kernel(const float* __restrict__ qkv, const float* 
                                     T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ block_table,
                                     int table_stride, int n_pages, int page, int nh, int nkv, int hd, int write_kv,
                                     int* __restrict__ status) {
-    const int n = blockIdx.x;
+    const int n = blockIdx.x, head = blockIdx.y;
     const int pos = tok_pos[n];
     const int seq = tok_seq[n];
     const int half = rot / 2;
@@ -42,11 +42,9 @@ __global__ void rope_kvwrite_kernel(const float* __restrict__ qkv, const float* 
         }
     }
     const int in_page = pos % page;
-    const int heads = nh + 2 * nkv;
-    for (int idx = threadIdx.x; idx < heads * hd; idx += blockDim.x) {
-        const int head = idx / hd, i = idx - head * hd;
-        const float* x = src + (size_t)head * hd;
-        const float* b = bias ? bias + (size_t)head * hd : nullptr;
+    const float* x = src + (size_t)head * hd;
+    const float* b = bias ? bias + (size_t)head * hd : nullptr;
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
         float v = x[i] + (b ? b[i] : 0.f);
         if (head < nh + nkv && i < rot) {          // queries and keys rotate, values do not
             if (i < half) {
@@ -58,7 +56,7 @@ __global__ void rope_kvwrite_kernel(const float* __restrict__ qkv, const float* 
             }
         }
         if (head < nh) {
-            q_out[(size_t)n * nh * hd + idx] = from_f32<T>(v);
+            q_out[((size_t)n * nh + head) * hd + i] = from_f32<T>(v);
         } else if (page_id >= 0) {
             const bool is_k = head < nh + nkv;
             const int kvh = is_k ? head - nh : head - nh - nkv;
@@ -73,13 +71,15 @@ ESP_API int esp_rope_kvwrite(const float* qkv, const float* bias, const int* tok
                              int is_bf16, const int* block_table, int table_stride, int n_pages, int page, int n_tokens,
                              int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (rot < 0 || rot > hd || (rot & 1)) return (int)cudaErrorInvalidValue;
+    if (rot < 0 || rot > hd || (rot & 1) || nh + 2 * nkv > 65535) return (int)cudaErrorInvalidValue;
+    const dim3 grid(n_tokens, nh + 2 * nkv);
+    const int threads = hd >= 128 ? 128 : (hd + 31) / 32 * 32;
     if (is_bf16)
-        rope_kvwrite_kernel<bf16><<<n_tokens, 256, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
+        rope_kvwrite_kernel<bf16><<<grid, threads, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
                                                                (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, block_table,
                                                                table_stride, n_pages, page, nh, nkv, hd, write_kv, status);
     else
-        rope_kvwrite_kernel<float><<<n_tokens, 256, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
+        rope_kvwrite_kernel<float><<<grid, threads, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
                                                                 (float*)q_out, (float*)k_cache, (float*)v_cache,
                                                                 block_table, table_stride, n_pages, page, nh, nkv, hd,
                                                                 write_kv, status);

@@ -25,6 +25,7 @@ from ..parts import Runtime, StepContext
 from ..weights import FolderSource, InitSpec, RandomSource, load_into
 from .model import DecoderModel
 
+GRAPH_STRIDE_PAGES = 8       # page tables of captured decode steps grow in steps of 8 pages (512 positions)
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
 
@@ -69,6 +70,12 @@ class Engine:
         self._pinned_event = None
         self._meta_dev = None
         self.steps_run = 0
+        # decode steps (one token per sequence) are captured into CUDA graphs, one per
+        # (batch size, page-table stride, what is wanted); see _run
+        self.use_graphs = True
+        self._graphs: dict = {}
+        self._graph_seen: dict = {}
+        self.graph_replays = 0
 
     # -- construction ---------------------------------------------------------
     @classmethod
@@ -153,7 +160,8 @@ class Engine:
         [number of wanted places, vocab] in the order of the entries and of
         their ``want`` lists.  On a validation error nothing is changed."""
         logits, _ = self._run(entries, aux, [])
-        return logits
+        # a replayed graph writes its logits into the same buffer every time: hand out a copy
+        return logits.clone() if self._graphs else logits
 
     def step_and_pick(self, entries: list, temperatures: list, top_ps: list, aux: Optional[dict] = None):
         """One step that ends with the choice of the next token of every entry
@@ -167,30 +175,27 @@ class Engine:
         temps = np.asarray(temperatures, dtype=np.float32)
         tops = np.asarray([-1.0 if t is None else t for t in top_ps], dtype=np.float32)
         rows = np.asarray([e.slot * STATE_WORDS + STATE_RNG for e in entries], dtype=np.int32)
-        logits, extra = self._run(entries, aux, [temps.view(np.int32), tops.view(np.int32), rows])
-        with torch.cuda.device(self.rt.device):
-            b = len(entries)
-            out = self.rt.ws.get("picked_tokens", (b + 1,), torch.int32)
-            ops.finite_check(logits, self.rt.status)
-            ops.pick_tokens(logits, extra[0].view(torch.float32), extra[1].view(torch.float32),
-                            self.cache.engine_state.view(-1), extra[2], out)
-            out[b:].copy_(self.rt.status)
+        logits, out = self._run(entries, aux, [temps.view(np.int32), tops.view(np.int32), rows], pick=True)
         return out, logits
 
     def seed_slot(self, slot: int, seed: int) -> None:
         """Starts the slot's sampling stream from ``seed``."""
         self.cache.engine_state[slot, STATE_RNG] = as_signed64(seed)
 
-    def _run(self, entries: list, aux, extra_arrays: list):
+    def _run(self, entries: list, aux, extra_arrays: list, pick: bool = False):
         with torch.cuda.device(self.rt.device):
             slots, news, pasts, starts, want_rows, growth = self.plan_step(entries)
             book = self.cache.book
             book.reserve(growth)
             b, n = len(entries), starts[-1]
+            decode = n == b
             tok_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
             tok_seq = np.repeat(np.arange(b, dtype=np.int32), news)
             tok_pos = np.concatenate([np.arange(p, p + t, dtype=np.int32) for p, t in zip(pasts, news)])
             stride = self.cache.max_table_stride(slots, growth)
+            graphable = decode and self.use_graphs and not self.rt.record_routing and aux is None
+            if graphable:
+                stride = (stride + GRAPH_STRIDE_PAGES - 1) // GRAPH_STRIDE_PAGES * GRAPH_STRIDE_PAGES
             tables = [np.asarray(g.table_rows(slots, stride), dtype=np.int32).reshape(b, stride)
                       for g in book.groups]
             arrays = [tok_ids, tok_seq, tok_pos, np.asarray(slots, dtype=np.int32),
@@ -204,10 +209,62 @@ class Engine:
                 want_rows=dev[6], block_tables=list(dev[7:nt]),
                 host={"slots": slots, "news": news, "pasts": pasts, "starts": starts, "want_rows": want_rows},
                 aux=aux if aux is not None else {})
-            logits = self.model.forward(ctx, self.cache)
+            extra = dev[nt:]
+            if graphable:
+                result = self._run_decode_graph(ctx, extra, pick, (b, stride, pick, tuple(want_rows)))
+            else:
+                result = self._forward(ctx, extra, pick)
             book.commit(growth)
             self.steps_run += 1
-            return logits, dev[nt:]
+            return result
+
+    def _forward(self, ctx, extra, pick: bool):
+        logits = self.model.forward(ctx, self.cache)
+        if not pick:
+            return logits, None
+        b = ctx.n_seqs
+        out = self.rt.ws.get("picked_tokens", (b + 1,), torch.int32)
+        ops.finite_check(logits, self.rt.status)
+        ops.pick_tokens(logits, extra[0].view(torch.float32), extra[1].view(torch.float32),
+                        self.cache.engine_state.view(-1), extra[2], out)
+        out[b:].copy_(self.rt.status)
+        return logits, out
+
+    def _run_decode_graph(self, ctx, extra, pick: bool, key):
+        """The first step of a shape runs eagerly (it sizes the scratch buffers and
+        loads the kernels), the second is captured, later ones replay the graph.
+        Everything that changes from step to step (token ids, positions, page
+        tables, sampling options) lives in the staged buffer, whose addresses a
+        shape fixes, so a replay needs one host-to-device copy and one launch."""
+        ws = self.rt.ws
+        entry = self._graphs.get(key)
+        if entry is not None and (entry[3] != ws.generation or entry[4] is not self._meta_dev):
+            del self._graphs[key]
+            entry = None
+        if entry is not None:
+            entry[0].replay()
+            self.graph_replays += 1
+            ops.add_launches(entry[5])
+            return entry[1], entry[2]
+        seen = self._graph_seen.get(key, 0)
+        self._graph_seen[key] = seen + 1
+        if seen == 0:
+            return self._forward(ctx, extra, pick)
+        graph = torch.cuda.CUDAGraph()
+        ws.frozen = True
+        before = ops.launch_count()
+        try:
+            with torch.cuda.graph(graph):
+                logits, out = self._forward(ctx, extra, pick)
+        finally:
+            ws.frozen = False
+        kernels = ops.launch_count() - before      # this library's kernels in the graph (library products not counted)
+        ops.add_launches(-kernels)                 # capturing runs nothing
+        self._graphs[key] = (graph, logits, out, ws.generation, self._meta_dev, kernels)
+        graph.replay()
+        ops.add_launches(kernels)
+        self.graph_replays += 1
+        return logits, out
 
     def read_status(self) -> int:
         """The device status word (0: nothing went wrong); reading it waits

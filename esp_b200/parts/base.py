@@ -95,6 +95,7 @@ class Workspace:
         self.device = device
         self._bufs: dict = {}
         self.frozen = False
+        self.generation = 0          # bumped whenever a buffer moves; captured graphs check it
 
     def get(self, name: str, shape: tuple, dtype) -> torch.Tensor:
         count = 1
@@ -107,6 +108,7 @@ class Workspace:
                 raise Backend(f"workspace buffer {name} would have to grow while a captured graph holds it")
             buf = torch.empty(max(count, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[:count].view(*shape)
 
     def bytes(self) -> int:

@@ -34,6 +34,9 @@ class FolderSource:
 
     def read_into(self, name, view: torch.Tensor) -> None:
         t = read_tensor(self.metas[name])
+        # non-finite weights are refused (crates/esp/src/infer/decoder/weight_format.rs:129-131)
+        if not bool(torch.isfinite(t if t.dtype == torch.float32 else t.float()).all()):
+            raise InvalidWeights(f"{name} holds values that are not finite")
         view.copy_(t.to(view.dtype) if t.dtype != view.dtype else t, non_blocking=False)
 
 
@@ -88,10 +91,5 @@ def load_into(root, source, rt, tolerated_suffixes=None) -> None:
         if name not in have:
             raise InvalidWeights(f"a part asked for {name}, which the checkpoint lacks")
         source.read_into(name, view)
-    # non-finite weights are refused (crates/esp/src/infer/decoder/weight_format.rs:129-131)
-    flags = [(name, torch.isfinite(view).all()) for name, view in views.items()]
-    bad = [name for name, ok in flags if not bool(ok)]
-    if bad:
-        raise InvalidWeights(f"non-finite values in: {', '.join(sorted(bad)[:8])}")
     for part in parts:
         part.finalize()
