@@ -33,6 +33,7 @@ _SIGNATURES = {
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
     "esp_gemm_skinny": [P, c_longlong, P, P, c_longlong, P, P, c_int, c_longlong, P, c_int, c_int, c_int, c_int, c_int,
                         c_int, P],
+    "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_attn_decode": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
 }
 
@@ -294,3 +295,17 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, tok_seq, tok_pos, blo
         _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
         k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), n_splits, _ptr(status, torch.int32), _stream()),
         "attn_decode")
+
+
+def attn_prefill(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,
+                 window, status):
+    """Flash-style attention for runs of new tokens (bfloat16; head sizes that are multiples of 8 up to
+    128; pages of 64 positions).  tile_seq / tile_first describe the tiles of 64 new tokens."""
+    if hd % 8 != 0 or hd > 128 or page != 64:
+        raise Backend(f"attn_prefill: head size {hd} / page {page} not taken (multiples of 8 up to 128; page 64)")
+    _check(_fn("bf16", "esp_attn_prefill")(
+        _ptr(q, torch.bfloat16, "q"), _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
+        _ptr(out, torch.bfloat16), _ptr(tile_seq, torch.int32), _ptr(tile_first, torch.int32),
+        _ptr(seq_start, torch.int32), _ptr(seq_past, torch.int32), _ptr(block_table, torch.int32),
+        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, int(window or 0),
+        _ptr(status, torch.int32), _stream()), "attn_prefill")

@@ -198,15 +198,17 @@ class Engine:
                 stride = (stride + GRAPH_STRIDE_PAGES - 1) // GRAPH_STRIDE_PAGES * GRAPH_STRIDE_PAGES
             tables = [np.asarray(g.table_rows(slots, stride), dtype=np.int32).reshape(b, stride)
                       for g in book.groups]
+            tiles = [(i, first) for i, t in enumerate(news) for first in range(0, t, 64)]
             arrays = [tok_ids, tok_seq, tok_pos, np.asarray(slots, dtype=np.int32),
                       np.asarray(starts, dtype=np.int32), np.asarray(pasts, dtype=np.int32),
-                      np.asarray(want_rows, dtype=np.int32), *tables, *extra_arrays]
+                      np.asarray(want_rows, dtype=np.int32), np.asarray([t[0] for t in tiles], dtype=np.int32),
+                      np.asarray([t[1] for t in tiles], dtype=np.int32), *tables, *extra_arrays]
             dev = self._stage(arrays)
-            nt = 7 + len(tables)
+            nt = 9 + len(tables)
             ctx = StepContext(
                 n_tokens=n, n_seqs=b, max_new=max(news), max_len=max(p + t for p, t in zip(pasts, news)),
                 tok_ids=dev[0], tok_seq=dev[1], tok_pos=dev[2], seq_slot=dev[3], seq_start=dev[4], seq_past=dev[5],
-                want_rows=dev[6], block_tables=list(dev[7:nt]),
+                want_rows=dev[6], q_tile_seq=dev[7], q_tile_first=dev[8], block_tables=list(dev[9:nt]),
                 host={"slots": slots, "news": news, "pasts": pasts, "starts": starts, "want_rows": want_rows},
                 aux=aux if aux is not None else {})
             extra = dev[nt:]

@@ -163,6 +163,8 @@ class StepContext:
     seq_start: torch.Tensor          # [B+1] offsets of the sequences in the token rows
     seq_past: torch.Tensor           # [B] cached length before the step
     want_rows: torch.Tensor          # [R] token rows whose logits are wanted
+    q_tile_seq: torch.Tensor         # [tiles] sequence of every tile of 64 new tokens
+    q_tile_first: torch.Tensor       # [tiles] index of the tile's first token among its sequence's new tokens
     block_tables: list               # per layer group: [B, stride] page ids
     host: dict                       # the same lists on the host (slots, starts, pasts, news)
     aux: dict

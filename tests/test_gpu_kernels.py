@@ -487,3 +487,47 @@ def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window):
     for i, (s, p, target) in enumerate(queries):
         ref = attention_reference(qd[i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(), p, window, group)
         close(out[i].view(nh, hd), ref, dtype, f"query {i} (sequence {s}, position {p}, target key {target})")
+
+
+@pytest.mark.parametrize("nh, nkv, hd, window", [(4, 4, 128, None), (6, 2, 64, None), (4, 1, 24, 16), (2, 1, 128, 100),
+                                                 (4, 2, 16, None), (3, 1, 80, 65)])
+def test_attn_prefill_against_reference(nh, nkv, hd, window):
+    """Runs of new tokens of unequal length, some continuing a cached past, in
+    interleaved pages; in every sequence some keys are made to dominate so that
+    a lost, shifted or wrongly masked key shows."""
+    torch.manual_seed(3)
+    dtype = torch.bfloat16
+    group = nh // nkv
+    runs = [(0, 200), (130, 70), (0, 1), (63, 66), (300, 129)]        # (past, new)
+    lens = [p + n for p, n in runs]
+    tables = [[5 * i + s for i in range(7)] for s in range(5)]
+    ks = [torch.randn(n, nkv, hd) * 0.3 for n in lens]
+    vs = [torch.randn(n, nkv, hd) for n in lens]
+    qs = [torch.randn(n, nh, hd) * 0.3 for _p, n in runs]
+    rng = np.random.default_rng(0)
+    for s, (past, new) in enumerate(runs):
+        for _ in range(12):                                            # a dozen (query, key) pairs that stand out
+            i = int(rng.integers(0, new))
+            pos = past + i
+            lo = 0 if not window else max(0, pos - window + 1)
+            target = int(rng.choice([lo, pos, (lo + pos) // 2, max(lo, pos - 63), max(lo, pos - 64), max(lo, (pos // 64) * 64)]))
+            for h in range(nh):
+                ks[s][target, h // group] = ks[s][target, h // group] / ks[s][target, h // group].norm() * 6.0
+                qs[s][i, h] = ks[s][target, h // group] * (np.sqrt(hd) * 3.0 / 6.0)
+    kc, vc = paged(ks, vs, tables, 35, nkv, hd, dtype)
+    q = torch.cat(qs).to(dtype)
+    n = q.shape[0]
+    out = torch.full((n, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    starts = np.concatenate([[0], np.cumsum([nw for _p, nw in runs])])
+    st = status()
+    ops.attn_prefill(q.reshape(n, nh * hd).to(DEV), kc, vc, out,
+                     i32([s for s, (_p, nw) in enumerate(runs) for _ in range(0, nw, 64)]),
+                     i32([f for _p, nw in runs for f in range(0, nw, 64)]), i32(starts), i32([p for p, _n in runs]),
+                     i32(tables), 64, nh, nkv, hd, window, st)
+    assert st.item() == 0
+    for s, (past, new) in enumerate(runs):
+        for i in range(new):
+            ref = attention_reference(q[starts[s] + i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(),
+                                      past + i, window, group)
+            close(out[starts[s] + i].view(nh, hd), ref, dtype, f"sequence {s}, new token {i} (position {past + i})")

@@ -47,7 +47,8 @@ def context(rt, cache, runs):
     ctx = StepContext(n_tokens=len(seq), n_seqs=len(runs), max_new=max(n for _, _, n in runs),
                       max_len=max(p + n for _, p, n in runs), tok_ids=t(np.zeros(len(seq))), tok_seq=t(seq),
                       tok_pos=t(pos), seq_slot=t(slots), seq_start=t(starts), seq_past=t([p for _, p, _ in runs]),
-                      want_rows=t([]), block_tables=tables,
+                      want_rows=t([]), q_tile_seq=t([i for i, (_s, _p, n) in enumerate(runs) for _ in range(0, n, 64)]),
+                      q_tile_first=t([f for _s, _p, n in runs for f in range(0, n, 64)]), block_tables=tables,
                       host={"slots": slots, "news": [n for _, _, n in runs], "pasts": [p for _, p, _ in runs],
                             "starts": list(starts)}, aux={})
     return ctx, growth
