@@ -32,6 +32,8 @@ LIBRARIES = {
     "core": ["elementwise.cu", "gemm_simt.cu", "rope_kv.cu", "attn_simt.cu", "moe_route.cu", "sampling.cu"],
     # bfloat16 only: loaded when a model runs in bfloat16
     "bf16": ["gemm_skinny.cu", "attn_decode.cu", "attn_prefill.cu"],
+    # TMA + tcgen05/TMEM products for steps with many rows (bfloat16 prefill)
+    "tc05": ["gemm_tc05.cu"],
 }
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

@@ -161,6 +161,27 @@ ESP_API int esp_swiglu(const float* gu, void* act, int act_is_bf16, long long ro
     return esp_launch_status();
 }
 
+// ---------------------------------------------------------------- row gather
+// out[r, :] = src[rows[r], :] for bfloat16 rows whose width is a multiple of 8 (16-byte pieces).
+__global__ void gather_rows_kernel(const bf16* __restrict__ src, const int* __restrict__ rows, bf16* __restrict__ out,
+                                   int n_rows, int pieces) {
+    const long long total = (long long)n_rows * pieces;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(idx / pieces), q = (int)(idx - (long long)r * pieces);
+        reinterpret_cast<uint4*>(out)[idx] = reinterpret_cast<const uint4*>(src)[(size_t)rows[r] * pieces + q];
+    }
+}
+
+ESP_API int esp_gather_rows(const void* src, const int* rows, void* out, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width % 8 != 0) return (int)cudaErrorInvalidValue;
+    const long long total = (long long)n_rows * (width / 8);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    gather_rows_kernel<<<(int)blocks, 256, 0, stream>>>((const bf16*)src, rows, (bf16*)out, n_rows, width / 8);
+    return esp_launch_status();
+}
+
 // ---------------------------------------------------------------- finite check
 __global__ void finite_check_kernel(const float* __restrict__ v, long long count, int* __restrict__ status) {
     bool bad = false;

@@ -1,0 +1,338 @@
+// Tensor-core matrix product for many rows (prefill) on the 5th-generation
+// tensor cores: operands travel global -> shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), tcgen05.mma accumulates a
+// 128 x 128 float tile in tensor memory (TMEM), and the epilogue reads it back
+// with tcgen05.ld.
+//
+//   PLAIN:  C[m, n]   = scale[m] * sum_k A[m, k] * W[g][n, k]                (float out)
+//   SWIGLU: act[m, j] = silu(A W_gate[g][j]) * (A W_up[g][j])                (bfloat16 out)
+//           W[g] = [gate rows; up rows], a tile holds 64 gate and the 64 matching up columns
+//
+// A is [rows, K] bfloat16, rows sorted by group; W is [G, Nw, K] bfloat16 (G = 1
+// for a dense product).  Row tiles of 128 never mix groups: the tile list
+// (group, first row) is made on the device by the routing kernels, and a tile
+// that reaches past its group's last row computes rows it does not store.
+//
+// One CTA = one output tile.  Warp 0 issues the TMA loads, warp 1 owns TMEM and
+// issues the MMAs, warps 2..5 are the epilogue (each reads the 32 TMEM lanes
+// that its position in the warpgroup may touch).  A ring of STAGES shared-memory
+// buffers is handed back and forth with mbarriers.  Every wait is bounded: if
+// one runs out the kernel raises ESP_STATUS_WAIT_EXPIRED in the status word,
+// stops issuing work, lets its own copies land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 5, THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+
+struct Tc05Params {
+    const int* group_offsets;     // [G+1] or null (dense)
+    const int* tile_group;        // [tiles] or null
+    const int* tile_row0;         // [tiles]
+    const int* n_tiles;           // device scalar or null
+    const float* row_scale;       // [rows] or null
+    void* C;
+    long long ldc;
+    int M, N, K;                  // N: output columns (SWIGLU: the intermediate size)
+    int* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, void* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, void* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b, unsigned idesc,
+                                       unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive float columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (64 bfloat16), written by TMA
+// with the 128-byte swizzle; groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ unsigned long long smem_desc(const void* p) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(p) & 0x3FFFFu) >> 4);       // start address, 16-byte units
+    d |= (unsigned long long)1 << 16;                                // leading byte offset: unused for this layout
+    d |= (unsigned long long)(1024 >> 4) << 32;                      // stride byte offset between 8-row groups
+    d |= (unsigned long long)1 << 46;                                // descriptor version of this architecture
+    d |= (unsigned long long)2 << 61;                                // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = 128.
+constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, Tc05Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+    unsigned long long* empty_bar = full_bar + STAGES;
+    unsigned long long* tmem_full_bar = empty_bar + STAGES;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(tmem_full_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int group = 0, row0 = blockIdx.y * BM, row_end = p.M;
+    if (p.tile_group) {
+        if ((int)blockIdx.y >= *p.n_tiles) return;                   // the whole CTA leaves before any barrier exists
+        group = p.tile_group[blockIdx.y];
+        row0 = p.tile_row0[blockIdx.y];
+        row_end = p.group_offsets[group + 1];
+    }
+    const int k_iters = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(tmem_full_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(BN));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int it = 0; it < k_iters && !*abort_flag; it++) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1)) {
+                    atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+                    *abort_flag = 1;
+                    break;
+                }
+                unsigned char* a_dst = smem + s * STAGE_BYTES;
+                unsigned char* b_dst = a_dst + A_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, it * BK, row0, &full_bar[s]);
+                if (SWIGLU) {
+                    tma_load_3d(b_dst, &map_w, it * BK, blockIdx.x * 64, group, &full_bar[s]);
+                    tma_load_3d(b_dst + B_BYTES / 2, &map_w, it * BK, p.N + blockIdx.x * 64, group, &full_bar[s]);
+                } else {
+                    tma_load_3d(b_dst, &map_w, it * BK, blockIdx.x * BN, group, &full_bar[s]);
+                }
+                issued = it + 1;
+            }
+            if (*abort_flag) {
+                // let this CTA's own copies land before its shared memory is given up
+                for (int it = max(0, issued - STAGES); it < issued; it++) mbar_wait(&full_bar[it % STAGES], (it / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int it = 0; it < k_iters && !*abort_flag; it++) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+                    atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const unsigned char* a_src = smem + s * STAGE_BYTES;
+                const unsigned char* b_src = a_src + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++)
+                    tc_mma(tmem_base, smem_desc(a_src + k * 32), smem_desc(b_src + k * 32), IDESC, (it > 0 || k > 0) ? 1u : 0u);
+                tc_commit(&empty_bar[s]);                             // the stage is free once these MMAs have read it
+            }
+            tc_commit(tmem_full_bar);                                 // the accumulator is complete once all MMAs are done
+        }
+    } else {
+        const int quad = warp & 3;                                   // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+        const bool ok = mbar_wait(tmem_full_bar, 0);
+        if (!ok && lane == 0) {
+            atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+            *abort_flag = 1;
+        }
+        tc_fence_after();
+        const int row = row0 + quad * 32 + lane;
+        const bool row_ok = ok && !*abort_flag && row < row_end;
+        const unsigned lane_addr = tmem_base + ((unsigned)(quad * 32) << 16);
+        if (SWIGLU) {
+            bf16* out = reinterpret_cast<bf16*>(p.C) + (size_t)row * p.ldc;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                float gate[32], up[32];
+                tc_ld32(lane_addr + c0, gate);
+                tc_ld32(lane_addr + 64 + c0, up);
+                const int j0 = blockIdx.x * 64 + c0;
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float a = gate[i] / (1.0f + expf(-gate[i])) * up[i];
+                        const float b = gate[i + 1] / (1.0f + expf(-gate[i + 1])) * up[i + 1];
+                        if (j0 + i + 1 < p.N) *reinterpret_cast<__nv_bfloat162*>(out + j0 + i) = __floats2bfloat162_rn(a, b);
+                        else if (j0 + i < p.N) out[j0 + i] = __float2bfloat16_rn(a);
+                    }
+                }
+            }
+        } else {
+            float* out = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc;
+            const float scale = (row_ok && p.row_scale) ? p.row_scale[row] : 1.0f;
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                float acc[32];
+                tc_ld32(lane_addr + c0, acc);
+                const int n0 = blockIdx.x * BN + c0;
+                if (row_ok) {
+                    if (n0 + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<float4*>(out + n0 + i) =
+                                make_float4(acc[i] * scale, acc[i + 1] * scale, acc[i + 2] * scale, acc[i + 3] * scale);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (n0 + i < p.N) out[n0 + i] = acc[i] * scale;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(BN));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// bfloat16 tensor [d2][d1][d0] (d0 innermost), box [1][box1][64], 128-byte swizzle, zero fill out of bounds
+int make_map(CUtensorMap* map, const void* base, unsigned long long d0, unsigned long long d1, unsigned long long d2,
+             unsigned box1) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[3] = {d0, d1, d2};
+    const cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+    const cuuint32_t box[3] = {BK, box1, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d2 > 1 ? 3 : 2, const_cast<void*>(base), dims, strides, box,
+                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+// A [rows_total, K] bfloat16 (row-major, contiguous), W [G, Nw, K] bfloat16.  Dense: tile_group = null and
+// M rows.  Grouped: the tile list on the device; ``max_tiles`` bounds the number of row tiles.
+// swiglu: N is the intermediate size and Nw = 2N.  K must be a multiple of 8, the bases 16-byte aligned.
+ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, int groups, int w_rows,
+                          const float* row_scale, void* C, long long ldc, const int* group_offsets,
+                          const int* tile_group, const int* tile_row0, const int* n_tiles, int max_tiles, int M, int N,
+                          int K, int swiglu, int* status, cudaStream_t stream) {
+    if (N <= 0 || K <= 0 || rows_total <= 0) return 0;
+    if (K % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_a, map_w;
+    int rc = make_map(&map_a, A, (unsigned long long)K, (unsigned long long)rows_total, 1, BM);
+    if (rc) return rc;
+    // the weights always use a 3-D map so that the kernel has one code path; a dense product is one group
+    {
+        EncodeTiledFn fn = encode_fn();
+        const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)w_rows, (cuuint64_t)groups};
+        const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * w_rows * 2};
+        const cuuint32_t box[3] = {BK, (cuuint32_t)(swiglu ? 64 : BN), 1};
+        const cuuint32_t elem[3] = {1, 1, 1};
+        if (fn(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(W), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return (int)cudaErrorInvalidValue;
+    }
+    Tc05Params p{group_offsets, tile_group, tile_row0, n_tiles, row_scale, C, ldc, M, N, K, status};
+    const int row_tiles = tile_group ? max_tiles : (M + BM - 1) / BM;
+    if (row_tiles <= 0) return 0;
+    if (row_tiles > 65535) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+    static bool raised[2] = {false, false};
+    if (!raised[swiglu ? 1 : 0]) {
+        cudaError_t e = swiglu ? cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                               : cudaFuncSetAttribute(gemm_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised[swiglu ? 1 : 0] = true;
+    }
+    dim3 grid(swiglu ? (N + 63) / 64 : (N + BN - 1) / BN, row_tiles);
+    if (swiglu) gemm_tc05_kernel<true><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
+    else gemm_tc05_kernel<false><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
+    return esp_launch_status();
+}

@@ -24,9 +24,14 @@ def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
     return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
 
 
-def close(got, ref, dtype, what=""):
+def close(got, ref, dtype, what="", k=None):
+    """``k``: length of the sums behind a tensor-core product.  Products of bfloat16 values are exact in
+    float; the tensor cores add them into a float accumulator 16 at a time and may truncate, so the
+    error is bounded by one float ulp (2^-24 relative) of the running sum per step of 16."""
     got, ref = got.double().cpu(), ref.double().cpu()
     tol = 2e-6 if dtype == torch.float32 else 2.0 ** -7
+    if k is not None and dtype == torch.float32:
+        tol = max(tol, (k / 16) * 2.0 ** -24)
     scale = max(1e-9, float(ref.abs().max()))
     err = float((got - ref).abs().max())
     assert err <= tol * scale, f"{what}: max error {err:.3e} on scale {scale:.3e} (bound {tol * scale:.3e})"
@@ -397,7 +402,7 @@ def test_gemm_skinny_dense(m, n, k):
     scale = rnd(m, seed=2)
     c = torch.full((m + 2, n), 7.0, device=DEV)
     ops.gemm_skinny(a, w, c, row_scale=scale, rows=m)
-    close(c[:m], (a.double() @ w.double().t()) * scale.double()[:, None], torch.float32, "skinny dense")
+    close(c[:m], (a.double() @ w.double().t()) * scale.double()[:, None], torch.float32, "skinny dense", k=k)
     assert torch.all(c[m:] == 7.0)
     # a row's bits do not depend on the rows beside it
     c1 = torch.empty(1, n, device=DEV)
@@ -531,3 +536,74 @@ def test_attn_prefill_against_reference(nh, nkv, hd, window):
             ref = attention_reference(q[starts[s] + i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(),
                                       past + i, window, group)
             close(out[starts[s] + i].view(nh, hd), ref, dtype, f"sequence {s}, new token {i} (position {past + i})")
+
+
+# ---------------------------------------------------------------------------
+# TMA + tcgen05 products
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (128, 128, 256), (300, 200, 2048), (77, 130, 200), (1, 24, 8),
+                                     (513, 384, 1408)])
+def test_gemm_tc05_dense(m, n, k):
+    a, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1)
+    scale = rnd(m, seed=2)
+    c = torch.full((m + 3, n), 7.0, device=DEV)
+    st = status()
+    ops.gemm_tc05(a, w, c, st, row_scale=scale, rows=m)
+    assert st.item() == 0
+    close(c[:m], (a.double() @ w.double().t()) * scale.double()[:, None], torch.float32, "tcgen05 dense", k=k)
+    assert torch.all(c[m:] == 7.0), "rows beyond the product were written"
+
+
+@pytest.mark.parametrize("m, inter, k", [(128, 64, 64), (200, 100, 192), (64, 1408, 2048)])
+def test_gemm_tc05_swiglu(m, inter, k):
+    a, w = rnd(m, k, dtype=torch.bfloat16), rnd(2 * inter, k, dtype=torch.bfloat16, seed=1, scale=0.1)
+    act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    st = status()
+    ops.gemm_tc05(a, w, act, st, swiglu=True)
+    assert st.item() == 0
+    g, u = a.double() @ w[:inter].double().t(), a.double() @ w[inter:].double().t()
+    close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "tcgen05 swiglu")
+
+
+def test_gemm_tc05_grouped_through_the_permutation():
+    """Router output -> permutation and tile list -> gathered rows -> grouped SwiGLU product -> grouped
+    down product with the routing weight; experts with no rows, one row and several tiles of rows."""
+    n_tok, k_top, e, width, inter = 700, 2, 7, 136, 72
+    rng = np.random.default_rng(0)
+    probs = np.array([0.55, 0.0, 0.25, 0.001, 0.1, 0.0, 0.099])
+    ids_np = np.stack([rng.choice(e, size=k_top, replace=False, p=probs) for _ in range(n_tok)]).astype(np.int32)
+    ids = torch.tensor(ids_np, device=DEV)
+    wts = rnd(n_tok, k_top).abs() + 0.1
+    rows = n_tok * k_top
+    i32 = lambda *shape: torch.empty(*shape, dtype=torch.int32, device=DEV)
+    offsets, perm_token, inverse = i32(e + 1), i32(rows), i32(n_tok, k_top)
+    perm_weight = torch.empty(rows, device=DEV)
+    max_tiles = (rows + 127) // 128 + e
+    tiles = (i32(max_tiles), i32(max_tiles), i32(1))
+    st = status()
+    ops.moe_permute(ids, wts, e, offsets, perm_token, perm_weight, inverse, st, tiles=(*tiles, 128))
+    off = offsets.cpu().numpy()
+    n_tiles = tiles[2].item()
+    assert n_tiles == sum((off[i + 1] - off[i] + 127) // 128 for i in range(e))
+    tg, tr = tiles[0].cpu().numpy()[:n_tiles], tiles[1].cpu().numpy()[:n_tiles]
+    assert all(off[g] <= r < off[g + 1] for g, r in zip(tg, tr))
+    h = rnd(n_tok, width, dtype=torch.bfloat16, seed=5)
+    h_perm = torch.empty(rows, width, dtype=torch.bfloat16, device=DEV)
+    ops.gather_rows(h, perm_token, h_perm)
+    assert torch.equal(h_perm, h[perm_token.long()])
+    w_gu = rnd(e, 2 * inter, width, dtype=torch.bfloat16, seed=6, scale=0.2)
+    w_d = rnd(e, width, inter, dtype=torch.bfloat16, seed=7, scale=0.2)
+    act = torch.empty(rows, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc05(h_perm, w_gu, act, st, swiglu=True, group_offsets=offsets, tiles=tiles)
+    out = torch.empty(rows, width, device=DEV)
+    ops.gemm_tc05(act, w_d, out, st, row_scale=perm_weight, group_offsets=offsets, tiles=tiles)
+    assert st.item() == 0
+    for g in range(e):
+        lo, hi = off[g], off[g + 1]
+        if lo == hi:
+            continue
+        x = h_perm[lo:hi].double()
+        gg, uu = x @ w_gu[g, :inter].double().t(), x @ w_gu[g, inter:].double().t()
+        close(act[lo:hi], gg / (1 + torch.exp(-gg)) * uu, torch.bfloat16, f"expert {g} gate/up")
+        ref = (act[lo:hi].double() @ w_d[g].double().t()) * perm_weight[lo:hi].double()[:, None]
+        close(out[lo:hi], ref, torch.float32, f"expert {g} down", k=inter)
