@@ -1,37 +1,44 @@
 // Tensor-core matrix product for many rows (prefill) on the 5th-generation
 // tensor cores: operands travel global -> shared memory by TMA
-// (cp.async.bulk.tensor, 128-byte swizzle), tcgen05.mma accumulates a
-// 128 x 128 float tile in tensor memory (TMEM), and the epilogue reads it back
-// with tcgen05.ld.
+// (cp.async.bulk.tensor, 128-byte swizzle), tcgen05.mma accumulates in tensor
+// memory (TMEM), and the epilogue reads the accumulator back with tcgen05.ld.
 //
 //   PLAIN:  C[m, n]   = scale[m] * sum_k A[m, k] * W[g][n, k]                (float out)
 //   SWIGLU: act[m, j] = silu(A W_gate[g][j]) * (A W_up[g][j])                (bfloat16 out)
-//           W[g] = [gate rows; up rows], a tile holds 64 gate and the 64 matching up columns
+//           W[g] = [gate rows; up rows]
 //
 // A is [rows, K] bfloat16, rows sorted by group; W is [G, Nw, K] bfloat16 (G = 1
-// for a dense product).  Row tiles of 128 never mix groups: the tile list
-// (group, first row) is made on the device by the routing kernels, and a tile
-// that reaches past its group's last row computes rows it does not store.
+// for a dense product).  The weights are the 128-row operand of the MMA and a
+// run of up to 256 token rows is its N side, so the accumulator holds
+// D[feature, token]: TMEM lane = output feature, TMEM column = token.  The width
+// of a token tile is whatever its group has left, rounded up to 16, which keeps
+// ragged groups (a handful of rows for one expert, hundreds for another) from
+// wasting tensor work.  A token tile never mixes groups: the tile list (group,
+// first row, rows) is made on the device by the routing kernels.
 //
-// One CTA = one output tile.  Warp 0 issues the TMA loads, warp 1 owns TMEM and
-// issues the MMAs, warps 2..5 are the epilogue (each reads the 32 TMEM lanes
-// that its position in the warpgroup may touch).  A ring of STAGES shared-memory
-// buffers is handed back and forth with mbarriers.  Every wait is bounded: if
-// one runs out the kernel raises ESP_STATUS_WAIT_EXPIRED in the status word,
-// stops issuing work, lets its own copies land, frees its TMEM and returns.
+// One CTA = 128 features x one token tile.  Warp 0 issues the TMA loads, warp 1
+// owns TMEM and issues the MMAs, warps 2..5 are the epilogue (each reads the 32
+// TMEM lanes that its position in the warpgroup may touch).  A ring of
+// shared-memory stages is handed back and forth with mbarriers.  Every wait is
+// bounded: if one runs out the kernel raises ESP_STATUS_WAIT_EXPIRED in the
+// status word, stops issuing work, lets its own copies land, frees its TMEM and
+// returns.
 #include <cuda.h>
 
 #include "common.cuh"
 
 namespace {
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 5, THREADS = 192;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BF = 128;            // features (weight rows) per tile: the M side of the MMA
+constexpr int MAX_TOK = 256;        // token rows per tile at most: the N side
+constexpr int TOK_BOX = 16;         // token rows per TMA box; a tile's width is a multiple of it
+constexpr int BK = 64, THREADS = 192;
+constexpr int W_BYTES = BF * BK * 2, TOK_BYTES = MAX_TOK * BK * 2;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 struct Tc05Params {
-    const int* group_offsets;     // [G+1] or null (dense)
-    const int* tile_group;        // [tiles] or null
+    const int* tile_group;        // [tiles] or null (dense)
     const int* tile_row0;         // [tiles]
+    const int* tile_rows;         // [tiles]
     const int* n_tiles;           // device scalar or null
     const float* row_scale;       // [rows] or null
     void* C;
@@ -114,12 +121,17 @@ __device__ __forceinline__ unsigned long long smem_desc(const void* p) {
     d |= (unsigned long long)2 << 61;                                // 128-byte swizzle
     return d;
 }
-// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = 128.
-constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ unsigned instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
+}
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, Tc05Params p) {
+    constexpr int STAGES = SWIGLU ? 3 : 4;
+    constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * W_BYTES + TOK_BYTES;
+    constexpr int TMEM_COLS = SWIGLU ? 512 : 256;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
@@ -129,13 +141,16 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int group = 0, row0 = blockIdx.y * BM, row_end = p.M;
+    int group = 0, row0 = blockIdx.y * MAX_TOK, n_rows = min(MAX_TOK, p.M - row0);
     if (p.tile_group) {
         if ((int)blockIdx.y >= *p.n_tiles) return;                   // the whole CTA leaves before any barrier exists
         group = p.tile_group[blockIdx.y];
         row0 = p.tile_row0[blockIdx.y];
-        row_end = p.group_offsets[group + 1];
+        n_rows = p.tile_rows[blockIdx.y];
     }
+    if (n_rows <= 0) return;
+    const int n_tok = min(MAX_TOK, (n_rows + TOK_BOX - 1) / TOK_BOX * TOK_BOX);      // width of the MMA's N side
+    const int f0 = blockIdx.x * BF;                                                 // first feature of the tile
     const int k_iters = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -148,7 +163,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(BN));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     tc_fence_before();
@@ -159,6 +174,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 0) {
         if (lane == 0) {
             int issued = 0;
+            const unsigned stage_tx = (SWIGLU ? 2 : 1) * W_BYTES + n_tok * BK * 2;
             for (int it = 0; it < k_iters && !*abort_flag; it++) {
                 const int s = it % STAGES;
                 if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1)) {
@@ -166,16 +182,13 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     *abort_flag = 1;
                     break;
                 }
-                unsigned char* a_dst = smem + s * STAGE_BYTES;
-                unsigned char* b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, it * BK, row0, &full_bar[s]);
-                if (SWIGLU) {
-                    tma_load_3d(b_dst, &map_w, it * BK, blockIdx.x * 64, group, &full_bar[s]);
-                    tma_load_3d(b_dst + B_BYTES / 2, &map_w, it * BK, p.N + blockIdx.x * 64, group, &full_bar[s]);
-                } else {
-                    tma_load_3d(b_dst, &map_w, it * BK, blockIdx.x * BN, group, &full_bar[s]);
-                }
+                unsigned char* w_dst = smem + s * STAGE_BYTES;
+                unsigned char* t_dst = w_dst + (SWIGLU ? 2 : 1) * W_BYTES;
+                mbar_expect_tx(&full_bar[s], stage_tx);
+                tma_load_3d(w_dst, &map_w, it * BK, f0, group, &full_bar[s]);
+                if (SWIGLU) tma_load_3d(w_dst + W_BYTES, &map_w, it * BK, p.N + f0, group, &full_bar[s]);
+                for (int r = 0; r < n_tok; r += TOK_BOX)
+                    tma_load_2d(t_dst + r * BK * 2, &map_a, it * BK, row0 + r, &full_bar[s]);
                 issued = it + 1;
             }
             if (*abort_flag) {
@@ -185,6 +198,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            const unsigned idesc = instr_desc(n_tok);
             for (int it = 0; it < k_iters && !*abort_flag; it++) {
                 const int s = it % STAGES;
                 if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
@@ -193,14 +207,17 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     break;
                 }
                 tc_fence_after();
-                const unsigned char* a_src = smem + s * STAGE_BYTES;
-                const unsigned char* b_src = a_src + A_BYTES;
+                const unsigned char* w_src = smem + s * STAGE_BYTES;
+                const unsigned char* t_src = w_src + (SWIGLU ? 2 : 1) * W_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++)
-                    tc_mma(tmem_base, smem_desc(a_src + k * 32), smem_desc(b_src + k * 32), IDESC, (it > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < BK / 16; k++) {
+                    const unsigned acc = (it > 0 || k > 0) ? 1u : 0u;
+                    tc_mma(tmem_base, smem_desc(w_src + k * 32), smem_desc(t_src + k * 32), idesc, acc);
+                    if (SWIGLU) tc_mma(tmem_base + MAX_TOK, smem_desc(w_src + W_BYTES + k * 32), smem_desc(t_src + k * 32), idesc, acc);
+                }
                 tc_commit(&empty_bar[s]);                             // the stage is free once these MMAs have read it
             }
-            tc_commit(tmem_full_bar);                                 // the accumulator is complete once all MMAs are done
+            tc_commit(tmem_full_bar);                                 // the accumulators are complete once all MMAs are done
         }
     } else {
         const int quad = warp & 3;                                   // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
@@ -210,45 +227,30 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             *abort_flag = 1;
         }
         tc_fence_after();
-        const int row = row0 + quad * 32 + lane;
-        const bool row_ok = ok && !*abort_flag && row < row_end;
+        const int f = f0 + quad * 32 + lane;                          // this thread's output feature
+        const bool f_ok = ok && !*abort_flag && f < p.N;
         const unsigned lane_addr = tmem_base + ((unsigned)(quad * 32) << 16);
-        if (SWIGLU) {
-            bf16* out = reinterpret_cast<bf16*>(p.C) + (size_t)row * p.ldc;
+        for (int c0 = 0; c0 < n_tok; c0 += 32) {
+            float acc[32];
+            tc_ld32(lane_addr + c0, acc);
+            if (SWIGLU) {
+                float up[32];
+                tc_ld32(lane_addr + MAX_TOK + c0, up);
+                bf16* out = reinterpret_cast<bf16*>(p.C);
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 32) {
-                float gate[32], up[32];
-                tc_ld32(lane_addr + c0, gate);
-                tc_ld32(lane_addr + 64 + c0, up);
-                const int j0 = blockIdx.x * 64 + c0;
-                if (row_ok) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float a = gate[i] / (1.0f + expf(-gate[i])) * up[i];
-                        const float b = gate[i + 1] / (1.0f + expf(-gate[i + 1])) * up[i + 1];
-                        if (j0 + i + 1 < p.N) *reinterpret_cast<__nv_bfloat162*>(out + j0 + i) = __floats2bfloat162_rn(a, b);
-                        else if (j0 + i < p.N) out[j0 + i] = __float2bfloat16_rn(a);
+                for (int i = 0; i < 32; i++) {
+                    if (f_ok && c0 + i < n_rows) {
+                        const float v = acc[i] / (1.0f + expf(-acc[i])) * up[i];
+                        out[(size_t)(row0 + c0 + i) * p.ldc + f] = __float2bfloat16_rn(v);
                     }
                 }
-            }
-        } else {
-            float* out = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc;
-            const float scale = (row_ok && p.row_scale) ? p.row_scale[row] : 1.0f;
+            } else {
+                float* out = reinterpret_cast<float*>(p.C);
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                float acc[32];
-                tc_ld32(lane_addr + c0, acc);
-                const int n0 = blockIdx.x * BN + c0;
-                if (row_ok) {
-                    if (n0 + 32 <= p.N && (p.ldc & 3) == 0) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            *reinterpret_cast<float4*>(out + n0 + i) =
-                                make_float4(acc[i] * scale, acc[i + 1] * scale, acc[i + 2] * scale, acc[i + 3] * scale);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            if (n0 + i < p.N) out[n0 + i] = acc[i] * scale;
+                for (int i = 0; i < 32; i++) {
+                    if (f_ok && c0 + i < n_rows) {
+                        const float scale = p.row_scale ? p.row_scale[row0 + c0 + i] : 1.0f;
+                        out[(size_t)(row0 + c0 + i) * p.ldc + f] = acc[i] * scale;
                     }
                 }
             }
@@ -258,7 +260,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(BN));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
 }
 
@@ -281,49 +283,41 @@ EncodeTiledFn encode_fn() {
 
 // bfloat16 tensor [d2][d1][d0] (d0 innermost), box [1][box1][64], 128-byte swizzle, zero fill out of bounds
 int make_map(CUtensorMap* map, const void* base, unsigned long long d0, unsigned long long d1, unsigned long long d2,
-             unsigned box1) {
+             unsigned box1, int rank) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return (int)cudaErrorNotSupported;
     const cuuint64_t dims[3] = {d0, d1, d2};
     const cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
     const cuuint32_t box[3] = {BK, box1, 1};
     const cuuint32_t elem[3] = {1, 1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d2 > 1 ? 3 : 2, const_cast<void*>(base), dims, strides, box,
-                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 }  // namespace
 
-// A [rows_total, K] bfloat16 (row-major, contiguous), W [G, Nw, K] bfloat16.  Dense: tile_group = null and
-// M rows.  Grouped: the tile list on the device; ``max_tiles`` bounds the number of row tiles.
-// swiglu: N is the intermediate size and Nw = 2N.  K must be a multiple of 8, the bases 16-byte aligned.
+// A [rows_total, K] bfloat16 (row-major, contiguous), W [G, w_rows, K] bfloat16.  Dense: tile_group = null,
+// M rows.  Grouped: the token-tile list on the device (tiles of at most 256 rows); ``max_tiles`` bounds
+// their number.  swiglu: N is the intermediate size and w_rows = 2N.  K must be a multiple of 8, the
+// bases 16-byte aligned.
 ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, int groups, int w_rows,
-                          const float* row_scale, void* C, long long ldc, const int* group_offsets,
-                          const int* tile_group, const int* tile_row0, const int* n_tiles, int max_tiles, int M, int N,
-                          int K, int swiglu, int* status, cudaStream_t stream) {
+                          const float* row_scale, void* C, long long ldc, const int* tile_group, const int* tile_row0,
+                          const int* tile_rows, const int* n_tiles, int max_tiles, int M, int N, int K, int swiglu,
+                          int* status, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || rows_total <= 0) return 0;
     if (K % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     CUtensorMap map_a, map_w;
-    int rc = make_map(&map_a, A, (unsigned long long)K, (unsigned long long)rows_total, 1, BM);
+    int rc = make_map(&map_a, A, (unsigned long long)K, (unsigned long long)rows_total, 1, TOK_BOX, 2);
     if (rc) return rc;
     // the weights always use a 3-D map so that the kernel has one code path; a dense product is one group
-    {
-        EncodeTiledFn fn = encode_fn();
-        const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)w_rows, (cuuint64_t)groups};
-        const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * w_rows * 2};
-        const cuuint32_t box[3] = {BK, (cuuint32_t)(swiglu ? 64 : BN), 1};
-        const cuuint32_t elem[3] = {1, 1, 1};
-        if (fn(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(W), dims, strides, box, elem,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return (int)cudaErrorInvalidValue;
-    }
-    Tc05Params p{group_offsets, tile_group, tile_row0, n_tiles, row_scale, C, ldc, M, N, K, status};
-    const int row_tiles = tile_group ? max_tiles : (M + BM - 1) / BM;
-    if (row_tiles <= 0) return 0;
-    if (row_tiles > 65535) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+    rc = make_map(&map_w, W, (unsigned long long)K, (unsigned long long)w_rows, (unsigned long long)groups, BF, 3);
+    if (rc) return rc;
+    Tc05Params p{tile_group, tile_row0, tile_rows, n_tiles, row_scale, C, ldc, M, N, K, status};
+    const int token_tiles = tile_group ? max_tiles : (M + MAX_TOK - 1) / MAX_TOK;
+    if (token_tiles <= 0) return 0;
+    if (token_tiles > 65535) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)(swiglu ? 3 * (2 * W_BYTES + TOK_BYTES) : 4 * (W_BYTES + TOK_BYTES)) + 1024 + 256;
     static bool raised[2] = {false, false};
     if (!raised[swiglu ? 1 : 0]) {
         cudaError_t e = swiglu ? cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
@@ -331,7 +325,7 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
         if (e != cudaSuccess) return (int)e;
         raised[swiglu ? 1 : 0] = true;
     }
-    dim3 grid(swiglu ? (N + 63) / 64 : (N + BN - 1) / BN, row_tiles);
+    dim3 grid((N + BF - 1) / BF, token_tiles);
     if (swiglu) gemm_tc05_kernel<true><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
     else gemm_tc05_kernel<false><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
     return esp_launch_status();

@@ -134,7 +134,8 @@ __global__ void __launch_bounds__(1024)
 moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ topk_w, int n_pairs, int n_experts,
                    int* __restrict__ offsets, int* __restrict__ perm_token, float* __restrict__ perm_weight,
                    int* __restrict__ inverse, int top_k, int* __restrict__ tile_group, int* __restrict__ tile_row0,
-                   int* __restrict__ n_tiles, int tile_rows, int max_tiles, int* __restrict__ status) {
+                   int* __restrict__ tile_count, int* __restrict__ n_tiles, int tile_rows, int max_tiles,
+                   int* __restrict__ status) {
     extern __shared__ int sm[];
     int* counts = sm;                      // [n_experts]
     int* cursor = sm + n_experts;          // [n_experts + 1]
@@ -162,6 +163,7 @@ moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ t
                 for (int r = 0; r < counts[e] && t < max_tiles; r += tile_rows, t++) {
                     tile_group[t] = e;
                     tile_row0[t] = offsets[e] + r;
+                    tile_count[t] = min(tile_rows, counts[e] - r);
                 }
             *n_tiles = t;
         }
@@ -233,18 +235,19 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
     return esp_launch_status();
 }
 
-// tile_group / tile_row0 / n_tiles (may be null): the list of row tiles of ``tile_rows`` rows, at most
-// ``max_tiles`` (pass at least ceil(pairs / tile_rows) + n_experts).
+// tile_group / tile_row0 / tile_count / n_tiles (may be null): the list of row tiles of at most
+// ``tile_rows`` rows each (group, first row, rows), at most ``max_tiles`` of them (pass at least
+// ceil(pairs / tile_rows) + n_experts).
 ESP_API int esp_moe_permute(const int* topk_ids, const float* topk_w, int n_tokens, int top_k, int n_experts,
                             int* offsets, int* perm_token, float* perm_weight, int* inverse, int* tile_group,
-                            int* tile_row0, int* n_tiles, int tile_rows, int max_tiles, int* status,
+                            int* tile_row0, int* tile_count, int* n_tiles, int tile_rows, int max_tiles, int* status,
                             cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     moe_permute_kernel<<<1, 1024, smem, stream>>>(topk_ids, topk_w, n_tokens * top_k, n_experts, offsets, perm_token,
-                                                  perm_weight, inverse, top_k, tile_group, tile_row0, n_tiles, tile_rows,
-                                                  max_tiles, status);
+                                                  perm_weight, inverse, top_k, tile_group, tile_row0, tile_count, n_tiles,
+                                                  tile_rows, max_tiles, status);
     return esp_launch_status();
 }
 

@@ -28,7 +28,7 @@ _SIGNATURES = {
                          c_int, c_int, P, P],
     "esp_attn_simt": [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
-    "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, c_int, c_int, P, P],
+    "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
     "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
@@ -213,8 +213,8 @@ def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, s
 
 
 def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, inverse, status, tiles=None):
-    """``tiles``: optional (tile_group, tile_row0, n_tiles, tile_rows) int32 tensors/int that receive the
-    list of row tiles for the grouped tensor-core products."""
+    """``tiles``: optional (tile_group, tile_row0, tile_count, n_tiles) int32 tensors that receive the
+    list of row tiles (of at most TC05_TILE_ROWS rows) for the grouped tensor-core products."""
     n, top_k = topk_ids.shape
     if (2 * n_experts + 1) * 4 > 48 * 1024:
         raise Backend(f"moe_permute: {n_experts} experts are beyond what this kernel takes")
@@ -222,8 +222,9 @@ def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, i
         _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32), n, top_k, n_experts, _ptr(offsets, torch.int32),
         _ptr(perm_token, torch.int32), _ptr(perm_weight, torch.float32), _ptr(inverse, torch.int32),
         _ptr(tiles[0], torch.int32) if tiles else None, _ptr(tiles[1], torch.int32) if tiles else None,
-        _ptr(tiles[2], torch.int32) if tiles else None, tiles[3] if tiles else 0, tiles[0].shape[0] if tiles else 0,
-        _ptr(status, torch.int32), _stream()), "moe_permute")
+        _ptr(tiles[2], torch.int32) if tiles else None, _ptr(tiles[3], torch.int32) if tiles else None,
+        TC05_TILE_ROWS if tiles else 0, tiles[0].shape[0] if tiles else 0, _ptr(status, torch.int32), _stream()),
+        "moe_permute")
 
 
 def moe_combine(expert_out, topk_ids, inverse, gate, shared, y):
@@ -324,13 +325,13 @@ def gather_rows(src, rows, out):
            "gather_rows")
 
 
-TC05_TILE_ROWS = 128
+TC05_TILE_ROWS = 256
 
 
-def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, group_offsets=None, tiles=None, rows=None):
+def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None):
     """TMA + tcgen05 product for many rows.  a [rows, K] bfloat16 contiguous; w [N, K] or [G, N, K]
     bfloat16.  Plain: c float32 [rows, N] = scale * a @ w[g].T.  swiglu: w rows are [gate; up] and c is
-    bfloat16 [rows, I].  Grouped: ``tiles`` = (tile_group, tile_row0, n_tiles) from moe_permute."""
+    bfloat16 [rows, I].  Grouped: ``tiles`` = (tile_group, tile_row0, tile_count, n_tiles) from moe_permute."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not a.is_contiguous() or not w.is_contiguous():
         raise Backend("gemm_tc05 takes contiguous bfloat16 operands")
     if w.dim() == 3:
@@ -348,8 +349,8 @@ def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, group_offsets=None,
     grouped = tiles is not None
     code = _fn("tc05", "esp_gemm_tc05")(
         a.data_ptr(), m, w.data_ptr(), groups, wn, _ptr(row_scale, torch.float32, "row_scale"), c.data_ptr(),
-        c.stride(0), _ptr(group_offsets, torch.int32) if grouped else None,
-        _ptr(tiles[0], torch.int32) if grouped else None, _ptr(tiles[1], torch.int32) if grouped else None,
-        _ptr(tiles[2], torch.int32) if grouped else None, tiles[0].shape[0] if grouped else 0, m, n, k,
+        c.stride(0), _ptr(tiles[0], torch.int32) if grouped else None,
+        _ptr(tiles[1], torch.int32) if grouped else None, _ptr(tiles[2], torch.int32) if grouped else None,
+        _ptr(tiles[3], torch.int32) if grouped else None, tiles[0].shape[0] if grouped else 0, m, n, k,
         1 if swiglu else 0, _ptr(status, torch.int32), _stream())
     _check(code, "gemm_tc05")

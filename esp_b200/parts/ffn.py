@@ -6,7 +6,7 @@ import torch
 
 from ..csrc import ops
 from .base import ParamSpec, Part, register
-from .linear import grouped_linear, grouped_swiglu_linear, linear, swiglu_linear
+from .linear import grouped_linear, grouped_swiglu_linear, grouped_uses_tc05, linear, swiglu_linear
 
 
 def _swiglu_mlp(rt, h, w_gate_up, w_down, out, tag):
@@ -137,21 +137,26 @@ class MoeSwiGluShared(Part):
         perm_token = ws.get("moe_perm_token", (n * k,), torch.int32)
         perm_weight = ws.get("moe_perm_weight", (n * k,), torch.float32)
         inverse = ws.get("moe_inverse", (n, k), torch.int32)
-        ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status)
-        expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n)
+        tiles = None
+        if grouped_uses_tc05(h, self.w_gate_up, n * k) and Im % 8 == 0:
+            max_tiles = (n * k + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
+            tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32), ws.get("moe_tile_row0", (max_tiles,), torch.int32),
+                     ws.get("moe_tile_count", (max_tiles,), torch.int32), ws.get("moe_n_tiles", (1,), torch.int32))
+        ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles)
+        expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
         shared = ws.get("moe_shared_out", (n, H), torch.float32)
         _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
         ops.moe_combine(expert_out, ids, inverse, gate, shared, y)
 
-    def experts(self, h, offsets, perm_token, perm_weight, rows, max_rows):
+    def experts(self, h, offsets, perm_token, perm_weight, rows, max_rows, tiles=None):
         """expert_out[r] = weight[r] * down_e(silu(gate_e x) * (up_e x)) for every
         permuted row r, x = h[perm_token[r]], e the expert whose range holds r.
         ``max_rows``: no expert has more rows than this (a token names an expert once)."""
         s, rt = self.spec, self.rt
         act = rt.ws.get("moe_act", (rows, s.expert_intermediate), rt.dtype)
-        grouped_swiglu_linear(rt, h, self.w_gate_up, act, offsets, perm_token, rows, max_rows, "moe")
+        grouped_swiglu_linear(rt, h, self.w_gate_up, act, offsets, perm_token, rows, max_rows, "moe", tiles)
         out = rt.ws.get("moe_expert_out", (rows, s.hidden), torch.float32)
-        grouped_linear(rt, act, self.w_down, out, offsets, perm_weight, rows, max_rows)
+        grouped_linear(rt, act, self.w_down, out, offsets, perm_weight, rows, max_rows, tiles)
         return out
 
 

@@ -15,8 +15,12 @@ import torch
 
 from ..csrc import ops
 
+import os
+
 SKINNY_ROWS = 16            # dense products with at most this many rows stream the weights once
-SKINNY_GROUPED_PAIRS = 1 << 30
+TC05_GROUPED_ROWS = 512     # grouped products with at least this many (token, expert) rows use TMA + tcgen05
+# dense products with many rows: "own" = this library's TMA + tcgen05 kernel, "library" = cuBLAS through torch
+DENSE_GEMM = os.environ.get("ESP_B200_DENSE_GEMM", "own")
 
 
 def _both_bf16(a, w) -> bool:
@@ -28,6 +32,8 @@ def linear(rt, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Ten
     if _both_bf16(a, w):
         if a.shape[0] <= SKINNY_ROWS and ops.skinny_fits(a.shape[1]):
             ops.gemm_skinny(a, w, out)
+        elif DENSE_GEMM == "own" and a.shape[1] % 8 == 0 and a.is_contiguous() and out.is_contiguous():
+            ops.gemm_tc05(a, w, out, rt.status)
         else:
             torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
     else:
@@ -43,15 +49,29 @@ def swiglu_linear(rt, a, w_gate_up, act, tag):
     if _both_bf16(a, w_gate_up) and n <= SKINNY_ROWS and ops.skinny_fits(a.shape[1]):
         ops.gemm_skinny(a, w_gate_up, act, swiglu=True)
         return act
+    if _both_bf16(a, w_gate_up) and DENSE_GEMM == "own" and a.shape[1] % 8 == 0 and a.is_contiguous() and act.is_contiguous():
+        ops.gemm_tc05(a, w_gate_up, act, rt.status, swiglu=True)
+        return act
     gu = rt.ws.get(tag + "_gu", (n, 2 * inter), torch.float32)
     linear(rt, a, w_gate_up, gu)
     ops.swiglu(gu, act)
     return act
 
 
-def grouped_swiglu_linear(rt, a, w_gate_up, act, group_offsets, a_rows, rows, max_rows, tag):
+def grouped_uses_tc05(a, w, rows) -> bool:
+    return _both_bf16(a, w) and rows >= TC05_GROUPED_ROWS and a.shape[1] % 8 == 0 and w.shape[1] % 16 == 0
+
+
+def grouped_swiglu_linear(rt, a, w_gate_up, act, group_offsets, a_rows, rows, max_rows, tag, tiles=None):
     """Grouped form of swiglu_linear: permuted row r reads a[a_rows[r]] and the
-    weights of the group whose range holds r (w_gate_up [G, 2I, K])."""
+    weights of the group whose range holds r (w_gate_up [G, 2I, K]).  With
+    ``tiles`` (the row-tile list of the permutation) the rows are gathered
+    once and the product runs on TMA + tcgen05."""
+    if tiles is not None:
+        gathered = rt.ws.get(tag + "_gathered", (rows, a.shape[1]), torch.bfloat16)
+        ops.gather_rows(a, a_rows, gathered)
+        ops.gemm_tc05(gathered, w_gate_up, act, rt.status, swiglu=True, tiles=tiles)
+        return act
     if _both_bf16(a, w_gate_up) and ops.skinny_fits(a.shape[1]):
         ops.gemm_skinny(a, w_gate_up, act, swiglu=True, a_rows=a_rows, group_offsets=group_offsets, rows=rows,
                         max_rows=max_rows)
@@ -63,8 +83,11 @@ def grouped_swiglu_linear(rt, a, w_gate_up, act, group_offsets, a_rows, rows, ma
     return act
 
 
-def grouped_linear(rt, a, w, out, group_offsets, row_scale, rows, max_rows):
+def grouped_linear(rt, a, w, out, group_offsets, row_scale, rows, max_rows, tiles=None):
     """out[r] = row_scale[r] * a[r] @ w[g].T for the rows of every group (w [G,N,K])."""
+    if tiles is not None:
+        ops.gemm_tc05(a, w, out, rt.status, row_scale=row_scale, tiles=tiles)
+        return out
     if _both_bf16(a, w) and ops.skinny_fits(a.shape[1]):
         ops.gemm_skinny(a, w, out, row_scale=row_scale, group_offsets=group_offsets, rows=rows, max_rows=max_rows)
     else:

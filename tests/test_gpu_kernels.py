@@ -541,8 +541,8 @@ def test_attn_prefill_against_reference(nh, nkv, hd, window):
 # ---------------------------------------------------------------------------
 # TMA + tcgen05 products
 # ---------------------------------------------------------------------------
-@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (128, 128, 256), (300, 200, 2048), (77, 130, 200), (1, 24, 8),
-                                     (513, 384, 1408)])
+@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (256, 128, 256), (300, 200, 2048), (77, 130, 200), (1, 24, 8),
+                                     (513, 384, 1408), (17, 129, 72)])
 def test_gemm_tc05_dense(m, n, k):
     a, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1)
     scale = rnd(m, seed=2)
@@ -578,15 +578,17 @@ def test_gemm_tc05_grouped_through_the_permutation():
     i32 = lambda *shape: torch.empty(*shape, dtype=torch.int32, device=DEV)
     offsets, perm_token, inverse = i32(e + 1), i32(rows), i32(n_tok, k_top)
     perm_weight = torch.empty(rows, device=DEV)
-    max_tiles = (rows + 127) // 128 + e
-    tiles = (i32(max_tiles), i32(max_tiles), i32(1))
+    tile = ops.TC05_TILE_ROWS
+    max_tiles = (rows + tile - 1) // tile + e
+    tiles = (i32(max_tiles), i32(max_tiles), i32(max_tiles), i32(1))
     st = status()
-    ops.moe_permute(ids, wts, e, offsets, perm_token, perm_weight, inverse, st, tiles=(*tiles, 128))
+    ops.moe_permute(ids, wts, e, offsets, perm_token, perm_weight, inverse, st, tiles=tiles)
     off = offsets.cpu().numpy()
-    n_tiles = tiles[2].item()
-    assert n_tiles == sum((off[i + 1] - off[i] + 127) // 128 for i in range(e))
-    tg, tr = tiles[0].cpu().numpy()[:n_tiles], tiles[1].cpu().numpy()[:n_tiles]
-    assert all(off[g] <= r < off[g + 1] for g, r in zip(tg, tr))
+    n_tiles = tiles[3].item()
+    assert n_tiles == sum((off[i + 1] - off[i] + tile - 1) // tile for i in range(e))
+    tg, tr, tc = (t.cpu().numpy()[:n_tiles] for t in tiles[:3])
+    assert all(off[g] <= r and r + c <= off[g + 1] and 0 < c <= tile for g, r, c in zip(tg, tr, tc))
+    assert sum(tc) == rows
     h = rnd(n_tok, width, dtype=torch.bfloat16, seed=5)
     h_perm = torch.empty(rows, width, dtype=torch.bfloat16, device=DEV)
     ops.gather_rows(h, perm_token, h_perm)
@@ -594,9 +596,9 @@ def test_gemm_tc05_grouped_through_the_permutation():
     w_gu = rnd(e, 2 * inter, width, dtype=torch.bfloat16, seed=6, scale=0.2)
     w_d = rnd(e, width, inter, dtype=torch.bfloat16, seed=7, scale=0.2)
     act = torch.empty(rows, inter, dtype=torch.bfloat16, device=DEV)
-    ops.gemm_tc05(h_perm, w_gu, act, st, swiglu=True, group_offsets=offsets, tiles=tiles)
+    ops.gemm_tc05(h_perm, w_gu, act, st, swiglu=True, tiles=tiles)
     out = torch.empty(rows, width, device=DEV)
-    ops.gemm_tc05(act, w_d, out, st, row_scale=perm_weight, group_offsets=offsets, tiles=tiles)
+    ops.gemm_tc05(act, w_d, out, st, row_scale=perm_weight, tiles=tiles)
     assert st.item() == 0
     for g in range(e):
         lo, hi = off[g], off[g + 1]
