@@ -9,7 +9,7 @@
 //
 // A is [rows, K] bfloat16, rows sorted by group; W is [G, Nw, K] bfloat16 (G = 1
 // for a dense product).  The weights are the 128-row operand of the MMA and a
-// run of up to 256 token rows is its N side, so the accumulator holds
+// run of up to 128 or 256 token rows is its N side, so the accumulator holds
 // D[feature, token]: TMEM lane = output feature, TMEM column = token.  The width
 // of a token tile is whatever its group has left, rounded up to 16, which keeps
 // ragged groups (a handful of rows for one expert, hundreds for another) from
@@ -29,10 +29,10 @@
 
 namespace {
 constexpr int BF = 128;            // features (weight rows) per tile: the M side of the MMA
-constexpr int MAX_TOK = 256;        // token rows per tile at most: the N side
 constexpr int TOK_BOX = 16;         // token rows per TMA box; a tile's width is a multiple of it
 constexpr int BK = 64, THREADS = 192;
-constexpr int W_BYTES = BF * BK * 2, TOK_BYTES = MAX_TOK * BK * 2;
+constexpr int W_BYTES = BF * BK * 2;
+constexpr int CTA_SMEM = 96 * 1024; // ring size: two CTAs fit one SM, so one's epilogue hides behind the other's loads
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 struct Tc05Params {
@@ -126,12 +126,15 @@ __device__ __forceinline__ unsigned instr_desc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
 }
 
-template <bool SWIGLU>
-__global__ void __launch_bounds__(THREADS, 1)
+// MAX_TOK: token rows per tile at most (the N side of the MMA): 128 or 256
+template <bool SWIGLU, int MAX_TOK>
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, Tc05Params p) {
-    constexpr int STAGES = SWIGLU ? 3 : 4;
+    constexpr int TOK_BYTES = MAX_TOK * BK * 2;
     constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * W_BYTES + TOK_BYTES;
-    constexpr int TMEM_COLS = SWIGLU ? 512 : 256;
+    constexpr int STAGES = CTA_SMEM / STAGE_BYTES;
+    constexpr int TMEM_COLS = (SWIGLU ? 2 : 1) * MAX_TOK;
+    static_assert(STAGES >= 2 && TMEM_COLS <= 256, "two CTAs share the SM's shared memory and its 512 TMEM columns");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
@@ -298,7 +301,7 @@ int make_map(CUtensorMap* map, const void* base, unsigned long long d0, unsigned
 }  // namespace
 
 // A [rows_total, K] bfloat16 (row-major, contiguous), W [G, w_rows, K] bfloat16.  Dense: tile_group = null,
-// M rows.  Grouped: the token-tile list on the device (tiles of at most 256 rows); ``max_tiles`` bounds
+// M rows.  Grouped: the token-tile list on the device (tiles of at most 128 rows); ``max_tiles`` bounds
 // their number.  swiglu: N is the intermediate size and w_rows = 2N.  K must be a multiple of 8, the
 // bases 16-byte aligned.
 ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, int groups, int w_rows,
@@ -314,19 +317,25 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
     rc = make_map(&map_w, W, (unsigned long long)K, (unsigned long long)w_rows, (unsigned long long)groups, BF, 3);
     if (rc) return rc;
     Tc05Params p{tile_group, tile_row0, tile_rows, n_tiles, row_scale, C, ldc, M, N, K, status};
-    const int token_tiles = tile_group ? max_tiles : (M + MAX_TOK - 1) / MAX_TOK;
+    // grouped products and SwiGLU products use token tiles of 128, dense plain products of 256
+    const int max_tok = (tile_group || swiglu) ? 128 : 256;
+    const int token_tiles = tile_group ? max_tiles : (M + max_tok - 1) / max_tok;
     if (token_tiles <= 0) return 0;
     if (token_tiles > 65535) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)(swiglu ? 3 * (2 * W_BYTES + TOK_BYTES) : 4 * (W_BYTES + TOK_BYTES)) + 1024 + 256;
-    static bool raised[2] = {false, false};
-    if (!raised[swiglu ? 1 : 0]) {
-        cudaError_t e = swiglu ? cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                               : cudaFuncSetAttribute(gemm_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = CTA_SMEM + 1024 + 256;
+    const int which = swiglu ? 0 : (max_tok == 128 ? 1 : 2);
+    static bool raised[3] = {false, false, false};
+    if (!raised[which]) {
+        cudaError_t e =
+            which == 0 ? cudaFuncSetAttribute(gemm_tc05_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+            : which == 1 ? cudaFuncSetAttribute(gemm_tc05_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                         : cudaFuncSetAttribute(gemm_tc05_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        raised[swiglu ? 1 : 0] = true;
+        raised[which] = true;
     }
     dim3 grid((N + BF - 1) / BF, token_tiles);
-    if (swiglu) gemm_tc05_kernel<true><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
-    else gemm_tc05_kernel<false><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
+    if (which == 0) gemm_tc05_kernel<true, 128><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
+    else if (which == 1) gemm_tc05_kernel<false, 128><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
+    else gemm_tc05_kernel<false, 256><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
     return esp_launch_status();
 }

@@ -8,122 +8,137 @@ namespace {
 constexpr int ROUTER_THREADS = 512;
 constexpr int MAX_TOPK = 32;
 
-// A lane's share of dot(hs, w): 8 consecutive elements at a time (16-byte loads
-// of bfloat16, 32-byte of float), lanes interleaved, several loads in flight.
-// The order of a lane's additions depends on the width alone.
-__device__ __forceinline__ float lane_dot(const float* __restrict__ hs, const bf16* __restrict__ w, int width, int lane) {
-    float s = 0.f;
-    const int vec_end = (width % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) ? width : 0;
-#pragma unroll 4
-    for (int i = lane * 8; i < vec_end; i += 256) {
-        const uint4 v = *reinterpret_cast<const uint4*>(w + i);
-        const unsigned u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            s = fmaf(hs[i + 2 * j], __uint_as_float(u[j] << 16), s);
-            s = fmaf(hs[i + 2 * j + 1], __uint_as_float(u[j] & 0xffff0000u), s);
-        }
-    }
-    for (int i = vec_end + lane; i < width; i += 32) s = fmaf(hs[i], __bfloat162float(w[i]), s);
-    return s;
+// A lane's share of dot(hs[t], w) for TPB token rows at once: 4 consecutive
+// weights at a time (8-byte loads of bfloat16, 16-byte of float), lanes
+// interleaved so that the float4 reads of hs fall into distinct banks, several
+// loads in flight; each weight is loaded once and used for every row.  The
+// order of a lane's additions depends on the width alone.
+__device__ __forceinline__ float4 load4(const bf16* w) {
+    const uint2 v = *reinterpret_cast<const uint2*>(w);
+    return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                       __uint_as_float(v.y & 0xffff0000u));
 }
-__device__ __forceinline__ float lane_dot(const float* __restrict__ hs, const float* __restrict__ w, int width, int lane) {
-    float s = 0.f;
+__device__ __forceinline__ float4 load4(const float* w) { return *reinterpret_cast<const float4*>(w); }
+
+template <int TPB, typename TW>
+__device__ __forceinline__ void lane_dots(const float* __restrict__ hs, int hs_stride, const TW* __restrict__ w, int width,
+                                          int lane, float (&s)[TPB]) {
+#pragma unroll
+    for (int t = 0; t < TPB; t++) s[t] = 0.f;
     const int vec_end = (width % 4 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) ? width : 0;
 #pragma unroll 4
     for (int i = lane * 4; i < vec_end; i += 128) {
-        const float4 v = *reinterpret_cast<const float4*>(w + i);
-        s = fmaf(hs[i], v.x, s);
-        s = fmaf(hs[i + 1], v.y, s);
-        s = fmaf(hs[i + 2], v.z, s);
-        s = fmaf(hs[i + 3], v.w, s);
+        const float4 f = load4(w + i);
+#pragma unroll
+        for (int t = 0; t < TPB; t++) {
+            const float4 x = *reinterpret_cast<const float4*>(hs + t * hs_stride + i);
+            s[t] = fmaf(x.x, f.x, s[t]);
+            s[t] = fmaf(x.y, f.y, s[t]);
+            s[t] = fmaf(x.z, f.z, s[t]);
+            s[t] = fmaf(x.w, f.w, s[t]);
+        }
     }
-    for (int i = vec_end + lane; i < width; i += 32) s = fmaf(hs[i], w[i], s);
-    return s;
+    for (int i = vec_end + lane; i < width; i += 32) {
+        const float wv = to_f32(w[i]);
+#pragma unroll
+        for (int t = 0; t < TPB; t++) s[t] = fmaf(hs[t * hs_stride + i], wv, s[t]);
+    }
 }
 
-// One block per token.  logits[e] = sum_k h[k] * Wr[e][k]: a warp per expert,
+// One block per TPB tokens.  logits[e] = sum_k h[k] * Wr[e][k]: a warp per expert,
 // lanes stride over k, partial sums combined by the fixed warp butterfly.
 // p = softmax(logits) over all experts; the k largest p win, ties to the lower
 // id; weights are p / (sum of the chosen p) if norm_topk else p.
 // gate[n] = sigmoid(h . w_gate) when w_gate is given.
-template <typename TH, typename TW>
+template <typename TH, typename TW, int TPB>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, const TW* __restrict__ w_gate,
                    int* __restrict__ topk_ids, float* __restrict__ topk_w, float* __restrict__ gate,
-                   float* __restrict__ probs_out, int width, int n_experts, int top_k, int norm_topk,
+                   float* __restrict__ probs_out, int n_tokens, int width, int n_experts, int top_k, int norm_topk,
                    int* __restrict__ status) {
     extern __shared__ float smem[];
-    float* hs = smem;                    // [width]
-    float* ps = smem + width;            // [n_experts]
+    float* hs = smem;                          // [TPB][width]
+    float* ps_all = smem + TPB * width;        // [TPB][n_experts]
     __shared__ float scratch[33];
     __shared__ int chosen[MAX_TOPK];
     __shared__ float chosen_p[MAX_TOPK];
-    const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = ROUTER_THREADS / 32;
-    const TH* hr = h + (size_t)n * width;
-    for (int i = tid; i < width; i += ROUTER_THREADS) hs[i] = to_f32(hr[i]);
+    const int n0 = blockIdx.x * TPB, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = ROUTER_THREADS / 32;
+    const int live = min(TPB, n_tokens - n0);
+    for (int i = tid; i < TPB * width; i += ROUTER_THREADS) {
+        const int t = i / width;
+        hs[i] = t < live ? to_f32(h[(size_t)n0 * width + i]) : 0.f;
+    }
     __syncthreads();
     for (int e = warp; e < n_experts + (w_gate ? 1 : 0); e += nwarp) {
         const TW* wr = e < n_experts ? w_router + (size_t)e * width : w_gate;
-        float s = lane_dot(hs, wr, width, lane);
-        s = warp_sum(s);
-        if (lane == 0) {
-            if (e < n_experts) ps[e] = s;
-            else gate[n] = 1.0f / (1.0f + expf(-s));
-        }
-    }
-    __syncthreads();
-    float lm = -INFINITY;
-    for (int e = tid; e < n_experts; e += ROUTER_THREADS) lm = fmaxf(lm, ps[e]);
-    const float mx = block_max(lm, scratch);
-    float ls = 0.f;
-    for (int e = tid; e < n_experts; e += ROUTER_THREADS) {
-        const float p = expf(ps[e] - mx);
-        ps[e] = p;
-        ls += p;
-    }
-    const float total = block_sum(ls, scratch);
-    for (int e = tid; e < n_experts; e += ROUTER_THREADS) {
-        const float p = ps[e] / total;
-        ps[e] = p;
-        if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
-    }
-    __syncthreads();
-    // top-k by repeated arg-max in warp 0 (k and E are small); ties go to the lower id
-    if (warp == 0) {
-        bool bad = false;
-        float mass = 0.f;
-        for (int r = 0; r < top_k; r++) {
-            float best = -INFINITY;
-            int best_e = 0x7fffffff;
-            for (int e = lane; e < n_experts; e += 32) {
-                const float p = ps[e];
-                if (!(p == p) || isinf(p)) bad = true;
-                if (p > best) { best = p; best_e = e; }   // ascending e per lane: the first maximum is the lowest id
-            }
+        float s[TPB];
+        lane_dots<TPB>(hs, width, wr, width, lane, s);
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        for (int t = 0; t < TPB; t++) {
+            const float v = warp_sum(s[t]);
+            if (lane == 0 && t < live) {
+                if (e < n_experts) ps_all[t * n_experts + e] = v;
+                else gate[n0 + t] = 1.0f / (1.0f + expf(-v));
             }
-            if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
-            if (lane == 0) {
-                chosen[r] = best_e;
-                chosen_p[r] = best;
-                ps[best_e] = -1.0f;           // probabilities are >= 0: taken out of the running
+        }
+    }
+    __syncthreads();
+    for (int t = 0; t < live; t++) {
+        const int n = n0 + t;
+        float* ps = ps_all + t * n_experts;
+        float lm = -INFINITY;
+        for (int e = tid; e < n_experts; e += ROUTER_THREADS) lm = fmaxf(lm, ps[e]);
+        const float mx = block_max(lm, scratch);
+        float ls = 0.f;
+        for (int e = tid; e < n_experts; e += ROUTER_THREADS) {
+            const float p = expf(ps[e] - mx);
+            ps[e] = p;
+            ls += p;
+        }
+        const float total = block_sum(ls, scratch);
+        for (int e = tid; e < n_experts; e += ROUTER_THREADS) {
+            const float p = ps[e] / total;
+            ps[e] = p;
+            if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
+        }
+        __syncthreads();
+        // top-k by repeated arg-max in warp 0 (k and E are small); ties go to the lower id
+        if (warp == 0) {
+            bool bad = false;
+            float mass = 0.f;
+            for (int r = 0; r < top_k; r++) {
+                float best = -INFINITY;
+                int best_e = 0x7fffffff;
+                for (int e = lane; e < n_experts; e += 32) {
+                    const float p = ps[e];
+                    if (!(p == p) || isinf(p)) bad = true;
+                    if (p > best) { best = p; best_e = e; }   // ascending e per lane: the first maximum is the lowest id
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                    if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+                }
+                if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
+                if (lane == 0) {
+                    chosen[r] = best_e;
+                    chosen_p[r] = best;
+                    ps[best_e] = -1.0f;           // probabilities are >= 0: taken out of the running
+                }
+                mass += best;
+                __syncwarp();
             }
-            mass += best;
-            __syncwarp();
+            const float denom = norm_topk ? mass : 1.0f;
+            if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
+                if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
+            }
+            for (int r = lane; r < top_k; r += 32) {
+                topk_ids[(size_t)n * top_k + r] = chosen[r];
+                topk_w[(size_t)n * top_k + r] = chosen_p[r] / denom;
+            }
         }
-        const float denom = norm_topk ? mass : 1.0f;
-        if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
-            if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
-        }
-        for (int r = lane; r < top_k; r += 32) {
-            topk_ids[(size_t)n * top_k + r] = chosen[r];
-            topk_w[(size_t)n * top_k + r] = chosen_p[r] / denom;
-        }
+        __syncthreads();
     }
 }
 
@@ -217,20 +232,26 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
                             int n_experts, int top_k, int norm_topk, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)(width + n_experts) * sizeof(float);
+    // many tokens: four per block, so that the router's weights are fetched a quarter as often
+    int tpb = n_tokens > 32 ? 4 : 1;
+    if ((size_t)tpb * (width + n_experts) * sizeof(float) > 200 * 1024) tpb = 1;
+    const size_t smem = (size_t)tpb * (width + n_experts) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-#define ESP_ROUTER(TH, TW)                                                                                          \
-    do {                                                                                                            \
-        if (smem > 48 * 1024)                                                                                       \
-            cudaFuncSetAttribute(router_topk_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        router_topk_kernel<TH, TW><<<n_tokens, ROUTER_THREADS, smem, stream>>>(                                      \
-            (const TH*)h, (const TW*)w_router, (const TW*)w_gate, topk_ids, topk_w, gate, probs_out, width,         \
-            n_experts, top_k, norm_topk, status);                                                                   \
+    const int blocks = (n_tokens + tpb - 1) / tpb;
+#define ESP_ROUTER(TH, TW, TPB)                                                                                       \
+    do {                                                                                                              \
+        if (smem > 48 * 1024)                                                                                         \
+            cudaFuncSetAttribute(router_topk_kernel<TH, TW, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        router_topk_kernel<TH, TW, TPB><<<blocks, ROUTER_THREADS, smem, stream>>>(                                     \
+            (const TH*)h, (const TW*)w_router, (const TW*)w_gate, topk_ids, topk_w, gate, probs_out, n_tokens, width, \
+            n_experts, top_k, norm_topk, status);                                                                     \
     } while (0)
-    if (h_is_bf16 && w_is_bf16) ESP_ROUTER(bf16, bf16);
-    else if (h_is_bf16) ESP_ROUTER(bf16, float);
-    else if (w_is_bf16) ESP_ROUTER(float, bf16);
-    else ESP_ROUTER(float, float);
+#define ESP_ROUTER_T(TH, TW) do { if (tpb == 4) ESP_ROUTER(TH, TW, 4); else ESP_ROUTER(TH, TW, 1); } while (0)
+    if (h_is_bf16 && w_is_bf16) ESP_ROUTER_T(bf16, bf16);
+    else if (h_is_bf16) ESP_ROUTER_T(bf16, float);
+    else if (w_is_bf16) ESP_ROUTER_T(float, bf16);
+    else ESP_ROUTER_T(float, float);
+#undef ESP_ROUTER_T
 #undef ESP_ROUTER
     return esp_launch_status();
 }

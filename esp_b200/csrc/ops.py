@@ -325,7 +325,7 @@ def gather_rows(src, rows, out):
            "gather_rows")
 
 
-TC05_TILE_ROWS = 256
+TC05_TILE_ROWS = 128
 
 
 def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None):

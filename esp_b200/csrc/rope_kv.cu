@@ -20,8 +20,8 @@ __global__ void rope_kvwrite_kernel(const float* __restrict__ qkv, const float* 
                                     const float* __restrict__ sin_t, int rot, int max_pos, T* __restrict__ q_out,
                                     T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ block_table,
                                     int table_stride, int n_pages, int page, int nh, int nkv, int hd, int write_kv,
-                                    int* __restrict__ status) {
-    const int n = blockIdx.x, head = blockIdx.y;
+                                    int heads_per_block, int* __restrict__ status) {
+    const int n = blockIdx.x;
     const int pos = tok_pos[n];
     const int seq = tok_seq[n];
     const int half = rot / 2;
@@ -42,9 +42,12 @@ __global__ void rope_kvwrite_kernel(const float* __restrict__ qkv, const float* 
         }
     }
     const int in_page = pos % page;
-    const float* x = src + (size_t)head * hd;
-    const float* b = bias ? bias + (size_t)head * hd : nullptr;
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    const int heads = nh + 2 * nkv;
+    const int head_lo = blockIdx.y * heads_per_block, head_hi = min(heads, head_lo + heads_per_block);
+    for (int idx = threadIdx.x; idx < (head_hi - head_lo) * hd; idx += blockDim.x) {
+        const int head = head_lo + idx / hd, i = idx % hd;
+        const float* x = src + (size_t)head * hd;
+        const float* b = bias ? bias + (size_t)head * hd : nullptr;
         float v = x[i] + (b ? b[i] : 0.f);
         if (head < nh + nkv && i < rot) {          // queries and keys rotate, values do not
             if (i < half) {
@@ -72,16 +75,19 @@ ESP_API int esp_rope_kvwrite(const float* qkv, const float* bias, const int* tok
                              int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rot < 0 || rot > hd || (rot & 1) || nh + 2 * nkv > 65535) return (int)cudaErrorInvalidValue;
-    const dim3 grid(n_tokens, nh + 2 * nkv);
-    const int threads = hd >= 128 ? 128 : (hd + 31) / 32 * 32;
+    // few tokens (decode): one head per block keeps every load in flight at once; many tokens: eight heads
+    // per block keep the number of blocks down
+    const int heads_per_block = n_tokens <= 64 ? 1 : 8;
+    const dim3 grid(n_tokens, (nh + 2 * nkv + heads_per_block - 1) / heads_per_block);
+    const int threads = heads_per_block == 1 ? (hd >= 128 ? 128 : (hd + 31) / 32 * 32) : 256;
     if (is_bf16)
         rope_kvwrite_kernel<bf16><<<grid, threads, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
                                                                (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, block_table,
-                                                               table_stride, n_pages, page, nh, nkv, hd, write_kv, status);
+                                                               table_stride, n_pages, page, nh, nkv, hd, write_kv, heads_per_block, status);
     else
         rope_kvwrite_kernel<float><<<grid, threads, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
                                                                 (float*)q_out, (float*)k_cache, (float*)v_cache,
                                                                 block_table, table_stride, n_pages, page, nh, nkv, hd,
-                                                                write_kv, status);
+                                                                write_kv, heads_per_block, status);
     return esp_launch_status();
 }
