@@ -279,3 +279,44 @@ ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_ca
 #undef ESP_HD
     return (int)cudaErrorInvalidValue;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same attention for callers that must not allocate (see attn_decode_noalloc.h).
+// ---------------------------------------------------------------------------------------------------
+#include "attn_decode_noalloc.h"
+
+// Scratch of the no-allocation entry point.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a pointer that a kernel may be given.
+static __device__ __align__(256) float esp_noalloc_scratch[ESP_ATTN_DECODE_NOALLOC_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* noalloc_scratch_of_device[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+extern "C" long long esp_attn_decode_noalloc_capacity(void) { return (long long)ESP_ATTN_DECODE_NOALLOC_FLOATS; }
+
+extern "C" int esp_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                       const int* tok_seq, const int* tok_pos, const int* block_table, int table_stride,
+                                       int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
+                                       int n_splits, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (nh <= 0 || hd <= 0 || n_splits <= 0) return (int)cudaErrorInvalidValue;
+    const unsigned long long need = (unsigned long long)n_tokens * nh * n_splits * (hd + 2);
+    if (need > ESP_ATTN_DECODE_NOALLOC_FLOATS) return ESP_NOALLOC_TOO_LARGE;
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= NOALLOC_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+    if (!noalloc_scratch_of_device[device]) {
+        // first call on this device: turn the symbol into the address that kernels can use
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, esp_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        noalloc_scratch_of_device[device] = ptr;
+    }
+    float* part_o = noalloc_scratch_of_device[device];
+    float* part_ml = part_o + (size_t)n_tokens * nh * n_splits * hd;
+    return esp_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, tok_seq, tok_pos, block_table, table_stride, n_pages,
+                           page, n_tokens, nh, nkv, hd, window, n_splits, status, stream);
+}
