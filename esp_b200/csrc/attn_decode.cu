@@ -27,7 +27,7 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 }
 
 template <int HD, int GT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 6)
 attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                   float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tok_seq,
                   const int* __restrict__ tok_pos, const int* __restrict__ block_table, int table_stride, int n_pages,

@@ -46,7 +46,10 @@ __device__ __forceinline__ uint4 load_stream(const bf16* p) {
     return __ldcs(reinterpret_cast<const uint4*>(p));
 }
 
-template <int NBLK, bool SWIGLU, typename TC>
+// KSPLIT = true: the block's 8 warps share one tile of weight rows and split K (few tiles: every SM still
+// gets work).  KSPLIT = false: each warp owns a tile of its own and walks all of K (many tiles: longer
+// streams per warp, no reduction between warps).
+template <int NBLK, bool SWIGLU, typename TC, bool KSPLIT>
 __global__ void __launch_bounds__(WARPS * 32, 3)
 gemm_skinny_kernel(SkinnyParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -68,13 +71,14 @@ gemm_skinny_kernel(SkinnyParams p) {
     // the two weight rows this lane streams
     int row_a, row_b;
     bool ok_a, ok_b;
+    const int tile = KSPLIT ? blockIdx.x : blockIdx.x * WARPS + warp;
     if (SWIGLU) {
-        const int j = blockIdx.x * 8 + g;
+        const int j = tile * 8 + g;
         ok_a = ok_b = j < p.N;
         row_a = j;
         row_b = p.N + j;
     } else {
-        row_a = blockIdx.x * 16 + g;
+        row_a = tile * 16 + g;
         row_b = row_a + 8;
         ok_a = row_a < p.N;
         ok_b = row_b < p.N;
@@ -84,8 +88,8 @@ gemm_skinny_kernel(SkinnyParams p) {
     // K slice of this warp, in whole groups of 32
     const int groups32 = (K + 31) / 32;
     const int per_warp = (groups32 + WARPS - 1) / WARPS;
-    const int k_lo = warp * per_warp * 32;
-    const int k_hi = min(K, (warp + 1) * per_warp * 32);
+    const int k_lo = KSPLIT ? warp * per_warp * 32 : 0;
+    const int k_hi = KSPLIT ? min(K, (warp + 1) * per_warp * 32) : K;
 
     for (int m0 = m_begin; m0 < m_end; m0 += 8 * NBLK) {
         const int cnt = min(8 * NBLK, m_end - m0);
@@ -132,6 +136,30 @@ gemm_skinny_kernel(SkinnyParams p) {
                 }
             }
         }
+        if constexpr (!KSPLIT) {
+            // this warp owns its tile: results go out straight from the accumulators
+#pragma unroll
+            for (int nb = 0; nb < NBLK; nb++) {
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int tok = nb * 8 + tg * 2 + i;
+                    if (tok >= cnt) continue;
+                    if (SWIGLU) {
+                        const int j = tile * 8 + g;
+                        if (j < p.N) {
+                            const float gate = acc[nb][i], up = acc[nb][2 + i];
+                            reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + j] =
+                                from_f32<TC>(gate / (1.0f + expf(-gate)) * up);
+                        }
+                    } else {
+                        const float scale = p.row_scale ? p.row_scale[m0 + tok] : 1.0f;
+                        const int n_lo = tile * 16 + g, n_hi = n_lo + 8;
+                        if (n_lo < p.N) reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n_lo] = from_f32<TC>(acc[nb][i] * scale);
+                        if (n_hi < p.N) reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n_hi] = from_f32<TC>(acc[nb][2 + i] * scale);
+                    }
+                }
+            }
+        } else {
         // partial sums of the 8 warps, added in warp order
 #pragma unroll
         for (int nb = 0; nb < NBLK; nb++)
@@ -166,24 +194,33 @@ gemm_skinny_kernel(SkinnyParams p) {
                 }
             }
         }
+        }
     }
 }
 
-template <int NBLK, bool SWIGLU, typename TC>
-int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
+template <int NBLK, bool SWIGLU, typename TC, bool KSPLIT>
+int launch_variant(const SkinnyParams& p, int groups, int tiles, cudaStream_t stream) {
     const size_t smem = (size_t)8 * NBLK * (p.K + 32) * sizeof(bf16) + (size_t)WARPS * NBLK * 32 * 4 * sizeof(float);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
     static bool raised = false;        // per instantiation
     if (smem > 48 * 1024 && !raised) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NBLK, SWIGLU, TC>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NBLK, SWIGLU, TC, KSPLIT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    const int tiles = SWIGLU ? (p.N + 7) / 8 : (p.N + 15) / 16;
-    dim3 grid(tiles, groups);
-    gemm_skinny_kernel<NBLK, SWIGLU, TC><<<grid, WARPS * 32, smem, stream>>>(p);
+    dim3 grid(KSPLIT ? tiles : (tiles + WARPS - 1) / WARPS, groups);
+    gemm_skinny_kernel<NBLK, SWIGLU, TC, KSPLIT><<<grid, WARPS * 32, smem, stream>>>(p);
     return esp_launch_status();
+}
+
+template <int NBLK, bool SWIGLU, typename TC>
+int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
+    const int tiles = SWIGLU ? (p.N + 7) / 8 : (p.N + 15) / 16;
+    // enough tiles to give every warp of every SM one of its own: no need to split K
+    const long long spread = (long long)tiles * (p.group_offsets ? (groups < p.M ? groups : p.M) : 1);
+    if (spread >= 148 * 8) return launch_variant<NBLK, SWIGLU, TC, false>(p, groups, tiles, stream);
+    return launch_variant<NBLK, SWIGLU, TC, true>(p, groups, tiles, stream);
 }
 }  // namespace
 

@@ -410,6 +410,36 @@ def test_gemm_skinny_dense(m, n, k):
     assert torch.equal(c1[0], c[m - 1])
 
 
+def test_gemm_skinny_many_tiles_one_tile_per_warp():
+    """With enough tiles of weight rows each warp takes a tile of its own and walks all of K: dense,
+    fused SwiGLU and grouped with a ragged last tile."""
+    m, n, k = 5, 19001, 72
+    a, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1)
+    scale = rnd(m, seed=2)
+    c = torch.empty(m, n, device=DEV)
+    ops.gemm_skinny(a, w, c, row_scale=scale)
+    close(c, (a.double() @ w.double().t()) * scale.double()[:, None], torch.float32, "one tile per warp, dense", k=k)
+    inter = 9500
+    w2 = rnd(2 * inter, k, dtype=torch.bfloat16, seed=3, scale=0.3)
+    act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(a, w2, act, swiglu=True)
+    g, u = a.double() @ w2[:inter].double().t(), a.double() @ w2[inter:].double().t()
+    close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "one tile per warp, swiglu")
+    groups, n3 = 40, 500
+    counts = [(3 * i) % 5 for i in range(groups)]
+    offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+    total = sum(counts)
+    a3 = rnd(total, k, dtype=torch.bfloat16, seed=4)
+    w3 = rnd(groups, n3, k, dtype=torch.bfloat16, seed=5)
+    c3 = torch.empty(total, n3, device=DEV)
+    ops.gemm_skinny(a3, w3, c3, group_offsets=offsets, rows=total, max_rows=4)
+    row = 0
+    for e, cnt in enumerate(counts):
+        if cnt:
+            close(c3[row:row + cnt], a3[row:row + cnt].double() @ w3[e].double().t(), torch.float32, f"group {e}", k=k)
+        row += cnt
+
+
 @pytest.mark.parametrize("m, inter, k", [(3, 44, 96), (16, 100, 2048), (9, 8, 64)])
 def test_gemm_skinny_swiglu(m, inter, k):
     a, w = rnd(m, k, dtype=torch.bfloat16), rnd(2 * inter, k, dtype=torch.bfloat16, seed=1, scale=0.2)
