@@ -14,7 +14,6 @@
 #include "common.cuh"
 
 namespace {
-constexpr int SPLIT = 256;
 constexpr int THREADS = 128;
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -26,7 +25,7 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     }
 }
 
-template <int HD, int GT>
+template <int HD, int GT, int SPLIT>
 __global__ void __launch_bounds__(THREADS, 6)
 attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                   float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tok_seq,
@@ -196,7 +195,7 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
 template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, const int* __restrict__ tok_pos, int nh, int window,
-                                    int n_splits) {
+                                    int n_splits, int SPLIT) {
     const int n = blockIdx.x, h = blockIdx.y;
     const int pos = tok_pos[n];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -217,7 +216,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     }
 }
 
-template <int HD, int GT>
+template <int HD, int GT, int SPLIT>
 int launch_split(const bf16* q, const bf16* k, const bf16* v, float* po, float* pml, const int* tok_seq,
                  const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
                  int window, int n_splits, int* status, cudaStream_t stream) {
@@ -225,25 +224,28 @@ int launch_split(const bf16* q, const bf16* k, const bf16* v, float* po, float* 
     const size_t dyn = (size_t)KG * GT * HD * sizeof(float);
     static bool raised = false;        // static + dynamic shared memory can pass 48 KB: always opt in
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<HD, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<HD, GT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)dyn);
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + GT - 1) / GT), n_splits);
-    attn_split_kernel<HD, GT><<<grid, THREADS, dyn, stream>>>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages,
+    attn_split_kernel<HD, GT, SPLIT><<<grid, THREADS, dyn, stream>>>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages,
                                                               page, nh, nkv, window, n_splits, status);
     return esp_launch_status();
 }
 
 template <int HD>
-int dispatch(int gt, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, const int* tok_seq,
+int dispatch(int gt, int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, const int* tok_seq,
              const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
              int window, int n_splits, int* status, cudaStream_t stream) {
     int rc;
-#define ESP_SPLIT(GT) launch_split<HD, GT>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
-                                            nh, nkv, window, n_splits, status, stream)
+#define ESP_SPLIT(GT)                                                                                                  \
+    (split == 256 ? launch_split<HD, GT, 256>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
+                                              nh, nkv, window, n_splits, status, stream)                                 \
+                  : launch_split<HD, GT, 512>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
+                                              nh, nkv, window, n_splits, status, stream))
     if (gt == 1) rc = ESP_SPLIT(1);
     else if (gt == 2) rc = ESP_SPLIT(2);
     else if (gt == 4) rc = ESP_SPLIT(4);
@@ -251,23 +253,25 @@ int dispatch(int gt, const bf16* q, const bf16* k, const bf16* v, bf16* out, flo
 #undef ESP_SPLIT
     if (rc != 0) return rc;
     dim3 grid(n_tokens, nh);
-    attn_combine_kernel<HD><<<grid, HD / 2 < 32 ? 32 : HD / 2, 0, stream>>>(po, pml, out, tok_pos, nh, window, n_splits);
+    attn_combine_kernel<HD><<<grid, HD / 2 < 32 ? 32 : HD / 2, 0, stream>>>(po, pml, out, tok_pos, nh, window, n_splits, split);
     return esp_launch_status();
 }
 }  // namespace
 
 // Scratch: part_o float [n_tokens, nh, n_splits, hd], part_ml float [n_tokens, nh, n_splits, 2];
-// n_splits >= ceil(longest sequence / 256).  Head sizes 64, 128, 192, 256; pages of 64 positions or any
+// split: key positions per block, 256 or 512 (the caller picks: short splits when there are few rows, so
+// that every SM still gets blocks); n_splits >= ceil(longest sequence / split).  Head sizes 64, 128, 192, 256; pages of 64 positions or any
 // size; any head counts with nh % nkv == 0.
 ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,
                             float* part_ml, const int* tok_seq, const int* tok_pos, const int* block_table,
                             int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
-                            int n_splits, int* status, cudaStream_t stream) {
+                            int split, int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535) return (int)cudaErrorInvalidValue;
+    if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || (split != 256 && split != 512))
+        return (int)cudaErrorInvalidValue;
     const int group = nh / nkv;
     const int gt = group >= 8 ? 8 : group >= 3 ? 4 : group;      // 1, 2, 4 or 8 heads per block
-#define ESP_HD(HD) return dispatch<HD>(gt, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
+#define ESP_HD(HD) return dispatch<HD>(gt, split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
                                        part_ml, tok_seq, tok_pos, block_table, table_stride, n_pages, page, n_tokens, nh,   \
                                        nkv, window, n_splits, status, stream)
     switch (hd) {
@@ -299,7 +303,7 @@ extern "C" long long esp_attn_decode_noalloc_capacity(void) { return (long long)
 extern "C" int esp_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                        const int* tok_seq, const int* tok_pos, const int* block_table, int table_stride,
                                        int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
-                                       int n_splits, int* status, cudaStream_t stream) {
+                                       int split, int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (nh <= 0 || hd <= 0 || n_splits <= 0) return (int)cudaErrorInvalidValue;
     const unsigned long long need = (unsigned long long)n_tokens * nh * n_splits * (hd + 2);
@@ -318,5 +322,5 @@ extern "C" int esp_attn_decode_noalloc(const void* q, const void* k_cache, const
     float* part_o = noalloc_scratch_of_device[device];
     float* part_ml = part_o + (size_t)n_tokens * nh * n_splits * hd;
     return esp_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, tok_seq, tok_pos, block_table, table_stride, n_pages,
-                           page, n_tokens, nh, nkv, hd, window, n_splits, status, stream);
+                           page, n_tokens, nh, nkv, hd, window, split, n_splits, status, stream);
 }

@@ -37,7 +37,7 @@ extern "C" {
 __attribute__((visibility("default"))) int esp_attn_decode_noalloc(
     const void* q, const void* k_cache, const void* v_cache, void* out, const int* tok_seq, const int* tok_pos,
     const int* block_table, int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
-    int n_splits, int* status, cudaStream_t stream);
+    int split, int n_splits, int* status, cudaStream_t stream);
 
 // Number of floats of the built-in scratch (the limit that the call checks against).
 __attribute__((visibility("default"))) long long esp_attn_decode_noalloc_capacity(void);

@@ -116,8 +116,20 @@ def build_library(name: str, verbose: bool = True) -> Path:
                 _say(f"  {src} done ({done[0]}/{len(sources)}, {time.time() - t0:.0f} s)")
             return obj
 
-        with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
-            objs = list(pool.map(compile_one, sources))
+        stop = threading.Event()
+
+        def heartbeat():
+            while not stop.wait(10.0):
+                if verbose:
+                    _say(f"  still compiling '{name}' ({done[0]}/{len(sources)} files done, {time.time() - t0:.0f} s)")
+
+        beat = threading.Thread(target=heartbeat, daemon=True)
+        beat.start()
+        try:
+            with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
+                objs = list(pool.map(compile_one, sources))
+        finally:
+            stop.set()
         tmp = out_dir / f"libesp_b200_{name}.{os.getpid()}.tmp.so"
         cmd = [nvcc, "-shared", "-o", str(tmp), *[str(o) for o in objs], "-lcudart", "-lcuda"]
         proc = subprocess.run(cmd, capture_output=True, text=True)

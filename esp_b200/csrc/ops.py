@@ -36,7 +36,8 @@ _SIGNATURES = {
     "esp_gemm_skinny": [P, c_longlong, P, P, c_longlong, P, P, c_int, c_longlong, P, c_int, c_int, c_int, c_int, c_int,
                         c_int, P],
     "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
-    "esp_attn_decode": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_attn_decode": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P,
+                        P],
 }
 
 _bound: dict = {}
@@ -284,13 +285,19 @@ def gemm_skinny(a, w, c, swiglu=False, row_scale=None, a_rows=None, group_offset
     _check(code, "gemm_skinny")
 
 
-ATTN_DECODE_SPLIT = 256
+def attn_decode_split(n_rows: int, nkv_blocks: int, positions: int) -> int:
+    """Key positions per block: 256 while that still gives few blocks (so that every SM has work at
+    batch 1), 512 once there are plenty (fewer partial results to combine)."""
+    return 256 if n_rows * nkv_blocks * ((positions + 255) // 256) <= 1024 else 512
 
 
 def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, tok_seq, tok_pos, block_table, page, nh, nkv, hd, window,
-                n_splits, status):
-    """Split-key attention for few token rows (bfloat16; head sizes 64, 128, 192, 256).
-    part_o float32 [N, nh, n_splits, hd] and part_ml float32 [N, nh, n_splits, 2] are scratch."""
+                split, n_splits, status):
+    """Split-key attention for few token rows (bfloat16; head sizes 64, 128, 192, 256).  ``split``: key
+    positions per block (256 or 512); n_splits >= ceil(positions / split).  part_o float32
+    [N, nh, n_splits, hd] and part_ml float32 [N, nh, n_splits, 2] are scratch."""
+    if split not in (256, 512):
+        raise Backend(f"attn_decode: split {split} is not 256 or 512")
     if hd not in (64, 128, 192, 256):
         raise Backend(f"attn_decode: head size {hd} is not one of 64, 128, 192, 256")
     n = q.shape[0]
@@ -300,8 +307,8 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, tok_seq, tok_pos, blo
         _ptr(q, torch.bfloat16, "q"), _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
         _ptr(out, torch.bfloat16), _ptr(part_o, torch.float32), _ptr(part_ml, torch.float32),
         _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
-        k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), n_splits, _ptr(status, torch.int32), _stream()),
-        "attn_decode")
+        k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), split, n_splits, _ptr(status, torch.int32),
+        _stream()), "attn_decode")
 
 
 def attn_prefill(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,

@@ -106,11 +106,15 @@ class Attention(Part):
         n = q.shape[0]
         if rt.dtype == torch.bfloat16 and s.head_dim in (64, 128, 192, 256) and n <= DECODE_ROWS:
             # few rows: split the keys over blocks so that the cache streams at full width
-            n_splits = (table.shape[1] * layer.page + ops.ATTN_DECODE_SPLIT - 1) // ops.ATTN_DECODE_SPLIT
+            positions = table.shape[1] * layer.page
+            group = s.num_heads // s.num_kv_heads
+            kv_blocks = s.num_kv_heads * ((group + 7) // 8 if group >= 8 else (group + 3) // 4 if group >= 3 else 1)
+            split = ops.attn_decode_split(n, kv_blocks, positions)
+            n_splits = (positions + split - 1) // split
             part_o = rt.ws.get("attn_part_o", (n, s.num_heads, n_splits, s.head_dim), torch.float32)
             part_ml = rt.ws.get("attn_part_ml", (n, s.num_heads, n_splits, 2), torch.float32)
             ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, ctx.tok_seq, ctx.tok_pos, table, layer.page,
-                            s.num_heads, s.num_kv_heads, s.head_dim, s.window, n_splits, rt.status)
+                            s.num_heads, s.num_kv_heads, s.head_dim, s.window, split, n_splits, rt.status)
             return
         if rt.dtype == torch.bfloat16 and s.head_dim <= 128 and layer.page == 64:
             ops.attn_prefill(q, layer.k, layer.v, o, ctx.q_tile_seq, ctx.q_tile_first, ctx.seq_start, ctx.seq_past,

@@ -481,9 +481,10 @@ def test_gemm_skinny_grouped_gather_scale_and_chunks():
             row += 1
 
 
+@pytest.mark.parametrize("split", [256, 512])
 @pytest.mark.parametrize("nh, nkv, hd, window", [(4, 4, 128, None), (6, 2, 64, None), (7, 1, 128, 100), (8, 1, 192, None),
                                                  (4, 2, 256, 300), (16, 16, 128, 65)])
-def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window):
+def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window, split):
     """The split-key kernel on the same kind of made-up cache as the plain one:
     far keys, keys at the window's edges, at page and split boundaries, other
     sequences in interleaved pages."""
@@ -510,14 +511,14 @@ def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window):
     table = torch.tensor(tables, dtype=torch.int32, device=DEV)
     n = len(queries)
     out = torch.empty(n, nh * hd, dtype=dtype, device=DEV)
-    n_splits = 3
+    n_splits = (700 + split - 1) // split
     part_o = torch.full((n, nh, n_splits, hd), float("nan"), device=DEV)
     part_ml = torch.full((n, nh, n_splits, 2), float("nan"), device=DEV)
     st = status()
     ops.attn_decode(qd.reshape(n, nh * hd).to(DEV), kc, vc, out, part_o, part_ml,
                     torch.tensor([s for s, _, _ in queries], dtype=torch.int32, device=DEV),
                     torch.tensor([p for _, p, _ in queries], dtype=torch.int32, device=DEV), table, 64, nh, nkv, hd,
-                    window, n_splits, st)
+                    window, split, n_splits, st)
     assert st.item() == 0
     for i, (s, p, target) in enumerate(queries):
         ref = attention_reference(qd[i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(), p, window, group)

@@ -21,13 +21,14 @@ from esp_b200.csrc.build import load_library
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 TOO_LARGE = -2
+SPLIT = 256          # key positions per block; the entry point takes 256 or 512
 
 
 def bind():
     lib = load_library("bf16")
     fn = lib.esp_attn_decode_noalloc
     P, I = ctypes.c_void_p, ctypes.c_int
-    fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P]
+    fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P]
     fn.restype = I
     cap = lib.esp_attn_decode_noalloc_capacity
     cap.argtypes, cap.restype = [], ctypes.c_longlong
@@ -48,7 +49,7 @@ def case(seed, n_seq, nh, nkv, hd, max_len, window):
     lens[0] = max_len
     pos = (lens - 1).to(torch.int32).to(DEV)
     seq = torch.arange(n_seq, dtype=torch.int32, device=DEV)
-    n_splits = (pages_per_seq * 64 + ops.ATTN_DECODE_SPLIT - 1) // ops.ATTN_DECODE_SPLIT
+    n_splits = (pages_per_seq * 64 + SPLIT - 1) // SPLIT
     return q, k, v, seq, pos, table, n_splits, (nh, nkv, hd, window)
 
 
@@ -59,10 +60,10 @@ def run_both(fn, c):
     ref = torch.empty(n, nh * hd, dtype=torch.bfloat16, device=DEV)
     part_o = torch.empty(n, nh, n_splits, hd, device=DEV)
     part_ml = torch.empty(n, nh, n_splits, 2, device=DEV)
-    ops.attn_decode(q, k, v, ref, part_o, part_ml, seq, pos, table, 64, nh, nkv, hd, window, n_splits, status)
+    ops.attn_decode(q, k, v, ref, part_o, part_ml, seq, pos, table, 64, nh, nkv, hd, window, SPLIT, n_splits, status)
     out = torch.full_like(ref, float("nan"))
     rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), seq.data_ptr(), pos.data_ptr(), table.data_ptr(),
-            table.shape[1], k.shape[0], 64, n, nh, nkv, hd, window or 0, n_splits, status.data_ptr(),
+            table.shape[1], k.shape[0], 64, n, nh, nkv, hd, window or 0, SPLIT, n_splits, status.data_ptr(),
             torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert rc == 0, f"esp_attn_decode_noalloc returned {rc}"
@@ -90,7 +91,7 @@ def test_a_request_beyond_the_built_in_scratch_is_refused():
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     big_splits = cap() // (2 * nh * (hd + 2)) + 1
     rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), seq.data_ptr(), pos.data_ptr(), table.data_ptr(),
-            table.shape[1], k.shape[0], 64, 2, nh, nkv, hd, 0, int(big_splits), status.data_ptr(),
+            table.shape[1], k.shape[0], 64, 2, nh, nkv, hd, 0, SPLIT, int(big_splits), status.data_ptr(),
             torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert rc == TOO_LARGE
