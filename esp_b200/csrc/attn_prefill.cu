@@ -60,7 +60,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
     bf16* k_s = q_s + BM * LDS;                                        // [2][BN][LDS]
     bf16* v_s = k_s + 2 * BN * LDS;                                    // [2][BN][LDS]
 
-    const int tile = blockIdx.x, h = blockIdx.y;
+    // tiles are listed in order of position; the last ones see the most keys, so they start first
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
     const int seq = tile_seq[tile], first = tile_first[tile];          // first: index of the tile's first token in its sequence's new tokens
     const int row0 = seq_start[seq] + first;                           // its row among the packed tokens
     const int n_new = seq_start[seq + 1] - seq_start[seq];

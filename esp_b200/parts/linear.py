@@ -19,8 +19,9 @@ import os
 
 SKINNY_ROWS = 16            # dense products with at most this many rows stream the weights once
 TC05_GROUPED_ROWS = 512     # grouped products with at least this many (token, expert) rows use TMA + tcgen05
-# dense products with many rows: "own" = this library's TMA + tcgen05 kernel, "library" = cuBLAS through torch
-DENSE_GEMM = os.environ.get("ESP_B200_DENSE_GEMM", "own")
+# dense products with many rows: "own" = this library's TMA + tcgen05 kernel everywhere; "library" = cuBLAS
+# through torch; "mixed" = cuBLAS for plain products, this library's kernel where SwiGLU is fused into it
+DENSE_GEMM = os.environ.get("ESP_B200_DENSE_GEMM", "mixed")
 
 
 def _both_bf16(a, w) -> bool:
@@ -49,7 +50,7 @@ def swiglu_linear(rt, a, w_gate_up, act, tag):
     if _both_bf16(a, w_gate_up) and n <= SKINNY_ROWS and ops.skinny_fits(a.shape[1]):
         ops.gemm_skinny(a, w_gate_up, act, swiglu=True)
         return act
-    if _both_bf16(a, w_gate_up) and DENSE_GEMM == "own" and a.shape[1] % 8 == 0 and a.is_contiguous() and act.is_contiguous():
+    if _both_bf16(a, w_gate_up) and DENSE_GEMM in ("own", "mixed") and a.shape[1] % 8 == 0 and a.is_contiguous() and act.is_contiguous():
         ops.gemm_tc05(a, w_gate_up, act, rt.status, swiglu=True)
         return act
     gu = rt.ws.get(tag + "_gu", (n, 2 * inter), torch.float32)
