@@ -142,6 +142,118 @@ router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, co
     }
 }
 
+// ---- few tokens (decode): logits spread over many blocks, then one block routes and permutes --------
+// logits[n, e] = dot(h[n], w_router[e]) for e < E and dot(h[n], w_gate) at e = E: one warp per (token,
+// expert), eight experts per block, so that a step of a handful of tokens still fills the machine.
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, const TW* __restrict__ w_gate,
+                     float* __restrict__ logits, int width, int n_experts) {
+    extern __shared__ float hs[];
+    const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rows = n_experts + (w_gate ? 1 : 0);
+    for (int i = tid; i < width; i += 256) hs[i] = to_f32(h[(size_t)n * width + i]);
+    __syncthreads();
+    const int e = blockIdx.y * 8 + warp;
+    if (e >= rows) return;
+    const TW* wr = e < n_experts ? w_router + (size_t)e * width : w_gate;
+    float s[1];
+    lane_dots<1>(hs, width, wr, width, lane, s);
+    const float v = warp_sum(s[0]);
+    if (lane == 0) logits[(size_t)n * (n_experts + 1) + e] = v;
+}
+
+// One block: a warp per token turns its logits into probabilities, picks the top k (ties to the lower
+// id) and the routing weights; then the whole block builds the permutation as moe_permute_kernel does.
+__global__ void __launch_bounds__(256)
+route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids, float* __restrict__ topk_w,
+                   float* __restrict__ gate, float* __restrict__ probs_out, int n_tokens, int n_experts, int top_k,
+                   int norm_topk, int has_gate, int* __restrict__ offsets, int* __restrict__ perm_token,
+                   float* __restrict__ perm_weight, int* __restrict__ inverse, int* __restrict__ status) {
+    extern __shared__ float sm_f[];
+    float* ps_all = sm_f;                                      // [8 warps][n_experts]
+    int* counts = reinterpret_cast<int*>(sm_f + 8 * n_experts); // [n_experts]
+    int* cursor = counts + n_experts;                           // [n_experts + 1]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < n_experts; e += 256) counts[e] = 0;
+    __syncthreads();
+    float* ps = ps_all + warp * n_experts;
+    for (int n = warp; n < n_tokens; n += 8) {
+        const float* lg = logits + (size_t)n * (n_experts + 1);
+        float mx = -INFINITY;
+        for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float p = expf(lg[e] - mx);
+            ps[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < n_experts; e += 32) {
+            const float p = ps[e] / sum;
+            ps[e] = p;
+            if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
+        }
+        if (lane == 0 && has_gate) gate[n] = 1.0f / (1.0f + expf(-lg[n_experts]));
+        __syncwarp();
+        bool bad = false;
+        float mass = 0.f, my_p = 0.f;
+        int my_e = 0;
+        for (int r = 0; r < top_k; r++) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+            for (int e = lane; e < n_experts; e += 32) {
+                const float p = ps[e];
+                if (!(p == p) || isinf(p)) bad = true;
+                if (p > best) { best = p; best_e = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+            }
+            if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
+            if (lane == 0) ps[best_e] = -1.0f;
+            if (lane == r) { my_p = best; my_e = best_e; }       // top_k <= 32: rank r is kept by lane r
+            mass += best;
+            __syncwarp();
+        }
+        const float denom = norm_topk ? mass : 1.0f;
+        if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
+            if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
+        }
+        if (lane < top_k) {
+            topk_ids[(size_t)n * top_k + lane] = my_e;
+            topk_w[(size_t)n * top_k + lane] = my_p / denom;
+            atomicAdd(&counts[my_e], 1);
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int e = 0; e < n_experts; e++) {
+            cursor[e] = run;
+            offsets[e] = run;
+            run += counts[e];
+        }
+        cursor[n_experts] = run;
+        offsets[n_experts] = run;
+    }
+    __syncthreads();
+    const int n_pairs = n_tokens * top_k;
+    for (int i = tid; i < n_pairs; i += 256) {
+        const int e = topk_ids[i];                                // written above by this block
+        const int row = atomicAdd(&cursor[e], 1);
+        perm_token[row] = i / top_k;
+        perm_weight[row] = topk_w[i];
+        inverse[i] = row;
+    }
+}
+
 // One block.  counts -> exclusive offsets -> placement of every (token, rank)
 // pair into its expert's range.  Which row of its expert's range a pair lands
 // in is left to the atomics; a row's arithmetic never depends on where it sits.
@@ -253,6 +365,32 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
     else ESP_ROUTER_T(float, float);
 #undef ESP_ROUTER_T
 #undef ESP_ROUTER
+    return esp_launch_status();
+}
+
+// Router and permutation for a step of few tokens (at most 32) in two launches.  ``logits`` is scratch
+// [n_tokens, n_experts + 1] float.
+ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, const void* w_gate, int w_is_bf16,
+                            float* logits, int* topk_ids, float* topk_w, float* gate, float* probs_out, int n_tokens,
+                            int width, int n_experts, int top_k, int norm_topk, int* offsets, int* perm_token,
+                            float* perm_weight, int* inverse, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts || n_tokens > 32) return (int)cudaErrorInvalidValue;
+    const size_t smem_a = (size_t)width * sizeof(float);
+    const size_t smem_b = (size_t)(8 * n_experts) * sizeof(float) + (size_t)(2 * n_experts + 1) * sizeof(int);
+    if (smem_a > 48 * 1024 || smem_b > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const dim3 grid(n_tokens, (n_experts + 1 + 7) / 8);
+#define ESP_LOGITS(TH, TW)                                                                                        \
+    router_logits_kernel<TH, TW><<<grid, 256, smem_a, stream>>>((const TH*)h, (const TW*)w_router, (const TW*)w_gate, \
+                                                                logits, width, n_experts)
+    if (h_is_bf16 && w_is_bf16) ESP_LOGITS(bf16, bf16);
+    else if (h_is_bf16) ESP_LOGITS(bf16, float);
+    else if (w_is_bf16) ESP_LOGITS(float, bf16);
+    else ESP_LOGITS(float, float);
+#undef ESP_LOGITS
+    route_small_kernel<<<1, 256, smem_b, stream>>>(logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k,
+                                                   norm_topk, w_gate ? 1 : 0, offsets, perm_token, perm_weight, inverse,
+                                                   status);
     return esp_launch_status();
 }
 

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
+    "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P],
     "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
@@ -211,6 +212,29 @@ def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, s
         _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32), _ptr(gate, torch.float32),
         _ptr(probs_out, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
         _ptr(status, torch.int32), _stream()), "router_topk")
+
+
+ROUTE_SMALL_TOKENS = 32
+
+
+def route_small_fits(width: int, n_experts: int) -> bool:
+    return width * 4 <= 48 * 1024 and (8 * n_experts) * 4 + (2 * n_experts + 1) * 4 <= 48 * 1024
+
+
+def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm_topk, offsets, perm_token,
+                perm_weight, inverse, status, probs_out=None):
+    """Router and permutation for at most ROUTE_SMALL_TOKENS tokens: logits over many blocks, then one
+    block for softmax, top-k and the permutation.  ``logits``: float32 scratch [N, E + 1]."""
+    n, width = h.shape
+    n_experts = w_router.shape[0]
+    if n > ROUTE_SMALL_TOKENS or top_k > 32 or not route_small_fits(width, n_experts):
+        raise Backend("route_small: too many tokens or experts for this kernel")
+    _check(_fn("core", "esp_route_small")(
+        _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(w_router, FLOATS), _ptr(w_gate, FLOATS), _is_bf16(w_router),
+        _ptr(logits, torch.float32), _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32),
+        _ptr(gate, torch.float32), _ptr(probs_out, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
+        _ptr(offsets, torch.int32), _ptr(perm_token, torch.int32), _ptr(perm_weight, torch.float32),
+        _ptr(inverse, torch.int32), _ptr(status, torch.int32), _stream()), "route_small")
 
 
 def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, inverse, status, tiles=None):

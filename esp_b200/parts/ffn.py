@@ -130,19 +130,27 @@ class MoeSwiGluShared(Part):
         probs = None
         if rt.record_routing:
             probs = torch.empty((n, E), dtype=torch.float32, device=rt.device)
-        ops.router_topk(router_in, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status, probs)
-        if rt.record_routing:
-            ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
         offsets = ws.get("moe_offsets", (E + 1,), torch.int32)
         perm_token = ws.get("moe_perm_token", (n * k,), torch.int32)
         perm_weight = ws.get("moe_perm_weight", (n * k,), torch.float32)
         inverse = ws.get("moe_inverse", (n, k), torch.int32)
         tiles = None
-        if grouped_uses_tc05(h, self.w_gate_up, n * k) and Im % 8 == 0:
-            max_tiles = (n * k + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
-            tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32), ws.get("moe_tile_row0", (max_tiles,), torch.int32),
-                     ws.get("moe_tile_count", (max_tiles,), torch.int32), ws.get("moe_n_tiles", (1,), torch.int32))
-        ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles)
+        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E):
+            # few tokens: router and permutation in two short launches
+            logits = ws.get("moe_logits", (n, E + 1), torch.float32)
+            ops.route_small(router_in, self.w_router, self.w_shared_gate, logits, ids, wts, gate, k, s.norm_topk,
+                            offsets, perm_token, perm_weight, inverse, rt.status, probs)
+        else:
+            ops.router_topk(router_in, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status,
+                            probs)
+            if grouped_uses_tc05(h, self.w_gate_up, n * k) and Im % 8 == 0:
+                max_tiles = (n * k + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
+                tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32),
+                         ws.get("moe_tile_row0", (max_tiles,), torch.int32),
+                         ws.get("moe_tile_count", (max_tiles,), torch.int32), ws.get("moe_n_tiles", (1,), torch.int32))
+            ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles)
+        if rt.record_routing:
+            ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
         expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
         shared = ws.get("moe_shared_out", (n, H), torch.float32)
         _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")

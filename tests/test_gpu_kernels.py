@@ -250,6 +250,39 @@ def test_router_topk(h_dt, w_dt, norm):
         close(wts[t], chosen / chosen.sum() if norm else chosen, torch.float32, "weights")
 
 
+@pytest.mark.parametrize("w_dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n, e, k, norm", [(1, 10, 3, False), (8, 60, 4, False), (32, 7, 7, True), (13, 64, 8, True)])
+def test_route_small_equals_router_and_permutation(w_dt, n, e, k, norm):
+    """The two-launch path for few tokens gives what router_topk + moe_permute give."""
+    width = 200
+    h = rnd(n, width)
+    wr = rnd(e, width, dtype=w_dt, seed=1, scale=0.3)
+    if e > 7:
+        wr[7] = wr[2]
+    wg = rnd(1, width, dtype=w_dt, seed=2, scale=0.3)
+    i32 = lambda *shape: torch.empty(*shape, dtype=torch.int32, device=DEV)
+    f32 = lambda *shape: torch.empty(*shape, device=DEV)
+    ids_a, w_a, gate_a, probs_a, st = i32(n, k), f32(n, k), f32(n), f32(n, e), status()
+    ops.router_topk(h, wr, wg, ids_a, w_a, gate_a, k, norm, st, probs_a)
+    ids_b, w_b, gate_b, probs_b = i32(n, k), f32(n, k), f32(n), f32(n, e)
+    offsets, perm_token, perm_weight, inverse = i32(e + 1), i32(n * k), f32(n * k), i32(n, k)
+    ops.route_small(h, wr, wg, f32(n, e + 1), ids_b, w_b, gate_b, k, norm, offsets, perm_token, perm_weight, inverse, st,
+                    probs_b)
+    assert st.item() == 0
+    assert torch.equal(ids_a, ids_b)
+    close(w_b, w_a, torch.float32, "routing weights")
+    close(gate_b, gate_a, torch.float32, "shared gate")
+    close(probs_b, probs_a, torch.float32, "probabilities")
+    ids_np, off = ids_b.cpu().numpy(), offsets.cpu().numpy()
+    assert list(off) == list(np.concatenate([[0], np.cumsum(np.bincount(ids_np.reshape(-1), minlength=e))]))
+    inv, pt, pw = inverse.cpu().numpy(), perm_token.cpu().numpy(), perm_weight.cpu().numpy()
+    assert sorted(inv.reshape(-1)) == list(range(n * k))
+    for t in range(n):
+        for r in range(k):
+            row = inv[t, r]
+            assert off[ids_np[t, r]] <= row < off[ids_np[t, r] + 1] and pt[row] == t and pw[row] == w_b[t, r].item()
+
+
 def test_moe_permute_and_combine():
     n, k, e, width = 37, 3, 6, 50
     rng = np.random.default_rng(0)
