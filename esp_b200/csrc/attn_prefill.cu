@@ -47,7 +47,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 template <int HDB>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 3)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                     bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_first,
                     const int* __restrict__ seq_start, const int* __restrict__ seq_past,
@@ -56,9 +56,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
     constexpr int LDS = HDB + 8;                     // row stride in elements: 16 bytes of padding against bank conflicts
     constexpr int PIECES = HDB / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                    // [BM][LDS]
-    bf16* k_s = q_s + BM * LDS;                                        // [2][BN][LDS]
+    bf16* k_s = reinterpret_cast<bf16*>(smem_raw);                    // [2][BN][LDS]
     bf16* v_s = k_s + 2 * BN * LDS;                                    // [2][BN][LDS]
+    bf16* q_s = k_s + BN * LDS;                                        // [BM][LDS]: the tile's queries borrow the second
+                                                                       // key buffer until their fragments are in registers
 
     // tiles are listed in order of position; the last ones see the most keys, so they start first
     const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
@@ -111,6 +112,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
 #pragma unroll
     for (int kk = 0; kk < HDB / 16; kk++)
         ldmatrix_x4(qf[kk], q_s + (warp * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
+    __syncthreads();                                                   // the borrowed buffer may now be refilled with keys
 
     float o[HDB / 8][4];
 #pragma unroll
@@ -240,7 +242,8 @@ template <int HDB>
 int launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* tile_seq, const int* tile_first,
            const int* seq_start, const int* seq_past, const int* table, int stride, int n_pages, int n_tiles, int nh,
            int nkv, int hd, int window, int* status, cudaStream_t stream) {
-    const size_t smem = (size_t)(BM + 4 * BN) * (HDB + 8) * sizeof(bf16);
+    static_assert(BM <= BN, "the queries borrow a key buffer");
+    const size_t smem = (size_t)(4 * BN) * (HDB + 8) * sizeof(bf16);
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HDB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
