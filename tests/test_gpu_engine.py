@@ -13,7 +13,7 @@ from tiny import CASES, make_folder, random_ids
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [100, 45, 70, 33, 128, 7], "B": [200, 40, 130, 65, 256, 1]}
+LENGTHS = {"A": [100, 45, 70, 33, 128, 7], "B": [200, 40, 130, 65, 256, 1], "C": [150, 40, 90, 33, 160, 2]}
 
 
 @pytest.fixture(scope="module")
@@ -29,7 +29,7 @@ def requests_for(case, seed=0):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 def test_each_request_alone_and_whole(folders, case, dtype):
     eng = engine_for(folders[case], dtype)
     reqs = requests_for(case)
@@ -39,7 +39,7 @@ def test_each_request_alone_and_whole(folders, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 def test_last_32_tokens_one_by_one(folders, case, dtype):
     eng = engine_for(folders[case], dtype)
     reqs = requests_for(case)
@@ -49,11 +49,11 @@ def test_last_32_tokens_one_by_one(folders, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 def test_unequal_batches_one_after_another(folders, case, dtype):
     # a cache just large enough for one batch, so that the second batch can only
     # run in the slots and pages that the first one gave back
-    eng = engine_for(folders[case], dtype, max_tokens=3 * 256 if case == "B" else 3 * 128)
+    eng = engine_for(folders[case], dtype, max_tokens={"A": 3 * 128, "B": 3 * 256, "C": 3 * 192}[case])
     reqs = requests_for(case)
     prompt_lens = {rid: max(1, len(t) - d) for (rid, t), d in zip(reqs.items(), [32, 5, 50, 32, 1, 0])}
     batches = [["r0", "r1", "r5"], ["r2", "r3", "r4"]]

@@ -31,7 +31,20 @@ TINY_B = {
 INIT_B = dict(weight_std=0.05, bias_std=0.0, norm_std=0.0)
 PROMPTS_B = (1, 7, 23, 40)
 
-CASES = {"A": (TINY_A, INIT_A), "B": (TINY_B, INIT_B)}
+# Sizes that fit none of the fast kernels' alignments: a width that is no multiple of 8, five heads whose
+# size times count differs from the width, an odd vocabulary, intermediate sizes that are multiples of 4 only.
+TINY_C = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "hidden_act": "silu",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 24,
+    "vocab_size": 301, "rope_theta": 50000.0, "rms_norm_eps": 2e-6, "max_position_embeddings": 160,
+    "intermediate_size": 44, "num_experts": 5, "num_experts_per_tok": 2, "norm_topk_prob": True,
+    "moe_intermediate_size": 20, "shared_expert_intermediate_size": 36, "decoder_sparse_step": 1,
+    "mlp_only_layers": [1], "use_sliding_window": True, "sliding_window": 70, "max_window_layers": 0,
+    "tie_word_embeddings": False,
+}
+INIT_C = dict(weight_std=0.04, bias_std=0.03, norm_std=0.02)
+
+CASES = {"A": (TINY_A, INIT_A), "B": (TINY_B, INIT_B), "C": (TINY_C, INIT_C)}
 
 
 def make_folder(tmp: Path, case: str, seed: int = 1234, store: str = "bfloat16", **overrides) -> Path:
