@@ -126,12 +126,14 @@ class Runtime:
         self.dtype = dtype
         self.shared_parts: dict = {}
         self.device = None
+        self.side_stream = None
         if device is not None:
             self.device = torch.device(device)
             if self.device.type != "cuda":
                 raise Backend("esp_b200 runs on a CUDA device only; there is no CPU path")
             self.ws = Workspace(self.device)
             self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.side_stream = torch.cuda.Stream(device=self.device)     # for work that may run beside the main stream
         self.ffn_chunk_tokens = ffn_chunk_tokens
         self.record_routing = False       # debugging aid: MoE parts put their choices into ctx.aux
 

@@ -9,6 +9,9 @@ from .base import ParamSpec, Part, register
 from .linear import grouped_linear, grouped_swiglu_linear, grouped_uses_tc05, linear, swiglu_linear
 
 
+SIDE_STREAM_ROWS = 64      # steps with at most this many rows run the shared expert on a second stream
+
+
 def _swiglu_mlp(rt, h, w_gate_up, w_down, out, tag):
     """out = down(silu(gate h) * (up h)); w_gate_up is [2I, H], gate rows first."""
     n = h.shape[0]
@@ -151,9 +154,19 @@ class MoeSwiGluShared(Part):
             ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles)
         if rt.record_routing:
             ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
-        expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
         shared = ws.get("moe_shared_out", (n, H), torch.float32)
-        _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
+        if n <= SIDE_STREAM_ROWS and rt.side_stream is not None:
+            # few rows: the shared expert does not depend on the routing, so it runs beside the routed
+            # experts on a second stream (in a captured step: a parallel branch of the graph)
+            main = torch.cuda.current_stream()
+            rt.side_stream.wait_stream(main)
+            with torch.cuda.stream(rt.side_stream):
+                _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
+            expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
+            main.wait_stream(rt.side_stream)
+        else:
+            expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
+            _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
         ops.moe_combine(expert_out, ids, inverse, gate, shared, y)
 
     def experts(self, h, offsets, perm_token, perm_weight, rows, max_rows, tiles=None):
