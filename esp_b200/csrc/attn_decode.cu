@@ -1,9 +1,9 @@
-// Decode attention over the paged bfloat16 cache, split over the keys.
+// Decode attention over the paged bfloat16 cache (pages of 64 positions), split over the keys.
 //
 // One block = one token row, one key/value head (with up to GT of the query
 // heads that share it) and one split of SPLIT consecutive key positions
-// aligned to absolute multiples of SPLIT.  The block reads its keys and values
-// once from HBM in 16-byte pieces, keeps scores, softmax and sums in float, and
+// aligned to absolute multiples of SPLIT.  The block streams its pages' keys and
+// values once from HBM with bulk copies, keeps scores, softmax and sums in float, and
 // writes an unnormalised partial result (running maximum, sum, weighted
 // values) to scratch.  A second kernel combines a row's splits in ascending
 // order.  Which splits a row has depends on its position (and window) alone,
@@ -25,22 +25,63 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     }
 }
 
+// ---- bulk-copy helpers (one thread issues, an mbarrier counts the bytes) -----------------------------
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+// Bounded wait for the phase with the given parity; false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
+    const unsigned addr = smem_addr(bar);
+    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, void* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+
+// One block = one token row, one key/value head (with up to GT query heads) and one split of SPLIT key
+// positions, i.e. SPLIT / 64 pages.  The pages' keys and values (64 x HD each, contiguous in the cache)
+// are fetched by bulk copies into a ring of RING shared-memory buffers while earlier pages are being
+// used: scores, a running maximum and sum (updated page by page) and the weighted values, all in
+// float.  Pages are walked in ascending order, so a row's arithmetic depends on its position alone.
+constexpr int PAGE_KEYS = 64, RING = 2;
+
 template <int HD, int GT, int SPLIT>
-__global__ void __launch_bounds__(THREADS, 6)
+__global__ void __launch_bounds__(THREADS)
 attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                   float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tok_seq,
                   const int* __restrict__ tok_pos, const int* __restrict__ block_table, int table_stride, int n_pages,
                   int page, int nh, int nkv, int window, int n_splits, int* __restrict__ status) {
     constexpr int PIECES = HD / 8;                 // 16-byte pieces of a key or value row
-    constexpr int PER_LANE = HD / 64;              // pieces each of the 8 lanes of a key group loads
+    constexpr int PER_LANE = HD / 64;              // pieces each of the 8 lanes of a key group handles
     constexpr int KG = THREADS / PIECES;           // key groups of the value pass
+    constexpr int ITEM = PAGE_KEYS * HD;           // elements of one page's keys (or values)
+    extern __shared__ __align__(128) unsigned char dyn[];
+    bf16* ring = reinterpret_cast<bf16*>(dyn);                                        // [RING][ITEM]
+    float* o_red = reinterpret_cast<float*>(dyn);                                     // [KG][GT][HD], after the ring is done
+    __shared__ __align__(8) unsigned long long full_bar[RING];
     __shared__ float q_s[GT][HD];
-    __shared__ float s_s[GT][SPLIT];
-    __shared__ int pg_s[SPLIT];
-    __shared__ float red[4][GT][2];
-    extern __shared__ float o_red[];               // [KG][GT][HD]
+    __shared__ float s_s[GT][PAGE_KEYS];
+    __shared__ int item_ok[RING];
 
-    const int n = blockIdx.x, split = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = blockIdx.x, split = blockIdx.z, tid = threadIdx.x, lane = tid & 31;
     const int group = nh / nkv, blocks_per_kv = (group + GT - 1) / GT;
     const int kvh = blockIdx.y / blocks_per_kv, h0 = kvh * group + (blockIdx.y % blocks_per_kv) * GT;
     const int heads = min(GT, (kvh + 1) * group - h0);
@@ -48,56 +89,87 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int j0 = max(lo, split * SPLIT), j1 = min(pos, split * SPLIT + SPLIT - 1);
     if (j0 > j1) return;                           // this row has no keys in this split
-    const int count = j1 - j0 + 1;
+    const int first_page = j0 / PAGE_KEYS, n_pg = j1 / PAGE_KEYS - first_page + 1, n_items = 2 * n_pg;
 
     for (int i = tid; i < GT * HD; i += THREADS) {
         const int g = i / HD, d = i - g * HD;
         q_s[g][d] = g < heads ? __bfloat162float(q[((size_t)n * nh + h0 + g) * HD + d]) : 0.f;
     }
-    for (int t = tid; t < count; t += THREADS) {
-        int pg = block_table[(size_t)seq * table_stride + (j0 + t) / page];
-        if (pg < 0 || pg >= n_pages) {
-            atomicOr(status, ESP_STATUS_BAD_INDEX);
-            pg = -1;
-        }
-        pg_s[t] = pg;
+    if (tid == 0) {
+        for (int r = 0; r < RING; r++) mbar_init(&full_bar[r], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
 
-    // ---- scores: 8 lanes per key, 16 keys in flight per pass --------------------
-    const float root = sqrtf((float)HD);
-    const int sub = tid & 7, slot = tid >> 3;      // lane within the key group, key slot 0..15
-    constexpr int KB = 4;                          // keys whose loads are in flight together, per thread
-    for (int t0 = slot; t0 < SPLIT; t0 += KB * (THREADS / 8)) {
-        uint4 kraw[KB][PER_LANE];
-        bool live[KB];
-#pragma unroll
-        for (int b = 0; b < KB; b++) {
-            const int t = t0 + b * (THREADS / 8);
-            live[b] = t < count && pg_s[t] >= 0;
-            if (live[b]) {
-                const int j = j0 + t;
-                const bf16* krow = k_cache + (((size_t)pg_s[t] * nkv + kvh) * page + j % page) * HD;
-#pragma unroll
-                for (int i = 0; i < PER_LANE; i++) kraw[b][i] = *reinterpret_cast<const uint4*>(krow + (sub + 8 * i) * 8);
-            }
+    // item 2p = keys of page p of the block, item 2p+1 = its values
+    auto issue = [&](int item) {
+        const int slot = item % RING;
+        int pg = block_table[(size_t)seq * table_stride + first_page + item / 2];
+        const bool ok = pg >= 0 && pg < n_pages;
+        if (!ok) atomicOr(status, ESP_STATUS_BAD_INDEX);
+        item_ok[slot] = ok ? 1 : 0;
+        if (ok) {
+            const bf16* src = ((item & 1) ? v_cache : k_cache) + ((size_t)pg * nkv + kvh) * ITEM;
+            mbar_expect_tx(&full_bar[slot], ITEM * 2);
+            bulk_copy(ring + (size_t)slot * ITEM, src, ITEM * 2, &full_bar[slot]);
+        } else {
+            mbar_arrive(&full_bar[slot]);          // nothing to fetch: the waiters go on and skip the page
         }
+    };
+    int issued = 0;
+    if (tid == 0) {
+        for (; issued < min(RING, n_items); issued++) issue(issued);
+    }
+
+    const float root = sqrtf((float)HD);
+    const int sub = tid & 7, slot8 = tid >> 3;     // lane within the key group, key slot 0..15
+    const int piece = tid % PIECES, kg = tid / PIECES;
+    // with one or two query heads per block the lane's share of q lives in registers
+    constexpr bool Q_REGS = GT <= 2;
+    float qr[Q_REGS ? GT : 1][Q_REGS ? PER_LANE * 8 : 1];
+    if (Q_REGS) {
 #pragma unroll
-        for (int b = 0; b < KB; b++) {
-            const int t = t0 + b * (THREADS / 8);
+        for (int g = 0; g < GT; g++)
+#pragma unroll
+            for (int i = 0; i < PER_LANE; i++)
+#pragma unroll
+                for (int e = 0; e < 8; e++) qr[Q_REGS ? g : 0][Q_REGS ? i * 8 + e : 0] = q_s[g][(sub + 8 * i) * 8 + e];
+    }
+    float m_run[GT], l_run[GT], acc[GT][8];
+#pragma unroll
+    for (int g = 0; g < GT; g++) {
+        m_run[g] = -INFINITY;
+        l_run[g] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[g][e] = 0.f;
+    }
+    bool failed = false;
+
+    for (int pi = 0; pi < n_pg; pi++) {
+        const int key0 = (first_page + pi) * PAGE_KEYS;
+        // ---- scores of this page's 64 keys -------------------------------------------------------
+        const int item_k = 2 * pi, slot_k = item_k % RING;
+        if (__syncthreads_or(!mbar_wait(&full_bar[slot_k], (item_k / RING) & 1))) { failed = true; break; }
+        const bf16* kp = ring + (size_t)slot_k * ITEM;
+        const bool page_ok = item_ok[slot_k] != 0;
+#pragma unroll
+        for (int pass = 0; pass < PAGE_KEYS / 16; pass++) {
+            const int t = pass * 16 + slot8, j = key0 + t;
+            const bool live = page_ok && j >= j0 && j <= j1;
             float dot[GT];
 #pragma unroll
             for (int g = 0; g < GT; g++) dot[g] = 0.f;
-            if (live[b]) {
+            if (live) {
 #pragma unroll
                 for (int i = 0; i < PER_LANE; i++) {
-                    const int piece = sub + 8 * i;
+                    const int pc = sub + 8 * i;
                     float kf[8];
-                    unpack8(kraw[b][i], kf);
+                    unpack8(*reinterpret_cast<const uint4*>(kp + (size_t)t * HD + pc * 8), kf);
 #pragma unroll
                     for (int g = 0; g < GT; g++)
 #pragma unroll
-                        for (int e = 0; e < 8; e++) dot[g] = fmaf(q_s[g][piece * 8 + e], kf[e], dot[g]);
+                        for (int e = 0; e < 8; e++)
+                            dot[g] = fmaf(Q_REGS ? qr[Q_REGS ? g : 0][Q_REGS ? i * 8 + e : 0] : q_s[g][pc * 8 + e], kf[e], dot[g]);
                 }
             }
 #pragma unroll
@@ -106,71 +178,56 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 4);
-                if (sub == 0 && t < SPLIT) s_s[g][t] = live[b] ? v / root : -INFINITY;
+                if (sub == 0) s_s[g][t] = live ? v / root : -INFINITY;
             }
         }
-    }
-    __syncthreads();
-
-    // ---- softmax pieces of this split ----------------------------------------------
-    float m_loc[GT], l_loc[GT];
+        __syncthreads();                           // scores are written; the key buffer is free
+        if (tid == 0 && issued < n_items) issue(issued++);
+        // ---- running maximum and sum (every warp computes the same values) ---------------------------
+        float scale[GT], m_use[GT];
 #pragma unroll
-    for (int g = 0; g < GT; g++) {
-        float mx = -INFINITY;
-        for (int t = tid; t < count; t += THREADS) mx = fmaxf(mx, s_s[g][t]);
-        mx = warp_max(mx);
-        if (lane == 0) red[warp][g][0] = mx;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GT; g++) {
-        m_loc[g] = fmaxf(fmaxf(red[0][g][0], red[1][g][0]), fmaxf(red[2][g][0], red[3][g][0]));
-        float sum = 0.f;
-        for (int t = tid; t < count; t += THREADS) {
-            const float pv = m_loc[g] == -INFINITY ? 0.f : expf(s_s[g][t] - m_loc[g]);
-            s_s[g][t] = pv;
-            sum += pv;
+        for (int g = 0; g < GT; g++) {
+            const float a = s_s[g][lane], b = s_s[g][lane + 32];
+            const float m_new = fmaxf(m_run[g], warp_max(fmaxf(a, b)));
+            m_use[g] = m_new == -INFINITY ? 0.f : m_new;
+            scale[g] = expf(m_run[g] - m_use[g]);                      // 0 while nothing has been seen
+            const float pa = a == -INFINITY ? 0.f : expf(a - m_use[g]), pb = b == -INFINITY ? 0.f : expf(b - m_use[g]);
+            l_run[g] = l_run[g] * scale[g] + warp_sum(pa + pb);
+            m_run[g] = m_new;
         }
-        sum = warp_sum(sum);
-        if (lane == 0) red[warp][g][1] = sum;
-    }
-    __syncthreads();
+        // ---- weighted values ------------------------------------------------------------------------
+        const int item_v = 2 * pi + 1, slot_v = item_v % RING;
+        if (__syncthreads_or(!mbar_wait(&full_bar[slot_v], (item_v / RING) & 1))) { failed = true; break; }
+        const bf16* vp = ring + (size_t)slot_v * ITEM;
 #pragma unroll
-    for (int g = 0; g < GT; g++) l_loc[g] = ((red[0][g][1] + red[1][g][1]) + red[2][g][1]) + red[3][g][1];
-
-    // ---- weighted values: a thread owns one 16-byte piece of the head and every KG-th key ----
-    const int piece = tid % PIECES, kg = tid / PIECES;
-    float acc[GT][8];
+        for (int g = 0; g < GT; g++)
 #pragma unroll
-    for (int g = 0; g < GT; g++)
+            for (int e = 0; e < 8; e++) acc[g][e] *= scale[g];
+        if (kg < KG && item_ok[slot_v]) {
+            for (int t = kg; t < PAGE_KEYS; t += KG) {
+                float vf[8];
+                unpack8(*reinterpret_cast<const uint4*>(vp + (size_t)t * HD + piece * 8), vf);
 #pragma unroll
-        for (int e = 0; e < 8; e++) acc[g][e] = 0.f;
-    for (int t0 = kg; t0 < count && kg < KG; t0 += KB * KG) {
-        uint4 vraw[KB];
-        bool live[KB];
+                for (int g = 0; g < GT; g++) {
+                    const float sc = s_s[g][t];
+                    const float pw = sc == -INFINITY ? 0.f : expf(sc - m_use[g]);
 #pragma unroll
-        for (int b = 0; b < KB; b++) {
-            const int t = t0 + b * KG;
-            live[b] = t < count && pg_s[t] >= 0;
-            if (live[b]) {
-                const int j = j0 + t;
-                vraw[b] = *reinterpret_cast<const uint4*>(v_cache + (((size_t)pg_s[t] * nkv + kvh) * page + j % page) * HD + piece * 8);
+                    for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pw, vf[e], acc[g][e]);
+                }
             }
         }
-#pragma unroll
-        for (int b = 0; b < KB; b++) {
-            if (!live[b]) continue;
-            const int t = t0 + b * KG;
-            float vf[8];
-            unpack8(vraw[b], vf);
-#pragma unroll
-            for (int g = 0; g < GT; g++) {
-                const float pw = s_s[g][t];
-#pragma unroll
-                for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pw, vf[e], acc[g][e]);
-            }
-        }
+        __syncthreads();                           // the value buffer and the scores are free
+        if (tid == 0 && issued < n_items) issue(issued++);
     }
+    if (failed) {
+        if (tid == 0) {
+            atomicOr(status, ESP_STATUS_WAIT_EXPIRED);
+            // let this block's own copies land before its shared memory is given up
+            for (int it = max(0, issued - RING); it < issued; it++) mbar_wait(&full_bar[it % RING], (it / RING) & 1);
+        }
+        return;
+    }
+    // ---- combine the key groups and store the partial result -------------------------------------------
     if (kg < KG) {
 #pragma unroll
         for (int g = 0; g < GT; g++)
@@ -187,8 +244,8 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     }
     if (tid < heads) {
         float* ml = part_ml + (((size_t)n * nh + h0 + tid) * n_splits + split) * 2;
-        ml[0] = m_loc[tid];
-        ml[1] = l_loc[tid];
+        ml[0] = m_run[tid];
+        ml[1] = l_run[tid];
     }
 }
 
@@ -221,7 +278,9 @@ int launch_split(const bf16* q, const bf16* k, const bf16* v, float* po, float* 
                  const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
                  int window, int n_splits, int* status, cudaStream_t stream) {
     constexpr int KG = THREADS / (HD / 8);
-    const size_t dyn = (size_t)KG * GT * HD * sizeof(float);
+    constexpr size_t ring_bytes = (size_t)RING * PAGE_KEYS * HD * sizeof(bf16);
+    constexpr size_t red_bytes = (size_t)KG * GT * HD * sizeof(float);
+    const size_t dyn = ring_bytes > red_bytes ? ring_bytes : red_bytes;
     static bool raised = false;        // static + dynamic shared memory can pass 48 KB: always opt in
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<HD, GT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -232,7 +291,7 @@ int launch_split(const bf16* q, const bf16* k, const bf16* v, float* po, float* 
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + GT - 1) / GT), n_splits);
     attn_split_kernel<HD, GT, SPLIT><<<grid, THREADS, dyn, stream>>>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages,
-                                                              page, nh, nkv, window, n_splits, status);
+                                                                     page, nh, nkv, window, n_splits, status);
     return esp_launch_status();
 }
 
@@ -267,7 +326,8 @@ ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_ca
                             int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
                             int split, int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || (split != 256 && split != 512))
+    if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || (split != 256 && split != 512) ||
+        page != PAGE_KEYS)
         return (int)cudaErrorInvalidValue;
     const int group = nh / nkv;
     const int gt = group >= 8 ? 8 : group >= 3 ? 4 : group;      // 1, 2, 4 or 8 heads per block
