@@ -250,7 +250,7 @@ class Engine:
             return entry[1], entry[2]
         seen = self._graph_seen.get(key, 0)
         self._graph_seen[key] = seen + 1
-        if seen == 0:
+        if seen == 0 or seen < 0:
             return self._forward(ctx, extra, pick)
         graph = torch.cuda.CUDAGraph()
         ws.frozen = True
@@ -258,6 +258,13 @@ class Engine:
         try:
             with torch.cuda.graph(graph):
                 logits, out = self._forward(ctx, extra, pick)
+        except (RuntimeError, Backend):
+            # a shape that cannot be captured (scratch would have to grow, or the runtime refuses the
+            # capture) keeps running eagerly; nothing ran during the failed capture
+            ws.frozen = False
+            self._graph_seen[key] = -(1 << 30)
+            torch.cuda.synchronize()
+            return self._forward(ctx, extra, pick)
         finally:
             ws.frozen = False
         kernels = ops.launch_count() - before      # this library's kernels in the graph (library products not counted)
