@@ -327,6 +327,25 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const i
     }
     __syncthreads();
     const float g = gate ? gate[t] : 0.f;
+    if ((width & 3) == 0) {
+        // four columns per thread; each column still adds its terms in the same order
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < top_k; r++) {
+                const int row = order[r];
+                if (row >= 0) {
+                    const float4 v = *reinterpret_cast<const float4*>(expert_out + (size_t)row * width + i);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+            }
+            if (shared) {
+                const float4 v = *reinterpret_cast<const float4*>(shared + (size_t)t * width + i);
+                acc.x += g * v.x; acc.y += g * v.y; acc.z += g * v.z; acc.w += g * v.w;
+            }
+            *reinterpret_cast<float4*>(y + (size_t)t * width + i) = acc;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float acc = 0.f;
         for (int r = 0; r < top_k; r++) {
