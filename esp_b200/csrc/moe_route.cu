@@ -59,9 +59,6 @@ router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, co
     extern __shared__ float smem[];
     float* hs = smem;                          // [TPB][width]
     float* ps_all = smem + TPB * width;        // [TPB][n_experts]
-    __shared__ float scratch[33];
-    __shared__ int chosen[MAX_TOPK];
-    __shared__ float chosen_p[MAX_TOPK];
     const int n0 = blockIdx.x * TPB, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = ROUTER_THREADS / 32;
     const int live = min(TPB, n_tokens - n0);
     for (int i = tid; i < TPB * width; i += ROUTER_THREADS) {
@@ -69,76 +66,119 @@ router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, co
         hs[i] = t < live ? to_f32(h[(size_t)n0 * width + i]) : 0.f;
     }
     __syncthreads();
-    for (int e = warp; e < n_experts + (w_gate ? 1 : 0); e += nwarp) {
-        const TW* wr = e < n_experts ? w_router + (size_t)e * width : w_gate;
-        float s[TPB];
-        lane_dots<TPB>(hs, width, wr, width, lane, s);
+    // Each warp takes EPW experts at a time and, for every chunk of four columns, holds the TPB rows' values
+    // in registers while it walks its experts: a weight is loaded once per block and a row value once
+    // per EPW experts.  A lane's additions per (expert, row) run in column order.
+    constexpr int EPW = 4;
+    const int rows = n_experts + (w_gate ? 1 : 0);
+    const bool vec = width % 4 == 0 && (reinterpret_cast<uintptr_t>(w_router) & 15) == 0 &&
+                     (!w_gate || (reinterpret_cast<uintptr_t>(w_gate) & 15) == 0) && (width * sizeof(TW)) % 16 == 0;
+    for (int e0 = warp * EPW; e0 < rows; e0 += nwarp * EPW) {
+        float acc[EPW][TPB];
 #pragma unroll
-        for (int t = 0; t < TPB; t++) {
-            const float v = warp_sum(s[t]);
-            if (lane == 0 && t < live) {
-                if (e < n_experts) ps_all[t * n_experts + e] = v;
-                else gate[n0 + t] = 1.0f / (1.0f + expf(-v));
+        for (int j = 0; j < EPW; j++)
+#pragma unroll
+            for (int t = 0; t < TPB; t++) acc[j][t] = 0.f;
+        const TW* wrow[EPW];
+#pragma unroll
+        for (int j = 0; j < EPW; j++) {
+            const int e = min(e0 + j, rows - 1);
+            wrow[j] = e < n_experts ? w_router + (size_t)e * width : w_gate;
+        }
+        if (vec) {
+#pragma unroll 2
+            for (int i = lane * 4; i < width; i += 128) {
+                float4 x[TPB];
+#pragma unroll
+                for (int t = 0; t < TPB; t++) x[t] = *reinterpret_cast<const float4*>(hs + t * width + i);
+#pragma unroll
+                for (int j = 0; j < EPW; j++) {
+                    const float4 f = load4(wrow[j] + i);
+#pragma unroll
+                    for (int t = 0; t < TPB; t++) {
+                        acc[j][t] = fmaf(x[t].x, f.x, acc[j][t]);
+                        acc[j][t] = fmaf(x[t].y, f.y, acc[j][t]);
+                        acc[j][t] = fmaf(x[t].z, f.z, acc[j][t]);
+                        acc[j][t] = fmaf(x[t].w, f.w, acc[j][t]);
+                    }
+                }
+            }
+        } else {
+            for (int i = lane; i < width; i += 32)
+#pragma unroll
+                for (int j = 0; j < EPW; j++) {
+                    const float wv = to_f32(wrow[j][i]);
+#pragma unroll
+                    for (int t = 0; t < TPB; t++) acc[j][t] = fmaf(hs[t * width + i], wv, acc[j][t]);
+                }
+        }
+#pragma unroll
+        for (int j = 0; j < EPW; j++) {
+            const int e = e0 + j;
+#pragma unroll
+            for (int t = 0; t < TPB; t++) {
+                const float v = warp_sum(acc[j][t]);
+                if (lane == 0 && t < live && e < rows) {
+                    if (e < n_experts) ps_all[t * n_experts + e] = v;
+                    else gate[n0 + t] = 1.0f / (1.0f + expf(-v));
+                }
             }
         }
     }
     __syncthreads();
-    for (int t = 0; t < live; t++) {
+    // softmax, top-k and weights: one warp per token row, everything at warp level
+    for (int t = warp; t < live; t += nwarp) {
         const int n = n0 + t;
         float* ps = ps_all + t * n_experts;
-        float lm = -INFINITY;
-        for (int e = tid; e < n_experts; e += ROUTER_THREADS) lm = fmaxf(lm, ps[e]);
-        const float mx = block_max(lm, scratch);
-        float ls = 0.f;
-        for (int e = tid; e < n_experts; e += ROUTER_THREADS) {
+        float mx = -INFINITY;
+        for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, ps[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < n_experts; e += 32) {
             const float p = expf(ps[e] - mx);
             ps[e] = p;
-            ls += p;
+            sum += p;
         }
-        const float total = block_sum(ls, scratch);
-        for (int e = tid; e < n_experts; e += ROUTER_THREADS) {
-            const float p = ps[e] / total;
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < n_experts; e += 32) {
+            const float p = ps[e] / sum;
             ps[e] = p;
             if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
         }
-        __syncthreads();
-        // top-k by repeated arg-max in warp 0 (k and E are small); ties go to the lower id
-        if (warp == 0) {
-            bool bad = false;
-            float mass = 0.f;
-            for (int r = 0; r < top_k; r++) {
-                float best = -INFINITY;
-                int best_e = 0x7fffffff;
-                for (int e = lane; e < n_experts; e += 32) {
-                    const float p = ps[e];
-                    if (!(p == p) || isinf(p)) bad = true;
-                    if (p > best) { best = p; best_e = e; }   // ascending e per lane: the first maximum is the lowest id
-                }
+        __syncwarp();
+        // top-k by repeated arg-max (k and E are small); ties go to the lower id; rank r is kept by lane r
+        bool bad = false;
+        float mass = 0.f, my_p = 0.f;
+        int my_e = 0;
+        for (int r = 0; r < top_k; r++) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+            for (int e = lane; e < n_experts; e += 32) {
+                const float p = ps[e];
+                if (!(p == p) || isinf(p)) bad = true;
+                if (p > best) { best = p; best_e = e; }   // ascending e per lane: the first maximum is the lowest id
+            }
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                    const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                    if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-                }
-                if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
-                if (lane == 0) {
-                    chosen[r] = best_e;
-                    chosen_p[r] = best;
-                    ps[best_e] = -1.0f;           // probabilities are >= 0: taken out of the running
-                }
-                mass += best;
-                __syncwarp();
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
             }
-            const float denom = norm_topk ? mass : 1.0f;
-            if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
-                if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
-            }
-            for (int r = lane; r < top_k; r += 32) {
-                topk_ids[(size_t)n * top_k + r] = chosen[r];
-                topk_w[(size_t)n * top_k + r] = chosen_p[r] / denom;
-            }
+            if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
+            if (lane == 0) ps[best_e] = -1.0f;            // probabilities are >= 0: taken out of the running
+            if (lane == r) { my_p = best; my_e = best_e; }
+            mass += best;
+            __syncwarp();
         }
-        __syncthreads();
+        const float denom = norm_topk ? mass : 1.0f;
+        if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
+            if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
+        }
+        if (lane < top_k) {
+            topk_ids[(size_t)n * top_k + lane] = my_e;
+            topk_w[(size_t)n * top_k + lane] = my_p / denom;
+        }
     }
 }
 
@@ -363,8 +403,8 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
                             int n_experts, int top_k, int norm_topk, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts) return (int)cudaErrorInvalidValue;
-    // many tokens: four per block, so that the router's weights are fetched a quarter as often
-    int tpb = n_tokens > 32 ? 4 : 1;
+    // many tokens: four or eight per block, so that the router's weights are fetched that much less often
+    int tpb = n_tokens > 256 ? 8 : n_tokens > 32 ? 4 : 1;
     if ((size_t)tpb * (width + n_experts) * sizeof(float) > 200 * 1024) tpb = 1;
     const size_t smem = (size_t)tpb * (width + n_experts) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
@@ -377,7 +417,12 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
             (const TH*)h, (const TW*)w_router, (const TW*)w_gate, topk_ids, topk_w, gate, probs_out, n_tokens, width, \
             n_experts, top_k, norm_topk, status);                                                                     \
     } while (0)
-#define ESP_ROUTER_T(TH, TW) do { if (tpb == 4) ESP_ROUTER(TH, TW, 4); else ESP_ROUTER(TH, TW, 1); } while (0)
+#define ESP_ROUTER_T(TH, TW)                                                                                          \
+    do {                                                                                                              \
+        if (tpb == 8) ESP_ROUTER(TH, TW, 8);                                                                          \
+        else if (tpb == 4) ESP_ROUTER(TH, TW, 4);                                                                     \
+        else ESP_ROUTER(TH, TW, 1);                                                                                   \
+    } while (0)
     if (h_is_bf16 && w_is_bf16) ESP_ROUTER_T(bf16, bf16);
     else if (h_is_bf16) ESP_ROUTER_T(bf16, float);
     else if (w_is_bf16) ESP_ROUTER_T(float, bf16);
