@@ -16,7 +16,7 @@
 // wasting tensor work.  A token tile never mixes groups: the tile list (group,
 // first row, rows) is made on the device by the routing kernels.
 //
-// One CTA = 128 features x one token tile.  Warp 0 issues the TMA loads, warp 1
+// One tile = 128 features x one token tile.  Warp 0 issues the TMA loads, warp 1
 // owns TMEM and issues the MMAs, warps 2..5 are the epilogue (each reads the 32
 // TMEM lanes that its position in the warpgroup may touch).  A ring of
 // shared-memory stages is handed back and forth with mbarriers.  Every wait is
@@ -32,7 +32,6 @@ constexpr int BF = 128;            // features (weight rows) per tile: the M sid
 constexpr int TOK_BOX = 16;         // token rows per TMA box; a tile's width is a multiple of it
 constexpr int BK = 64, THREADS = 192;
 constexpr int W_BYTES = BF * BK * 2;
-constexpr int CTA_SMEM = 96 * 1024; // ring size: two CTAs fit one SM, so one's epilogue hides behind the other's loads
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 struct Tc05Params {
@@ -126,34 +125,61 @@ __device__ __forceinline__ unsigned instr_desc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
 }
 
-// MAX_TOK: token rows per tile at most (the N side of the MMA): 128 or 256
-template <bool SWIGLU, int MAX_TOK>
-__global__ void __launch_bounds__(THREADS, 2)
-gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, Tc05Params p) {
-    constexpr int TOK_BYTES = MAX_TOK * BK * 2;
+// Persistent form: a CTA per SM walks the list of (token tile, feature tile) pairs with stride gridDim.x.
+// The producer runs ahead across tile boundaries, so the weight stream never pauses; the accumulator is
+// double-buffered in TMEM, so the epilogue of one tile overlaps the MMAs of the next.
+constexpr int MAX_TOK = 128;        // token rows per tile at most (the N side of the MMA)
+constexpr int TOK_BYTES = MAX_TOK * BK * 2;
+constexpr int RING_BYTES = 192 * 1024;
+
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+struct TileInfo {
+    int group, row0, n_rows, n_tok, f0;
+};
+
+template <bool SWIGLU>
+__device__ __forceinline__ TileInfo tile_info(const Tc05Params& p, int tile, int feat_tiles) {
+    TileInfo t;
+    const int tt = tile / feat_tiles, ft = tile - tt * feat_tiles;     // feature tiles vary fastest: neighbours share tokens
+    if (p.tile_group) {
+        t.group = p.tile_group[tt];
+        t.row0 = p.tile_row0[tt];
+        t.n_rows = min(MAX_TOK, p.tile_rows[tt]);
+    } else {
+        t.group = 0;
+        t.row0 = tt * MAX_TOK;
+        t.n_rows = min(MAX_TOK, p.M - t.row0);
+    }
+    t.n_tok = min(MAX_TOK, (max(t.n_rows, 1) + TOK_BOX - 1) / TOK_BOX * TOK_BOX);
+    t.f0 = ft * BF;
+    return t;
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a64,
+                 const __grid_constant__ CUtensorMap map_a128, const __grid_constant__ CUtensorMap map_w, Tc05Params p) {
     constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * W_BYTES + TOK_BYTES;
-    constexpr int STAGES = CTA_SMEM / STAGE_BYTES;
-    constexpr int TMEM_COLS = (SWIGLU ? 2 : 1) * MAX_TOK;
-    static_assert(STAGES >= 2 && TMEM_COLS <= 256, "two CTAs share the SM's shared memory and its 512 TMEM columns");
+    constexpr int STAGES = RING_BYTES / STAGE_BYTES;
+    constexpr int ACC_COLS = (SWIGLU ? 2 : 1) * MAX_TOK;       // TMEM columns of one accumulator buffer
+    constexpr int TMEM_COLS = 2 * ACC_COLS;                      // two buffers
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
     unsigned long long* empty_bar = full_bar + STAGES;
-    unsigned long long* tmem_full_bar = empty_bar + STAGES;
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(tmem_full_bar + 1);
+    unsigned long long* acc_full_bar = empty_bar + STAGES;       // [2]
+    unsigned long long* acc_empty_bar = acc_full_bar + 2;        // [2]
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int group = 0, row0 = blockIdx.y * MAX_TOK, n_rows = min(MAX_TOK, p.M - row0);
-    if (p.tile_group) {
-        if ((int)blockIdx.y >= *p.n_tiles) return;                   // the whole CTA leaves before any barrier exists
-        group = p.tile_group[blockIdx.y];
-        row0 = p.tile_row0[blockIdx.y];
-        n_rows = p.tile_rows[blockIdx.y];
-    }
-    if (n_rows <= 0) return;
-    const int n_tok = min(MAX_TOK, (n_rows + TOK_BOX - 1) / TOK_BOX * TOK_BOX);      // width of the MMA's N side
-    const int f0 = blockIdx.x * BF;                                                 // first feature of the tile
+    const int feat_tiles = (p.N + BF - 1) / BF;
+    const int token_tiles = p.tile_group ? *p.n_tiles : (p.M + MAX_TOK - 1) / MAX_TOK;
+    const int total_tiles = token_tiles * feat_tiles;
+    if ((int)blockIdx.x >= total_tiles) return;                      // the whole CTA leaves before any barrier exists
     const int k_iters = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -161,7 +187,10 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(tmem_full_bar, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full_bar[b], 1);
+            mbar_init(&acc_empty_bar[b], 4);                         // one arrival per epilogue warp
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -176,87 +205,122 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            const unsigned stage_tx = (SWIGLU ? 2 : 1) * W_BYTES + n_tok * BK * 2;
-            for (int it = 0; it < k_iters && !*abort_flag; it++) {
-                const int s = it % STAGES;
-                if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1)) {
-                    atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
-                    *abort_flag = 1;
-                    break;
+            int it = 0;                                              // stage counter, runs on across tiles
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+                const TileInfo t = tile_info<SWIGLU>(p, tile, feat_tiles);
+                const unsigned stage_tx = (SWIGLU ? 2 : 1) * W_BYTES + t.n_tok * BK * 2;
+                for (int k = 0; k < k_iters; k++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1)) {
+                        atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    unsigned char* w_dst = smem + s * STAGE_BYTES;
+                    unsigned char* t_dst = w_dst + (SWIGLU ? 2 : 1) * W_BYTES;
+                    mbar_expect_tx(&full_bar[s], stage_tx);
+                    tma_load_3d(w_dst, &map_w, k * BK, t.f0, t.group, &full_bar[s]);
+                    if (SWIGLU) tma_load_3d(w_dst + W_BYTES, &map_w, k * BK, p.N + t.f0, t.group, &full_bar[s]);
+                    int r = 0;
+                    if (t.n_tok == MAX_TOK) {                          // a full tile: one box of 128 token rows
+                        tma_load_2d(t_dst, &map_a128, k * BK, t.row0, &full_bar[s]);
+                        r = MAX_TOK;
+                    }
+                    for (; r + 64 <= t.n_tok; r += 64)                 // boxes of 64 token rows while they fit,
+                        tma_load_2d(t_dst + r * BK * 2, &map_a64, k * BK, t.row0 + r, &full_bar[s]);
+                    for (; r < t.n_tok; r += TOK_BOX)                  // boxes of 16 for the ragged rest
+                        tma_load_2d(t_dst + r * BK * 2, &map_a, k * BK, t.row0 + r, &full_bar[s]);
                 }
-                unsigned char* w_dst = smem + s * STAGE_BYTES;
-                unsigned char* t_dst = w_dst + (SWIGLU ? 2 : 1) * W_BYTES;
-                mbar_expect_tx(&full_bar[s], stage_tx);
-                tma_load_3d(w_dst, &map_w, it * BK, f0, group, &full_bar[s]);
-                if (SWIGLU) tma_load_3d(w_dst + W_BYTES, &map_w, it * BK, p.N + f0, group, &full_bar[s]);
-                for (int r = 0; r < n_tok; r += TOK_BOX)
-                    tma_load_2d(t_dst + r * BK * 2, &map_a, it * BK, row0 + r, &full_bar[s]);
-                issued = it + 1;
             }
             if (*abort_flag) {
                 // let this CTA's own copies land before its shared memory is given up
-                for (int it = max(0, issued - STAGES); it < issued; it++) mbar_wait(&full_bar[it % STAGES], (it / STAGES) & 1);
+                for (int j = max(0, it - STAGES); j < it; j++) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const unsigned idesc = instr_desc(n_tok);
-            for (int it = 0; it < k_iters && !*abort_flag; it++) {
-                const int s = it % STAGES;
-                if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
+                const TileInfo t = tile_info<SWIGLU>(p, tile, feat_tiles);
+                const unsigned idesc = instr_desc(t.n_tok);
+                const int buf = local & 1;
+                // the epilogue must have emptied this accumulator buffer (two tiles ago)
+                if (!mbar_wait(&acc_empty_bar[buf], ((local >> 1) & 1) ^ 1)) {
                     atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
                     *abort_flag = 1;
                     break;
                 }
                 tc_fence_after();
-                const unsigned char* w_src = smem + s * STAGE_BYTES;
-                const unsigned char* t_src = w_src + (SWIGLU ? 2 : 1) * W_BYTES;
+                const unsigned acc = tmem_base + buf * ACC_COLS;
+                for (int k = 0; k < k_iters; k++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+                        atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    tc_fence_after();
+                    const unsigned char* w_src = smem + s * STAGE_BYTES;
+                    const unsigned char* t_src = w_src + (SWIGLU ? 2 : 1) * W_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++) {
-                    const unsigned acc = (it > 0 || k > 0) ? 1u : 0u;
-                    tc_mma(tmem_base, smem_desc(w_src + k * 32), smem_desc(t_src + k * 32), idesc, acc);
-                    if (SWIGLU) tc_mma(tmem_base + MAX_TOK, smem_desc(w_src + W_BYTES + k * 32), smem_desc(t_src + k * 32), idesc, acc);
+                    for (int kk = 0; kk < BK / 16; kk++) {
+                        const unsigned accum = (k > 0 || kk > 0) ? 1u : 0u;
+                        tc_mma(acc, smem_desc(w_src + kk * 32), smem_desc(t_src + kk * 32), idesc, accum);
+                        if (SWIGLU) tc_mma(acc + MAX_TOK, smem_desc(w_src + W_BYTES + kk * 32), smem_desc(t_src + kk * 32), idesc, accum);
+                    }
+                    tc_commit(&empty_bar[s]);                         // the stage is free once these MMAs have read it
                 }
-                tc_commit(&empty_bar[s]);                             // the stage is free once these MMAs have read it
+                if (*abort_flag) break;
+                tc_commit(&acc_full_bar[buf]);                        // the accumulator is complete once all MMAs are done
             }
-            tc_commit(tmem_full_bar);                                 // the accumulators are complete once all MMAs are done
         }
     } else {
         const int quad = warp & 3;                                   // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
-        const bool ok = mbar_wait(tmem_full_bar, 0);
-        if (!ok && lane == 0) {
-            atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
-            *abort_flag = 1;
-        }
-        tc_fence_after();
-        const int f = f0 + quad * 32 + lane;                          // this thread's output feature
-        const bool f_ok = ok && !*abort_flag && f < p.N;
-        const unsigned lane_addr = tmem_base + ((unsigned)(quad * 32) << 16);
-        for (int c0 = 0; c0 < n_tok; c0 += 32) {
-            float acc[32];
-            tc_ld32(lane_addr + c0, acc);
-            if (SWIGLU) {
-                float up[32];
-                tc_ld32(lane_addr + MAX_TOK + c0, up);
-                bf16* out = reinterpret_cast<bf16*>(p.C);
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    if (f_ok && c0 + i < n_rows) {
-                        const float v = acc[i] / (1.0f + expf(-acc[i])) * up[i];
-                        out[(size_t)(row0 + c0 + i) * p.ldc + f] = __float2bfloat16_rn(v);
-                    }
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
+            const TileInfo t = tile_info<SWIGLU>(p, tile, feat_tiles);
+            const int buf = local & 1;
+            const bool ok = !*abort_flag && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
+            if (!ok) {
+                if (lane == 0) {
+                    atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+                    *abort_flag = 1;
                 }
-            } else {
-                float* out = reinterpret_cast<float*>(p.C);
+                break;
+            }
+            tc_fence_after();
+            const int f = t.f0 + quad * 32 + lane;                    // this thread's output feature
+            const bool f_ok = f < p.N;
+            const unsigned lane_addr = tmem_base + buf * ACC_COLS + ((unsigned)(quad * 32) << 16);
+            for (int c0 = 0; c0 < t.n_tok; c0 += 32) {
+                float acc[32];
+                tc_ld32(lane_addr + c0, acc);
+                if (SWIGLU) {
+                    float up[32];
+                    tc_ld32(lane_addr + MAX_TOK + c0, up);
+                    bf16* out = reinterpret_cast<bf16*>(p.C);
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    if (f_ok && c0 + i < n_rows) {
-                        const float scale = p.row_scale ? p.row_scale[row0 + c0 + i] : 1.0f;
-                        out[(size_t)(row0 + c0 + i) * p.ldc + f] = acc[i] * scale;
+                    for (int i = 0; i < 32; i++) {
+                        if (f_ok && c0 + i < t.n_rows) {
+                            const float v = acc[i] / (1.0f + expf(-acc[i])) * up[i];
+                            out[(size_t)(t.row0 + c0 + i) * p.ldc + f] = __float2bfloat16_rn(v);
+                        }
+                    }
+                } else {
+                    float* out = reinterpret_cast<float*>(p.C);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        if (f_ok && c0 + i < t.n_rows) {
+                            const float scale = p.row_scale ? p.row_scale[t.row0 + c0 + i] : 1.0f;
+                            out[(size_t)(t.row0 + c0 + i) * p.ldc + f] = acc[i] * scale;
+                        }
                     }
                 }
             }
+            // this warp has read its part of the buffer: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
         }
     }
     tc_fence_before();
@@ -310,32 +374,37 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
                           int* status, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || rows_total <= 0) return 0;
     if (K % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
-    CUtensorMap map_a, map_w;
+    CUtensorMap map_a, map_a64, map_a128, map_w;
     int rc = make_map(&map_a, A, (unsigned long long)K, (unsigned long long)rows_total, 1, TOK_BOX, 2);
+    if (rc) return rc;
+    rc = make_map(&map_a64, A, (unsigned long long)K, (unsigned long long)rows_total, 1, 64, 2);
+    if (rc) return rc;
+    rc = make_map(&map_a128, A, (unsigned long long)K, (unsigned long long)rows_total, 1, MAX_TOK, 2);
     if (rc) return rc;
     // the weights always use a 3-D map so that the kernel has one code path; a dense product is one group
     rc = make_map(&map_w, W, (unsigned long long)K, (unsigned long long)w_rows, (unsigned long long)groups, BF, 3);
     if (rc) return rc;
     Tc05Params p{tile_group, tile_row0, tile_rows, n_tiles, row_scale, C, ldc, M, N, K, status};
-    // grouped products and SwiGLU products use token tiles of 128, dense plain products of 256
-    const int max_tok = (tile_group || swiglu) ? 128 : 256;
-    const int token_tiles = tile_group ? max_tiles : (M + max_tok - 1) / max_tok;
+    const int token_tiles = tile_group ? max_tiles : (M + MAX_TOK - 1) / MAX_TOK;     // upper bound when grouped
     if (token_tiles <= 0) return 0;
-    if (token_tiles > 65535) return (int)cudaErrorInvalidValue;
-    const size_t smem = CTA_SMEM + 1024 + 256;
-    const int which = swiglu ? 0 : (max_tok == 128 ? 1 : 2);
-    static bool raised[3] = {false, false, false};
-    if (!raised[which]) {
-        cudaError_t e =
-            which == 0 ? cudaFuncSetAttribute(gemm_tc05_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-            : which == 1 ? cudaFuncSetAttribute(gemm_tc05_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                         : cudaFuncSetAttribute(gemm_tc05_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        raised[which] = true;
+    const long long tiles_bound = (long long)token_tiles * ((N + BF - 1) / BF);
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
     }
-    dim3 grid((N + BF - 1) / BF, token_tiles);
-    if (which == 0) gemm_tc05_kernel<true, 128><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
-    else if (which == 1) gemm_tc05_kernel<false, 128><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
-    else gemm_tc05_kernel<false, 256><<<grid, THREADS, smem, stream>>>(map_a, map_w, p);
+    const size_t smem = RING_BYTES + 1024 + 256;
+    static bool raised[2] = {false, false};
+    if (!raised[swiglu ? 1 : 0]) {
+        cudaError_t e = swiglu ? cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                               : cudaFuncSetAttribute(gemm_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised[swiglu ? 1 : 0] = true;
+    }
+    const int grid = (int)(tiles_bound < sm_count ? tiles_bound : sm_count);
+    if (swiglu) gemm_tc05_kernel<true><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
+    else gemm_tc05_kernel<false><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
     return esp_launch_status();
 }
