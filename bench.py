@@ -39,6 +39,11 @@ A27B = {
     "tie_word_embeddings": False,
 }
 FULL_LAYERS = 24
+# the second shape that the reference's real-model gates use: Qwen2-57B-A14B layer sizes (--shape 57b-a14b)
+Q57B = dict(A27B, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+            max_position_embeddings=32768, intermediate_size=18944, num_experts=64, num_experts_per_tok=8,
+            moe_intermediate_size=2560, shared_expert_intermediate_size=20480)
+SHAPES = {"a2.7b": (A27B, "Qwen1.5-MoE-A2.7B layer sizes"), "57b-a14b": (Q57B, "Qwen2-57B-A14B layer sizes")}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -167,7 +172,8 @@ def main() -> int:
     ap.add_argument("--impl", default="esp_b200")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both are reported)")
+    ap.add_argument("--shape", default="a2.7b", choices=sorted(SHAPES), help="layer sizes (default: the headline shape)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (both are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement (for profiling decode)")
@@ -192,7 +198,11 @@ def main() -> int:
     from esp_b200.weights import InitSpec
 
     pk = peaks()
-    raw = dict(A27B, num_hidden_layers=a.layers)
+    shape, shape_name = SHAPES[a.shape]
+    full_layers = shape["num_hidden_layers"]
+    if a.layers is None:
+        a.layers = full_layers
+    raw = dict(shape, num_hidden_layers=a.layers)
     cfg = config_from_dict(raw)
     nums = model_numbers(raw, a.layers)
     vocab = raw["vocab_size"]
@@ -264,9 +274,12 @@ def main() -> int:
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights N(0,0.02)",
         "impl": "esp_b200",
-        "config": {"model": "Qwen1.5-MoE-A2.7B layer sizes", "layers": a.layers, "layers_of_model": FULL_LAYERS,
-                   "hidden": 2048, "heads": 16, "kv_heads": 16, "head_dim": 128, "vocab": vocab, "experts": 60,
-                   "top_k": 4, "moe_intermediate": 1408, "shared_intermediate": 5632, "global_batch": a.batch,
+        "config": {"model": shape_name, "layers": a.layers, "layers_of_model": full_layers,
+                   "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"],
+                   "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"], "vocab": vocab,
+                   "experts": raw["num_experts"], "top_k": raw["num_experts_per_tok"],
+                   "moe_intermediate": raw["moe_intermediate_size"],
+                   "shared_intermediate": raw["shared_expert_intermediate_size"], "global_batch": a.batch,
                    "seq_len": a.context, "prompt_len": prompt_len, "parallelism": "1 GPU",
                    "l2": "inputs larger than L2 (a step reads >10 GB)", "distinct_experts_per_layer": round(distinct, 1)},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(), "prefill": prefill,
