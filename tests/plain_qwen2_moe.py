@@ -123,7 +123,7 @@ def apply_rope(x, cos, sin):
     return np.concatenate([a * c - b * s, b * c + a * s], axis=-1)
 
 
-def attention(c, w, prefix, x, window, forced=None):
+def attention(c, w, prefix, x, window):
     """GQA attention of one layer over a whole sequence x [T, H]
     (crates/esp/src/infer/decoder/attention.rs:292-404): q/k/v with bias,
     rotary on q and k, scores divided by sqrt(hd) after the product, key j of
