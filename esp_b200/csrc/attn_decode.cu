@@ -66,9 +66,10 @@ constexpr int PAGE_KEYS = 64, RING = 2;
 template <int HD, int GT, int SPLIT>
 __global__ void __launch_bounds__(THREADS)
 attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                  float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tok_seq,
-                  const int* __restrict__ tok_pos, const int* __restrict__ block_table, int table_stride, int n_pages,
-                  int page, int nh, int nkv, int window, int n_splits, int* __restrict__ status) {
+                  bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                  int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                  const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv,
+                  int window, int n_splits, int* __restrict__ status) {
     constexpr int PIECES = HD / 8;                 // 16-byte pieces of a key or value row
     constexpr int PER_LANE = HD / 64;              // pieces each of the 8 lanes of a key group handles
     constexpr int KG = THREADS / PIECES;           // key groups of the value pass
@@ -247,34 +248,40 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
         ml[0] = m_run[tid];
         ml[1] = l_run[tid];
     }
-}
-
-template <int HD>
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, const int* __restrict__ tok_pos, int nh, int window,
-                                    int n_splits, int SPLIT) {
-    const int n = blockIdx.x, h = blockIdx.y;
-    const int pos = tok_pos[n];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    // ---- the last block of this (row, head group) to finish combines the row's splits, in ascending order.
+    // ``counters`` holds one zero per (row, head group) between launches: the combining block puts it back.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
     const int s0 = lo / SPLIT, s1 = pos / SPLIT;
-    const float* ml = part_ml + ((size_t)n * nh + h) * n_splits * 2;
-    const float* po = part_o + ((size_t)n * nh + h) * n_splits * HD;
-    float mx = -INFINITY;
-    for (int s = s0; s <= s1; s++) mx = fmaxf(mx, ml[2 * s]);
-    float denom = 0.f;
-    for (int s = s0; s <= s1; s++) denom += ml[2 * s + 1] * (ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - mx));
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = s0; s <= s1; s++) {
-            const float w = ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - mx);
-            acc += po[(size_t)s * HD + d] * w;
+    if (tid == 0) {
+        int* c = counters + (size_t)n * gridDim.y + blockIdx.y;
+        const int done = atomicAdd(c, 1);
+        is_last = done == s1 - s0;
+        if (is_last) *c = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int i = tid; i < heads * HD; i += THREADS) {
+        const int g = i / HD, d = i - g * HD;
+        const float* ml = part_ml + ((size_t)n * nh + h0 + g) * n_splits * 2;
+        const float* po = part_o + ((size_t)n * nh + h0 + g) * n_splits * HD;
+        float mx = -INFINITY;
+        for (int sp = s0; sp <= s1; sp++) mx = fmaxf(mx, __ldcg(ml + 2 * sp));
+        float denom = 0.f, num = 0.f;
+        for (int sp = s0; sp <= s1; sp++) {
+            const float m_sp = __ldcg(ml + 2 * sp);
+            const float w = m_sp == -INFINITY ? 0.f : expf(m_sp - mx);
+            denom += __ldcg(ml + 2 * sp + 1) * w;
+            num += __ldcg(po + (size_t)sp * HD + d) * w;
         }
-        out[((size_t)n * nh + h) * HD + d] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
+        out[((size_t)n * nh + h0 + g) * HD + d] = __float2bfloat16_rn(denom > 0.f ? num / denom : 0.f);
     }
 }
 
 template <int HD, int GT, int SPLIT>
-int launch_split(const bf16* q, const bf16* k, const bf16* v, float* po, float* pml, const int* tok_seq,
+int launch_split(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters, const int* tok_seq,
                  const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
                  int window, int n_splits, int* status, cudaStream_t stream) {
     constexpr int KG = THREADS / (HD / 8);
@@ -290,39 +297,38 @@ int launch_split(const bf16* q, const bf16* k, const bf16* v, float* po, float* 
     }
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + GT - 1) / GT), n_splits);
-    attn_split_kernel<HD, GT, SPLIT><<<grid, THREADS, dyn, stream>>>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages,
+    attn_split_kernel<HD, GT, SPLIT><<<grid, THREADS, dyn, stream>>>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
                                                                      page, nh, nkv, window, n_splits, status);
     return esp_launch_status();
 }
 
 template <int HD>
-int dispatch(int gt, int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, const int* tok_seq,
+int dispatch(int gt, int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
+             const int* tok_seq,
              const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
              int window, int n_splits, int* status, cudaStream_t stream) {
     int rc;
 #define ESP_SPLIT(GT)                                                                                                  \
-    (split == 256 ? launch_split<HD, GT, 256>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
+    (split == 256 ? launch_split<HD, GT, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
                                               nh, nkv, window, n_splits, status, stream)                                 \
-                  : launch_split<HD, GT, 512>(q, k, v, po, pml, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
+                  : launch_split<HD, GT, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
                                               nh, nkv, window, n_splits, status, stream))
     if (gt == 1) rc = ESP_SPLIT(1);
     else if (gt == 2) rc = ESP_SPLIT(2);
     else if (gt == 4) rc = ESP_SPLIT(4);
     else rc = ESP_SPLIT(8);
 #undef ESP_SPLIT
-    if (rc != 0) return rc;
-    dim3 grid(n_tokens, nh);
-    attn_combine_kernel<HD><<<grid, HD / 2 < 32 ? 32 : HD / 2, 0, stream>>>(po, pml, out, tok_pos, nh, window, n_splits, split);
-    return esp_launch_status();
+    return rc;
 }
 }  // namespace
 
 // Scratch: part_o float [n_tokens, nh, n_splits, hd], part_ml float [n_tokens, nh, n_splits, 2];
+// counters int [n_tokens * head groups], all zero when the call starts (the kernel leaves them zero);
 // split: key positions per block, 256 or 512 (the caller picks: short splits when there are few rows, so
 // that every SM still gets blocks); n_splits >= ceil(longest sequence / split).  Head sizes 64, 128, 192, 256; pages of 64 positions or any
 // size; any head counts with nh % nkv == 0.
 ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,
-                            float* part_ml, const int* tok_seq, const int* tok_pos, const int* block_table,
+                            float* part_ml, int* counters, const int* tok_seq, const int* tok_pos, const int* block_table,
                             int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
                             int split, int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
@@ -332,7 +338,7 @@ ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_ca
     const int group = nh / nkv;
     const int gt = group >= 8 ? 8 : group >= 3 ? 4 : group;      // 1, 2, 4 or 8 heads per block
 #define ESP_HD(HD) return dispatch<HD>(gt, split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
-                                       part_ml, tok_seq, tok_pos, block_table, table_stride, n_pages, page, n_tokens, nh,   \
+                                       part_ml, counters, tok_seq, tok_pos, block_table, table_stride, n_pages, page, n_tokens, nh,   \
                                        nkv, window, n_splits, status, stream)
     switch (hd) {
         case 64: ESP_HD(64);
@@ -358,16 +364,23 @@ constexpr int NOALLOC_MAX_DEVICES = 64;
 float* noalloc_scratch_of_device[NOALLOC_MAX_DEVICES] = {nullptr};
 }  // namespace
 
-extern "C" long long esp_attn_decode_noalloc_capacity(void) { return (long long)ESP_ATTN_DECODE_NOALLOC_FLOATS; }
+// The last ESP_NOALLOC_COUNTERS words of the array are the kernel's (row, head group) counters.  They sit at a
+// fixed place so that no call's partial results are ever written over them: they must read zero when a
+// call starts, and every call leaves them zero.
+extern "C" long long esp_attn_decode_noalloc_capacity(void) {
+    return (long long)ESP_ATTN_DECODE_NOALLOC_FLOATS - ESP_NOALLOC_COUNTERS;
+}
 
 extern "C" int esp_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                        const int* tok_seq, const int* tok_pos, const int* block_table, int table_stride,
                                        int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
                                        int split, int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (nh <= 0 || hd <= 0 || n_splits <= 0) return (int)cudaErrorInvalidValue;
+    if (nh <= 0 || hd <= 0 || n_splits <= 0 || nkv <= 0) return (int)cudaErrorInvalidValue;
     const unsigned long long need = (unsigned long long)n_tokens * nh * n_splits * (hd + 2);
-    if (need > ESP_ATTN_DECODE_NOALLOC_FLOATS) return ESP_NOALLOC_TOO_LARGE;
+    if (need > (unsigned long long)esp_attn_decode_noalloc_capacity() ||
+        (unsigned long long)n_tokens * nh > ESP_NOALLOC_COUNTERS)
+        return ESP_NOALLOC_TOO_LARGE;
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
@@ -381,6 +394,7 @@ extern "C" int esp_attn_decode_noalloc(const void* q, const void* k_cache, const
     }
     float* part_o = noalloc_scratch_of_device[device];
     float* part_ml = part_o + (size_t)n_tokens * nh * n_splits * hd;
-    return esp_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, tok_seq, tok_pos, block_table, table_stride, n_pages,
-                           page, n_tokens, nh, nkv, hd, window, split, n_splits, status, stream);
+    int* counters = reinterpret_cast<int*>(noalloc_scratch_of_device[device] + esp_attn_decode_noalloc_capacity());
+    return esp_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, block_table, table_stride,
+                           n_pages, page, n_tokens, nh, nkv, hd, window, split, n_splits, status, stream);
 }

@@ -14,13 +14,15 @@
 //
 // Set-up: the first call on a device (with that device current) looks up the array's device address
 // with cudaGetSymbolAddress and keeps it; make that first call before any stream capture begins.
-// Limits: n_tokens * nh * n_splits * (hd + 2) must not exceed ESP_ATTN_DECODE_NOALLOC_FLOATS, else the
-// call returns ESP_NOALLOC_TOO_LARGE and launches nothing (esp_attn_decode_noalloc_capacity() gives
-// the limit).  hd is 64, 128, 192 or 256, as for esp_attn_decode.
-// Sharing: all calls on a device use the same array.  It keeps whatever the last call left there; the
-// kernels write every element they later read, so nothing has to be cleared between calls.  Two calls
-// whose kernels can overlap on the GPU (different streams, no ordering between them) race on the array:
-// order them.
+// Limits: n_tokens * nh * n_splits * (hd + 2) must not exceed esp_attn_decode_noalloc_capacity() (the
+// array less the ESP_NOALLOC_COUNTERS words kept for the kernel's counters) and n_tokens * nh must not
+// exceed ESP_NOALLOC_COUNTERS, else the call returns ESP_NOALLOC_TOO_LARGE and launches nothing.  hd is
+// 64, 128, 192 or 256 and split 256 or 512, as for esp_attn_decode.
+// Sharing: all calls on a device use the same array.  It keeps whatever the last call left there.  The
+// kernel writes every partial result it later reads, so that part needs no clearing; the counters at
+// the array's end must be zero when a call starts: they are zero when the library is loaded and each
+// call puts them back to zero before it ends.  Two calls whose kernels can overlap on the GPU (different
+// streams, no ordering between them) race on the array: order them.
 //
 // Arguments and result are those of esp_attn_decode without the two scratch pointers; the return value
 // is 0, a cudaError_t, or ESP_NOALLOC_TOO_LARGE.
@@ -28,6 +30,7 @@
 #include <cuda_runtime.h>
 
 #define ESP_ATTN_DECODE_NOALLOC_FLOATS (2u << 20)
+#define ESP_NOALLOC_COUNTERS 65536
 #define ESP_NOALLOC_TOO_LARGE (-2)
 
 #ifdef __cplusplus
@@ -39,7 +42,7 @@ __attribute__((visibility("default"))) int esp_attn_decode_noalloc(
     const int* block_table, int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
     int split, int n_splits, int* status, cudaStream_t stream);
 
-// Number of floats of the built-in scratch (the limit that the call checks against).
+// Number of floats of the built-in scratch that partial results may use (the limit the call checks against).
 __attribute__((visibility("default"))) long long esp_attn_decode_noalloc_capacity(void);
 
 #ifdef __cplusplus

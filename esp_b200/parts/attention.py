@@ -113,7 +113,9 @@ class Attention(Part):
             n_splits = (positions + split - 1) // split
             part_o = rt.ws.get("attn_part_o", (n, s.num_heads, n_splits, s.head_dim), torch.float32)
             part_ml = rt.ws.get("attn_part_ml", (n, s.num_heads, n_splits, 2), torch.float32)
-            ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, ctx.tok_seq, ctx.tok_pos, table, layer.page,
+            if getattr(rt, "attn_counters", None) is None:
+                rt.attn_counters = torch.zeros(ops.ATTN_DECODE_COUNTERS, dtype=torch.int32, device=rt.device)
+            ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, rt.attn_counters, ctx.tok_seq, ctx.tok_pos, table, layer.page,
                             s.num_heads, s.num_kv_heads, s.head_dim, s.window, split, n_splits, rt.status)
             return
         if rt.dtype == torch.bfloat16 and s.head_dim <= 128 and layer.page == 64:

@@ -548,11 +548,12 @@ def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window, split):
     part_o = torch.full((n, nh, n_splits, hd), float("nan"), device=DEV)
     part_ml = torch.full((n, nh, n_splits, 2), float("nan"), device=DEV)
     st = status()
-    ops.attn_decode(qd.reshape(n, nh * hd).to(DEV), kc, vc, out, part_o, part_ml,
+    counters = torch.zeros(n * nh, dtype=torch.int32, device=DEV)
+    ops.attn_decode(qd.reshape(n, nh * hd).to(DEV), kc, vc, out, part_o, part_ml, counters,
                     torch.tensor([s for s, _, _ in queries], dtype=torch.int32, device=DEV),
                     torch.tensor([p for _, p, _ in queries], dtype=torch.int32, device=DEV), table, 64, nh, nkv, hd,
                     window, split, n_splits, st)
-    assert st.item() == 0
+    assert st.item() == 0 and not counters.any(), "the counters must be left at zero"
     for i, (s, p, target) in enumerate(queries):
         ref = attention_reference(qd[i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(), p, window, group)
         close(out[i].view(nh, hd), ref, dtype, f"query {i} (sequence {s}, position {p}, target key {target})")
