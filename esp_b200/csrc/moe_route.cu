@@ -396,6 +396,78 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const i
         y[(size_t)t * width + i] = acc;
     }
 }
+// The combine above fused with what follows it in a pre-norm block: the residual add and the next RMSNorm.
+//   y = (sum of the row's expert outputs in ascending expert id) + gate * shared      (as moe_combine_kernel)
+//   v = x[s] + y;  if (write_x) x[s] = v;  h[r] = v * rsqrt(mean(v^2) + eps) * gamma  (as add_rmsnorm)
+// with s = rows ? rows[r] : r.  Same operations in the same order as the two separate kernels, so the
+// results are the same bits.  Width a multiple of 4, at most 16384.
+template <typename TH>
+__global__ void __launch_bounds__(1024)
+moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* __restrict__ topk_ids,
+                               const int* __restrict__ inverse, const float* __restrict__ gate,
+                               const float* __restrict__ shared, float* __restrict__ x, const float* __restrict__ gamma,
+                               const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
+                               int top_k, float eps, int write_x) {
+    __shared__ int order[MAX_TOPK];
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t t = rows ? (size_t)rows[r] : (size_t)r;
+    if (threadIdx.x == 0) {
+        int ids[MAX_TOPK];
+        for (int j = 0; j < top_k; j++) { ids[j] = topk_ids[t * top_k + j]; order[j] = j; }
+        for (int a = 1; a < top_k; a++) {
+            const int oa = order[a], ia = ids[oa];
+            int b = a - 1;
+            while (b >= 0 && ids[order[b]] > ia) { order[b + 1] = order[b]; b--; }
+            order[b + 1] = oa;
+        }
+        for (int j = 0; j < top_k; j++) order[j] = inverse[t * top_k + order[j]];
+    }
+    __syncthreads();
+    const float g = gate ? gate[t] : 0.f;
+    const int pieces = width / 4;
+    float4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < pieces) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < top_k; j++) {
+                const int row = order[j];
+                if (row >= 0) {
+                    const float4 e = reinterpret_cast<const float4*>(expert_out + (size_t)row * width)[q];
+                    acc.x += e.x; acc.y += e.y; acc.z += e.z; acc.w += e.w;
+                }
+            }
+            if (shared) {
+                const float4 e = reinterpret_cast<const float4*>(shared + t * width)[q];
+                acc.x += g * e.x; acc.y += g * e.y; acc.z += g * e.z; acc.w += g * e.w;
+            }
+            float4 xv = reinterpret_cast<float4*>(x + t * width)[q];
+            xv.x += acc.x; xv.y += acc.y; xv.z += acc.z; xv.w += acc.w;
+            if (write_x) reinterpret_cast<float4*>(x + t * width)[q] = xv;
+            v[i] = xv;
+            ss = fmaf(xv.x, xv.x, ss);
+            ss = fmaf(xv.y, xv.y, ss);
+            ss = fmaf(xv.z, xv.z, ss);
+            ss = fmaf(xv.w, xv.w, ss);
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < pieces) {
+            const float4 gm = reinterpret_cast<const float4*>(gamma)[q];
+            const float o0 = v[i].x * inv * gm.x, o1 = v[i].y * inv * gm.y, o2 = v[i].z * inv * gm.z, o3 = v[i].w * inv * gm.w;
+            TH* hr = h + (size_t)r * width + 4 * q;
+            hr[0] = from_f32<TH>(o0); hr[1] = from_f32<TH>(o1); hr[2] = from_f32<TH>(o2); hr[3] = from_f32<TH>(o3);
+            if (h32) reinterpret_cast<float4*>(h32 + (size_t)r * width)[q] = make_float4(o0, o1, o2, o3);
+        }
+    }
+}
 }  // namespace
 
 ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, const void* w_gate, int w_is_bf16,
@@ -479,5 +551,23 @@ ESP_API int esp_moe_combine(const float* expert_out, const int* topk_ids, const 
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK) return (int)cudaErrorInvalidValue;
     moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(expert_out, topk_ids, inverse, gate, shared, y, width, top_k);
+    return esp_launch_status();
+}
+
+ESP_API int esp_moe_combine_add_rmsnorm(const float* expert_out, const int* topk_ids, const int* inverse, const float* gate,
+                                        const float* shared, float* x, const float* gamma, const int* rows, void* h,
+                                        int h_is_bf16, float* h32, int n_rows, int width, int top_k, float eps, int write_x,
+                                        cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (top_k > MAX_TOPK || width % 4 != 0 || width > 16384) return (int)cudaErrorInvalidValue;
+    int threads = ((width / 4 + 3) / 4 + 31) / 32 * 32;
+    if (width / 4 <= 1024) threads = (width / 4 + 31) / 32 * 32;
+    if (h_is_bf16)
+        moe_combine_add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(expert_out, topk_ids, inverse, gate, shared, x, gamma,
+                                                                            rows, (bf16*)h, h32, width, top_k, eps, write_x);
+    else
+        moe_combine_add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(expert_out, topk_ids, inverse, gate, shared, x,
+                                                                             gamma, rows, (float*)h, h32, width, top_k, eps,
+                                                                             write_x);
     return esp_launch_status();
 }

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
+    "esp_moe_combine_add_rmsnorm": [P, P, P, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, c_int, P],
     "esp_gemm_skinny": [P, c_longlong, P, P, c_longlong, P, P, c_int, c_longlong, P, c_int, c_int, c_int, c_int, c_int,
                         c_int, P],
     "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
@@ -258,6 +259,20 @@ def moe_combine(expert_out, topk_ids, inverse, gate, shared, y):
         _ptr(expert_out, torch.float32), _ptr(topk_ids, torch.int32), _ptr(inverse, torch.int32),
         _ptr(gate, torch.float32), _ptr(shared, torch.float32), _ptr(y, torch.float32), n, width, topk_ids.shape[1],
         _stream()), "moe_combine")
+
+
+def moe_combine_add_rmsnorm(expert_out, topk_ids, inverse, gate, shared, x, gamma, h, eps, rows=None, write_x=True,
+                            h32=None):
+    """moe_combine followed by add_rmsnorm in one kernel (same operations in the same order): x (+)= combined
+    expert outputs, h = rmsnorm(x) * gamma.  Width a multiple of 4, at most 16384."""
+    n_rows, width = h.shape
+    if width % 4 != 0 or width > 16384:
+        raise Backend(f"moe_combine_add_rmsnorm: width {width} not taken")
+    _check(_fn("core", "esp_moe_combine_add_rmsnorm")(
+        _ptr(expert_out, torch.float32), _ptr(topk_ids, torch.int32), _ptr(inverse, torch.int32),
+        _ptr(gate, torch.float32), _ptr(shared, torch.float32), _ptr(x, torch.float32), _ptr(gamma, torch.float32),
+        _ptr(rows, torch.int32), _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(h32, torch.float32), n_rows, width,
+        topk_ids.shape[1], float(eps), 1 if write_x else 0, _stream()), "moe_combine_add_rmsnorm")
 
 
 def pick_tokens(logits, temperature, top_p, rng_state, row_slot, tokens):

@@ -8,7 +8,7 @@ to be stored, and then runs on packed token rows.
 Interfaces (all tensors live on the GPU; N = tokens of the step, H = width):
 
 * norm:      ``forward(x, delta, h, rows=None, write_x=True, h32=None)``: x [N,H] float32 is the residual stream;
-             ``delta`` (float32 [N,H] or None) is added to it first; h receives the normed rows in the
+             ``delta`` (float32 [N,H], None, or a deferred output with ``materialize()``) is added to it first; h receives the normed rows in the
              activation dtype.
 * mixer:     ``forward(h, ctx, layer) -> delta`` float32 [N,H]; ``kv_layout()`` and ``state_spec()`` say
              what it keeps per sequence (``layer`` is a ``cache.LayerCache``).

@@ -9,6 +9,25 @@ from .base import ParamSpec, Part, register
 from .linear import grouped_linear, grouped_swiglu_linear, grouped_uses_tc05, linear, swiglu_linear
 
 
+class DeferredMoeCombine:
+    """What a sparse block hands on instead of its output when nothing has to see that output by itself:
+    the pieces of the combine.  A norm that knows the fused kernel adds and normalises in one launch
+    (``fused_add_rmsnorm``); anything else calls ``materialize()`` and gets the plain tensor."""
+
+    def __init__(self, rt, expert_out, ids, inverse, gate, shared, width):
+        self.rt, self.expert_out, self.ids, self.inverse, self.gate, self.shared = rt, expert_out, ids, inverse, gate, shared
+        self.width = width
+
+    def materialize(self):
+        y = self.rt.ws.get("ffn_out", (self.ids.shape[0], self.width), torch.float32)
+        ops.moe_combine(self.expert_out, self.ids, self.inverse, self.gate, self.shared, y)
+        return y
+
+    def fused_add_rmsnorm(self, x, gamma, h, eps, rows, write_x, h32):
+        ops.moe_combine_add_rmsnorm(self.expert_out, self.ids, self.inverse, self.gate, self.shared, x, gamma, h, eps,
+                                    rows=rows, write_x=write_x, h32=h32)
+
+
 SIDE_STREAM_ROWS = 64      # steps with at most this many rows run the shared expert on a second stream
 
 
@@ -116,8 +135,11 @@ class MoeSwiGluShared(Part):
     def forward(self, h, ctx, h32=None):
         rt = self.rt
         n = h.shape[0]
-        y = rt.ws.get("ffn_out", (n, self.spec.hidden), torch.float32)
         step = rt.ffn_chunk_tokens
+        if n <= step and self.spec.hidden % 4 == 0 and self.spec.hidden <= 16384:
+            # one chunk: leave the combine to the norm that follows (one launch for combine, add and norm)
+            return self._forward_rows(h, None, ctx, 0, h32 if h32 is not None else h)
+        y = rt.ws.get("ffn_out", (n, self.spec.hidden), torch.float32)
         for a in range(0, n, step):
             b = min(n, a + step)
             self._forward_rows(h[a:b], y[a:b], ctx, a, h32[a:b] if h32 is not None else h[a:b])
@@ -167,7 +189,10 @@ class MoeSwiGluShared(Part):
         else:
             expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
             _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
+        if y is None:
+            return DeferredMoeCombine(rt, expert_out, ids, inverse, gate, shared, H)
         ops.moe_combine(expert_out, ids, inverse, gate, shared, y)
+        return y
 
     def experts(self, h, offsets, perm_token, perm_weight, rows, max_rows, tiles=None):
         """expert_out[r] = weight[r] * down_e(silu(gate_e x) * (up_e x)) for every

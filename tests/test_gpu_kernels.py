@@ -319,6 +319,29 @@ def test_moe_permute_and_combine():
         assert np.allclose(y[t].cpu().numpy(), acc, rtol=0, atol=1e-6), t
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [200, 2048])
+def test_combine_add_norm_in_one_kernel_gives_the_same_bits(dtype, width):
+    n, k, e = 19, 3, 6
+    rng = np.random.default_rng(1)
+    ids = torch.tensor(np.stack([rng.permutation(e)[:k] for _ in range(n)]).astype(np.int32), device=DEV)
+    inverse = torch.tensor(rng.permutation(n * k).reshape(n, k).astype(np.int32), device=DEV)
+    expert_out, shared, gate = rnd(n * k, width, seed=3), rnd(n, width, seed=4), rnd(n, seed=5).abs()
+    x, gamma = rnd(n, width, seed=6), 1 + 0.1 * rnd(width, seed=7)
+    y = torch.empty(n, width, device=DEV)
+    ops.moe_combine(expert_out, ids, inverse, gate, shared, y)
+    x_ref, h_ref, h32_ref = x.clone(), torch.empty(n, width, dtype=dtype, device=DEV), torch.empty(n, width, device=DEV)
+    ops.add_rmsnorm(x_ref, y, gamma, h_ref, 1e-6, h32=h32_ref)
+    x_got, h_got, h32_got = x.clone(), torch.empty_like(h_ref), torch.empty_like(h32_ref)
+    ops.moe_combine_add_rmsnorm(expert_out, ids, inverse, gate, shared, x_got, gamma, h_got, 1e-6, h32=h32_got)
+    assert torch.equal(x_got, x_ref) and torch.equal(h_got, h_ref) and torch.equal(h32_got, h32_ref)
+    rows = torch.tensor([4, 0, 18], dtype=torch.int32, device=DEV)
+    h_ref2, h_got2, x_keep = torch.empty(3, width, dtype=dtype, device=DEV), torch.empty(3, width, dtype=dtype, device=DEV), x.clone()
+    ops.add_rmsnorm(x.clone(), y, gamma, h_ref2, 1e-6, rows=rows, write_x=False)
+    ops.moe_combine_add_rmsnorm(expert_out, ids, inverse, gate, shared, x_keep, gamma, h_got2, 1e-6, rows=rows, write_x=False)
+    assert torch.equal(h_got2, h_ref2) and torch.equal(x_keep, x)
+
+
 def test_argmax_takes_the_lower_id_on_ties():
     logits = rnd(4, 1000)
     logits[0, 900] = logits[0, 17] = 50.0
