@@ -39,3 +39,32 @@ def test_medium_layer_whole_and_tail(folder, dtype):
     rec = Recorder(eng.plan.vocab)
     run_steps(eng, steps_tail({"b": reqs["b"]}, 8), rec)
     check_against_plain(folder, dtype, {"b": reqs["b"]}, rec, "medium, last 8 one by one")
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_medium_layer_batched_prefill_equals_prefill_alone(folder, dtype):
+    """Six prompts of unequal length in one step (thousands of (token, expert) rows: several tiles per
+    expert in the grouped products) against the same prompts one at a time."""
+    from esp_b200.engine import StepEntry
+    eng = engine_for(folder, dtype, max_tokens=4096)
+    eng.rt.record_routing = False
+    try:
+        rng = np.random.default_rng(9)
+        prompts = [random_ids(rng, n, 1000) for n in (700, 64, 333, 1, 129, 450)]
+        slots = [eng.open() for _ in prompts]
+        together = eng.step([StepEntry(s, p, [len(p) - 1, 0]) for s, p in zip(slots, prompts)]).float().cpu().numpy()
+        for s in slots:
+            eng.close(s)
+        for i, p in enumerate(prompts):
+            s = eng.open()
+            alone = eng.step([StepEntry(s, p, [len(p) - 1, 0])]).float().cpu().numpy()
+            eng.close(s)
+            got = together[2 * i:2 * i + 2]
+            if dtype == "float32":
+                assert np.array_equal(got, alone), f"prompt {i}"
+            else:
+                scale = np.abs(alone).max()
+                assert np.abs(got - alone).max() <= 4 * 2.0 ** -8 * scale, f"prompt {i}"
+        assert eng.read_status() == 0
+    finally:
+        eng.rt.record_routing = True
