@@ -284,3 +284,109 @@ def test_schedule_may_run_a_layer_twice_and_share_a_cache(tmp_path):
     eng.close(s)
     assert np.array_equal(np.concatenate(rows), whole)
     assert np.isfinite(whole).all() and eng.read_status() == 0
+
+
+# ---------------------------------------------------------------------------
+# a toy position encoding and a toy routed feed-forward, both defined here
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class ScaledPositionSpec:
+    """Queries and keys of position p are multiplied by 1 + slope * p (a made-up encoding)."""
+    slope: float
+    kind: str = "toy_scaled_position"
+
+
+class ScaledPosition(Part):
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+
+    def rotate_and_store(self, qkv, bias, ctx, q_out, layer, nh, nkv, hd, status):
+        from esp_b200.csrc import ops
+        scale = 1.0 + self.spec.slope * ctx.tok_pos.float()
+        if bias is not None:
+            qkv.add_(bias)
+        qkv[:, :(nh + nkv) * hd].mul_(scale[:, None])
+        table = ctx.block_tables[layer.group]
+        ops.rope_kvwrite(qkv, None, ctx.tok_seq, ctx.tok_pos, None, None, 0, q_out, layer.k, layer.v, table, layer.page,
+                         nh, nkv, hd, layer.writes, status)
+
+
+@dataclass(frozen=True)
+class Top1FfnSpec:
+    hidden: int
+    choices: int
+    inner: int
+    prefix: str
+    kind: str = "toy_top1_ffn"
+
+
+class Top1Ffn(Part):
+    """Each token goes to the one of ``choices`` small MLPs whose key has the largest dot product with it."""
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.keys = self.w_in = self.w_out = None
+
+    def param_specs(self):
+        s, p = self.spec, self.spec.prefix
+        return [ParamSpec(p + "keys", (s.choices, s.hidden), "matrix"),
+                ParamSpec(p + "w_in", (s.choices * s.inner, s.hidden), "matrix"),
+                ParamSpec(p + "w_out", (s.choices * s.hidden, s.inner), "matrix")]
+
+    def allocate(self, stored, rt):
+        s, p, f32 = self.spec, self.spec.prefix, dict(dtype=torch.float32, device=rt.device)
+        self.keys = torch.empty(s.choices, s.hidden, **f32)
+        self.w_in = torch.empty(s.choices * s.inner, s.hidden, **f32)
+        self.w_out = torch.empty(s.choices * s.hidden, s.inner, **f32)
+        return {p + "keys": self.keys, p + "w_in": self.w_in, p + "w_out": self.w_out}
+
+    def forward(self, h, ctx, h32=None):
+        s = self.spec
+        x = h.float()
+        choice = (x @ self.keys.t()).argmax(-1)
+        out = torch.zeros(x.shape[0], s.hidden, device=x.device)
+        for c in range(s.choices):
+            rows = (choice == c).nonzero()[:, 0]
+            if rows.numel():
+                w_in, w_out = self.w_in[c * s.inner:(c + 1) * s.inner], self.w_out[c * s.hidden:(c + 1) * s.hidden]
+                out[rows] = torch.relu(x[rows] @ w_in.t()) @ w_out.t()
+        return out
+
+
+class ToyAttentionConfig:
+    """Attention with the toy position encoding, the toy routed feed-forward, two layers."""
+
+    def plan(self):
+        hidden, blocks = 64, []
+        for i in range(2):
+            p = f"t.{i}."
+            mixer = AttentionSpec(hidden, 4, 2, 16, True, False, None, ScaledPositionSpec(0.01), p + "attn.")
+            blocks.append(BlockSpec(mixer, Top1FfnSpec(hidden, 3, 40, p + "ffn."),
+                                    NormSpec("rmsnorm", hidden, 1e-6, p + "n1.weight"),
+                                    NormSpec("rmsnorm", hidden, 1e-6, p + "n2.weight")))
+        return ModelPlan("ToyScaledTop1", hidden, 90, 256, blocks, [ScheduleEntry(0), ScheduleEntry(1)],
+                         NormSpec("rmsnorm", hidden, 1e-6, "t.norm.weight"), "t.embed.weight", None)
+
+
+def test_toy_position_encoding_and_toy_routed_ffn_run_through_the_engine():
+    """Parts of two more families, registered from outside: another position encoding (used by the library's
+    own attention) and a feed-forward with routing of its own; whole prompt equals token by token."""
+    register("position", "toy_scaled_position", ScaledPosition)
+    register("ffn", "toy_top1_ffn", Top1Ffn)
+    eng = Engine.from_random(ToyAttentionConfig(), seed=3, init=InitSpec(0.2, 0.05, 0.0), dtype="float32", max_tokens=512)
+    toks = [int(t) for t in np.random.default_rng(1).integers(0, 90, 70)]
+    s = eng.open()
+    whole = eng.step([StepEntry(s, toks, list(range(70)))]).cpu().numpy()
+    eng.close(s)
+    s = eng.open()
+    rows = [eng.step([StepEntry(s, toks[:33], list(range(33)))]).cpu().numpy()]
+    rows += [eng.step([StepEntry(s, [t], [0])]).cpu().numpy() for t in toks[33:]]
+    eng.close(s)
+    cut = np.concatenate(rows)
+    assert np.isfinite(whole).all() and eng.read_status() == 0
+    assert np.abs(cut - whole).max() <= 1e-5 * np.abs(whole).max()
+    # the encoding is felt: the same token at another position gives other logits
+    s = eng.open()
+    a = eng.step([StepEntry(s, [5, 7, 7], [1, 2])]).cpu().numpy()
+    eng.close(s)
+    assert np.abs(a[0] - a[1]).max() > 1e-4
