@@ -160,7 +160,7 @@ class MoeSwiGluShared(Part):
         perm_weight = ws.get("moe_perm_weight", (n * k,), torch.float32)
         inverse = ws.get("moe_inverse", (n, k), torch.int32)
         tiles = None
-        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E):
+        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E) and not grouped_uses_tc05(h, self.w_gate_up, n * k):
             # few tokens: router and permutation in two short launches
             logits = ws.get("moe_logits", (n, E + 1), torch.float32)
             ops.route_small(router_in, self.w_router, self.w_shared_gate, logits, ids, wts, gate, k, s.norm_topk,

@@ -18,7 +18,7 @@ from ..csrc import ops
 import os
 
 SKINNY_ROWS = 16            # dense products with at most this many rows stream the weights once
-TC05_GROUPED_ROWS = 512     # grouped products with at least this many (token, expert) rows use TMA + tcgen05
+TC05_GROUPED_ROWS = int(os.environ.get("ESP_B200_TC05_ROWS", "128"))   # grouped products with at least this many (token, expert) rows use TMA + tcgen05
 # dense products with many rows: "own" = this library's TMA + tcgen05 kernel everywhere; "library" = cuBLAS
 # through torch; "mixed" = cuBLAS for plain products, this library's kernel where SwiGLU is fused into it
 DENSE_GEMM = os.environ.get("ESP_B200_DENSE_GEMM", "mixed")
