@@ -280,6 +280,260 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
     }
 }
 
+// ---- the same for several query heads per key/value head (grouped-query attention) ---------------------
+// With G >= 3 heads sharing the keys, multiply-adds on the CUDA cores cost more than the loads, so both
+// products run on the tensor cores (mma.sync m16n8k16): the block's up to 16 heads are the 16-row operand.
+// Scores: warp w takes keys 16w..16w+15 of the page, key fragments by ldmatrix from the page as it lies in
+// shared memory.  Softmax: warp w owns heads w, w+4, ...; probabilities go to shared memory in bfloat16.
+// Values: warp w takes a quarter of the head's columns, value fragments by ldmatrix.trans.
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int MMA_HEADS = 16;
+
+template <int HD, int SPLIT>
+__global__ void __launch_bounds__(THREADS)
+attn_split_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                      bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                      int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                      const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv,
+                      int window, int n_splits, int* __restrict__ status) {
+    constexpr int ITEM = PAGE_KEYS * HD;
+    constexpr int NBW = HD / 32;                   // 8-column blocks of the head that one warp accumulates
+    constexpr int PLD = PAGE_KEYS + 8;             // row stride of the probabilities (bfloat16)
+    extern __shared__ __align__(128) unsigned char dyn[];
+    bf16* ring = reinterpret_cast<bf16*>(dyn);     // [RING][ITEM]
+    __shared__ __align__(8) unsigned long long full_bar[RING];
+    __shared__ float s_s[MMA_HEADS][PAGE_KEYS];
+    __shared__ __align__(16) bf16 p_s[MMA_HEADS][PLD];
+    __shared__ float m_s[MMA_HEADS], l_s[MMA_HEADS], scale_s[MMA_HEADS];
+    __shared__ int item_ok[RING];
+
+    const int n = blockIdx.x, split = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g8 = lane >> 2, tg = lane & 3;
+    const int group = nh / nkv, blocks_per_kv = (group + MMA_HEADS - 1) / MMA_HEADS;
+    const int kvh = blockIdx.y / blocks_per_kv, h0 = kvh * group + (blockIdx.y % blocks_per_kv) * MMA_HEADS;
+    const int heads = min(MMA_HEADS, (kvh + 1) * group - h0);
+    const int pos = tok_pos[n], seq = tok_seq[n];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int j0 = max(lo, split * SPLIT), j1 = min(pos, split * SPLIT + SPLIT - 1);
+    if (j0 > j1) return;
+    const int first_page = j0 / PAGE_KEYS, n_pg = j1 / PAGE_KEYS - first_page + 1, n_items = 2 * n_pg;
+
+    if (tid < MMA_HEADS) {
+        m_s[tid] = -INFINITY;
+        l_s[tid] = 0.f;
+    }
+    if (tid == 0) {
+        for (int r = 0; r < RING; r++) mbar_init(&full_bar[r], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    // the query fragments of the block's heads (rows beyond ``heads`` are zero)
+    unsigned qa[HD / 16][4];
+    {
+        const bf16* q0 = q + ((size_t)n * nh + h0 + g8) * HD;
+        const bf16* q1 = q + ((size_t)n * nh + h0 + g8 + 8) * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++) {
+            const int c = kk * 16 + tg * 2;
+            qa[kk][0] = g8 < heads ? *reinterpret_cast<const unsigned*>(q0 + c) : 0u;
+            qa[kk][1] = g8 + 8 < heads ? *reinterpret_cast<const unsigned*>(q1 + c) : 0u;
+            qa[kk][2] = g8 < heads ? *reinterpret_cast<const unsigned*>(q0 + c + 8) : 0u;
+            qa[kk][3] = g8 + 8 < heads ? *reinterpret_cast<const unsigned*>(q1 + c + 8) : 0u;
+        }
+    }
+    __syncthreads();
+
+    auto issue = [&](int item) {
+        const int slot = item % RING;
+        int pg = block_table[(size_t)seq * table_stride + first_page + item / 2];
+        const bool ok = pg >= 0 && pg < n_pages;
+        if (!ok) atomicOr(status, ESP_STATUS_BAD_INDEX);
+        item_ok[slot] = ok ? 1 : 0;
+        if (ok) {
+            const bf16* src = ((item & 1) ? v_cache : k_cache) + ((size_t)pg * nkv + kvh) * ITEM;
+            mbar_expect_tx(&full_bar[slot], ITEM * 2);
+            bulk_copy(ring + (size_t)slot * ITEM, src, ITEM * 2, &full_bar[slot]);
+        } else {
+            mbar_arrive(&full_bar[slot]);
+        }
+    };
+    int issued = 0;
+    if (tid == 0) {
+        for (; issued < min(RING, n_items); issued++) issue(issued);
+    }
+
+    const float root = sqrtf((float)HD);
+    float o[NBW][4];
+#pragma unroll
+    for (int i = 0; i < NBW; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) o[i][j] = 0.f;
+    bool failed = false;
+
+    for (int pi = 0; pi < n_pg; pi++) {
+        const int key0 = (first_page + pi) * PAGE_KEYS;
+        const int item_k = 2 * pi, slot_k = item_k % RING;
+        if (__syncthreads_or(!mbar_wait(&full_bar[slot_k], (item_k / RING) & 1))) { failed = true; break; }
+        const bf16* kp = ring + (size_t)slot_k * ITEM;
+        const bool page_ok = item_ok[slot_k] != 0;
+        // ---- scores of keys 16*warp .. 16*warp+15 for all heads
+        float sc[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) sc[i][j] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++) {
+            unsigned kf[4];
+            ldsm_x4(kf, kp + (size_t)(warp * 16 + (lane & 7) + (lane >> 4) * 8) * HD + kk * 16 + ((lane >> 3) & 1) * 8);
+            mma_16816(sc[0], qa[kk], kf[0], kf[1]);
+            mma_16816(sc[1], qa[kk], kf[2], kf[3]);
+        }
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int t = warp * 16 + nb * 8 + tg * 2 + (j & 1), key = key0 + t;
+                const bool live = page_ok && key >= j0 && key <= j1;
+                s_s[g8 + (j >> 1) * 8][t] = live ? sc[nb][j] / root : -INFINITY;
+            }
+        __syncthreads();                           // scores are written; the key buffer is free
+        if (tid == 0 && issued < n_items) issue(issued++);
+        // ---- running maximum and sum: warp w owns heads w, w+4, w+8, w+12
+        for (int h = warp; h < MMA_HEADS; h += 4) {
+            const float a = s_s[h][lane], b = s_s[h][lane + 32];
+            const float m_old = m_s[h];
+            const float m_new = fmaxf(m_old, warp_max(fmaxf(a, b)));
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float pa = a == -INFINITY ? 0.f : expf(a - m_use), pb = b == -INFINITY ? 0.f : expf(b - m_use);
+            const float sum = warp_sum(pa + pb);
+            p_s[h][lane] = __float2bfloat16_rn(pa);
+            p_s[h][lane + 32] = __float2bfloat16_rn(pb);
+            if (lane == 0) {
+                const float scale = expf(m_old - m_use);
+                scale_s[h] = scale;
+                l_s[h] = l_s[h] * scale + sum;
+                m_s[h] = m_new;
+            }
+        }
+        // ---- weighted values: this warp's quarter of the columns
+        const int item_v = 2 * pi + 1, slot_v = item_v % RING;
+        if (__syncthreads_or(!mbar_wait(&full_bar[slot_v], (item_v / RING) & 1))) { failed = true; break; }
+        const bf16* vp = ring + (size_t)slot_v * ITEM;
+        const float sc_lo = scale_s[g8], sc_hi = scale_s[g8 + 8];
+#pragma unroll
+        for (int i = 0; i < NBW; i++) {
+            o[i][0] *= sc_lo;
+            o[i][1] *= sc_lo;
+            o[i][2] *= sc_hi;
+            o[i][3] *= sc_hi;
+        }
+        if (item_ok[slot_v]) {
+#pragma unroll
+            for (int kt = 0; kt < PAGE_KEYS / 16; kt++) {
+                unsigned pf[4];
+                ldsm_x4(pf, &p_s[lane & 15][kt * 16 + (lane >> 4) * 8]);
+#pragma unroll
+                for (int nb2 = 0; nb2 < NBW / 2; nb2++) {
+                    unsigned vf[4];
+                    ldsm_x4_trans(vf, vp + (size_t)(kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * HD + warp * (HD / 4) +
+                                          nb2 * 16 + (lane >> 4) * 8);
+                    mma_16816(o[2 * nb2], pf, vf[0], vf[1]);
+                    mma_16816(o[2 * nb2 + 1], pf, vf[2], vf[3]);
+                }
+            }
+        }
+        __syncthreads();                           // the value buffer, the scores and the probabilities are free
+        if (tid == 0 && issued < n_items) issue(issued++);
+    }
+    if (failed) {
+        if (tid == 0) {
+            atomicOr(status, ESP_STATUS_WAIT_EXPIRED);
+            for (int it = max(0, issued - RING); it < issued; it++) mbar_wait(&full_bar[it % RING], (it / RING) & 1);
+        }
+        return;
+    }
+    // ---- partial results: rows g8 and g8+8, this warp's columns
+#pragma unroll
+    for (int i = 0; i < NBW; i++) {
+        const int d = warp * (HD / 4) + i * 8 + tg * 2;
+        if (g8 < heads) {
+            float* po = part_o + (((size_t)n * nh + h0 + g8) * n_splits + split) * HD + d;
+            po[0] = o[i][0];
+            po[1] = o[i][1];
+        }
+        if (g8 + 8 < heads) {
+            float* po = part_o + (((size_t)n * nh + h0 + g8 + 8) * n_splits + split) * HD + d;
+            po[0] = o[i][2];
+            po[1] = o[i][3];
+        }
+    }
+    if (tid < heads) {
+        float* ml = part_ml + (((size_t)n * nh + h0 + tid) * n_splits + split) * 2;
+        ml[0] = m_s[tid];
+        ml[1] = l_s[tid];
+    }
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    const int s0 = lo / SPLIT, s1 = pos / SPLIT;
+    if (tid == 0) {
+        int* c = counters + (size_t)n * gridDim.y + blockIdx.y;
+        const int done = atomicAdd(c, 1);
+        is_last = done == s1 - s0;
+        if (is_last) *c = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int i = tid; i < heads * HD; i += THREADS) {
+        const int g = i / HD, d = i - g * HD;
+        const float* ml = part_ml + ((size_t)n * nh + h0 + g) * n_splits * 2;
+        const float* po = part_o + ((size_t)n * nh + h0 + g) * n_splits * HD;
+        float mx = -INFINITY;
+        for (int sp = s0; sp <= s1; sp++) mx = fmaxf(mx, __ldcg(ml + 2 * sp));
+        float denom = 0.f, num = 0.f;
+        for (int sp = s0; sp <= s1; sp++) {
+            const float m_sp = __ldcg(ml + 2 * sp);
+            const float w = m_sp == -INFINITY ? 0.f : expf(m_sp - mx);
+            denom += __ldcg(ml + 2 * sp + 1) * w;
+            num += __ldcg(po + (size_t)sp * HD + d) * w;
+        }
+        out[((size_t)n * nh + h0 + g) * HD + d] = __float2bfloat16_rn(denom > 0.f ? num / denom : 0.f);
+    }
+}
+
+template <int HD, int SPLIT>
+int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
+                     const int* tok_seq, const int* tok_pos, const int* table, int stride, int n_pages, int page,
+                     int n_tokens, int nh, int nkv, int window, int n_splits, int* status, cudaStream_t stream) {
+    const size_t dyn = (size_t)RING * PAGE_KEYS * HD * sizeof(bf16);
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel<HD, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    const int group = nh / nkv;
+    dim3 grid(n_tokens, nkv * ((group + MMA_HEADS - 1) / MMA_HEADS), n_splits);
+    attn_split_mma_kernel<HD, SPLIT><<<grid, THREADS, dyn, stream>>>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table,
+                                                                     stride, n_pages, page, nh, nkv, window, n_splits, status);
+    return esp_launch_status();
+}
+
 template <int HD, int GT, int SPLIT>
 int launch_split(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters, const int* tok_seq,
                  const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
@@ -308,15 +562,20 @@ int dispatch(int gt, int split, const bf16* q, const bf16* k, const bf16* v, bf1
              const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
              int window, int n_splits, int* status, cudaStream_t stream) {
     int rc;
+    if (gt > 2) {
+        // three or more heads per key/value head: both products on the tensor cores
+        return split == 256 ? launch_split_mma<HD, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
+                                                         page, n_tokens, nh, nkv, window, n_splits, status, stream)
+                            : launch_split_mma<HD, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
+                                                         page, n_tokens, nh, nkv, window, n_splits, status, stream);
+    }
 #define ESP_SPLIT(GT)                                                                                                  \
     (split == 256 ? launch_split<HD, GT, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
                                               nh, nkv, window, n_splits, status, stream)                                 \
                   : launch_split<HD, GT, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
                                               nh, nkv, window, n_splits, status, stream))
     if (gt == 1) rc = ESP_SPLIT(1);
-    else if (gt == 2) rc = ESP_SPLIT(2);
-    else if (gt == 4) rc = ESP_SPLIT(4);
-    else rc = ESP_SPLIT(8);
+    else rc = ESP_SPLIT(2);
 #undef ESP_SPLIT
     return rc;
 }
