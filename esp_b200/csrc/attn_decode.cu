@@ -1,31 +1,24 @@
 // Decode attention over the paged bfloat16 cache (pages of 64 positions), split over the keys.
 //
-// One block = one token row, one key/value head (with up to GT of the query
-// heads that share it) and one split of SPLIT consecutive key positions
-// aligned to absolute multiples of SPLIT.  The block streams its pages' keys and
-// values once from HBM with bulk copies, keeps scores, softmax and sums in float, and
-// writes an unnormalised partial result (running maximum, sum, weighted
-// values) to scratch.  A second kernel combines a row's splits in ascending
-// order.  Which splits a row has depends on its position (and window) alone,
-// so the result does not depend on the batch around it.
+// One block = one token row, one key/value head with the query heads that share
+// it, and one split of SPLIT consecutive key positions aligned to absolute
+// multiples of SPLIT.  The block streams its pages' keys and values once from
+// HBM by TMA, keeps scores, softmax and sums in float, and writes an
+// unnormalised partial result (running maximum, sum, weighted values) to
+// scratch.  The last block of a row to finish combines the row's splits in
+// ascending order.  Which splits a row has depends on its position (and window)
+// alone, so the result does not depend on the batch around it.
 //
 // The query at position a sees key j iff j <= a and (window == 0 or a - j < window);
 // score = dot(q, k) / sqrt(hd).
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace {
 constexpr int THREADS = 128;
 
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-    const unsigned w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
-// ---- bulk-copy helpers (one thread issues, an mbarrier counts the bytes) -----------------------------
+// ---- mbarrier helpers (one thread issues the copies, an mbarrier counts their bytes) ---------------------
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
@@ -51,241 +44,17 @@ __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
     }
     return false;
 }
-__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, void* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
-}
-
-// One block = one token row, one key/value head (with up to GT query heads) and one split of SPLIT key
-// positions, i.e. SPLIT / 64 pages.  The pages' keys and values (64 x HD each, contiguous in the cache)
-// are fetched by bulk copies into a ring of RING shared-memory buffers while earlier pages are being
-// used: scores, a running maximum and sum (updated page by page) and the weighted values, all in
-// float.  Pages are walked in ascending order, so a row's arithmetic depends on its position alone.
 constexpr int PAGE_KEYS = 64, RING = 2;
 
-template <int HD, int GT, int SPLIT>
-__global__ void __launch_bounds__(THREADS)
-attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                  bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                  int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                  const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv,
-                  int window, int n_splits, int* __restrict__ status) {
-    constexpr int PIECES = HD / 8;                 // 16-byte pieces of a key or value row
-    constexpr int PER_LANE = HD / 64;              // pieces each of the 8 lanes of a key group handles
-    constexpr int KG = THREADS / PIECES;           // key groups of the value pass
-    constexpr int ITEM = PAGE_KEYS * HD;           // elements of one page's keys (or values)
-    extern __shared__ __align__(128) unsigned char dyn[];
-    bf16* ring = reinterpret_cast<bf16*>(dyn);                                        // [RING][ITEM]
-    float* o_red = reinterpret_cast<float*>(dyn);                                     // [KG][GT][HD], after the ring is done
-    __shared__ __align__(8) unsigned long long full_bar[RING];
-    __shared__ float q_s[GT][HD];
-    __shared__ float s_s[GT][PAGE_KEYS];
-    __shared__ int item_ok[RING];
-
-    const int n = blockIdx.x, split = blockIdx.z, tid = threadIdx.x, lane = tid & 31;
-    const int group = nh / nkv, blocks_per_kv = (group + GT - 1) / GT;
-    const int kvh = blockIdx.y / blocks_per_kv, h0 = kvh * group + (blockIdx.y % blocks_per_kv) * GT;
-    const int heads = min(GT, (kvh + 1) * group - h0);
-    const int pos = tok_pos[n], seq = tok_seq[n];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int j0 = max(lo, split * SPLIT), j1 = min(pos, split * SPLIT + SPLIT - 1);
-    if (j0 > j1) return;                           // this row has no keys in this split
-    const int first_page = j0 / PAGE_KEYS, n_pg = j1 / PAGE_KEYS - first_page + 1, n_items = 2 * n_pg;
-
-    for (int i = tid; i < GT * HD; i += THREADS) {
-        const int g = i / HD, d = i - g * HD;
-        q_s[g][d] = g < heads ? __bfloat162float(q[((size_t)n * nh + h0 + g) * HD + d]) : 0.f;
-    }
-    if (tid == 0) {
-        for (int r = 0; r < RING; r++) mbar_init(&full_bar[r], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    __syncthreads();
-
-    // item 2p = keys of page p of the block, item 2p+1 = its values
-    auto issue = [&](int item) {
-        const int slot = item % RING;
-        int pg = block_table[(size_t)seq * table_stride + first_page + item / 2];
-        const bool ok = pg >= 0 && pg < n_pages;
-        if (!ok) atomicOr(status, ESP_STATUS_BAD_INDEX);
-        item_ok[slot] = ok ? 1 : 0;
-        if (ok) {
-            const bf16* src = ((item & 1) ? v_cache : k_cache) + ((size_t)pg * nkv + kvh) * ITEM;
-            mbar_expect_tx(&full_bar[slot], ITEM * 2);
-            bulk_copy(ring + (size_t)slot * ITEM, src, ITEM * 2, &full_bar[slot]);
-        } else {
-            mbar_arrive(&full_bar[slot]);          // nothing to fetch: the waiters go on and skip the page
-        }
-    };
-    int issued = 0;
-    if (tid == 0) {
-        for (; issued < min(RING, n_items); issued++) issue(issued);
-    }
-
-    const float root = sqrtf((float)HD);
-    const int sub = tid & 7, slot8 = tid >> 3;     // lane within the key group, key slot 0..15
-    const int piece = tid % PIECES, kg = tid / PIECES;
-    // with one or two query heads per block the lane's share of q lives in registers
-    constexpr bool Q_REGS = GT <= 2;
-    float qr[Q_REGS ? GT : 1][Q_REGS ? PER_LANE * 8 : 1];
-    if (Q_REGS) {
-#pragma unroll
-        for (int g = 0; g < GT; g++)
-#pragma unroll
-            for (int i = 0; i < PER_LANE; i++)
-#pragma unroll
-                for (int e = 0; e < 8; e++) qr[Q_REGS ? g : 0][Q_REGS ? i * 8 + e : 0] = q_s[g][(sub + 8 * i) * 8 + e];
-    }
-    float m_run[GT], l_run[GT], acc[GT][8];
-#pragma unroll
-    for (int g = 0; g < GT; g++) {
-        m_run[g] = -INFINITY;
-        l_run[g] = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; e++) acc[g][e] = 0.f;
-    }
-    bool failed = false;
-
-    for (int pi = 0; pi < n_pg; pi++) {
-        const int key0 = (first_page + pi) * PAGE_KEYS;
-        // ---- scores of this page's 64 keys -------------------------------------------------------
-        const int item_k = 2 * pi, slot_k = item_k % RING;
-        if (__syncthreads_or(!mbar_wait(&full_bar[slot_k], (item_k / RING) & 1))) { failed = true; break; }
-        const bf16* kp = ring + (size_t)slot_k * ITEM;
-        const bool page_ok = item_ok[slot_k] != 0;
-#pragma unroll
-        for (int pass = 0; pass < PAGE_KEYS / 16; pass++) {
-            const int t = pass * 16 + slot8, j = key0 + t;
-            const bool live = page_ok && j >= j0 && j <= j1;
-            float dot[GT];
-#pragma unroll
-            for (int g = 0; g < GT; g++) dot[g] = 0.f;
-            if (live) {
-#pragma unroll
-                for (int i = 0; i < PER_LANE; i++) {
-                    const int pc = sub + 8 * i;
-                    float kf[8];
-                    unpack8(*reinterpret_cast<const uint4*>(kp + (size_t)t * HD + pc * 8), kf);
-#pragma unroll
-                    for (int g = 0; g < GT; g++)
-#pragma unroll
-                        for (int e = 0; e < 8; e++)
-                            dot[g] = fmaf(Q_REGS ? qr[Q_REGS ? g : 0][Q_REGS ? i * 8 + e : 0] : q_s[g][pc * 8 + e], kf[e], dot[g]);
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < GT; g++) {
-                float v = dot[g];
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                v += __shfl_xor_sync(0xffffffffu, v, 4);
-                if (sub == 0) s_s[g][t] = live ? v / root : -INFINITY;
-            }
-        }
-        __syncthreads();                           // scores are written; the key buffer is free
-        if (tid == 0 && issued < n_items) issue(issued++);
-        // ---- running maximum and sum (every warp computes the same values) ---------------------------
-        float scale[GT], m_use[GT];
-#pragma unroll
-        for (int g = 0; g < GT; g++) {
-            const float a = s_s[g][lane], b = s_s[g][lane + 32];
-            const float m_new = fmaxf(m_run[g], warp_max(fmaxf(a, b)));
-            m_use[g] = m_new == -INFINITY ? 0.f : m_new;
-            scale[g] = expf(m_run[g] - m_use[g]);                      // 0 while nothing has been seen
-            const float pa = a == -INFINITY ? 0.f : expf(a - m_use[g]), pb = b == -INFINITY ? 0.f : expf(b - m_use[g]);
-            l_run[g] = l_run[g] * scale[g] + warp_sum(pa + pb);
-            m_run[g] = m_new;
-        }
-        // ---- weighted values ------------------------------------------------------------------------
-        const int item_v = 2 * pi + 1, slot_v = item_v % RING;
-        if (__syncthreads_or(!mbar_wait(&full_bar[slot_v], (item_v / RING) & 1))) { failed = true; break; }
-        const bf16* vp = ring + (size_t)slot_v * ITEM;
-#pragma unroll
-        for (int g = 0; g < GT; g++)
-#pragma unroll
-            for (int e = 0; e < 8; e++) acc[g][e] *= scale[g];
-        if (kg < KG && item_ok[slot_v]) {
-            for (int t = kg; t < PAGE_KEYS; t += KG) {
-                float vf[8];
-                unpack8(*reinterpret_cast<const uint4*>(vp + (size_t)t * HD + piece * 8), vf);
-#pragma unroll
-                for (int g = 0; g < GT; g++) {
-                    const float sc = s_s[g][t];
-                    const float pw = sc == -INFINITY ? 0.f : expf(sc - m_use[g]);
-#pragma unroll
-                    for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pw, vf[e], acc[g][e]);
-                }
-            }
-        }
-        __syncthreads();                           // the value buffer and the scores are free
-        if (tid == 0 && issued < n_items) issue(issued++);
-    }
-    if (failed) {
-        if (tid == 0) {
-            atomicOr(status, ESP_STATUS_WAIT_EXPIRED);
-            // let this block's own copies land before its shared memory is given up
-            for (int it = max(0, issued - RING); it < issued; it++) mbar_wait(&full_bar[it % RING], (it / RING) & 1);
-        }
-        return;
-    }
-    // ---- combine the key groups and store the partial result -------------------------------------------
-    if (kg < KG) {
-#pragma unroll
-        for (int g = 0; g < GT; g++)
-#pragma unroll
-            for (int e = 0; e < 8; e++) o_red[((size_t)kg * GT + g) * HD + piece * 8 + e] = acc[g][e];
-    }
-    __syncthreads();
-    for (int i = tid; i < heads * HD; i += THREADS) {
-        const int g = i / HD, d = i - g * HD;
-        float v = 0.f;
-#pragma unroll
-        for (int c = 0; c < KG; c++) v += o_red[((size_t)c * GT + g) * HD + d];
-        part_o[(((size_t)n * nh + h0 + g) * n_splits + split) * HD + d] = v;
-    }
-    if (tid < heads) {
-        float* ml = part_ml + (((size_t)n * nh + h0 + tid) * n_splits + split) * 2;
-        ml[0] = m_run[tid];
-        ml[1] = l_run[tid];
-    }
-    // ---- the last block of this (row, head group) to finish combines the row's splits, in ascending order.
-    // ``counters`` holds one zero per (row, head group) between launches: the combining block puts it back.
-    __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    const int s0 = lo / SPLIT, s1 = pos / SPLIT;
-    if (tid == 0) {
-        int* c = counters + (size_t)n * gridDim.y + blockIdx.y;
-        const int done = atomicAdd(c, 1);
-        is_last = done == s1 - s0;
-        if (is_last) *c = 0;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    for (int i = tid; i < heads * HD; i += THREADS) {
-        const int g = i / HD, d = i - g * HD;
-        const float* ml = part_ml + ((size_t)n * nh + h0 + g) * n_splits * 2;
-        const float* po = part_o + ((size_t)n * nh + h0 + g) * n_splits * HD;
-        float mx = -INFINITY;
-        for (int sp = s0; sp <= s1; sp++) mx = fmaxf(mx, __ldcg(ml + 2 * sp));
-        float denom = 0.f, num = 0.f;
-        for (int sp = s0; sp <= s1; sp++) {
-            const float m_sp = __ldcg(ml + 2 * sp);
-            const float w = m_sp == -INFINITY ? 0.f : expf(m_sp - mx);
-            denom += __ldcg(ml + 2 * sp + 1) * w;
-            num += __ldcg(po + (size_t)sp * HD + d) * w;
-        }
-        out[((size_t)n * nh + h0 + g) * HD + d] = __float2bfloat16_rn(denom > 0.f ? num / denom : 0.f);
-    }
-}
-
-// ---- the same for several query heads per key/value head (grouped-query attention) ---------------------
-// With G >= 3 heads sharing the keys, multiply-adds on the CUDA cores cost more than the loads, so both
-// products run on the tensor cores (mma.sync m16n8k16): the block's up to 16 heads are the 16-row operand.
-// Scores: warp w takes keys 16w..16w+15 of the page, key fragments by ldmatrix from the page as it lies in
-// shared memory.  Softmax: warp w owns heads w, w+4, ...; probabilities go to shared memory in bfloat16.
-// Values: warp w takes a quarter of the head's columns, value fragments by ldmatrix.trans.
+// One block = one token row, one key/value head with the (up to 16) query heads that share it, and one split
+// of SPLIT key positions, i.e. SPLIT / 64 pages.  The pages' keys and values are fetched by TMA into a ring
+// of RING shared-memory buffers while earlier pages are being used.  Both products run on the tensor cores
+// (mma.sync m16n8k16) with the block's heads as the 16-row operand, so a page costs the same whether one
+// head or sixteen read it.  Scores: warp w takes keys 16w..16w+15 of the page, key fragments by ldmatrix.
+// Softmax: a running maximum and sum per head, updated page by page in float; warp w owns heads w, w+4, ...;
+// probabilities go to shared memory in bfloat16.  Values: warp w takes a quarter of the head's columns,
+// value fragments by ldmatrix.trans.  Pages are walked in ascending order, so a row's arithmetic depends on
+// its position alone.
 __device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
@@ -303,18 +72,30 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4],
 
 constexpr int MMA_HEADS = 16;
 
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, void* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+// A page's keys (or values) lie in shared memory as HD/64 sub-tiles of 64 rows x 64 columns (128 bytes a
+// row), written by TMA with the 128-byte swizzle: the 16-byte piece c of row r sits at piece c ^ (r % 8).
+// That makes the 8 rows of an ldmatrix fall into distinct banks.  d is a multiple of 8.
+__device__ __forceinline__ const bf16* tile_at(const bf16* tile, int r, int d) {
+    return tile + (d >> 6) * (PAGE_KEYS * 64) + r * 64 + ((((d & 63) >> 3) ^ (r & 7)) << 3);
+}
+
 template <int HD, int SPLIT>
 __global__ void __launch_bounds__(THREADS)
-attn_split_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                      bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv,
                       int window, int n_splits, int* __restrict__ status) {
     constexpr int ITEM = PAGE_KEYS * HD;
     constexpr int NBW = HD / 32;                   // 8-column blocks of the head that one warp accumulates
     constexpr int PLD = PAGE_KEYS + 8;             // row stride of the probabilities (bfloat16)
-    extern __shared__ __align__(128) unsigned char dyn[];
-    bf16* ring = reinterpret_cast<bf16*>(dyn);     // [RING][ITEM]
+    extern __shared__ unsigned char dyn_raw[];
+    bf16* ring = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(dyn_raw) + 1023) & ~(uintptr_t)1023);   // [RING][ITEM]
     __shared__ __align__(8) unsigned long long full_bar[RING];
     __shared__ float s_s[MMA_HEADS][PAGE_KEYS];
     __shared__ __align__(16) bf16 p_s[MMA_HEADS][PLD];
@@ -363,9 +144,12 @@ attn_split_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
         if (!ok) atomicOr(status, ESP_STATUS_BAD_INDEX);
         item_ok[slot] = ok ? 1 : 0;
         if (ok) {
-            const bf16* src = ((item & 1) ? v_cache : k_cache) + ((size_t)pg * nkv + kvh) * ITEM;
+            const int row0 = (pg * nkv + kvh) * PAGE_KEYS;       // the page's first row in the cache seen as [rows, HD]
             mbar_expect_tx(&full_bar[slot], ITEM * 2);
-            bulk_copy(ring + (size_t)slot * ITEM, src, ITEM * 2, &full_bar[slot]);
+#pragma unroll
+            for (int sub = 0; sub < HD / 64; sub++)
+                tma_load_2d(ring + (size_t)slot * ITEM + sub * (PAGE_KEYS * 64), (item & 1) ? &map_v : &map_k, sub * 64, row0,
+                            &full_bar[slot]);
         } else {
             mbar_arrive(&full_bar[slot]);
         }
@@ -398,7 +182,7 @@ attn_split_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
 #pragma unroll
         for (int kk = 0; kk < HD / 16; kk++) {
             unsigned kf[4];
-            ldsm_x4(kf, kp + (size_t)(warp * 16 + (lane & 7) + (lane >> 4) * 8) * HD + kk * 16 + ((lane >> 3) & 1) * 8);
+            ldsm_x4(kf, tile_at(kp, warp * 16 + (lane & 7) + (lane >> 4) * 8, kk * 16 + ((lane >> 3) & 1) * 8));
             mma_16816(sc[0], qa[kk], kf[0], kf[1]);
             mma_16816(sc[1], qa[kk], kf[2], kf[3]);
         }
@@ -408,12 +192,12 @@ attn_split_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
             for (int j = 0; j < 4; j++) {
                 const int t = warp * 16 + nb * 8 + tg * 2 + (j & 1), key = key0 + t;
                 const bool live = page_ok && key >= j0 && key <= j1;
-                s_s[g8 + (j >> 1) * 8][t] = live ? sc[nb][j] / root : -INFINITY;
+                if (g8 + (j >> 1) * 8 < heads) s_s[g8 + (j >> 1) * 8][t] = live ? sc[nb][j] / root : -INFINITY;
             }
         __syncthreads();                           // scores are written; the key buffer is free
         if (tid == 0 && issued < n_items) issue(issued++);
         // ---- running maximum and sum: warp w owns heads w, w+4, w+8, w+12
-        for (int h = warp; h < MMA_HEADS; h += 4) {
+        for (int h = warp; h < heads; h += 4) {   // rows beyond ``heads`` feed accumulator rows that are never stored
             const float a = s_s[h][lane], b = s_s[h][lane + 32];
             const float m_old = m_s[h];
             const float m_new = fmaxf(m_old, warp_max(fmaxf(a, b)));
@@ -449,8 +233,8 @@ attn_split_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
 #pragma unroll
                 for (int nb2 = 0; nb2 < NBW / 2; nb2++) {
                     unsigned vf[4];
-                    ldsm_x4_trans(vf, vp + (size_t)(kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * HD + warp * (HD / 4) +
-                                          nb2 * 16 + (lane >> 4) * 8);
+                    ldsm_x4_trans(vf, tile_at(vp, kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                              warp * (HD / 4) + nb2 * 16 + (lane >> 4) * 8));
                     mma_16816(o[2 * nb2], pf, vf[0], vf[1]);
                     mma_16816(o[2 * nb2 + 1], pf, vf[2], vf[3]);
                 }
@@ -516,11 +300,42 @@ attn_split_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
     }
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The cache of one layer seen as a matrix [pages * kv heads * 64 rows, hd]; boxes of 64 rows x 64 columns.
+int make_cache_map(CUtensorMap* map, const void* base, unsigned long long rows, int hd) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return (int)cudaErrorNotSupported;
+        fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)hd, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    const cuuint32_t box[2] = {64, PAGE_KEYS};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 template <int HD, int SPLIT>
 int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
                      const int* tok_seq, const int* tok_pos, const int* table, int stride, int n_pages, int page,
                      int n_tokens, int nh, int nkv, int window, int n_splits, int* status, cudaStream_t stream) {
-    const size_t dyn = (size_t)RING * PAGE_KEYS * HD * sizeof(bf16);
+    CUtensorMap map_k, map_v;
+    const unsigned long long rows = (unsigned long long)n_pages * nkv * PAGE_KEYS;
+    int rc = make_cache_map(&map_k, k, rows, HD);
+    if (rc) return rc;
+    rc = make_cache_map(&map_v, v, rows, HD);
+    if (rc) return rc;
+    const size_t dyn = (size_t)RING * PAGE_KEYS * HD * sizeof(bf16) + 1024;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel<HD, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
@@ -529,55 +344,20 @@ int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, flo
     }
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + MMA_HEADS - 1) / MMA_HEADS), n_splits);
-    attn_split_mma_kernel<HD, SPLIT><<<grid, THREADS, dyn, stream>>>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table,
-                                                                     stride, n_pages, page, nh, nkv, window, n_splits, status);
-    return esp_launch_status();
-}
-
-template <int HD, int GT, int SPLIT>
-int launch_split(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters, const int* tok_seq,
-                 const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
-                 int window, int n_splits, int* status, cudaStream_t stream) {
-    constexpr int KG = THREADS / (HD / 8);
-    constexpr size_t ring_bytes = (size_t)RING * PAGE_KEYS * HD * sizeof(bf16);
-    constexpr size_t red_bytes = (size_t)KG * GT * HD * sizeof(float);
-    const size_t dyn = ring_bytes > red_bytes ? ring_bytes : red_bytes;
-    static bool raised = false;        // static + dynamic shared memory can pass 48 KB: always opt in
-    if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<HD, GT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)dyn);
-        if (e != cudaSuccess) return (int)e;
-        raised = true;
-    }
-    const int group = nh / nkv;
-    dim3 grid(n_tokens, nkv * ((group + GT - 1) / GT), n_splits);
-    attn_split_kernel<HD, GT, SPLIT><<<grid, THREADS, dyn, stream>>>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
-                                                                     page, nh, nkv, window, n_splits, status);
+    attn_split_mma_kernel<HD, SPLIT><<<grid, THREADS, dyn, stream>>>(map_k, map_v, q, out, po, pml, counters, tok_seq, tok_pos,
+                                                                     table, stride, n_pages, page, nh, nkv, window, n_splits,
+                                                                     status);
     return esp_launch_status();
 }
 
 template <int HD>
-int dispatch(int gt, int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
-             const int* tok_seq,
-             const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh, int nkv,
-             int window, int n_splits, int* status, cudaStream_t stream) {
-    int rc;
-    if (gt > 2) {
-        // three or more heads per key/value head: both products on the tensor cores
-        return split == 256 ? launch_split_mma<HD, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
-                                                         page, n_tokens, nh, nkv, window, n_splits, status, stream)
-                            : launch_split_mma<HD, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
-                                                         page, n_tokens, nh, nkv, window, n_splits, status, stream);
-    }
-#define ESP_SPLIT(GT)                                                                                                  \
-    (split == 256 ? launch_split<HD, GT, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
-                                              nh, nkv, window, n_splits, status, stream)                                 \
-                  : launch_split<HD, GT, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages, page, n_tokens, \
-                                              nh, nkv, window, n_splits, status, stream))
-    if (gt == 1) rc = ESP_SPLIT(1);
-    else rc = ESP_SPLIT(2);
-#undef ESP_SPLIT
-    return rc;
+int dispatch(int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
+             const int* tok_seq, const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh,
+             int nkv, int window, int n_splits, int* status, cudaStream_t stream) {
+    return split == 256 ? launch_split_mma<HD, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
+                                                     page, n_tokens, nh, nkv, window, n_splits, status, stream)
+                        : launch_split_mma<HD, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
+                                                     page, n_tokens, nh, nkv, window, n_splits, status, stream);
 }
 }  // namespace
 
@@ -594,9 +374,7 @@ ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_ca
     if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || (split != 256 && split != 512) ||
         page != PAGE_KEYS)
         return (int)cudaErrorInvalidValue;
-    const int group = nh / nkv;
-    const int gt = group >= 8 ? 8 : group >= 3 ? 4 : group;      // 1, 2, 4 or 8 heads per block
-#define ESP_HD(HD) return dispatch<HD>(gt, split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
+#define ESP_HD(HD) return dispatch<HD>(split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
                                        part_ml, counters, tok_seq, tok_pos, block_table, table_stride, n_pages, page, n_tokens, nh,   \
                                        nkv, window, n_splits, status, stream)
     switch (hd) {

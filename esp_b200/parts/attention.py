@@ -108,7 +108,7 @@ class Attention(Part):
             # few rows: split the keys over blocks so that the cache streams at full width
             positions = table.shape[1] * layer.page
             group = s.num_heads // s.num_kv_heads
-            kv_blocks = s.num_kv_heads * ((group + 15) // 16 if group >= 3 else 1)
+            kv_blocks = s.num_kv_heads * ((group + 15) // 16)
             split = ops.attn_decode_split(n, kv_blocks, positions)
             n_splits = (positions + split - 1) // split
             part_o = rt.ws.get("attn_part_o", (n, s.num_heads, n_splits, s.head_dim), torch.float32)
