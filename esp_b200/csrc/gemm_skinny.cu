@@ -46,10 +46,10 @@ __device__ __forceinline__ uint4 load_stream(const bf16* p) {
     return __ldcs(reinterpret_cast<const uint4*>(p));
 }
 
-// KSPLIT = true: the block's 8 warps share one tile of weight rows and split K (few tiles: every SM still
-// gets work).  KSPLIT = false: each warp owns a tile of its own and walks all of K (many tiles: longer
-// streams per warp, no reduction between warps).
-template <int NBLK, bool SWIGLU, typename TC, bool KSPLIT>
+// KS: how many of the block's 8 warps share one tile of weight rows, each with its own slice of K (8 / KS
+// tiles per block).  Few tiles: KS = 8, so that every SM still gets work; many tiles: KS = 1, each warp
+// walks all of K of its own tile (longer streams per warp, no reduction between warps); 2 and 4 lie between.
+template <int NBLK, bool SWIGLU, typename TC, int KS>
 __global__ void __launch_bounds__(WARPS * 32, 3)
 gemm_skinny_kernel(SkinnyParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -71,7 +71,8 @@ gemm_skinny_kernel(SkinnyParams p) {
     // the two weight rows this lane streams
     int row_a, row_b;
     bool ok_a, ok_b;
-    const int tile = KSPLIT ? blockIdx.x : blockIdx.x * WARPS + warp;
+    constexpr int TILES = WARPS / KS;              // tiles of weight rows per block
+    const int tile = blockIdx.x * TILES + warp / KS, kslice = warp % KS;
     if (SWIGLU) {
         const int j = tile * 8 + g;
         ok_a = ok_b = j < p.N;
@@ -87,9 +88,9 @@ gemm_skinny_kernel(SkinnyParams p) {
     const bf16* wb_ptr = W + (size_t)(ok_b ? row_b : 0) * K;
     // K slice of this warp, in whole groups of 32
     const int groups32 = (K + 31) / 32;
-    const int per_warp = (groups32 + WARPS - 1) / WARPS;
-    const int k_lo = KSPLIT ? warp * per_warp * 32 : 0;
-    const int k_hi = KSPLIT ? min(K, (warp + 1) * per_warp * 32) : K;
+    const int per_warp = (groups32 + KS - 1) / KS;
+    const int k_lo = min(K, kslice * per_warp * 32);
+    const int k_hi = min(K, (kslice + 1) * per_warp * 32);
 
     for (int m0 = m_begin; m0 < m_end; m0 += 8 * NBLK) {
         const int cnt = min(8 * NBLK, m_end - m0);
@@ -136,7 +137,7 @@ gemm_skinny_kernel(SkinnyParams p) {
                 }
             }
         }
-        if constexpr (!KSPLIT) {
+        if constexpr (KS == 1) {
             // this warp owns its tile: results go out straight from the accumulators
 #pragma unroll
             for (int nb = 0; nb < NBLK; nb++) {
@@ -160,34 +161,37 @@ gemm_skinny_kernel(SkinnyParams p) {
                 }
             }
         } else {
-        // partial sums of the 8 warps, added in warp order
+        // partial sums of the KS warps of a tile, added in warp order
 #pragma unroll
         for (int nb = 0; nb < NBLK; nb++)
             *reinterpret_cast<float4*>(red + (((size_t)warp * NBLK + nb) * 32 + lane) * 4) =
                 make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
         __syncthreads();
         if (SWIGLU) {
-            for (int e = tid; e < NBLK * 64; e += WARPS * 32) {
-                const int nb = e / 64, ln = (e % 64) / 2, i = e & 1;
+            for (int e = tid; e < TILES * NBLK * 64; e += WARPS * 32) {
+                const int tl = e / (NBLK * 64), rem = e % (NBLK * 64);
+                const int nb = rem / 64, ln = (rem % 64) / 2, i = rem & 1;
                 float gate = 0.f, up = 0.f;
 #pragma unroll
-                for (int w = 0; w < WARPS; w++) {
-                    gate += red[(((size_t)w * NBLK + nb) * 32 + ln) * 4 + i];
-                    up += red[(((size_t)w * NBLK + nb) * 32 + ln) * 4 + 2 + i];
+                for (int w = 0; w < KS; w++) {
+                    gate += red[(((size_t)(tl * KS + w) * NBLK + nb) * 32 + ln) * 4 + i];
+                    up += red[(((size_t)(tl * KS + w) * NBLK + nb) * 32 + ln) * 4 + 2 + i];
                 }
-                const int tok = nb * 8 + (ln & 3) * 2 + i, j = blockIdx.x * 8 + (ln >> 2);
+                const int tok = nb * 8 + (ln & 3) * 2 + i, j = (blockIdx.x * TILES + tl) * 8 + (ln >> 2);
                 if (tok < cnt && j < p.N) {
                     const float v = gate / (1.0f + expf(-gate)) * up;
                     reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + j] = from_f32<TC>(v);
                 }
             }
         } else {
-            for (int e = tid; e < NBLK * 128; e += WARPS * 32) {
-                const int nb = e / 128, ln = (e % 128) / 4, i = e & 3;
+            for (int e = tid; e < TILES * NBLK * 128; e += WARPS * 32) {
+                const int tl = e / (NBLK * 128), rem = e % (NBLK * 128);
+                const int nb = rem / 128, ln = (rem % 128) / 4, i = rem & 3;
                 float v = 0.f;
 #pragma unroll
-                for (int w = 0; w < WARPS; w++) v += red[(((size_t)w * NBLK + nb) * 32 + ln) * 4 + i];
-                const int tok = nb * 8 + (ln & 3) * 2 + (i & 1), n = blockIdx.x * 16 + (ln >> 2) + (i >= 2 ? 8 : 0);
+                for (int w = 0; w < KS; w++) v += red[(((size_t)(tl * KS + w) * NBLK + nb) * 32 + ln) * 4 + i];
+                const int tok = nb * 8 + (ln & 3) * 2 + (i & 1);
+                const int n = (blockIdx.x * TILES + tl) * 16 + (ln >> 2) + (i >= 2 ? 8 : 0);
                 if (tok < cnt && n < p.N) {
                     if (p.row_scale) v *= p.row_scale[m0 + tok];
                     reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n] = from_f32<TC>(v);
@@ -198,29 +202,32 @@ gemm_skinny_kernel(SkinnyParams p) {
     }
 }
 
-template <int NBLK, bool SWIGLU, typename TC, bool KSPLIT>
+template <int NBLK, bool SWIGLU, typename TC, int KS>
 int launch_variant(const SkinnyParams& p, int groups, int tiles, cudaStream_t stream) {
     const size_t smem = (size_t)8 * NBLK * (p.K + 32) * sizeof(bf16) + (size_t)WARPS * NBLK * 32 * 4 * sizeof(float);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
     static bool raised = false;        // per instantiation
     if (smem > 48 * 1024 && !raised) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NBLK, SWIGLU, TC, KSPLIT>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NBLK, SWIGLU, TC, KS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    dim3 grid(KSPLIT ? tiles : (tiles + WARPS - 1) / WARPS, groups);
-    gemm_skinny_kernel<NBLK, SWIGLU, TC, KSPLIT><<<grid, WARPS * 32, smem, stream>>>(p);
+    constexpr int TILES = WARPS / KS;
+    dim3 grid((tiles + TILES - 1) / TILES, groups);
+    gemm_skinny_kernel<NBLK, SWIGLU, TC, KS><<<grid, WARPS * 32, smem, stream>>>(p);
     return esp_launch_status();
 }
 
 template <int NBLK, bool SWIGLU, typename TC>
 int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
     const int tiles = SWIGLU ? (p.N + 7) / 8 : (p.N + 15) / 16;
-    // enough tiles to give every warp of every SM one of its own: no need to split K
+    // warps wanted: about one per warp slot of the machine.  The fewer tiles there are, the more warps share one.
     const long long spread = (long long)tiles * (p.group_offsets ? (groups < p.M ? groups : p.M) : 1);
-    if (spread >= 148 * 8) return launch_variant<NBLK, SWIGLU, TC, false>(p, groups, tiles, stream);
-    return launch_variant<NBLK, SWIGLU, TC, true>(p, groups, tiles, stream);
+    if (spread >= 148 * 8) return launch_variant<NBLK, SWIGLU, TC, 1>(p, groups, tiles, stream);
+    if (spread * 2 >= 148 * 8) return launch_variant<NBLK, SWIGLU, TC, 2>(p, groups, tiles, stream);
+    if (spread * 4 >= 148 * 8) return launch_variant<NBLK, SWIGLU, TC, 4>(p, groups, tiles, stream);
+    return launch_variant<NBLK, SWIGLU, TC, 8>(p, groups, tiles, stream);
 }
 }  // namespace
 

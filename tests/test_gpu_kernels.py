@@ -466,6 +466,21 @@ def test_gemm_skinny_dense(m, n, k):
     assert torch.equal(c1[0], c[m - 1])
 
 
+@pytest.mark.parametrize("n", [6000, 12000])
+def test_gemm_skinny_two_and_four_warps_per_tile(n):
+    """Between few tiles (eight warps share one) and many (one each): 375 tiles -> four, 750 -> two."""
+    m, k = 7, 200
+    a, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1)
+    c = torch.empty(m, n, device=DEV)
+    ops.gemm_skinny(a, w, c)
+    close(c, a.double() @ w.double().t(), torch.float32, f"{n} rows of weights", k=k)
+    inter = n // 2
+    act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(a, w, act, swiglu=True)
+    g, u = a.double() @ w[:inter].double().t(), a.double() @ w[inter:].double().t()
+    close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "swiglu")
+
+
 def test_gemm_skinny_many_tiles_one_tile_per_warp():
     """With enough tiles of weight rows each warp takes a tile of its own and walks all of K: dense,
     fused SwiGLU and grouped with a ragged last tile."""
