@@ -16,7 +16,13 @@
 // wasting tensor work.  A token tile never mixes groups: the tile list (group,
 // first row, rows) is made on the device by the routing kernels.
 //
-// One tile = 128 features x one token tile.  Warp 0 issues the TMA loads, warp 1
+// One tile = 128 weight rows x one token tile.  PLAIN: the rows are 128 output
+// features.  SWIGLU: they are the gate rows of 64 features followed by the up rows
+// of the same 64 features, so that one MMA per 16-wide k step makes both and one
+// accumulator of n_tok columns holds them (lanes 0..63 gate, 64..127 up).  A
+// tcgen05.mma with M = 128 keeps its issuing thread for about 83 cycles at any
+// N up to 128 and for 128 cycles at N = 256 (measured), so few wide MMAs beat many
+// narrow ones: token tiles reach 256 rows.  Warp 0 issues the TMA loads, warp 1
 // owns TMEM and issues the MMAs, warps 2..5 are the epilogue (each reads the 32
 // TMEM lanes that its position in the warpgroup may touch).  A ring of
 // shared-memory stages is handed back and forth with mbarriers.  Every wait is
@@ -30,7 +36,7 @@
 namespace {
 constexpr int BF = 128;            // features (weight rows) per tile: the M side of the MMA
 constexpr int TOK_BOX = 16;         // token rows per TMA box; a tile's width is a multiple of it
-constexpr int BK = 64, THREADS = 192;
+constexpr int BK = 64, THREADS = 352;   // warps: 0 producer, 1 MMA, 2..5 epilogue, 6 producer, 7..10 epilogue
 constexpr int W_BYTES = BF * BK * 2;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
@@ -68,11 +74,6 @@ __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
         if (done) return true;
     }
     return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, void* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, void* bar) {
     asm volatile(
@@ -128,9 +129,23 @@ __device__ __forceinline__ unsigned instr_desc(int n) {
 // Persistent form: a CTA per SM walks the list of (token tile, feature tile) pairs with stride gridDim.x.
 // The producer runs ahead across tile boundaries, so the weight stream never pauses; the accumulator is
 // double-buffered in TMEM, so the epilogue of one tile overlaps the MMAs of the next.
-constexpr int MAX_TOK = 128;        // token rows per tile at most (the N side of the MMA)
-constexpr int TOK_BYTES = MAX_TOK * BK * 2;
-constexpr int RING_BYTES = 192 * 1024;
+//
+// Each producer warp has a ring of its own, and a ring is a byte queue: a stage takes the 16 KB of its
+// weight rows and 128 bytes for each of its tile's token rows, not the room of the widest tile, so that
+// short tiles keep more k steps in flight (a load takes a microsecond or more to arrive).  A stage that
+// would run over the end of its ring starts at the front again and owns the bytes it skipped.  The
+// producer and the MMA thread derive the same offsets from the same list of tiles.
+//
+// What bounds a k step is the time its instructions keep the issuing threads (measured here: a wait on an
+// mbarrier that is already complete 185 cycles, expect_tx 50, the first cp.async.bulk.tensor of a thread
+// 310 and each further one 145, or 50 when other lanes of the warp issue them in the same instruction; a
+// tcgen05.mma 83).  So the loads of a stage are issued by several lanes at once, and two producer warps
+// take the k steps in turn.
+constexpr int PRODUCERS = 2;               // warps that issue the loads, taking the k steps in turn
+constexpr int RING_KB = 96, RING_BYTES = RING_KB * 1024;    // each producer's own ring
+constexpr int NSLOT = 8;                   // stages of one ring in flight at most (pairs of mbarriers)
+constexpr int BAR_BYTES = 512;             // the mbarriers and two words behind the ring
+constexpr int SWAP_BYTES = 2 * 2 * 2 * 2 * 16 * 32 * 4;   // the epilogue's exchange of gate and up halves
 
 __device__ __forceinline__ void mbar_arrive(void* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
@@ -140,7 +155,7 @@ struct TileInfo {
     int group, row0, n_rows, n_tok, f0;
 };
 
-template <bool SWIGLU>
+template <int MAX_TOK, int FEATS>
 __device__ __forceinline__ TileInfo tile_info(const Tc05Params& p, int tile, int feat_tiles) {
     TileInfo t;
     const int tt = tile / feat_tiles, ft = tile - tt * feat_tiles;     // feature tiles vary fastest: neighbours share tokens
@@ -154,42 +169,48 @@ __device__ __forceinline__ TileInfo tile_info(const Tc05Params& p, int tile, int
         t.n_rows = min(MAX_TOK, p.M - t.row0);
     }
     t.n_tok = min(MAX_TOK, (max(t.n_rows, 1) + TOK_BOX - 1) / TOK_BOX * TOK_BOX);
-    t.f0 = ft * BF;
+    t.f0 = ft * FEATS;
     return t;
 }
 
-template <bool SWIGLU>
+// MAX_TOK: token rows per tile at most (the N side of the MMA): 128 or 256.  Two accumulators of MAX_TOK
+// columns fit the 512 columns of TMEM in either case.
+template <bool SWIGLU, int MAX_TOK>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a64,
                  const __grid_constant__ CUtensorMap map_a128, const __grid_constant__ CUtensorMap map_w, Tc05Params p) {
-    constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * W_BYTES + TOK_BYTES;
-    constexpr int STAGES = RING_BYTES / STAGE_BYTES;
-    constexpr int ACC_COLS = (SWIGLU ? 2 : 1) * MAX_TOK;       // TMEM columns of one accumulator buffer
-    constexpr int TMEM_COLS = 2 * ACC_COLS;                      // two buffers
+    constexpr int TOK_BYTES = MAX_TOK * BK * 2;
+    static_assert(2 * (W_BYTES + TOK_BYTES) <= RING_BYTES, "two stages of the widest tile must fit a ring");
+    constexpr int FEATS = SWIGLU ? BF / 2 : BF;                  // output features of one tile
+    constexpr int ACC_COLS = MAX_TOK;                            // TMEM columns of one accumulator buffer
+    constexpr int NBUF = 2;
+    constexpr int TMEM_COLS = NBUF * ACC_COLS;
+    static_assert(TMEM_COLS <= 512, "the accumulators do not fit");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
-    unsigned long long* empty_bar = full_bar + STAGES;
-    unsigned long long* acc_full_bar = empty_bar + STAGES;       // [2]
+    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + PRODUCERS * RING_BYTES);   // [ring][slot]
+    unsigned long long* empty_bar = full_bar + PRODUCERS * NSLOT;
+    unsigned long long* acc_full_bar = empty_bar + PRODUCERS * NSLOT;   // [2]
     unsigned long long* acc_empty_bar = acc_full_bar + 2;        // [2]
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* swap = reinterpret_cast<float*>(smem + PRODUCERS * RING_BYTES + BAR_BYTES);     // SWIGLU: [2 halves][2][2 pairs][2 roles][16][32]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int feat_tiles = (p.N + BF - 1) / BF;
+    const int feat_tiles = (p.N + FEATS - 1) / FEATS;
     const int token_tiles = p.tile_group ? *p.n_tiles : (p.M + MAX_TOK - 1) / MAX_TOK;
     const int total_tiles = token_tiles * feat_tiles;
     if ((int)blockIdx.x >= total_tiles) return;                      // the whole CTA leaves before any barrier exists
     const int k_iters = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < PRODUCERS * NSLOT; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&acc_full_bar[b], 1);
-            mbar_init(&acc_empty_bar[b], 4);                         // one arrival per epilogue warp
+            mbar_init(&acc_empty_bar[b], 8);                         // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -203,70 +224,118 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
 
-    if (warp == 0) {
-        if (lane == 0) {
-            int it = 0;                                              // stage counter, runs on across tiles
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-                const TileInfo t = tile_info<SWIGLU>(p, tile, feat_tiles);
-                const unsigned stage_tx = (SWIGLU ? 2 : 1) * W_BYTES + t.n_tok * BK * 2;
-                for (int k = 0; k < k_iters; k++, it++) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1)) {
-                        atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
-                        *abort_flag = 1;
-                        break;
+    if (warp == 0 || warp == 6) {
+        // Producer warps: warp 0 takes the even k steps of the CTA's run of tiles, warp 6 the odd ones.  Lane 0
+        // waits for the stage and announces its bytes; then the lanes issue one box each in one instruction:
+        // lane 0 the weight rows (PLAIN: 128 rows; SWIGLU: the 64 gate rows), lane 1 the 64 up rows, lanes 2..
+        // the token rows in boxes of 128, then 64, then 16.
+        const int me = warp == 0 ? 0 : 1;
+        unsigned char* ring = smem + me * RING_BYTES;
+        unsigned long long* my_full = full_bar + me * NSLOT;
+        unsigned long long* my_empty = empty_bar + me * NSLOT;
+        int it = 0;                                                  // k steps of the CTA so far
+        int issued = 0, tail = 0;                                    // this ring: stages issued; the oldest not yet known free
+        int off_kb = 0, free_kb = RING_KB;
+        unsigned long long held = 0;                                 // lane 0: KB that each stage in flight holds, 8 bits a slot
+        bool ok = true;
+        TileInfo next = tile_info<MAX_TOK, FEATS>(p, blockIdx.x, feat_tiles);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const TileInfo t = next;
+            if (tile + (int)gridDim.x < total_tiles)                  // the list entry of the next tile is fetched early
+                next = tile_info<MAX_TOK, FEATS>(p, tile + gridDim.x, feat_tiles);
+            const unsigned stage_tx = W_BYTES + t.n_tok * BK * 2;
+            const int size_kb = stage_tx >> 10;                       // n_tok is a multiple of 16: whole KB
+            // this lane's box: the map, the row it starts at, the bytes into the stage
+            const int n128 = t.n_tok >> 7, n64 = (t.n_tok >> 6) & 1, n16 = (t.n_tok >> 4) & 3;
+            const CUtensorMap* box_map = nullptr;
+            int box_row = 0, box_grp = 0, box_off = 0;
+            if (lane == 0) {
+                box_map = &map_w, box_row = t.f0, box_grp = t.group;
+            } else if (lane == 1) {
+                if (SWIGLU) box_map = &map_w, box_row = p.N + t.f0, box_grp = t.group, box_off = W_BYTES / 2;
+            } else {
+                const int j = lane - 2;
+                int r = -1;
+                if (j < n128) r = j * 128, box_map = &map_a128;
+                else if (j < n128 + n64) r = n128 * 128, box_map = &map_a64;
+                else if (j < n128 + n64 + n16) r = n128 * 128 + n64 * 64 + (j - n128 - n64) * TOK_BOX, box_map = &map_a;
+                if (r >= 0) box_row = t.row0 + r, box_off = W_BYTES + r * BK * 2;
+            }
+            for (int k = 0; k < k_iters && ok; k++, it++) {
+                if (it % PRODUCERS != me) continue;
+                const bool wrap = off_kb + size_kb > RING_KB;
+                const int need_kb = size_kb + (wrap ? RING_KB - off_kb : 0);
+                const int s = issued % NSLOT;
+                if (lane == 0) {
+                    ok = !*abort_flag;
+                    while (ok && (free_kb < need_kb || issued - tail == NSLOT)) {     // the oldest stages give their bytes back
+                        ok = mbar_wait(&my_empty[tail % NSLOT], (tail / NSLOT) & 1);
+                        free_kb += (int)((held >> (8 * (tail % NSLOT))) & 0xFF);
+                        tail++;
                     }
-                    unsigned char* w_dst = smem + s * STAGE_BYTES;
-                    unsigned char* t_dst = w_dst + (SWIGLU ? 2 : 1) * W_BYTES;
-                    mbar_expect_tx(&full_bar[s], stage_tx);
-                    tma_load_3d(w_dst, &map_w, k * BK, t.f0, t.group, &full_bar[s]);
-                    if (SWIGLU) tma_load_3d(w_dst + W_BYTES, &map_w, k * BK, p.N + t.f0, t.group, &full_bar[s]);
-                    int r = 0;
-                    if (t.n_tok == MAX_TOK) {                          // a full tile: one box of 128 token rows
-                        tma_load_2d(t_dst, &map_a128, k * BK, t.row0, &full_bar[s]);
-                        r = MAX_TOK;
-                    }
-                    for (; r + 64 <= t.n_tok; r += 64)                 // boxes of 64 token rows while they fit,
-                        tma_load_2d(t_dst + r * BK * 2, &map_a64, k * BK, t.row0 + r, &full_bar[s]);
-                    for (; r < t.n_tok; r += TOK_BOX)                  // boxes of 16 for the ragged rest
-                        tma_load_2d(t_dst + r * BK * 2, &map_a, k * BK, t.row0 + r, &full_bar[s]);
+                    held = (held & ~(0xFFull << (8 * s))) | ((unsigned long long)need_kb << (8 * s));
+                    free_kb -= need_kb;
+                    if (ok) mbar_expect_tx(&my_full[s], stage_tx);
                 }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (wrap) off_kb = 0;
+                if (box_map) tma_load_3d(ring + off_kb * 1024 + box_off, box_map, k * BK, box_row, box_grp, &my_full[s]);
+                off_kb += size_kb;
+                issued++;
             }
-            if (*abort_flag) {
-                // let this CTA's own copies land before its shared memory is given up
-                for (int j = max(0, it - STAGES); j < it; j++) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
-            }
+        }
+        if (lane == 0 && (!ok || *abort_flag)) {
+            atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+            *abort_flag = 1;
+            // let this warp's own copies land before the CTA's shared memory is given up: the stages not yet
+            // known free may still be in flight, each on the phase of its own use of its slot
+            for (int j = tail; j < issued; j++) mbar_wait(&my_full[j % NSLOT], (j / NSLOT) & 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            int it = 0, local = 0;
+            int used = 0, local = 0;
+            int off0 = 0, off1 = 0, count0 = 0, count1 = 0;           // per ring: the next offset (KB), the stages consumed
+            // descriptors differ from stage to stage and from one 16-wide k step to the next only in the
+            // address field (16-byte units): the low word is a base plus a constant
+            const unsigned long long desc0 = smem_desc(smem);
+            const unsigned desc_hi = (unsigned)(desc0 >> 32), desc_lo0 = (unsigned)desc0;
+            TileInfo next = tile_info<MAX_TOK, FEATS>(p, blockIdx.x, feat_tiles);
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
-                const TileInfo t = tile_info<SWIGLU>(p, tile, feat_tiles);
+                const TileInfo t = next;
+                if (tile + (int)gridDim.x < total_tiles) next = tile_info<MAX_TOK, FEATS>(p, tile + gridDim.x, feat_tiles);
                 const unsigned idesc = instr_desc(t.n_tok);
-                const int buf = local & 1;
-                // the epilogue must have emptied this accumulator buffer (two tiles ago)
-                if (!mbar_wait(&acc_empty_bar[buf], ((local >> 1) & 1) ^ 1)) {
+                const int buf = local % NBUF;
+                // the epilogue must have emptied this accumulator buffer (NBUF tiles ago)
+                if (!mbar_wait(&acc_empty_bar[buf], ((local / NBUF) & 1) ^ 1)) {
                     atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
                     *abort_flag = 1;
                     break;
                 }
                 tc_fence_after();
                 const unsigned acc = tmem_base + buf * ACC_COLS;
-                for (int k = 0; k < k_iters; k++, it++) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+                const int size_kb = (W_BYTES + t.n_tok * BK * 2) >> 10;
+                for (int k = 0; k < k_iters; k++, used++) {
+                    const int ring = used % PRODUCERS;
+                    int off = ring ? off1 : off0;
+                    const int count = ring ? count1 : count0;
+                    const int s = ring * NSLOT + count % NSLOT;
+                    if (!mbar_wait(&full_bar[s], (count / NSLOT) & 1)) {
                         atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
                         *abort_flag = 1;
                         break;
                     }
                     tc_fence_after();
-                    const unsigned char* w_src = smem + s * STAGE_BYTES;
-                    const unsigned char* t_src = w_src + (SWIGLU ? 2 : 1) * W_BYTES;
+                    if (off + size_kb > RING_KB) off = 0;               // the producer's rule
+                    const unsigned w_lo = desc_lo0 + (ring * RING_KB + off) * (1024 >> 4);
+                    if (ring) off1 = off + size_kb, count1 = count + 1;
+                    else off0 = off + size_kb, count0 = count + 1;
+                    const unsigned t_lo = w_lo + (W_BYTES >> 4);
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; kk++) {
-                        const unsigned accum = (k > 0 || kk > 0) ? 1u : 0u;
-                        tc_mma(acc, smem_desc(w_src + kk * 32), smem_desc(t_src + kk * 32), idesc, accum);
-                        if (SWIGLU) tc_mma(acc + MAX_TOK, smem_desc(w_src + W_BYTES + kk * 32), smem_desc(t_src + kk * 32), idesc, accum);
+                        const unsigned accum = (kk > 0 || k > 0) ? 1u : 0u;
+                        tc_mma(acc, ((unsigned long long)desc_hi << 32) | (w_lo + kk * 2),
+                               ((unsigned long long)desc_hi << 32) | (t_lo + kk * 2), idesc, accum);
                     }
                     tc_commit(&empty_bar[s]);                         // the stage is free once these MMAs have read it
                 }
@@ -275,12 +344,29 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
         }
     } else {
-        const int quad = warp & 3;                                   // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+        // Eight epilogue warps, two for each quarter of the TMEM lanes (a warp may read lanes 32*(warp%4)..+31
+        // only): warps 2..5 take the even runs of 32 tokens, warps 7..10 the odd ones.  A store to global
+        // memory keeps a warp for tens of cycles here, so the warps are what hides it.
+        const int quad = warp & 3;
+        const int half = warp >= 7 ? 1 : 0;
         int local = 0;
+        TileInfo next = tile_info<MAX_TOK, FEATS>(p, blockIdx.x, feat_tiles);
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
-            const TileInfo t = tile_info<SWIGLU>(p, tile, feat_tiles);
-            const int buf = local & 1;
-            const bool ok = !*abort_flag && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
+            const TileInfo t = next;
+            if (tile + (int)gridDim.x < total_tiles) next = tile_info<MAX_TOK, FEATS>(p, tile + gridDim.x, feat_tiles);
+            const int buf = local % NBUF;
+            bool ok = !*abort_flag && mbar_wait(&acc_full_bar[buf], (local / NBUF) & 1);
+            if (SWIGLU) {
+                // the two warps of a pair meet at a named barrier for every run of tokens: they go on or leave together
+                unsigned both;
+                asm volatile(
+                    "{\n.reg .pred p, q;\n"
+                    "setp.ne.u32 p, %1, 0;\n"
+                    "bar.red.and.pred q, %2, 64, p;\n"
+                    "selp.u32 %0, 1, 0, q;\n}\n"
+                    : "=r"(both) : "r"(ok ? 1u : 0u), "r"(1 + half * 2 + (quad & 1)) : "memory");
+                ok = both != 0;
+            }
             if (!ok) {
                 if (lane == 0) {
                     atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
@@ -289,25 +375,44 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 break;
             }
             tc_fence_after();
-            const int f = t.f0 + quad * 32 + lane;                    // this thread's output feature
-            const bool f_ok = f < p.N;
             const unsigned lane_addr = tmem_base + buf * ACC_COLS + ((unsigned)(quad * 32) << 16);
-            for (int c0 = 0; c0 < t.n_tok; c0 += 32) {
-                float acc[32];
-                tc_ld32(lane_addr + c0, acc);
-                if (SWIGLU) {
-                    float up[32];
-                    tc_ld32(lane_addr + MAX_TOK + c0, up);
-                    bf16* out = reinterpret_cast<bf16*>(p.C);
+            if (SWIGLU) {
+                // Lanes 0..63 hold the gate of 64 features, lanes 64..127 the up of the same features: the warp of
+                // quad q (gate) and that of quad q + 2 (up) hold the two halves of every product.  Of each run of 32
+                // tokens the gate warp finishes the first 16 and the up warp the last 16; each hands the other the
+                // half it needs through shared memory (two buffers in turn, one named barrier per run).
+                const int pair = quad & 1;
+                const bool is_up = quad >= 2;
+                const int f = t.f0 + pair * 32 + lane;
+                const bool f_ok = f < p.N;
+                bf16* out = reinterpret_cast<bf16*>(p.C);
+                int flip = 0;
+                for (int c0 = half * 32; c0 < t.n_tok; c0 += 64, flip ^= 1) {
+                    float acc[32];
+                    tc_ld32(lane_addr + c0, acc);
+                    float* mine = swap + ((((half * 2 + flip) * 2 + pair) * 2 + (is_up ? 1 : 0)) * 16) * 32;
+                    const float* theirs = swap + ((((half * 2 + flip) * 2 + pair) * 2 + (is_up ? 0 : 1)) * 16) * 32;
+                    const int keep = is_up ? 16 : 0;                            // the up warp gives tokens 0..15 away
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        if (f_ok && c0 + i < t.n_rows) {
-                            const float v = acc[i] / (1.0f + expf(-acc[i])) * up[i];
-                            out[(size_t)(t.row0 + c0 + i) * p.ldc + f] = __float2bfloat16_rn(v);
-                        }
+                    for (int i = 0; i < 16; i++) mine[i * 32 + lane] = is_up ? acc[i] : acc[16 + i];
+                    asm volatile("bar.sync %0, 64;\n" ::"r"(1 + half * 2 + pair) : "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float other = theirs[i * 32 + lane];
+                        const float own = is_up ? acc[16 + i] : acc[i];
+                        const float g = is_up ? other : own, u = is_up ? own : other;
+                        const int row = c0 + keep + i;
+                        if (f_ok && row < t.n_rows)
+                            out[(size_t)(t.row0 + row) * p.ldc + f] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);
                     }
-                } else {
-                    float* out = reinterpret_cast<float*>(p.C);
+                }
+            } else {
+                const int f = t.f0 + quad * 32 + lane;                    // this thread's output feature
+                const bool f_ok = f < p.N;
+                float* out = reinterpret_cast<float*>(p.C);
+                for (int c0 = half * 32; c0 < t.n_tok; c0 += 64) {
+                    float acc[32];
+                    tc_ld32(lane_addr + c0, acc);
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
                         if (f_ok && c0 + i < t.n_rows) {
@@ -365,29 +470,35 @@ int make_map(CUtensorMap* map, const void* base, unsigned long long d0, unsigned
 }  // namespace
 
 // A [rows_total, K] bfloat16 (row-major, contiguous), W [G, w_rows, K] bfloat16.  Dense: tile_group = null,
-// M rows.  Grouped: the token-tile list on the device (tiles of at most 128 rows); ``max_tiles`` bounds
+// M rows.  Grouped: the token-tile list on the device (tiles of at most ``tile_max`` rows); ``max_tiles`` bounds
 // their number.  swiglu: N is the intermediate size and w_rows = 2N.  K must be a multiple of 8, the
 // bases 16-byte aligned.
 ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, int groups, int w_rows,
                           const float* row_scale, void* C, long long ldc, const int* tile_group, const int* tile_row0,
-                          const int* tile_rows, const int* n_tiles, int max_tiles, int M, int N, int K, int swiglu,
+                          const int* tile_rows, const int* n_tiles, int max_tiles, int tile_max, int M, int N, int K, int swiglu,
                           int* status, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || rows_total <= 0) return 0;
     if (K % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     CUtensorMap map_a, map_a64, map_a128, map_w;
-    int rc = make_map(&map_a, A, (unsigned long long)K, (unsigned long long)rows_total, 1, TOK_BOX, 2);
+    int rc = make_map(&map_a, A, (unsigned long long)K, (unsigned long long)rows_total, 1, TOK_BOX, 3);
     if (rc) return rc;
-    rc = make_map(&map_a64, A, (unsigned long long)K, (unsigned long long)rows_total, 1, 64, 2);
+    rc = make_map(&map_a64, A, (unsigned long long)K, (unsigned long long)rows_total, 1, 64, 3);
     if (rc) return rc;
-    rc = make_map(&map_a128, A, (unsigned long long)K, (unsigned long long)rows_total, 1, MAX_TOK, 2);
+    rc = make_map(&map_a128, A, (unsigned long long)K, (unsigned long long)rows_total, 1, 128, 3);
     if (rc) return rc;
     // the weights always use a 3-D map so that the kernel has one code path; a dense product is one group
-    rc = make_map(&map_w, W, (unsigned long long)K, (unsigned long long)w_rows, (unsigned long long)groups, BF, 3);
+    rc = make_map(&map_w, W, (unsigned long long)K, (unsigned long long)w_rows, (unsigned long long)groups, swiglu ? BF / 2 : BF, 3);
     if (rc) return rc;
     Tc05Params p{tile_group, tile_row0, tile_rows, n_tiles, row_scale, C, ldc, M, N, K, status};
-    const int token_tiles = tile_group ? max_tiles : (M + MAX_TOK - 1) / MAX_TOK;     // upper bound when grouped
+    // ``tile_max``: the most rows a tile of the list has, 128 or 256 (with 256 an expert's weights pass once
+    // for up to 256 of its rows); dense products cut tiles of 256 rows with SwiGLU (MMAs of N = 256 run at
+    // the full rate) and of 128 without (more tiles to spread over the SMs)
+    if (tile_group && tile_max != 128 && tile_max != 256) return (int)cudaErrorInvalidValue;
+    const int max_tok = tile_group ? tile_max : (swiglu ? 256 : 128);
+    const int token_tiles = tile_group ? max_tiles : (M + max_tok - 1) / max_tok;     // upper bound when grouped
     if (token_tiles <= 0) return 0;
-    const long long tiles_bound = (long long)token_tiles * ((N + BF - 1) / BF);
+    const int feats = swiglu ? BF / 2 : BF;
+    const long long tiles_bound = (long long)token_tiles * ((N + feats - 1) / feats);
     static int sm_count = 0;
     if (!sm_count) {
         int dev = 0;
@@ -395,16 +506,22 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
-    const size_t smem = RING_BYTES + 1024 + 256;
-    static bool raised[2] = {false, false};
-    if (!raised[swiglu ? 1 : 0]) {
-        cudaError_t e = swiglu ? cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                               : cudaFuncSetAttribute(gemm_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = PRODUCERS * RING_BYTES + 1024 + BAR_BYTES + SWAP_BYTES;     // 230,656 of the 232,448 bytes a block may have
+    const int which = (swiglu ? 2 : 0) + (max_tok == 256 ? 1 : 0);
+    static bool raised[4] = {false, false, false, false};
+    if (!raised[which]) {
+        cudaError_t e = cudaSuccess;
+        if (which == 0) e = cudaFuncSetAttribute(gemm_tc05_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (which == 1) e = cudaFuncSetAttribute(gemm_tc05_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (which == 2) e = cudaFuncSetAttribute(gemm_tc05_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (which == 3) e = cudaFuncSetAttribute(gemm_tc05_kernel<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        raised[swiglu ? 1 : 0] = true;
+        raised[which] = true;
     }
     const int grid = (int)(tiles_bound < sm_count ? tiles_bound : sm_count);
-    if (swiglu) gemm_tc05_kernel<true><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
-    else gemm_tc05_kernel<false><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
+    if (which == 0) gemm_tc05_kernel<false, 128><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
+    if (which == 1) gemm_tc05_kernel<false, 256><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
+    if (which == 2) gemm_tc05_kernel<true, 128><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
+    if (which == 3) gemm_tc05_kernel<true, 256><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
     return esp_launch_status();
 }

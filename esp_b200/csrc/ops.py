@@ -31,7 +31,8 @@ _SIGNATURES = {
     "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
     "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P],
-    "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                      P, P],
     "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
     "esp_moe_combine_add_rmsnorm": [P, P, P, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, c_int, P],
@@ -377,13 +378,14 @@ def gather_rows(src, rows, out):
            "gather_rows")
 
 
-TC05_TILE_ROWS = 128
+TC05_TILE_ROWS = 256
 
 
-def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None):
+def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None, tile_rows=None):
     """TMA + tcgen05 product for many rows.  a [rows, K] bfloat16 contiguous; w [N, K] or [G, N, K]
     bfloat16.  Plain: c float32 [rows, N] = scale * a @ w[g].T.  swiglu: w rows are [gate; up] and c is
-    bfloat16 [rows, I].  Grouped: ``tiles`` = (tile_group, tile_row0, tile_count, n_tiles) from moe_permute."""
+    bfloat16 [rows, I].  Grouped: ``tiles`` = (tile_group, tile_row0, tile_count, n_tiles) from moe_permute,
+    ``tile_rows`` the most rows a tile has (128 or 256; TC05_TILE_ROWS when not given)."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not a.is_contiguous() or not w.is_contiguous():
         raise Backend("gemm_tc05 takes contiguous bfloat16 operands")
     if w.dim() == 3:
@@ -399,10 +401,12 @@ def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=No
     if c.dtype != (torch.bfloat16 if swiglu else torch.float32):
         raise Backend("gemm_tc05: the plain product writes float32, the SwiGLU product bfloat16")
     grouped = tiles is not None
+    tile_rows = TC05_TILE_ROWS if tile_rows is None else tile_rows
     code = _fn("tc05", "esp_gemm_tc05")(
         a.data_ptr(), m, w.data_ptr(), groups, wn, _ptr(row_scale, torch.float32, "row_scale"), c.data_ptr(),
         c.stride(0), _ptr(tiles[0], torch.int32) if grouped else None,
         _ptr(tiles[1], torch.int32) if grouped else None, _ptr(tiles[2], torch.int32) if grouped else None,
-        _ptr(tiles[3], torch.int32) if grouped else None, tiles[0].shape[0] if grouped else 0, m, n, k,
+        _ptr(tiles[3], torch.int32) if grouped else None, tiles[0].shape[0] if grouped else 0,
+        tile_rows if grouped else 0, m, n, k,
         1 if swiglu else 0, _ptr(status, torch.int32), _stream())
     _check(code, "gemm_tc05")

@@ -712,3 +712,41 @@ def test_gemm_tc05_grouped_through_the_permutation():
         close(act[lo:hi], gg / (1 + torch.exp(-gg)) * uu, torch.bfloat16, f"expert {g} gate/up")
         ref = (act[lo:hi].double() @ w_d[g].double().t()) * perm_weight[lo:hi].double()[:, None]
         close(out[lo:hi], ref, torch.float32, f"expert {g} down", k=inter)
+
+
+@pytest.mark.parametrize("tile_rows", [128, 256])
+@pytest.mark.parametrize("counts", [
+    [80] * 9,                                   # stages of 26 KB: eight of them end exactly at the ring's end
+    [137, 9, 256, 1, 300, 16, 200, 33, 77, 128, 145, 250],
+    [16, 240, 48, 176, 112, 96, 208, 64],       # every width of stage in turn
+])
+def test_gemm_tc05_grouped_stages_of_many_widths(tile_rows, counts):
+    """The ring of stages is a byte queue whose stages are as wide as their tile: tiles of many widths in a
+    row, long enough in k that the ring turns over many times, against the dense product of each group."""
+    e, width, inter = len(counts), 64 * 13, 64 * 3 + 40
+    mk = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    g, r0, rc, off = [], [], [], [0]
+    for grp, c in enumerate(counts):
+        for s0 in range(0, c, tile_rows):
+            g.append(grp), r0.append(off[-1] + s0), rc.append(min(tile_rows, c - s0))
+        off.append(off[-1] + c)
+    rows = off[-1]
+    tiles = (mk(g), mk(r0), mk(rc), mk([len(g)]))
+    x = rnd(rows, width, dtype=torch.bfloat16, seed=3)
+    w_gu = rnd(e, 2 * inter, width, dtype=torch.bfloat16, seed=6, scale=0.1)
+    w_d = rnd(e, width, inter, dtype=torch.bfloat16, seed=7, scale=0.2)
+    scale = rnd(rows, seed=8).abs() + 0.1
+    st = status()
+    act = torch.full((rows + 2, inter), 3.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc05(x, w_gu, act, st, swiglu=True, tiles=tiles, rows=rows, tile_rows=tile_rows)
+    out = torch.full((rows + 2, width), 5.0, device=DEV)
+    ops.gemm_tc05(act, w_d, out, st, row_scale=scale, tiles=tiles, rows=rows, tile_rows=tile_rows)
+    assert st.item() == 0
+    assert torch.all(act[rows:] == 3.0) and torch.all(out[rows:] == 5.0), "rows beyond the product were written"
+    for grp in range(e):
+        lo, hi = off[grp], off[grp + 1]
+        xx = x[lo:hi].double()
+        gg, uu = xx @ w_gu[grp, :inter].double().t(), xx @ w_gu[grp, inter:].double().t()
+        close(act[lo:hi], gg / (1 + torch.exp(-gg)) * uu, torch.bfloat16, f"group {grp} gate/up")
+        ref = (act[lo:hi].double() @ w_d[grp].double().t()) * scale[lo:hi].double()[:, None]
+        close(out[lo:hi], ref, torch.float32, f"group {grp} down", k=inter)
