@@ -1,0 +1,423 @@
+// Prefill attention on the 5th-generation tensor cores: causal, optionally
+// windowed, grouped query heads, sequences of unequal length packed back to
+// back, keys and values read from the paged bfloat16 cache.
+//
+// A block owns 128 consecutive new tokens of one sequence and one query head
+// and walks the keys it may see in blocks of 128 (two pages of 64):
+//
+//   S  = Q K^T       tcgen05.mma, M = 128 queries, N = 128 keys, K = head size; float accumulator in TMEM
+//   P  = exp2(S * log2(e) / sqrt(hd) - m)   in 32-bit, by the thread that owns the row (TMEM lane = row,
+//        so the row's maximum and sum need no exchange between threads); rounded to bfloat16 into shared
+//        memory in the layout the tensor core reads (rows of 128 bytes, 128-byte swizzle)
+//   PV = P V         tcgen05.mma, N = head size, K = 128 keys, a fresh accumulator per block of keys
+//   O  = O * exp2(m_old - m_new) + PV        in registers of the row's thread; O / l at the end
+//
+// Warp 0 loads (TMA: queries once, then keys and values page by page into two-stage rings of their own:
+// a key stage is free as soon as S is done, before its block's PV), warp 1 issues the MMAs, warps 2..9
+// are the row threads, two to a row (each half of the keys of a block and half of the head's columns:
+// with one warp per scheduler the chain multiply, exp2, add, round would run at its latency).  S and PV have two TMEM buffers each (4 x 128 = all 512 columns), so S of the
+// next block runs while the row threads work on this one.  Every wait is bounded.
+//
+// Head sizes 64 and 128.  The page size is 64.  Rows of the tile beyond the sequence's new tokens are
+// computed and not stored; keys beyond a row's position are masked before the maximum is taken.
+#include "tc05.cuh"
+
+namespace {
+using namespace tc05;
+constexpr int BM = 128, BN = 128, PAGE = 64, THREADS = 320;   // warps: 0 loads, 1 MMA, 2..9 row threads
+constexpr int ATOM_BYTES = 128 * 128;           // 128 rows of 128 bytes: one 64-wide slice of a 128-row operand
+
+struct AttnParams {
+    bf16* out;
+    const int* tile_seq;
+    const int* tile_first;
+    const int* seq_start;
+    const int* seq_past;
+    const int* block_table;
+    int table_stride, n_pages, nh, nkv, window, kv_rows;
+    int* status;
+};
+
+// instruction descriptor: bfloat16 x bfloat16 -> float, M = 128, N = n, A K-major, B K-major or MN-major
+__device__ __forceinline__ unsigned idesc_attn(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((unsigned)(n >> 3) << 17) |
+           ((unsigned)(128 >> 4) << 24);
+}
+// descriptor of an MN-major operand: rows are 16 consecutive k (keys), 128 bytes of n (head columns) each;
+// the next 64 columns lie ``lbo`` bytes further, the next 8 keys 1024 bytes further
+__device__ __forceinline__ unsigned long long smem_desc_mn(const void* p, unsigned lbo) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(p) & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+
+// 2^x by the special function unit (ex2.approx: relative error about 2^-22; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// the 64 threads that meet at named barrier ``id`` learn whether all of them are well
+__device__ __forceinline__ bool pair_agree(bool ok, int id) {
+    unsigned all;
+    asm volatile(
+        "{\n.reg .pred p, q;\n"
+        "setp.ne.u32 p, %1, 0;\n"
+        "bar.red.and.pred q, %2, 64, p;\n"
+        "selp.u32 %0, 1, 0, q;\n}\n"
+        : "=r"(all) : "r"(ok ? 1u : 0u), "r"(id) : "memory");
+    return all != 0;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, AttnParams p) {
+    constexpr int HALVES = HD / 64;                       // 64-column slices of a head
+    constexpr int Q_BYTES = HALVES * ATOM_BYTES, KV_BYTES = HALVES * ATOM_BYTES, P_BYTES = 2 * ATOM_BYTES;
+    // tiles are listed in order of position; the last ones see the most keys, so they start first
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
+    const int first = p.tile_first[tile];
+    if (first % BM != 0) return;                          // the list has tiles of 64 rows: every second one starts a block
+    const int seq = p.tile_seq[tile];
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;
+    unsigned char* k_s = q_s + Q_BYTES;                   // [2 stages]
+    unsigned char* v_s = k_s + 2 * KV_BYTES;              // [2 stages]
+    unsigned char* p_s = v_s + 2 * KV_BYTES;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + P_BYTES);
+    unsigned long long* q_full = bars;                    // [1]
+    unsigned long long* k_full = bars + 1;                // [2]
+    unsigned long long* k_empty = bars + 3;               // [2]
+    unsigned long long* v_full = bars + 5;                // [2]
+    unsigned long long* v_empty = bars + 7;               // [2]
+    unsigned long long* s_full = bars + 9;                // [2]
+    unsigned long long* pv_full = bars + 11;              // [2]
+    unsigned long long* p_ready = bars + 13;              // [1]
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xchg = reinterpret_cast<float*>(bars) + 64;                  // [2][2][128] maxima, [2][128] sums of the row threads
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = p.seq_start[seq] + first;                          // the tile's first row among the packed tokens
+    const int n_new = p.seq_start[seq + 1] - p.seq_start[seq];
+    const int rows = min(BM, n_new - first);
+    const int pos0 = p.seq_past[seq] + first, pos_last = pos0 + rows - 1;
+    const int kvh = h / (p.nh / p.nkv);
+    const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int blk_lo = key_lo / BN, nb = pos_last / BN - blk_lo + 1;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 13; i++) mbar_init(&bars[i], 1);
+        mbar_init(p_ready, 8);                                           // one arrival per warp of row threads
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    const unsigned tm_s = tmem_base, tm_pv = tmem_base + 256;          // S buffers at columns 0 and 128, PV at 256 and 384
+
+    if (warp == 0) {
+        // ---- loads: lanes 0..HALVES-1 the queries; then per block of keys, lane = (page of the block, slice)
+        bool ok = true;
+        if (lane == 0) mbar_expect_tx(q_full, Q_BYTES);
+        __syncwarp();
+        if (lane < HALVES) tma_load_2d(q_s + lane * ATOM_BYTES, &map_q, h * HD + lane * 64, row0, q_full);
+        const int pg_in_blk = lane / HALVES, half = lane % HALVES;      // lanes 0..2*HALVES-1 issue boxes
+        int issued_k = 0, issued_v = 0;
+        for (int j = 0; j < nb && ok; j++) {
+            const int s = j & 1;
+            // the page of this lane's box; a page past the tile's last key is read as zeros (a row past the cache)
+            int box_row = p.kv_rows;
+            if (lane < 2 * HALVES) {
+                const int page_idx = (blk_lo + j) * 2 + pg_in_blk;
+                if (page_idx <= pos_last / PAGE) {
+                    const int pg = p.block_table[(size_t)seq * p.table_stride + page_idx];
+                    if (pg >= 0 && pg < p.n_pages) box_row = (pg * p.nkv + kvh) * PAGE;
+                    else atomicOr(p.status, ESP_STATUS_BAD_INDEX);
+                }
+            }
+            if (lane == 0) {
+                ok = !*abort_flag && mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1);
+                if (ok) mbar_expect_tx(&k_full[s], KV_BYTES);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (lane < 2 * HALVES)
+                tma_load_2d(k_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_k, half * 64, box_row, &k_full[s]);
+            issued_k = j + 1;
+            if (lane == 0) {
+                ok = !*abort_flag && mbar_wait(&v_empty[s], ((j >> 1) & 1) ^ 1);
+                if (ok) mbar_expect_tx(&v_full[s], KV_BYTES);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (lane < 2 * HALVES)
+                tma_load_2d(v_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_v, half * 64, box_row, &v_full[s]);
+            issued_v = j + 1;
+        }
+        if (lane == 0 && (!ok || *abort_flag)) {
+            atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+            *abort_flag = 1;
+            // let this CTA's own copies land before its shared memory is given up
+            mbar_wait(q_full, 0);
+            for (int j = max(0, issued_k - 2); j < issued_k; j++) mbar_wait(&k_full[j & 1], (j >> 1) & 1);
+            for (int j = max(0, issued_v - 2); j < issued_v; j++) mbar_wait(&v_full[j & 1], (j >> 1) & 1);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned idesc_s = idesc_attn(BN, false), idesc_pv = idesc_attn(HD, true);
+            const unsigned long long dq = smem_desc(q_s), dk = smem_desc(k_s), dp = smem_desc(p_s);
+            const unsigned long long dv = smem_desc_mn(v_s, ATOM_BYTES);
+            bool ok = mbar_wait(q_full, 0);
+            auto issue_s = [&](int j) {                                   // S(j) = Q K(j)^T into S buffer j % 2
+                const int s = j & 1;
+                if (!mbar_wait(&k_full[s], (j >> 1) & 1)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; kk++) {
+                    const unsigned off = ((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4;
+                    tc_mma(tm_s + s * BN, dq + off, dk + ((s * KV_BYTES) >> 4) + off, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(&k_empty[s]);                                   // the keys are free once S is done
+                tc_commit(&s_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; j < nb && ok && !*abort_flag; j++) {
+                const int s = j & 1;
+                if (j + 1 < nb) ok = issue_s(j + 1);                      // runs while the row threads work on S(j)
+                if (!ok) break;
+                // P(j) is in shared memory (and with that: S(j) and PV(j - 2) have been read), V(j) has landed
+                if (!mbar_wait(p_ready, j & 1) || !mbar_wait(&v_full[s], (j >> 1) & 1)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; kk++) {
+                    const unsigned a_off = ((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4;
+                    const unsigned b_off = (s * KV_BYTES + kk * 16 * 128) >> 4;
+                    tc_mma(tm_pv + s * BN, dp + a_off, dv + b_off, idesc_pv, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(&v_empty[s]);
+                tc_commit(&pv_full[s]);
+            }
+            if (!ok) {
+                atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+                *abort_flag = 1;
+            }
+        }
+    } else {
+        // ---- row threads: TMEM lane = query row of the tile; two threads a row.  The warps w and w + 4 may read
+        // the same 32 lanes; the first takes keys 0..63 of a block and the lower half of the head's columns, the
+        // second keys 64..127 and the upper half.  They exchange their maxima of a block through shared memory
+        // and meet at a named barrier of their own; their sums stay apart until the end.
+        const int quad = warp & 3, r = quad * 32 + lane, side = (warp - 2) >> 2;
+        const unsigned lane_sel = (unsigned)(quad * 32) << 16;
+        const int pos = pos0 + r;
+        const int key_first = p.window > 0 ? pos - p.window + 1 : 0;     // the keys this row sees: key_first .. pos
+        const float sc = 1.4426950408889634f / sqrtf((float)HD);
+        constexpr int OW = HD / 2;                                       // columns of O that this thread keeps
+        float o[OW];
+#pragma unroll
+        for (int i = 0; i < OW; i++) o[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, pending = 0.f;             // pending: the factor O takes before PV(j - 1) is added
+        bool ok = true;
+        for (int j = 0; j < nb; j++) {
+            const int s = j & 1, key0 = (blk_lo + j) * BN;
+            ok = !*abort_flag && mbar_wait(&s_full[s], (j >> 1) & 1);
+            ok = pair_agree(ok, 1 + quad);                                // the two warps of a row go on or leave together
+            if (!ok) break;
+            tc_fence_after();
+            // does any (row of the tile, key of the block) pair need the mask?
+            const bool edge = key0 + BN - 1 > pos0 || (p.window > 0 && key0 < pos0 + BM - 1 - p.window + 1);
+            // live columns of this row: c_lo .. c_lo + c_span (every column where no pair needs the mask); one
+            // unsigned comparison per element, no branch
+            const int c_lo = edge ? key_first - key0 : -(1 << 20);
+            const unsigned c_span = edge ? (unsigned)(pos - key_first) : (1u << 30);
+            const unsigned s_addr = tm_s + s * BN + lane_sel + side * 64;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                float v[32];
+                tc_ld32(s_addr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const float t = (unsigned)(side * 64 + c * 32 + i - c_lo) <= c_span ? v[i] * sc : -INFINITY;
+                    mx = fmaxf(mx, t);
+                }
+            }
+            float* xm = xchg + (j & 1) * 256;                             // [2 blocks in turn][side][row]
+            xm[side * 128 + r] = mx;
+            asm volatile("bar.sync %0, 64;\n" ::"r"(1 + quad) : "memory");
+            mx = fmaxf(mx, xm[(side ^ 1) * 128 + r]);
+            const float m_new = fmaxf(m_run, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = fast_exp2(m_run - m_use);                 // m_run = -inf gives 0
+            m_run = m_new;
+            if (j > 0) {                                                  // PV(j - 1) is done: P may be overwritten
+                ok = mbar_wait(&pv_full[s ^ 1], ((j - 1) >> 1) & 1);
+                ok = pair_agree(ok, 1 + quad);
+                if (!ok) break;
+                tc_fence_after();
+            }
+            float l_add = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                float v[32];
+                tc_ld32(s_addr + c * 32, v);
+                unsigned packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float t0 = (unsigned)(side * 64 + c * 32 + i - c_lo) <= c_span ? v[i] * sc : -INFINITY;
+                    const float t1 = (unsigned)(side * 64 + c * 32 + i + 1 - c_lo) <= c_span ? v[i + 1] * sc : -INFINITY;
+                    const float p0 = fast_exp2(t0 - m_use), p1 = fast_exp2(t1 - m_use);
+                    l_add += p0 + p1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                    packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
+                }
+                // 32 keys = 64 bytes = four 16-byte pieces of this row's 128-byte line in the slice of this side
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) {
+                    const int piece = c * 4 + q4;
+                    unsigned char* dst = p_s + side * ATOM_BYTES + r * 128 + ((piece ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+            }
+            l_run = l_run * alpha + l_add;
+            fence_async_smem();                                           // P: visible to the tensor core's reads
+            tc_fence_before();                                            // S(j) has been read
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready);
+            if (j > 0) {                                                  // O = O * factor + PV(j - 1)
+#pragma unroll
+                for (int c = 0; c < OW / 32; c++) {
+                    float v[32];
+                    tc_ld32(tm_pv + (s ^ 1) * BN + lane_sel + side * OW + c * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
+                }
+            }
+            pending = alpha;
+        }
+        if (ok) {
+            const int s = (nb - 1) & 1;
+            ok = mbar_wait(&pv_full[s], ((nb - 1) >> 1) & 1);
+            ok = pair_agree(ok, 1 + quad);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < OW / 32; c++) {
+                    float v[32];
+                    tc_ld32(tm_pv + s * BN + lane_sel + side * OW + c * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
+                }
+                float* xl = xchg + 512;                                   // the two sums of a row
+                xl[side * 128 + r] = l_run;
+                asm volatile("bar.sync %0, 64;\n" ::"r"(1 + quad) : "memory");
+                const float l_all = side == 0 ? l_run + xl[128 + r] : xl[r] + l_run;     // keys in ascending order
+                if (r < rows) {
+                    const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+                    bf16* orow = p.out + ((size_t)(row0 + r) * p.nh + h) * HD + side * OW;
+#pragma unroll
+                    for (int i = 0; i < OW; i += 8) {
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
+                        __nv_bfloat162 b1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
+                        __nv_bfloat162 b3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+                        *reinterpret_cast<uint4*>(orow + i) = make_uint4(*reinterpret_cast<unsigned*>(&b0), *reinterpret_cast<unsigned*>(&b1),
+                                                                         *reinterpret_cast<unsigned*>(&b2), *reinterpret_cast<unsigned*>(&b3));
+                    }
+                }
+            }
+        }
+        if (!ok && lane == 0) {
+            atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+            *abort_flag = 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// a bfloat16 matrix [rows, cols] (row-major, contiguous) in boxes of box_rows x 64 columns, 128-byte swizzle, zeros outside
+int make_map2d(CUtensorMap* map, const void* base, unsigned long long cols, unsigned long long rows, unsigned box_rows) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return (int)cudaErrorNotSupported;
+        fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int n_tiles,
+           cudaStream_t stream) {
+    const size_t smem = (size_t)(HD / 64) * ATOM_BYTES * 5 + 2 * ATOM_BYTES + 1024 + 256 + 768 * 4;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    attn_prefill_tc05_kernel<HD><<<dim3(n_tiles, p.nh), THREADS, smem, stream>>>(mq, mk, mv, p);
+    return esp_launch_status();
+}
+}  // namespace
+
+// q [n_tokens, nh, hd] and out the same shape, bfloat16; tile_seq / tile_first: the tiles of 64 new tokens
+// (those whose first token's index is a multiple of 128 start a block); hd 64 or 128; pages of 64 positions.
+ESP_API int esp_attn_prefill_tc05(const void* q, long long n_tokens, const void* k_cache, const void* v_cache, void* out,
+                                  const int* tile_seq, const int* tile_first, const int* seq_start, const int* seq_past,
+                                  const int* block_table, int table_stride, int n_pages, int page, int n_tiles, int nh,
+                                  int nkv, int hd, int window, int* status, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (page != PAGE || (hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || nh > 65535 || n_tokens <= 0)
+        return (int)cudaErrorInvalidValue;
+    const unsigned long long kv_rows = (unsigned long long)n_pages * nkv * PAGE;
+    if (kv_rows >= (1ull << 31)) return (int)cudaErrorInvalidValue;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map2d(&mq, q, (unsigned long long)nh * hd, (unsigned long long)n_tokens, BM);
+    if (rc) return rc;
+    rc = make_map2d(&mk, k_cache, (unsigned long long)hd, kv_rows, PAGE);
+    if (rc) return rc;
+    rc = make_map2d(&mv, v_cache, (unsigned long long)hd, kv_rows, PAGE);
+    if (rc) return rc;
+    AttnParams p{(bf16*)out, tile_seq, tile_first, seq_start, seq_past, block_table, table_stride, n_pages, nh, nkv,
+                 window, (int)kv_rows, status};
+    if (hd == 64) return launch<64>(mq, mk, mv, p, n_tiles, stream);
+    return launch<128>(mq, mk, mv, p, n_tiles, stream);
+}

@@ -33,7 +33,7 @@ LIBRARIES = {
     # bfloat16 only: loaded when a model runs in bfloat16
     "bf16": ["gemm_skinny.cu", "attn_decode.cu", "attn_prefill.cu"],
     # TMA + tcgen05/TMEM products for steps with many rows (bfloat16 prefill)
-    "tc05": ["gemm_tc05.cu"],
+    "tc05": ["gemm_tc05.cu", "attn_prefill_tc05.cu"],
 }
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

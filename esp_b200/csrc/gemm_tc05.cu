@@ -29,16 +29,14 @@
 // bounded: if one runs out the kernel raises ESP_STATUS_WAIT_EXPIRED in the
 // status word, stops issuing work, lets its own copies land, frees its TMEM and
 // returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc05.cuh"
 
 namespace {
+using namespace tc05;
 constexpr int BF = 128;            // features (weight rows) per tile: the M side of the MMA
 constexpr int TOK_BOX = 16;         // token rows per TMA box; a tile's width is a multiple of it
 constexpr int BK = 64, THREADS = 352;   // warps: 0 producer, 1 MMA, 2..5 epilogue, 6 producer, 7..10 epilogue
 constexpr int W_BYTES = BF * BK * 2;
-constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 struct Tc05Params {
     const int* tile_group;        // [tiles] or null (dense)
@@ -52,75 +50,6 @@ struct Tc05Params {
     int* status;
 };
 
-// ---- PTX wrappers ----------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
-        unsigned done;
-        asm volatile(
-            "{\n.reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            "selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, void* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(void* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b, unsigned idesc,
-                                       unsigned accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 32 consecutive float columns of this thread's TMEM lane
-__device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
-    unsigned r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (64 bfloat16), written by TMA
-// with the 128-byte swizzle; groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ unsigned long long smem_desc(const void* p) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_u32(p) & 0x3FFFFu) >> 4);       // start address, 16-byte units
-    d |= (unsigned long long)1 << 16;                                // leading byte offset: unused for this layout
-    d |= (unsigned long long)(1024 >> 4) << 32;                      // stride byte offset between 8-row groups
-    d |= (unsigned long long)1 << 46;                                // descriptor version of this architecture
-    d |= (unsigned long long)2 << 61;                                // 128-byte swizzle
-    return d;
-}
 // Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = n.
 __device__ __forceinline__ unsigned instr_desc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
@@ -146,10 +75,6 @@ constexpr int RING_KB = 96, RING_BYTES = RING_KB * 1024;    // each producer's o
 constexpr int NSLOT = 8;                   // stages of one ring in flight at most (pairs of mbarriers)
 constexpr int BAR_BYTES = 512;             // the mbarriers and two words behind the ring
 constexpr int SWAP_BYTES = 2 * 2 * 2 * 2 * 16 * 32 * 4;   // the epilogue's exchange of gate and up halves
-
-__device__ __forceinline__ void mbar_arrive(void* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
 
 struct TileInfo {
     int group, row0, n_rows, n_tok, f0;

@@ -39,6 +39,8 @@ _SIGNATURES = {
     "esp_gemm_skinny": [P, c_longlong, P, P, c_longlong, P, P, c_int, c_longlong, P, c_int, c_int, c_int, c_int, c_int,
                         c_int, P],
     "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_attn_prefill_tc05": [P, c_longlong, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              P, P],
     "esp_attn_decode": [P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                         P, P],
 }
@@ -369,6 +371,28 @@ def attn_prefill(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_
         _ptr(seq_start, torch.int32), _ptr(seq_past, torch.int32), _ptr(block_table, torch.int32),
         block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, int(window or 0),
         _ptr(status, torch.int32), _stream()), "attn_prefill")
+
+
+def attn_prefill_tc05_fits(hd, page) -> bool:
+    """Head sizes and page size that the tensor-memory prefill attention takes."""
+    return hd in (64, 128) and page == 64
+
+
+def attn_prefill_tc05(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,
+                      window, status):
+    """Prefill attention on tcgen05 with accumulators in tensor memory (bfloat16; head size 64 or 128; pages
+    of 64 positions).  Same arguments as attn_prefill; of the tiles of 64 new tokens, those whose first
+    token's index is a multiple of 128 start a block of 128 rows."""
+    if not attn_prefill_tc05_fits(hd, page):
+        raise Backend(f"attn_prefill_tc05: head size {hd} / page {page} not taken (64 or 128; page 64)")
+    if not q.is_contiguous() or q.numel() != q.shape[0] * nh * hd:
+        raise Backend("attn_prefill_tc05 takes contiguous queries [tokens, heads * head size]")
+    _check(_fn("tc05", "esp_attn_prefill_tc05")(
+        _ptr(q, torch.bfloat16, "q"), q.shape[0], _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
+        _ptr(out, torch.bfloat16), _ptr(tile_seq, torch.int32), _ptr(tile_first, torch.int32),
+        _ptr(seq_start, torch.int32), _ptr(seq_past, torch.int32), _ptr(block_table, torch.int32),
+        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, int(window or 0),
+        _ptr(status, torch.int32), _stream()), "attn_prefill_tc05")
 
 
 def gather_rows(src, rows, out):

@@ -603,6 +603,17 @@ def test_attn_prefill_against_reference(nh, nkv, hd, window):
     """Runs of new tokens of unequal length, some continuing a cached past, in
     interleaved pages; in every sequence some keys are made to dominate so that
     a lost, shifted or wrongly masked key shows."""
+    check_attn_prefill(ops.attn_prefill, nh, nkv, hd, window)
+
+
+@pytest.mark.parametrize("nh, nkv, hd, window", [(4, 4, 128, None), (6, 2, 64, None), (2, 1, 128, 100), (3, 1, 64, 65),
+                                                 (2, 2, 128, 300)])
+def test_attn_prefill_tc05_against_reference(nh, nkv, hd, window):
+    """The same runs through the kernel that keeps scores and weighted values in tensor memory."""
+    check_attn_prefill(ops.attn_prefill_tc05, nh, nkv, hd, window)
+
+
+def check_attn_prefill(fn, nh, nkv, hd, window):
     torch.manual_seed(3)
     dtype = torch.bfloat16
     group = nh // nkv
@@ -629,10 +640,10 @@ def test_attn_prefill_against_reference(nh, nkv, hd, window):
     i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
     starts = np.concatenate([[0], np.cumsum([nw for _p, nw in runs])])
     st = status()
-    ops.attn_prefill(q.reshape(n, nh * hd).to(DEV), kc, vc, out,
-                     i32([s for s, (_p, nw) in enumerate(runs) for _ in range(0, nw, 64)]),
-                     i32([f for _p, nw in runs for f in range(0, nw, 64)]), i32(starts), i32([p for p, _n in runs]),
-                     i32(tables), 64, nh, nkv, hd, window, st)
+    fn(q.reshape(n, nh * hd).to(DEV), kc, vc, out,
+       i32([s for s, (_p, nw) in enumerate(runs) for _ in range(0, nw, 64)]),
+       i32([f for _p, nw in runs for f in range(0, nw, 64)]), i32(starts), i32([p for p, _n in runs]),
+       i32(tables), 64, nh, nkv, hd, window, st)
     assert st.item() == 0
     for s, (past, new) in enumerate(runs):
         for i in range(new):
