@@ -2,8 +2,9 @@
 // windowed, grouped query heads, sequences of unequal length packed back to
 // back, keys and values read from the paged bfloat16 cache.
 //
-// A block owns 128 consecutive new tokens of one sequence and one query head
-// and walks the keys it may see in blocks of 128 (two pages of 64):
+// An item is 128 consecutive new tokens of one sequence and one query head; a
+// block works through a run of items, and for each walks the keys the item may
+// see in blocks of 128 (two pages of 64):
 //
 //   S  = Q K^T       tcgen05.mma, M = 128 queries, N = 128 keys, K = head size; float accumulator in TMEM
 //   P  = exp2(S * log2(e) / sqrt(hd) - m)   in 32-bit, by the thread that owns the row (TMEM lane = row,
@@ -34,7 +35,7 @@ struct AttnParams {
     const int* seq_start;
     const int* seq_past;
     const int* block_table;
-    int table_stride, n_pages, nh, nkv, window, kv_rows;
+    int table_stride, n_pages, nh, nkv, window, kv_rows, n_tiles;
     int* status;
 };
 
@@ -73,17 +74,39 @@ __device__ __forceinline__ bool pair_agree(bool ok, int id) {
     return all != 0;
 }
 
+// the tile of 128 query rows and the head that a block works on
+struct Item {
+    int seq, h, kvh, row0, rows, pos0, pos_last, blk_lo, nb;
+};
+__device__ __forceinline__ Item load_item(const AttnParams& p, int item) {
+    Item it;
+    const int tile = item / p.nh;
+    it.h = item - tile * p.nh;
+    it.kvh = it.h / (p.nh / p.nkv);
+    it.seq = p.tile_seq[tile];
+    const int first = p.tile_first[tile];
+    it.row0 = p.seq_start[it.seq] + first;                               // the tile's first row among the packed tokens
+    it.rows = min(BM, p.seq_start[it.seq + 1] - p.seq_start[it.seq] - first);
+    it.pos0 = p.seq_past[it.seq] + first;
+    it.pos_last = it.pos0 + it.rows - 1;
+    const int key_lo = p.window > 0 ? max(0, it.pos0 - p.window + 1) : 0;
+    it.blk_lo = key_lo / BN;
+    it.nb = it.pos_last / BN - it.blk_lo + 1;
+    return it;
+}
+
+// Persistent: the (tile, head) items are listed with the most keys first; block b takes the items
+// b, 2G-1-b, 2G+b, 4G-1-b, ... (G blocks), so that a long item is followed by a short one.  Every role
+// derives the same run of items, and the counters of key blocks (g) and items (n_items_done) that choose
+// the stage, the TMEM buffer and the phase of each mbarrier run on from one item to the next.
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, AttnParams p) {
     constexpr int HALVES = HD / 64;                       // 64-column slices of a head
     constexpr int Q_BYTES = HALVES * ATOM_BYTES, KV_BYTES = HALVES * ATOM_BYTES, P_BYTES = 2 * ATOM_BYTES;
-    // tiles are listed in order of position; the last ones see the most keys, so they start first
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
-    const int first = p.tile_first[tile];
-    if (first % BM != 0) return;                          // the list has tiles of 64 rows: every second one starts a block
-    const int seq = p.tile_seq[tile];
+    const int n_items = p.n_tiles * p.nh, G = gridDim.x;
+    auto item_of = [&](int round) { return round * G + ((round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x); };
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -99,22 +122,15 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned long long* v_empty = bars + 7;               // [2]
     unsigned long long* s_full = bars + 9;                // [2]
     unsigned long long* pv_full = bars + 11;              // [2]
-    unsigned long long* p_ready = bars + 13;              // [1]
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
+    unsigned long long* q_empty = bars + 13;              // [1]
+    unsigned long long* p_ready = bars + 14;              // [1]
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xchg = reinterpret_cast<float*>(bars) + 64;                  // [2][2][128] maxima, [2][128] sums of the row threads
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = p.seq_start[seq] + first;                          // the tile's first row among the packed tokens
-    const int n_new = p.seq_start[seq + 1] - p.seq_start[seq];
-    const int rows = min(BM, n_new - first);
-    const int pos0 = p.seq_past[seq] + first, pos_last = pos0 + rows - 1;
-    const int kvh = h / (p.nh / p.nkv);
-    const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    const int blk_lo = key_lo / BN, nb = pos_last / BN - blk_lo + 1;
-
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 13; i++) mbar_init(&bars[i], 1);
+        for (int i = 0; i < 14; i++) mbar_init(&bars[i], 1);
         mbar_init(p_ready, 8);                                           // one arrival per warp of row threads
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -132,47 +148,57 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 0) {
         // ---- loads: lanes 0..HALVES-1 the queries; then per block of keys, lane = (page of the block, slice)
         bool ok = true;
-        if (lane == 0) mbar_expect_tx(q_full, Q_BYTES);
-        __syncwarp();
-        if (lane < HALVES) tma_load_2d(q_s + lane * ATOM_BYTES, &map_q, h * HD + lane * 64, row0, q_full);
         const int pg_in_blk = lane / HALVES, half = lane % HALVES;      // lanes 0..2*HALVES-1 issue boxes
-        int issued_k = 0, issued_v = 0;
-        for (int j = 0; j < nb && ok; j++) {
-            const int s = j & 1;
-            // the page of this lane's box; a page past the tile's last key is read as zeros (a row past the cache)
-            int box_row = p.kv_rows;
-            if (lane < 2 * HALVES) {
-                const int page_idx = (blk_lo + j) * 2 + pg_in_blk;
-                if (page_idx <= pos_last / PAGE) {
-                    const int pg = p.block_table[(size_t)seq * p.table_stride + page_idx];
-                    if (pg >= 0 && pg < p.n_pages) box_row = (pg * p.nkv + kvh) * PAGE;
-                    else atomicOr(p.status, ESP_STATUS_BAD_INDEX);
+        int g = 0, issued_q = 0, issued_k = 0, issued_v = 0;
+        for (int round = 0; ok; round++) {
+            const int item = item_of(round);
+            if (item >= n_items) break;
+            const Item t = load_item(p, item);
+            if (lane == 0) {                                             // the last item's S products have read its queries
+                ok = !*abort_flag && mbar_wait(q_empty, (round & 1) ^ 1);
+                if (ok) mbar_expect_tx(q_full, Q_BYTES);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (lane < HALVES) tma_load_2d(q_s + lane * ATOM_BYTES, &map_q, t.h * HD + lane * 64, t.row0, q_full);
+            issued_q = round + 1;
+            for (int j = 0; j < t.nb && ok; j++, g++) {
+                const int s = g & 1;
+                // the page of this lane's box; a page past the tile's last key is read as zeros (a row past the cache)
+                int box_row = p.kv_rows;
+                if (lane < 2 * HALVES) {
+                    const int page_idx = (t.blk_lo + j) * 2 + pg_in_blk;
+                    if (page_idx <= t.pos_last / PAGE) {
+                        const int pg = p.block_table[(size_t)t.seq * p.table_stride + page_idx];
+                        if (pg >= 0 && pg < p.n_pages) box_row = (pg * p.nkv + t.kvh) * PAGE;
+                        else atomicOr(p.status, ESP_STATUS_BAD_INDEX);
+                    }
                 }
+                if (lane == 0) {
+                    ok = !*abort_flag && mbar_wait(&k_empty[s], ((g >> 1) & 1) ^ 1);
+                    if (ok) mbar_expect_tx(&k_full[s], KV_BYTES);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (lane < 2 * HALVES)
+                    tma_load_2d(k_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_k, half * 64, box_row, &k_full[s]);
+                issued_k = g + 1;
+                if (lane == 0) {
+                    ok = !*abort_flag && mbar_wait(&v_empty[s], ((g >> 1) & 1) ^ 1);
+                    if (ok) mbar_expect_tx(&v_full[s], KV_BYTES);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (lane < 2 * HALVES)
+                    tma_load_2d(v_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_v, half * 64, box_row, &v_full[s]);
+                issued_v = g + 1;
             }
-            if (lane == 0) {
-                ok = !*abort_flag && mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1);
-                if (ok) mbar_expect_tx(&k_full[s], KV_BYTES);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (lane < 2 * HALVES)
-                tma_load_2d(k_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_k, half * 64, box_row, &k_full[s]);
-            issued_k = j + 1;
-            if (lane == 0) {
-                ok = !*abort_flag && mbar_wait(&v_empty[s], ((j >> 1) & 1) ^ 1);
-                if (ok) mbar_expect_tx(&v_full[s], KV_BYTES);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (lane < 2 * HALVES)
-                tma_load_2d(v_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_v, half * 64, box_row, &v_full[s]);
-            issued_v = j + 1;
         }
         if (lane == 0 && (!ok || *abort_flag)) {
             atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
             *abort_flag = 1;
             // let this CTA's own copies land before its shared memory is given up
-            mbar_wait(q_full, 0);
+            if (issued_q > 0) mbar_wait(q_full, (issued_q - 1) & 1);
             for (int j = max(0, issued_k - 2); j < issued_k; j++) mbar_wait(&k_full[j & 1], (j >> 1) & 1);
             for (int j = max(0, issued_v - 2); j < issued_v; j++) mbar_wait(&v_full[j & 1], (j >> 1) & 1);
         }
@@ -181,10 +207,11 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const unsigned idesc_s = idesc_attn(BN, false), idesc_pv = idesc_attn(HD, true);
             const unsigned long long dq = smem_desc(q_s), dk = smem_desc(k_s), dp = smem_desc(p_s);
             const unsigned long long dv = smem_desc_mn(v_s, ATOM_BYTES);
-            bool ok = mbar_wait(q_full, 0);
-            auto issue_s = [&](int j) {                                   // S(j) = Q K(j)^T into S buffer j % 2
-                const int s = j & 1;
-                if (!mbar_wait(&k_full[s], (j >> 1) & 1)) return false;
+            bool ok = true;
+            int g = 0;
+            auto issue_s = [&](int gg, bool last_of_item) {               // S = Q K^T of key block gg into S buffer gg % 2
+                const int s = gg & 1;
+                if (!mbar_wait(&k_full[s], (gg >> 1) & 1)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; kk++) {
@@ -192,28 +219,36 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     tc_mma(tm_s + s * BN, dq + off, dk + ((s * KV_BYTES) >> 4) + off, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 tc_commit(&k_empty[s]);                                   // the keys are free once S is done
+                if (last_of_item) tc_commit(q_empty);                     // and so are the queries after the item's last S
                 tc_commit(&s_full[s]);
                 return true;
             };
-            if (ok) ok = issue_s(0);
-            for (int j = 0; j < nb && ok && !*abort_flag; j++) {
-                const int s = j & 1;
-                if (j + 1 < nb) ok = issue_s(j + 1);                      // runs while the row threads work on S(j)
-                if (!ok) break;
-                // P(j) is in shared memory (and with that: S(j) and PV(j - 2) have been read), V(j) has landed
-                if (!mbar_wait(p_ready, j & 1) || !mbar_wait(&v_full[s], (j >> 1) & 1)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
+            for (int round = 0; ok && !*abort_flag; round++) {
+                const int item = item_of(round);
+                if (item >= n_items) break;
+                const Item t = load_item(p, item);
+                ok = mbar_wait(q_full, round & 1);
+                if (ok) ok = issue_s(g, t.nb == 1);
+                for (int j = 0; j < t.nb && ok && !*abort_flag; j++, g++) {
+                    const int s = g & 1;
+                    if (j + 1 < t.nb) ok = issue_s(g + 1, j + 2 == t.nb);  // runs while the row threads work on this block
+                    if (!ok) break;
+                    // P is in shared memory (and with that: S of this block and PV of two blocks ago have been
+                    // read), the values have landed
+                    if (!mbar_wait(p_ready, g & 1) || !mbar_wait(&v_full[s], (g >> 1) & 1)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; kk++) {
-                    const unsigned a_off = ((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4;
-                    const unsigned b_off = (s * KV_BYTES + kk * 16 * 128) >> 4;
-                    tc_mma(tm_pv + s * BN, dp + a_off, dv + b_off, idesc_pv, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < BN / 16; kk++) {
+                        const unsigned a_off = ((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4;
+                        const unsigned b_off = (s * KV_BYTES + kk * 16 * 128) >> 4;
+                        tc_mma(tm_pv + s * BN, dp + a_off, dv + b_off, idesc_pv, kk > 0 ? 1u : 0u);
+                    }
+                    tc_commit(&v_empty[s]);
+                    tc_commit(&pv_full[s]);
                 }
-                tc_commit(&v_empty[s]);
-                tc_commit(&pv_full[s]);
             }
             if (!ok) {
                 atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
@@ -227,121 +262,136 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // and meet at a named barrier of their own; their sums stay apart until the end.
         const int quad = warp & 3, r = quad * 32 + lane, side = (warp - 2) >> 2;
         const unsigned lane_sel = (unsigned)(quad * 32) << 16;
-        const int pos = pos0 + r;
-        const int key_first = p.window > 0 ? pos - p.window + 1 : 0;     // the keys this row sees: key_first .. pos
         const float sc = 1.4426950408889634f / sqrtf((float)HD);
         constexpr int OW = HD / 2;                                       // columns of O that this thread keeps
-        float o[OW];
-#pragma unroll
-        for (int i = 0; i < OW; i++) o[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, pending = 0.f;             // pending: the factor O takes before PV(j - 1) is added
         bool ok = true;
-        for (int j = 0; j < nb; j++) {
-            const int s = j & 1, key0 = (blk_lo + j) * BN;
-            ok = !*abort_flag && mbar_wait(&s_full[s], (j >> 1) & 1);
-            ok = pair_agree(ok, 1 + quad);                                // the two warps of a row go on or leave together
-            if (!ok) break;
-            tc_fence_after();
-            // does any (row of the tile, key of the block) pair need the mask?
-            const bool edge = key0 + BN - 1 > pos0 || (p.window > 0 && key0 < pos0 + BM - 1 - p.window + 1);
-            // live columns of this row: c_lo .. c_lo + c_span (every column where no pair needs the mask); one
-            // unsigned comparison per element, no branch
-            const int c_lo = edge ? key_first - key0 : -(1 << 20);
-            const unsigned c_span = edge ? (unsigned)(pos - key_first) : (1u << 30);
-            const unsigned s_addr = tm_s + s * BN + lane_sel + side * 64;
-            float mx = -INFINITY;
+        int g = 0;
+        for (int round = 0; ok; round++) {
+            const int item = item_of(round);
+            if (item >= n_items) break;
+            const Item t = load_item(p, item);
+            const int pos = t.pos0 + r;
+            const int key_first = p.window > 0 ? pos - p.window + 1 : 0; // the keys this row sees: key_first .. pos
+            float o[OW];
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                float v[32];
-                tc_ld32(s_addr + c * 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float t = (unsigned)(side * 64 + c * 32 + i - c_lo) <= c_span ? v[i] * sc : -INFINITY;
-                    mx = fmaxf(mx, t);
-                }
-            }
-            float* xm = xchg + (j & 1) * 256;                             // [2 blocks in turn][side][row]
-            xm[side * 128 + r] = mx;
-            asm volatile("bar.sync %0, 64;\n" ::"r"(1 + quad) : "memory");
-            mx = fmaxf(mx, xm[(side ^ 1) * 128 + r]);
-            const float m_new = fmaxf(m_run, mx);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = fast_exp2(m_run - m_use);                 // m_run = -inf gives 0
-            m_run = m_new;
-            if (j > 0) {                                                  // PV(j - 1) is done: P may be overwritten
-                ok = mbar_wait(&pv_full[s ^ 1], ((j - 1) >> 1) & 1);
-                ok = pair_agree(ok, 1 + quad);
+            for (int i = 0; i < OW; i++) o[i] = 0.f;
+            float m_run = -INFINITY, l_run = 0.f, pending = 0.f;         // pending: the factor O takes before the last PV is added
+            for (int j = 0; j < t.nb; j++, g++) {
+                const int s = g & 1, key0 = (t.blk_lo + j) * BN;
+                ok = !*abort_flag && mbar_wait(&s_full[s], (g >> 1) & 1);
+                ok = pair_agree(ok, 1 + quad);                            // the two warps of a row go on or leave together
                 if (!ok) break;
                 tc_fence_after();
-            }
-            float l_add = 0.f;
+                // does any (row of the tile, key of the block) pair need the mask?
+                const bool edge = key0 + BN - 1 > t.pos0 || (p.window > 0 && key0 < t.pos0 + BM - 1 - p.window + 1);
+                // live columns of this row: c_lo .. c_lo + c_span; one unsigned comparison per element, no branch
+                const int c_lo = key_first - key0 - side * 64;
+                const unsigned c_span = (unsigned)(pos - key_first);
+                const unsigned s_addr = tm_s + s * BN + lane_sel + side * 64;
+                float mx = -INFINITY;                                     // of the raw scores: the scale is positive
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                float v[32];
-                tc_ld32(s_addr + c * 32, v);
-                unsigned packed[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float t0 = (unsigned)(side * 64 + c * 32 + i - c_lo) <= c_span ? v[i] * sc : -INFINITY;
-                    const float t1 = (unsigned)(side * 64 + c * 32 + i + 1 - c_lo) <= c_span ? v[i + 1] * sc : -INFINITY;
-                    const float p0 = fast_exp2(t0 - m_use), p1 = fast_exp2(t1 - m_use);
-                    l_add += p0 + p1;
-                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                    packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
-                }
-                // 32 keys = 64 bytes = four 16-byte pieces of this row's 128-byte line in the slice of this side
-#pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {
-                    const int piece = c * 4 + q4;
-                    unsigned char* dst = p_s + side * ATOM_BYTES + r * 128 + ((piece ^ (r & 7)) << 4);
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
-            }
-            l_run = l_run * alpha + l_add;
-            fence_async_smem();                                           // P: visible to the tensor core's reads
-            tc_fence_before();                                            // S(j) has been read
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready);
-            if (j > 0) {                                                  // O = O * factor + PV(j - 1)
-#pragma unroll
-                for (int c = 0; c < OW / 32; c++) {
+                for (int c = 0; c < 2; c++) {
                     float v[32];
-                    tc_ld32(tm_pv + (s ^ 1) * BN + lane_sel + side * OW + c * 32, v);
+                    tc_ld32(s_addr + c * 32, v);
+                    if (edge) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
-                }
-            }
-            pending = alpha;
-        }
-        if (ok) {
-            const int s = (nb - 1) & 1;
-            ok = mbar_wait(&pv_full[s], ((nb - 1) >> 1) & 1);
-            ok = pair_agree(ok, 1 + quad);
-            if (ok) {
-                tc_fence_after();
+                        for (int i = 0; i < 32; i++) mx = fmaxf(mx, (unsigned)(c * 32 + i - c_lo) <= c_span ? v[i] : -INFINITY);
+                    } else {
 #pragma unroll
-                for (int c = 0; c < OW / 32; c++) {
-                    float v[32];
-                    tc_ld32(tm_pv + s * BN + lane_sel + side * OW + c * 32, v);
-#pragma unroll
-                    for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
-                }
-                float* xl = xchg + 512;                                   // the two sums of a row
-                xl[side * 128 + r] = l_run;
-                asm volatile("bar.sync %0, 64;\n" ::"r"(1 + quad) : "memory");
-                const float l_all = side == 0 ? l_run + xl[128 + r] : xl[r] + l_run;     // keys in ascending order
-                if (r < rows) {
-                    const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
-                    bf16* orow = p.out + ((size_t)(row0 + r) * p.nh + h) * HD + side * OW;
-#pragma unroll
-                    for (int i = 0; i < OW; i += 8) {
-                        __nv_bfloat162 b0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
-                        __nv_bfloat162 b1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
-                        __nv_bfloat162 b3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
-                        *reinterpret_cast<uint4*>(orow + i) = make_uint4(*reinterpret_cast<unsigned*>(&b0), *reinterpret_cast<unsigned*>(&b1),
-                                                                         *reinterpret_cast<unsigned*>(&b2), *reinterpret_cast<unsigned*>(&b3));
+                        for (int i = 0; i < 32; i++) mx = fmaxf(mx, v[i]);
                     }
+                }
+                float* xm = xchg + (g & 1) * 256;                         // [2 blocks in turn][side][row]
+                xm[side * 128 + r] = mx;
+                asm volatile("bar.sync %0, 64;\n" ::"r"(1 + quad) : "memory");
+                mx = fmaxf(mx, xm[(side ^ 1) * 128 + r]) * sc;
+                const float m_new = fmaxf(m_run, mx);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                const float alpha = fast_exp2(m_run - m_use);             // m_run = -inf gives 0
+                m_run = m_new;
+                if (j > 0) {                                              // the last PV is done: P may be overwritten
+                    ok = mbar_wait(&pv_full[s ^ 1], ((g - 1) >> 1) & 1);
+                    ok = pair_agree(ok, 1 + quad);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                float l_add = 0.f;
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    float v[32];
+                    tc_ld32(s_addr + c * 32, v);
+                    unsigned packed[16];
+                    if (edge) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = (unsigned)(c * 32 + i - c_lo) <= c_span ? fast_exp2(fmaf(v[i], sc, -m_use)) : 0.f;
+                            const float p1 = (unsigned)(c * 32 + i + 1 - c_lo) <= c_span ? fast_exp2(fmaf(v[i + 1], sc, -m_use)) : 0.f;
+                            l_add += p0 + p1;
+                            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                            packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = fast_exp2(fmaf(v[i], sc, -m_use)), p1 = fast_exp2(fmaf(v[i + 1], sc, -m_use));
+                            l_add += p0 + p1;
+                            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                            packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
+                        }
+                    }
+                    // 32 keys = 64 bytes = four 16-byte pieces of this row's 128-byte line in the slice of this side
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; q4++) {
+                        const int piece = c * 4 + q4;
+                        unsigned char* dst = p_s + side * ATOM_BYTES + r * 128 + ((piece ^ (r & 7)) << 4);
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                    }
+                }
+                l_run = l_run * alpha + l_add;
+                fence_async_smem();                                       // P: visible to the tensor core's reads
+                tc_fence_before();                                        // S of this block has been read
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_ready);
+                if (j > 0) {                                              // O = O * factor + PV of the block before
+#pragma unroll
+                    for (int c = 0; c < OW / 32; c++) {
+                        float v[32];
+                        tc_ld32(tm_pv + (s ^ 1) * BN + lane_sel + side * OW + c * 32, v);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
+                    }
+                }
+                pending = alpha;
+            }
+            if (!ok) break;
+            const int s = (g - 1) & 1;                                    // the item's last block
+            ok = mbar_wait(&pv_full[s], ((g - 1) >> 1) & 1);
+            ok = pair_agree(ok, 1 + quad);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < OW / 32; c++) {
+                float v[32];
+                tc_ld32(tm_pv + s * BN + lane_sel + side * OW + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
+            }
+            tc_fence_before();
+            float* xl = xchg + 512;                                       // the two sums of a row
+            xl[side * 128 + r] = l_run;
+            asm volatile("bar.sync %0, 64;\n" ::"r"(1 + quad) : "memory");
+            const float l_all = side == 0 ? l_run + xl[128 + r] : xl[r] + l_run;     // keys in ascending order
+            if (r < t.rows) {
+                const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+                bf16* orow = p.out + ((size_t)(t.row0 + r) * p.nh + t.h) * HD + side * OW;
+#pragma unroll
+                for (int i = 0; i < OW; i += 8) {
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
+                    __nv_bfloat162 b1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
+                    __nv_bfloat162 b3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+                    *reinterpret_cast<uint4*>(orow + i) = make_uint4(*reinterpret_cast<unsigned*>(&b0), *reinterpret_cast<unsigned*>(&b1),
+                                                                     *reinterpret_cast<unsigned*>(&b2), *reinterpret_cast<unsigned*>(&b3));
                 }
             }
         }
@@ -393,13 +443,25 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
-    attn_prefill_tc05_kernel<HD><<<dim3(n_tiles, p.nh), THREADS, smem, stream>>>(mq, mk, mv, p);
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    const long long items = (long long)n_tiles * p.nh;
+    // with more items than SMs, blocks take pairs (a long item and a short one): as many blocks as halve the list
+    long long grid = items <= sm_count ? items : (items + 1) / 2;
+    if (grid > sm_count) grid = sm_count;
+    attn_prefill_tc05_kernel<HD><<<(int)grid, THREADS, smem, stream>>>(mq, mk, mv, p);
     return esp_launch_status();
 }
 }  // namespace
 
-// q [n_tokens, nh, hd] and out the same shape, bfloat16; tile_seq / tile_first: the tiles of 64 new tokens
-// (those whose first token's index is a multiple of 128 start a block); hd 64 or 128; pages of 64 positions.
+// q [n_tokens, nh, hd] and out the same shape, bfloat16; tile_seq / tile_first: the tiles of 128 new tokens
+// (sequence, index of the tile's first token among the sequence's new tokens), best listed with the tiles
+// that see the most keys first; hd 64 or 128; pages of 64 positions.
 ESP_API int esp_attn_prefill_tc05(const void* q, long long n_tokens, const void* k_cache, const void* v_cache, void* out,
                                   const int* tile_seq, const int* tile_first, const int* seq_start, const int* seq_past,
                                   const int* block_table, int table_stride, int n_pages, int page, int n_tiles, int nh,
@@ -417,7 +479,7 @@ ESP_API int esp_attn_prefill_tc05(const void* q, long long n_tokens, const void*
     rc = make_map2d(&mv, v_cache, (unsigned long long)hd, kv_rows, PAGE);
     if (rc) return rc;
     AttnParams p{(bf16*)out, tile_seq, tile_first, seq_start, seq_past, block_table, table_stride, n_pages, nh, nkv,
-                 window, (int)kv_rows, status};
+                 window, (int)kv_rows, n_tiles, status};
     if (hd == 64) return launch<64>(mq, mk, mv, p, n_tiles, stream);
     return launch<128>(mq, mk, mv, p, n_tiles, stream);
 }

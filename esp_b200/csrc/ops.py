@@ -381,8 +381,8 @@ def attn_prefill_tc05_fits(hd, page) -> bool:
 def attn_prefill_tc05(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,
                       window, status):
     """Prefill attention on tcgen05 with accumulators in tensor memory (bfloat16; head size 64 or 128; pages
-    of 64 positions).  Same arguments as attn_prefill; of the tiles of 64 new tokens, those whose first
-    token's index is a multiple of 128 start a block of 128 rows."""
+    of 64 positions).  Same arguments as attn_prefill, but tile_seq / tile_first list tiles of 128 new
+    tokens, best with the tiles that see the most keys first (the order only matters for the balance)."""
     if not attn_prefill_tc05_fits(hd, page):
         raise Backend(f"attn_prefill_tc05: head size {hd} / page {page} not taken (64 or 128; page 64)")
     if not q.is_contiguous() or q.numel() != q.shape[0] * nh * hd:

@@ -199,16 +199,21 @@ class Engine:
             tables = [np.asarray(g.table_rows(slots, stride), dtype=np.int32).reshape(b, stride)
                       for g in book.groups]
             tiles = [(i, first) for i, t in enumerate(news) for first in range(0, t, 64)]
+            # tiles of 128 rows for the tensor-memory attention, those that see the most keys first
+            wide = sorted(((i, first) for i, t in enumerate(news) for first in range(0, t, 128)),
+                          key=lambda sf: -(pasts[sf[0]] + min(sf[1] + 128, news[sf[0]])))
             arrays = [tok_ids, tok_seq, tok_pos, np.asarray(slots, dtype=np.int32),
                       np.asarray(starts, dtype=np.int32), np.asarray(pasts, dtype=np.int32),
                       np.asarray(want_rows, dtype=np.int32), np.asarray([t[0] for t in tiles], dtype=np.int32),
-                      np.asarray([t[1] for t in tiles], dtype=np.int32), *tables, *extra_arrays]
+                      np.asarray([t[1] for t in tiles], dtype=np.int32), np.asarray([t[0] for t in wide], dtype=np.int32),
+                      np.asarray([t[1] for t in wide], dtype=np.int32), *tables, *extra_arrays]
             dev = self._stage(arrays)
-            nt = 9 + len(tables)
+            nt = 11 + len(tables)
             ctx = StepContext(
                 n_tokens=n, n_seqs=b, max_new=max(news), max_len=max(p + t for p, t in zip(pasts, news)),
                 tok_ids=dev[0], tok_seq=dev[1], tok_pos=dev[2], seq_slot=dev[3], seq_start=dev[4], seq_past=dev[5],
-                want_rows=dev[6], q_tile_seq=dev[7], q_tile_first=dev[8], block_tables=list(dev[9:nt]),
+                want_rows=dev[6], q_tile_seq=dev[7], q_tile_first=dev[8], q_wide_seq=dev[9], q_wide_first=dev[10],
+                block_tables=list(dev[11:nt]),
                 host={"slots": slots, "news": news, "pasts": pasts, "starts": starts, "want_rows": want_rows},
                 aux=aux if aux is not None else {})
             extra = dev[nt:]

@@ -118,9 +118,9 @@ class Attention(Part):
             ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, rt.attn_counters, ctx.tok_seq, ctx.tok_pos, table, layer.page,
                             s.num_heads, s.num_kv_heads, s.head_dim, s.window, split, n_splits, rt.status)
             return
-        if rt.dtype == torch.bfloat16 and ops.attn_prefill_tc05_fits(s.head_dim, layer.page):
+        if rt.dtype == torch.bfloat16 and ops.attn_prefill_tc05_fits(s.head_dim, layer.page) and ctx.q_wide_seq is not None:
             # many rows, head size 64 or 128: scores and weighted values in tensor memory (tcgen05)
-            ops.attn_prefill_tc05(q, layer.k, layer.v, o, ctx.q_tile_seq, ctx.q_tile_first, ctx.seq_start, ctx.seq_past,
+            ops.attn_prefill_tc05(q, layer.k, layer.v, o, ctx.q_wide_seq, ctx.q_wide_first, ctx.seq_start, ctx.seq_past,
                                   table, layer.page, s.num_heads, s.num_kv_heads, s.head_dim, s.window, rt.status)
             return
         if rt.dtype == torch.bfloat16 and s.head_dim <= 128 and layer.page == 64:

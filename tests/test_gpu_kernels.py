@@ -610,10 +610,10 @@ def test_attn_prefill_against_reference(nh, nkv, hd, window):
                                                  (2, 2, 128, 300)])
 def test_attn_prefill_tc05_against_reference(nh, nkv, hd, window):
     """The same runs through the kernel that keeps scores and weighted values in tensor memory."""
-    check_attn_prefill(ops.attn_prefill_tc05, nh, nkv, hd, window)
+    check_attn_prefill(ops.attn_prefill_tc05, nh, nkv, hd, window, tile=128)
 
 
-def check_attn_prefill(fn, nh, nkv, hd, window):
+def check_attn_prefill(fn, nh, nkv, hd, window, tile=64):
     torch.manual_seed(3)
     dtype = torch.bfloat16
     group = nh // nkv
@@ -641,8 +641,8 @@ def check_attn_prefill(fn, nh, nkv, hd, window):
     starts = np.concatenate([[0], np.cumsum([nw for _p, nw in runs])])
     st = status()
     fn(q.reshape(n, nh * hd).to(DEV), kc, vc, out,
-       i32([s for s, (_p, nw) in enumerate(runs) for _ in range(0, nw, 64)]),
-       i32([f for _p, nw in runs for f in range(0, nw, 64)]), i32(starts), i32([p for p, _n in runs]),
+       i32([s for s, (_p, nw) in enumerate(runs) for _ in range(0, nw, tile)]),
+       i32([f for _p, nw in runs for f in range(0, nw, tile)]), i32(starts), i32([p for p, _n in runs]),
        i32(tables), 64, nh, nkv, hd, window, st)
     assert st.item() == 0
     for s, (past, new) in enumerate(runs):
