@@ -29,6 +29,8 @@
 // bounded: if one runs out the kernel raises ESP_STATUS_WAIT_EXPIRED in the
 // status word, stops issuing work, lets its own copies land, frees its TMEM and
 // returns.
+#include <type_traits>
+
 #include "tc05.cuh"
 
 namespace {
@@ -219,12 +221,33 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            int used = 0, local = 0;
+            int local = 0, ring = 0;
             int off0 = 0, off1 = 0, count0 = 0, count1 = 0;           // per ring: the next offset (KB), the stages consumed
             // descriptors differ from stage to stage and from one 16-wide k step to the next only in the
             // address field (16-byte units): the low word is a base plus a constant
             const unsigned long long desc0 = smem_desc(smem);
             const unsigned desc_hi = (unsigned)(desc0 >> 32), desc_lo0 = (unsigned)desc0;
+            const unsigned full_addr = smem_u32(full_bar), empty_addr = smem_u32(empty_bar);
+            bool ok = true;
+            // one k step out of ring R: wait for its stage, four MMAs, hand the stage back
+            auto k_step = [&](auto ring_tag, int& off, int& count, unsigned acc, unsigned idesc, int size_kb, bool first) {
+                constexpr int R = decltype(ring_tag)::value;
+                const unsigned slot8 = (unsigned)(R * NSLOT + (count & (NSLOT - 1))) << 3;
+                if (!mbar_wait_addr(full_addr + slot8, (count >> 3) & 1)) return false;
+                tc_fence_after();
+                if (off + size_kb > RING_KB) off = 0;                   // the producer's rule
+                const unsigned w_lo = desc_lo0 + (R * RING_KB + off) * (1024 >> 4);
+                const unsigned t_lo = w_lo + (W_BYTES >> 4);
+                off += size_kb;
+                count++;
+                tc_mma_lo(acc, w_lo, t_lo, desc_hi, idesc, first ? 0u : 1u);
+                tc_mma_lo(acc, w_lo + 2, t_lo + 2, desc_hi, idesc, 1u);
+                tc_mma_lo(acc, w_lo + 4, t_lo + 4, desc_hi, idesc, 1u);
+                tc_mma_lo(acc, w_lo + 6, t_lo + 6, desc_hi, idesc, 1u);
+                tc_commit_addr(empty_addr + slot8);                     // the stage is free once these MMAs have read it
+                return true;
+            };
+            static_assert(NSLOT == 8 && BK == 64, "the slot arithmetic and the four MMAs of a k step are written out");
             TileInfo next = tile_info<MAX_TOK, FEATS>(p, blockIdx.x, feat_tiles);
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
                 const TileInfo t = next;
@@ -233,39 +256,22 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const int buf = local % NBUF;
                 // the epilogue must have emptied this accumulator buffer (NBUF tiles ago)
                 if (!mbar_wait(&acc_empty_bar[buf], ((local / NBUF) & 1) ^ 1)) {
-                    atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
-                    *abort_flag = 1;
+                    ok = false;
                     break;
                 }
                 tc_fence_after();
                 const unsigned acc = tmem_base + buf * ACC_COLS;
                 const int size_kb = (W_BYTES + t.n_tok * BK * 2) >> 10;
-                for (int k = 0; k < k_iters; k++, used++) {
-                    const int ring = used % PRODUCERS;
-                    int off = ring ? off1 : off0;
-                    const int count = ring ? count1 : count0;
-                    const int s = ring * NSLOT + count % NSLOT;
-                    if (!mbar_wait(&full_bar[s], (count / NSLOT) & 1)) {
-                        atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
-                        *abort_flag = 1;
-                        break;
-                    }
-                    tc_fence_after();
-                    if (off + size_kb > RING_KB) off = 0;               // the producer's rule
-                    const unsigned w_lo = desc_lo0 + (ring * RING_KB + off) * (1024 >> 4);
-                    if (ring) off1 = off + size_kb, count1 = count + 1;
-                    else off0 = off + size_kb, count0 = count + 1;
-                    const unsigned t_lo = w_lo + (W_BYTES >> 4);
-#pragma unroll
-                    for (int kk = 0; kk < BK / 16; kk++) {
-                        const unsigned accum = (kk > 0 || k > 0) ? 1u : 0u;
-                        tc_mma(acc, ((unsigned long long)desc_hi << 32) | (w_lo + kk * 2),
-                               ((unsigned long long)desc_hi << 32) | (t_lo + kk * 2), idesc, accum);
-                    }
-                    tc_commit(&empty_bar[s]);                         // the stage is free once these MMAs have read it
+                for (int k = 0; k < k_iters && ok; k++, ring ^= 1) {
+                    if (ring == 0) ok = k_step(std::integral_constant<int, 0>{}, off0, count0, acc, idesc, size_kb, k == 0);
+                    else ok = k_step(std::integral_constant<int, 1>{}, off1, count1, acc, idesc, size_kb, k == 0);
                 }
-                if (*abort_flag) break;
+                if (!ok || *abort_flag) break;
                 tc_commit(&acc_full_bar[buf]);                        // the accumulator is complete once all MMAs are done
+            }
+            if (!ok) {
+                atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
+                *abort_flag = 1;
             }
         }
     } else {

@@ -30,6 +30,19 @@ __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
     }
     return false;
 }
+// the same on the barrier's shared-memory address
+__device__ __forceinline__ bool mbar_wait_addr(unsigned addr, unsigned parity) {
+    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, void* bar) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
@@ -47,6 +60,21 @@ __device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long desc_
         "setp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit_addr(unsigned bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_addr) : "memory");
+}
+// the same MMA with the two operand descriptors given as their low words and the high word they share: the
+// thread that issues the MMAs is alone on its critical path, every instruction it saves counts
+__device__ __forceinline__ void tc_mma_lo(unsigned tmem_d, unsigned a_lo, unsigned b_lo, unsigned hi, unsigned idesc,
+                                          unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "mov.b64 da, {%1, %3};\n"
+        "mov.b64 db, {%2, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}\n"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 // 32 consecutive float columns of this thread's TMEM lane
 __device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
