@@ -256,7 +256,7 @@ def main() -> int:
 
         prov.generate(reqs, on_token)
         t0, t1 = marks[a.warmup], marks[a.warmup + a.steps]
-        h2d = 4 * (7 * a.batch + 1 + a.batch * ((a.context + 63) // 64) + 3 * a.batch)
+        h2d = engine.staged_bytes         # the last step's staged arrays: ids, positions, page tables, sampling options
         e2e = {"value": round(a.batch * a.steps / (t1 - t0), 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": 4 * (a.batch + 1)}
 

@@ -86,8 +86,11 @@ class GroupBook:
         """Page indices that a step taking the slot from old_len to new_len
         needs and does not hold yet."""
         table = self.tables.get(slot, [])
-        lo = self.first_needed(old_len) // PAGE
         hi = pages_for(new_len)
+        if self.layout.window is None:
+            # nothing is ever given back before the slot closes: the table has no gaps
+            return list(range(len(table), hi)) if hi > len(table) else []
+        lo = self.first_needed(old_len) // PAGE
         return [i for i in range(lo, hi) if i >= len(table) or table[i] < 0]
 
     def reserve(self, slot: int, old_len: int, new_len: int) -> None:

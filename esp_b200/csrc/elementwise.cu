@@ -29,6 +29,20 @@ ESP_API int esp_embed_gather(const void* table, int table_is_bf16, const int* id
     return esp_launch_status();
 }
 
+// ---------------------------------------------------------------- token ids from the last step's choices
+// ids[j] = picks[src[j]] where src[j] >= 0: a step that follows a step can take its tokens from the device,
+// before the host has seen them.
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ picks, const int* __restrict__ src, int n) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n && src[j] >= 0) ids[j] = picks[src[j]];
+}
+
+ESP_API int esp_feed_tokens(int* ids, const int* picks, const int* src, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    feed_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, picks, src, n);
+    return esp_launch_status();
+}
+
 // ---------------------------------------------------------------- add + RMSNorm
 // Row r works on source row s = rows ? rows[r] : r.
 //   v = x[s] + (y ? y[s] : 0);  if (write_x) x[s] = v;

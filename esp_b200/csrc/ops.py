@@ -19,6 +19,7 @@ P = c_void_p
 
 _SIGNATURES = {
     "esp_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, P, P],
+    "esp_feed_tokens": [P, P, P, c_int, P],
     "esp_add_rmsnorm": [P, P, P, P, P, c_int, P, c_int, c_int, c_float, c_int, P],
     "esp_swiglu": [P, P, c_int, c_longlong, c_int, P],
     "esp_finite_check": [P, c_longlong, P, P],
@@ -115,6 +116,12 @@ def embed_gather(table, ids, x, status):
     _check(_fn("core", "esp_embed_gather")(
         _ptr(table, FLOATS, "embedding table"), _is_bf16(table), _ptr(ids, torch.int32, "ids"),
         _ptr(x, torch.float32, "x"), n, width, table.shape[0], _ptr(status, torch.int32), _stream()), "embed_gather")
+
+
+def feed_tokens(ids, picks, src):
+    """ids[j] = picks[src[j]] where src[j] >= 0 (all int32 on the device)."""
+    _check(_fn("core", "esp_feed_tokens")(_ptr(ids, torch.int32, "ids"), _ptr(picks, torch.int32, "picks"),
+                                           _ptr(src, torch.int32, "src"), ids.shape[0], _stream()), "feed_tokens")
 
 
 def add_rmsnorm(x, y, gamma, h, eps, rows=None, write_x=True, h32=None):

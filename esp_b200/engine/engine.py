@@ -37,6 +37,21 @@ def parse_dtype(name) -> torch.dtype:
     return DTYPES[name]
 
 
+class PendingTokens:
+    """Tokens of a step on their way to the host.  ``device`` is the step's own
+    copy on the device (a later step may take its tokens from it), ``result()``
+    waits for the copy to the host and returns the list."""
+
+    def __init__(self, device: torch.Tensor, host: torch.Tensor, landed):
+        self.device = device
+        self._host = host
+        self._landed = landed
+
+    def result(self) -> list:
+        self._landed.synchronize()
+        return self._host.tolist()
+
+
 @dataclass
 class StepEntry:
     slot: int
@@ -68,6 +83,8 @@ class Engine:
                                self.dtype, self.rt.device)
         self._pinned = None
         self._pinned_event = None
+        self._copy_stream = None
+        self.staged_bytes = 0
         self._meta_dev = None
         self.steps_run = 0
         # decode steps (one token per sequence) are captured into CUDA graphs, one per
@@ -120,6 +137,7 @@ class Engine:
         for a, off in zip(arrays, offsets):
             host[off:off + a.size] = a.reshape(-1)
         self._meta_dev[:total].copy_(self._pinned[:total], non_blocking=True)
+        self.staged_bytes = 4 * total                # what the last step copied to the device
         self._pinned_event = torch.cuda.Event()
         self._pinned_event.record()
         return [self._meta_dev[off:off + a.size].view(a.shape) for a, off in zip(arrays, offsets)]
@@ -163,26 +181,61 @@ class Engine:
         # a replayed graph writes its logits into the same buffer every time: hand out a copy
         return logits.clone() if self._graphs else logits
 
-    def step_and_pick(self, entries: list, temperatures: list, top_ps: list, aux: Optional[dict] = None):
+    def step_and_pick(self, entries: list, temperatures: list, top_ps: list, aux: Optional[dict] = None, feed=None):
         """One step that ends with the choice of the next token of every entry
         (each entry must want exactly one place).  ``temperatures[i] == 0``
         chooses the arg-max, otherwise a draw from the slot's own stream;
         ``top_ps[i]`` None means no nucleus cut.  Returns (tokens, logits):
         tokens is an int32 device tensor [B + 1] whose last element is the
-        device status word."""
+        device status word.
+
+        ``feed`` = (picks, src): ``picks`` is an int32 device tensor of tokens
+        chosen by an earlier step and ``src[i] >= 0`` says that entry i (of one
+        token) takes ``picks[src[i]]`` instead of the token it names, so that a
+        step can follow a step before the host has read the tokens."""
         if any(len(e.want) != 1 for e in entries):
             raise InvalidRequest("step_and_pick needs exactly one wanted place per entry")
         temps = np.asarray(temperatures, dtype=np.float32)
         tops = np.asarray([-1.0 if t is None else t for t in top_ps], dtype=np.float32)
         rows = np.asarray([e.slot * STATE_WORDS + STATE_RNG for e in entries], dtype=np.int32)
-        logits, out = self._run(entries, aux, [temps.view(np.int32), tops.view(np.int32), rows], pick=True)
+        extra = [temps.view(np.int32), tops.view(np.int32), rows]
+        if feed is not None:
+            picks, src = feed
+            if len(src) != len(entries) or any(i >= 0 and len(e.tokens) != 1 for e, i in zip(entries, src)):
+                raise InvalidRequest("a fed entry brings exactly one token, and every entry needs a source index")
+            if any(i >= picks.shape[0] for i in src):
+                raise InvalidRequest("a source index lies beyond the earlier step's tokens")
+            extra.append(np.asarray(src, dtype=np.int32))
+        logits, out = self._run(entries, aux, extra, pick=True, feed=None if feed is None else feed[0])
         return out, logits
+
+    def fetch_async(self, tokens: torch.Tensor) -> "PendingTokens":
+        """Starts the copy of a step's tokens to the host on a stream of its own
+        and returns at once; ``result()`` waits for that copy only, not for
+        steps launched since."""
+        with torch.cuda.device(self.rt.device):
+            if self._copy_stream is None:
+                self._copy_stream = torch.cuda.Stream()
+                self._fetch_ring = [torch.empty(self.cache.book.slots.n + 1, dtype=torch.int32, pin_memory=True)
+                                    for _ in range(4)]
+                self._fetch_turn = 0
+            kept = tokens.clone()                     # a replayed graph writes its tokens into the same buffer every time
+            done = torch.cuda.Event()
+            done.record()
+            host = self._fetch_ring[self._fetch_turn % len(self._fetch_ring)][:kept.shape[0]]
+            self._fetch_turn += 1
+            self._copy_stream.wait_event(done)
+            with torch.cuda.stream(self._copy_stream):
+                host.copy_(kept, non_blocking=True)
+                landed = torch.cuda.Event()
+                landed.record()
+            return PendingTokens(kept, host, landed)
 
     def seed_slot(self, slot: int, seed: int) -> None:
         """Starts the slot's sampling stream from ``seed``."""
         self.cache.engine_state[slot, STATE_RNG] = as_signed64(seed)
 
-    def _run(self, entries: list, aux, extra_arrays: list, pick: bool = False):
+    def _run(self, entries: list, aux, extra_arrays: list, pick: bool = False, feed=None):
         with torch.cuda.device(self.rt.device):
             slots, news, pasts, starts, want_rows, growth = self.plan_step(entries)
             book = self.cache.book
@@ -209,6 +262,8 @@ class Engine:
                       np.asarray([t[1] for t in wide], dtype=np.int32), *tables, *extra_arrays]
             dev = self._stage(arrays)
             nt = 11 + len(tables)
+            if feed is not None:                      # token ids from the earlier step's choices, on the device
+                ops.feed_tokens(dev[0], feed, dev[-1])
             ctx = StepContext(
                 n_tokens=n, n_seqs=b, max_new=max(news), max_len=max(p + t for p, t in zip(pasts, news)),
                 tok_ids=dev[0], tok_seq=dev[1], tok_pos=dev[2], seq_slot=dev[3], seq_start=dev[4], seq_past=dev[5],

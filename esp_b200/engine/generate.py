@@ -21,7 +21,7 @@ from dataclasses import dataclass, field
 from typing import Callable, Optional
 
 from ..cache.book import PAGE
-from ..errors import InvalidRequest, PromptTooLong
+from ..errors import CacheFull, InvalidRequest, PromptTooLong
 from ..sampling import SamplingParams
 
 
@@ -109,6 +109,8 @@ class GenerationLoop:
         return results
 
     def _run_batch(self, batch, requests, budgets, results, on_token):
+        if hasattr(self.backend, "decode_async"):
+            return self._run_batch_ahead(batch, requests, budgets, results, on_token)
         slots, seeds, outs = {}, {}, {}
         live = []
         try:
@@ -142,6 +144,60 @@ class GenerationLoop:
                 live = nxt
                 if live:
                     tokens = self.backend.decode([slots[i] for i in live], feed)
+        finally:
+            for s in slots.values():      # only reached with slots left over when something raised
+                self.backend.close(s)
+
+    def _settle(self, i, tok, requests, budgets, outs, on_token):
+        """What a chosen token means for its sequence: the reason it ends, or None."""
+        stops = self.default_stop_ids + tuple(requests[i].stop_token_ids)
+        if tok in stops:
+            return "stop"
+        outs[i].append(tok)
+        if on_token is not None and on_token(i, tok):
+            return "cancelled"
+        if len(outs[i]) == budgets[i]:
+            return "length"
+        return None
+
+    def _run_batch_ahead(self, batch, requests, budgets, results, on_token):
+        """The same decisions with the backend one step ahead: the next decode
+        step is launched, with its tokens taken on the device, before the host
+        reads the tokens of this one.  Whether a sequence ends by its budget is
+        known beforehand; a stop token or the caller's wish to stop is not, so a
+        sequence that ends that way has one more row computed, which is thrown
+        away (rows of a batch do not depend on each other)."""
+        slots, seeds, outs = {}, {}, {}
+        try:
+            for i in batch:
+                seed = None if requests[i].sampling.greedy else requests[i].sampling.resolved_seed()
+                seeds[i] = seed
+                slots[i] = self.backend.open(requests[i].sampling, seed)
+                outs[i] = []
+            order = list(batch)                          # whose token stands where in the step being waited for
+            handle = self.backend.prefill_async([slots[i] for i in order], [list(requests[i].prompt_ids) for i in order])
+            while handle is not None:
+                # those that go on unless their token, still on its way, ends them
+                ahead = [i for i in order if i in slots and len(outs[i]) + 1 < budgets[i]]
+                nxt = None
+                if ahead:
+                    try:
+                        nxt = self.backend.decode_async([slots[i] for i in ahead], handle, [order.index(i) for i in ahead])
+                    except CacheFull:
+                        nxt = None                       # a page for a row that may not be needed: decide after the tokens
+                tokens = handle.result()
+                for i, tok in zip(order, tokens):
+                    if i not in slots:
+                        continue                         # ended a step ago: this row was computed for nothing
+                    reason = self._settle(i, int(tok), requests, budgets, outs, on_token)
+                    if reason is not None:
+                        results[i] = SequenceResult(outs[i], reason, len(requests[i].prompt_ids), seeds[i])
+                        self.backend.close(slots.pop(i))
+                if nxt is None:
+                    ahead = [i for i in order if i in slots]
+                    if ahead:
+                        nxt = self.backend.decode_async([slots[i] for i in ahead], handle, [order.index(i) for i in ahead])
+                handle, order = nxt, ahead
         finally:
             for s in slots.values():      # only reached with slots left over when something raised
                 self.backend.close(s)

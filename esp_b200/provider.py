@@ -85,6 +85,33 @@ class _EngineBackend:
     def decode(self, slots, tokens):
         return self._pick([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
 
+    # The same two calls without waiting for the tokens: they return a handle whose ``result()`` gives the
+    # tokens, and a decode step takes its tokens on the device from the handle of the step before, so that it
+    # can be launched before the host has read them.
+    def _pick_async(self, entries, feed=None):
+        temps = [self.options[e.slot].temperature for e in entries]
+        tops = [self.options[e.slot].top_p for e in entries]
+        out, _ = self.engine.step_and_pick(entries, temps, tops, feed=feed)
+        return _StepHandle(self.engine, self.engine.fetch_async(out), len(entries))
+
+    def prefill_async(self, slots, prompts):
+        return self._pick_async([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+
+    def decode_async(self, slots, earlier, places):
+        """``places[i]``: where slot i's token stands among the tokens of ``earlier``."""
+        return self._pick_async([StepEntry(s, [0], [0]) for s in slots], feed=(earlier.pending.device, list(places)))
+
+
+class _StepHandle:
+    def __init__(self, engine, pending, n):
+        self.engine, self.pending, self.n = engine, pending, n
+
+    def result(self) -> list:
+        host = self.pending.result()
+        if host[self.n]:
+            self.engine.raise_on_status()
+        return host[:self.n]
+
 
 class DecoderProvider:
     def __init__(self, engine: Engine, tokenizer=None, max_batch: int = 64):

@@ -153,3 +153,56 @@ def test_slots_are_closed_when_the_backend_fails():
     with pytest.raises(RuntimeError):
         loop(be).run([SequenceRequest([1], 4), SequenceRequest([2], 4)])
     assert not be.held
+
+
+class AheadBackend(ScriptedBackend):
+    """The same sequences through the calls that do not wait: a step's tokens are read only when the loop
+    asks for them, and a decode step takes its tokens from the handle of the step before."""
+
+    class Handle:
+        def __init__(self, tokens):
+            self.tokens = tokens
+            self.read = False
+
+        def result(self):
+            self.read = True
+            return list(self.tokens)
+
+    def prefill_async(self, slots, prompts):
+        return self.Handle(self.prefill(slots, prompts))
+
+    def decode_async(self, slots, earlier, places):
+        self.launched_before_read = getattr(self, "launched_before_read", 0) + (0 if earlier.read else 1)
+        return self.Handle(self.decode(slots, [earlier.tokens[p] for p in places]))
+
+
+@pytest.mark.parametrize("case", range(4))
+def test_one_step_ahead_gives_the_same_results(case):
+    """Stop tokens, budgets, a caller that stops a sequence, batches one after another: the loop that
+    launches the next step before it reads this one's tokens ends every sequence as the waiting loop does."""
+    cases = [
+        [SequenceRequest([10, 0, 0], max_tokens=3)],
+        [SequenceRequest([10], max_tokens=8, stop_token_ids=(12,)), SequenceRequest([20, 1], max_tokens=5),
+         SequenceRequest([12], max_tokens=5, stop_token_ids=(12,))],
+        [SequenceRequest([5 * i + 1] * (1 + i % 3), max_tokens=1 + (7 * i) % 5, stop_token_ids=(5 * i + 3,) if i % 2 else ())
+         for i in range(11)],
+        [SequenceRequest([30], max_tokens=6), SequenceRequest([40], max_tokens=6), SequenceRequest([50], max_tokens=1)],
+    ]
+    reqs = cases[case]
+
+    def cancel(i, tok):
+        return case == 3 and i == 1 and tok == 42            # the caller stops the second sequence at its third token
+
+    plain, ahead = ScriptedBackend(), AheadBackend()
+    want = loop(plain).run(reqs, cancel)
+    got = loop(ahead).run(reqs, cancel)
+    assert [(r.token_ids, r.finish_reason, r.prompt_tokens) for r in got] == \
+           [(r.token_ids, r.finish_reason, r.prompt_tokens) for r in want]
+    assert not ahead.held and sorted(ahead.free) == list(range(4)), "a slot was lost"
+    assert ahead.max_live <= 4
+    if any(len(r.token_ids) > 2 for r in want):
+        assert ahead.launched_before_read > 0, "no step was launched ahead of the tokens of the one before"
+    # a sequence that ends by a stop token or by the caller has had at most one row too many
+    extra = sum(len(c[1]) for c in ahead.calls if c[0] == "decode") - sum(len(c[1]) for c in plain.calls if c[0] == "decode")
+    ended_early = sum(r.finish_reason in ("stop", "cancelled") for r in want)
+    assert 0 <= extra <= ended_early
