@@ -114,3 +114,32 @@ def test_command_line_generates(folders, capsys):
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     c, w = plain.load_model(folders["A"])
     assert out["token_ids"] == plain.generate(c, w, p, 5) and out["finish_reason"] == "length"
+
+
+def test_waiting_and_one_step_ahead_agree_bfloat16(folders):
+    """Seeded sampling in bfloat16 with a stop token and unequal budgets: the loop that launches the next step
+    before it reads this one's tokens gives the tokens of the loop that waits, and hands every slot back."""
+    from esp_b200.engine.generate import GenerationLoop, SequenceRequest
+    from esp_b200.sampling import SamplingParams
+
+    prov = DecoderProvider.load(folders["B"], dtype="bfloat16", max_batch=4)
+    backend = prov._backend
+
+    class Waiting:                                   # the same backend without the calls that do not wait
+        open, close, prefill, decode = backend.open, backend.close, backend.prefill, backend.decode
+
+    ps = prompts("B", PROMPTS_B, seed=11)
+    window = prov.capability.context_window
+
+    def run(be, stop):
+        reqs = [SequenceRequest(p, max_tokens=6 + 3 * i, stop_token_ids=stop if i == 0 else (),
+                                sampling=SamplingParams(temperature=0.9, top_p=0.8, seed=100 + i))
+                for i, p in enumerate(ps)]
+        return GenerationLoop(be, window, 4, 1 << 14).run(reqs)
+
+    free = run(Waiting, ())
+    stop = (free[0].token_ids[2],)
+    want, got = run(Waiting, stop), run(backend, stop)
+    assert [(r.token_ids, r.finish_reason) for r in got] == [(r.token_ids, r.finish_reason) for r in want]
+    assert want[0].finish_reason == "stop" and len(want[0].token_ids) <= 2
+    assert prov.engine.cache.book.slots.available == prov.engine.max_slots
