@@ -134,7 +134,10 @@ ESP_API int esp_add_rmsnorm(float* x, const float* y, const float* gamma, const 
     if (n_rows <= 0) return 0;
     if (width % 4 == 0 && width <= 16384) {
         int threads = ((width / 4 + 3) / 4 + 31) / 32 * 32;       // up to four pieces per thread
-        if (width / 4 <= 1024) threads = (width / 4 + 31) / 32 * 32;   // one piece per thread while a block can hold them
+        // one piece per thread while a block can hold them: a row's sum then has the same order whatever else is in
+        // the step (the 32-bit path relies on it).  Many rows rounded to bfloat16: four pieces per thread, smaller
+        // blocks, more rows in flight per SM.
+        if (width / 4 <= 1024 && !(h_is_bf16 && n_rows >= 256)) threads = (width / 4 + 31) / 32 * 32;
         if (h_is_bf16)
             add_rmsnorm_rows_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
         else

@@ -561,7 +561,10 @@ ESP_API int esp_moe_combine_add_rmsnorm(const float* expert_out, const int* topk
     if (n_rows <= 0) return 0;
     if (top_k > MAX_TOPK || width % 4 != 0 || width > 16384) return (int)cudaErrorInvalidValue;
     int threads = ((width / 4 + 3) / 4 + 31) / 32 * 32;
-    if (width / 4 <= 1024) threads = (width / 4 + 31) / 32 * 32;
+    // one piece per thread while a block can hold them: a row's sum then has the same order whatever else is in the
+    // step (the 32-bit path relies on it).  Many rows rounded to bfloat16: four pieces per thread, smaller blocks,
+    // more rows in flight per SM.
+    if (width / 4 <= 1024 && !(h_is_bf16 && n_rows >= 256)) threads = (width / 4 + 31) / 32 * 32;
     if (h_is_bf16)
         moe_combine_add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(expert_out, topk_ids, inverse, gate, shared, x, gamma,
                                                                             rows, (bf16*)h, h32, width, top_k, eps, write_x);

@@ -156,8 +156,8 @@ ESP_API int esp_rope_kvwrite(const float* qkv, const float* bias, const int* tok
     // few tokens (decode): one head per block keeps every load in flight at once; many tokens: eight heads
     // per block keep the number of blocks down
     if (rot == hd && hd % 8 == 0 && cos_t && n_tokens > 64) {
-        // many tokens, full rotation: the 16-byte version, sixteen heads per block
-        const int hpb = 16;
+        // many tokens, full rotation: the 16-byte version, 64 heads per block (several pieces in flight per thread)
+        const int hpb = 64;
         const dim3 vgrid(n_tokens, (nh + 2 * nkv + hpb - 1) / hpb);
         if (is_bf16)
             rope_kvwrite_vec_kernel<bf16><<<vgrid, 256, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, max_pos,
