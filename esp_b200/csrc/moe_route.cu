@@ -182,6 +182,161 @@ router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, co
     }
 }
 
+// ---- many tokens, bfloat16 weights: the logits on the tensor cores, in 32-bit precision ----------------
+// A float x is the sum of three bfloat16 numbers a + b + c exactly (8 bits of its 24-bit mantissa each), and a
+// product of two bfloat16 numbers is exact in float, so  x . w = a . w + b . w + c . w  accumulated in float
+// is a 32-bit dot product in another order of summation.  mma.sync m16n8k16: 16 tokens are the rows, 8
+// experts a column tile.  A block takes 16 tokens; its eight (or four) warps take a share of the columns each
+// and their partial sums are added in warp order.  logits[n, e] for e < E, and the shared gate's at e = E.
+__device__ __forceinline__ unsigned pack2_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void split3(float x0, float x1, unsigned& a, unsigned& b, unsigned& c) {
+    const float a0 = __bfloat162float(__float2bfloat16_rn(x0)), a1 = __bfloat162float(__float2bfloat16_rn(x1));
+    const float r0 = x0 - a0, r1 = x1 - a1;
+    const float b0 = __bfloat162float(__float2bfloat16_rn(r0)), b1 = __bfloat162float(__float2bfloat16_rn(r1));
+    a = pack2_bf16(a0, a1);
+    b = pack2_bf16(b0, b1);
+    c = pack2_bf16(r0 - b0, r1 - b1);
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                          unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT, int KW>                                        // KW: warps that share the columns
+__global__ void __launch_bounds__(KW * 32)
+router_logits_mma_kernel(const float* __restrict__ h, const bf16* __restrict__ w_router, const bf16* __restrict__ w_gate,
+                         float* __restrict__ logits, int n_tokens, int width, int n_experts) {
+    __shared__ float part[KW - 1][16][NT * 8 + 1];               // the partial sums of warps 1..
+    const int n0 = blockIdx.x * 16, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+    const int rows = n_experts + (w_gate ? 1 : 0);
+    const int row_a = min(n0 + g, n_tokens - 1), row_b = min(n0 + g + 8, n_tokens - 1);
+    const float* xa = h + (size_t)row_a * width;
+    const float* xb = h + (size_t)row_b * width;
+    // this lane's weight row in every column tile (rows beyond the last read the last one; never stored)
+    const bf16* wrow[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+        const int e = min(t * 8 + g, rows - 1);
+        wrow[t] = e < n_experts ? w_router + (size_t)e * width : w_gate;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; t++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[t][i] = 0.f;
+    // the MMA's k index may be any fixed rearrangement of the columns as long as both operands use it: of a run
+    // of 32 columns this lane takes the 8 from tg * 8 on, four in each of two MMAs, so that its loads are 16 bytes
+    const int share = width / KW;                                 // width is a multiple of KW * 32
+    for (int k0 = warp * share; k0 < (warp + 1) * share; k0 += 32) {
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            const int k = k0 + tg * 8 + s * 4;
+            const float4 va = *reinterpret_cast<const float4*>(xa + k), vb = *reinterpret_cast<const float4*>(xb + k);
+            unsigned a[3][4];                                      // [part of the split][fragment register]
+            split3(va.x, va.y, a[0][0], a[1][0], a[2][0]);
+            split3(vb.x, vb.y, a[0][1], a[1][1], a[2][1]);
+            split3(va.z, va.w, a[0][2], a[1][2], a[2][2]);
+            split3(vb.z, vb.w, a[0][3], a[1][3], a[2][3]);
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                const uint2 wv = *reinterpret_cast<const uint2*>(wrow[t] + k);
+#pragma unroll
+                for (int part_i = 2; part_i >= 0; part_i--)        // the smallest part first
+                    mma_16816(acc[t], a[part_i][0], a[part_i][1], a[part_i][2], a[part_i][3], wv.x, wv.y);
+            }
+        }
+    }
+    if (warp > 0) {
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            part[warp - 1][g][t * 8 + tg * 2] = acc[t][0];
+            part[warp - 1][g][t * 8 + tg * 2 + 1] = acc[t][1];
+            part[warp - 1][g + 8][t * 8 + tg * 2] = acc[t][2];
+            part[warp - 1][g + 8][t * 8 + tg * 2 + 1] = acc[t][3];
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int t = 0; t < NT; t++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int r = g + (i >> 1) * 8, e = t * 8 + tg * 2 + (i & 1);
+                float v = acc[t][i];
+#pragma unroll
+                for (int w = 0; w < KW - 1; w++) v += part[w][r][e];   // in warp order
+                if (n0 + r < n_tokens && e < rows) logits[(size_t)(n0 + r) * (n_experts + 1) + e] = v;
+            }
+    }
+}
+
+// softmax, top-k and weights of a token from its logits [n, E + 1]: one warp per token
+__global__ void __launch_bounds__(256)
+router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids, float* __restrict__ topk_w,
+                     float* __restrict__ gate, float* __restrict__ probs_out, int n_tokens, int n_experts, int top_k,
+                     int norm_topk, int has_gate, int* __restrict__ status) {
+    extern __shared__ float sel_ps[];                               // [8 warps][n_experts]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= n_tokens) return;
+    float* ps = sel_ps + warp * n_experts;
+    const float* lg = logits + (size_t)n * (n_experts + 1);
+    float mx = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n_experts; e += 32) {
+        const float p = expf(lg[e] - mx);
+        ps[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < n_experts; e += 32) {
+        const float p = ps[e] / sum;
+        ps[e] = p;
+        if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
+    }
+    if (lane == 0 && has_gate) gate[n] = 1.0f / (1.0f + expf(-lg[n_experts]));
+    __syncwarp();
+    bool bad = false;
+    float mass = 0.f, my_p = 0.f;
+    int my_e = 0;
+    for (int r = 0; r < top_k; r++) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float p = ps[e];
+            if (!(p == p) || isinf(p)) bad = true;
+            if (p > best) { best = p; best_e = e; }           // ascending e per lane: the first maximum is the lowest id
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (best_e == 0x7fffffff) { best_e = 0; bad = true; }
+        if (lane == 0) ps[best_e] = -1.0f;
+        if (lane == r) { my_p = best; my_e = best_e; }
+        mass += best;
+        __syncwarp();
+    }
+    const float denom = norm_topk ? mass : 1.0f;
+    if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
+        if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
+    }
+    if (lane < top_k) {
+        topk_ids[(size_t)n * top_k + lane] = my_e;
+        topk_w[(size_t)n * top_k + lane] = my_p / denom;
+    }
+}
+
 // ---- few tokens (decode): logits spread over many blocks, then one block routes and permutes --------
 // logits[n, e] = dot(h[n], w_router[e]) for e < E and dot(h[n], w_gate) at e = E: one warp per (token,
 // expert), eight experts per block, so that a step of a handful of tokens still fills the machine.
@@ -470,11 +625,33 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
 }
 }  // namespace
 
+// ``logits`` (may be null): scratch [n_tokens, n_experts + 1] float.  With it, 32-bit activations, bfloat16
+// weights, many tokens and a width that is a multiple of 128, the logits are made on the tensor cores.
 ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, const void* w_gate, int w_is_bf16,
-                            int* topk_ids, float* topk_w, float* gate, float* probs_out, int n_tokens, int width,
-                            int n_experts, int top_k, int norm_topk, int* status, cudaStream_t stream) {
+                            int* topk_ids, float* topk_w, float* gate, float* probs_out, float* logits, int n_tokens,
+                            int width, int n_experts, int top_k, int norm_topk, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts) return (int)cudaErrorInvalidValue;
+    const int rows = n_experts + (w_gate ? 1 : 0);
+    if (logits && !h_is_bf16 && w_is_bf16 && n_tokens >= 64 && width % 128 == 0 && rows <= 72 &&
+        (size_t)8 * n_experts * sizeof(float) <= 48 * 1024 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(w_router) & 7) == 0 && (!w_gate || (reinterpret_cast<uintptr_t>(w_gate) & 7) == 0)) {
+        const int blocks = (n_tokens + 15) / 16;
+#define ESP_ROUTER_MMA(NT, KW)                                                                                         \
+    router_logits_mma_kernel<NT, KW><<<blocks, KW * 32, 0, stream>>>((const float*)h, (const bf16*)w_router,            \
+                                                                      (const bf16*)w_gate, logits, n_tokens, width, n_experts)
+        if (width % 256 == 0) {
+            if (rows <= 64) ESP_ROUTER_MMA(8, 8);
+            else ESP_ROUTER_MMA(9, 8);
+        } else {
+            if (rows <= 64) ESP_ROUTER_MMA(8, 4);
+            else ESP_ROUTER_MMA(9, 4);
+        }
+#undef ESP_ROUTER_MMA
+        router_select_kernel<<<(n_tokens + 7) / 8, 256, (size_t)8 * n_experts * sizeof(float), stream>>>(
+            logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k, norm_topk, w_gate ? 1 : 0, status);
+        return esp_launch_status();
+    }
     // many tokens: four or eight per block, so that the router's weights are fetched that much less often
     int tpb = n_tokens > 256 ? 8 : n_tokens > 32 ? 4 : 1;
     if ((size_t)tpb * (width + n_experts) * sizeof(float) > 200 * 1024) tpb = 1;

@@ -28,7 +28,7 @@ _SIGNATURES = {
     "esp_rope_kvwrite": [P, P, P, P, P, P, c_int, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_int, c_int, P, P],
     "esp_attn_simt": [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
-    "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
     "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P],
@@ -209,7 +209,10 @@ def attn_simt(q, k_cache, v_cache, out, tok_seq, tok_pos, block_table, page, nh,
         "attn_simt")
 
 
-def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, status, probs_out=None):
+def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, status, probs_out=None, logits=None):
+    """``logits``: optional float32 scratch [n, experts + 1]; with it, 32-bit activations and bfloat16 weights
+    the logits of a step of many tokens are made on the tensor cores (three bfloat16 parts of every
+    activation: products exact, sums in float)."""
     n, width = h.shape
     n_experts = w_router.shape[0]
     if top_k > 32:
@@ -218,10 +221,12 @@ def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, s
         raise Backend(f"router: width {width} + experts {n_experts} do not fit the kernel's shared memory")
     if w_gate is not None and w_gate.dtype != w_router.dtype:
         raise Backend("router: router and shared-gate weights must share a dtype")
+    if logits is not None and logits.numel() < n * (n_experts + 1):
+        raise Backend("router: the logits scratch is smaller than [tokens, experts + 1]")
     _check(_fn("core", "esp_router_topk")(
         _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(w_router, FLOATS), _ptr(w_gate, FLOATS), _is_bf16(w_router),
         _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32), _ptr(gate, torch.float32),
-        _ptr(probs_out, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
+        _ptr(probs_out, torch.float32), _ptr(logits, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
         _ptr(status, torch.int32), _stream()), "router_topk")
 
 

@@ -167,7 +167,7 @@ class MoeSwiGluShared(Part):
                             offsets, perm_token, perm_weight, inverse, rt.status, probs)
         else:
             ops.router_topk(router_in, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status,
-                            probs)
+                            probs, logits=ws.get("moe_logits", (n, E + 1), torch.float32))
             if grouped_uses_tc05(h, self.w_gate_up, n * k) and Im % 8 == 0:
                 max_tiles = (n * k + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
                 tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32),

@@ -761,3 +761,50 @@ def test_gemm_tc05_grouped_stages_of_many_widths(tile_rows, counts):
         close(act[lo:hi], gg / (1 + torch.exp(-gg)) * uu, torch.bfloat16, f"group {grp} gate/up")
         ref = (act[lo:hi].double() @ w_d[grp].double().t()) * scale[lo:hi].double()[:, None]
         close(out[lo:hi], ref, torch.float32, f"group {grp} down", k=inter)
+
+
+@pytest.mark.parametrize("n, width, e, k, with_gate", [(700, 256, 60, 4, True), (65, 128, 64, 8, True), (300, 384, 7, 2, False),
+                                                        (2048, 2048, 60, 4, True)])
+def test_router_on_tensor_cores_keeps_32_bit_precision(n, width, e, k, with_gate):
+    """Many tokens, 32-bit activations, bfloat16 weights: the logits come from mma.sync over three bfloat16 parts of
+    every activation.  They must be as good as a 32-bit dot product (far better than bfloat16 activations would
+    give), ties must still go to the lower id, and the choices must be those of the exact probabilities."""
+    h = rnd(n, width) * 3.0
+    wr = rnd(e, width, dtype=torch.bfloat16, seed=1, scale=0.2)
+    if e > 5:
+        wr[5] = wr[2]                      # experts 2 and 5 always tie: the lower id must win
+    wg = rnd(1, width, dtype=torch.bfloat16, seed=2, scale=0.2) if with_gate else None
+    ids = torch.empty(n, k, dtype=torch.int32, device=DEV)
+    wts = torch.empty(n, k, device=DEV)
+    gate = torch.zeros(n, device=DEV)
+    probs = torch.empty(n, e, device=DEV)
+    logits = torch.empty(n, e + 1, device=DEV)
+    st = status()
+    ops.router_topk(h, wr, wg, ids, wts, gate, k, True, st, probs, logits=logits)
+    assert st.item() == 0
+    exact = h.double() @ wr.double().t()
+    # a 32-bit dot product of `width` terms is good to about width * 2^-24 of the sum of magnitudes
+    bound = (h.double().abs() @ wr.double().abs().t()) * (width * 2.0 ** -24)
+    err = (logits[:, :e].double() - exact).abs()
+    assert torch.all(err <= bound + 1e-30), f"logits off by {float((err / bound).max()):.2f} of the 32-bit bound"
+    assert float((err / bound).max()) < 0.25, "the error should sit well inside the bound"
+    p = torch.softmax(exact, -1)
+    # a probability moves by at most p * (its own logit's error + the largest error of the row), plus float rounding
+    p_err = (probs.double() - p).abs()
+    p_bound = p * (bound + bound.max(-1, keepdim=True).values) + 4 * 2.0 ** -24
+    assert torch.all(p_err <= p_bound), f"probabilities off by {float((p_err / p_bound).max()):.2f} of their bound"
+    if with_gate:
+        g_exact = (h.double() @ wg.double().t())[:, 0]
+        g_bound = (h.double().abs() @ wg.double().abs().t())[:, 0] * (width * 2.0 ** -24)
+        assert torch.all((logits[:, e].double() - g_exact).abs() <= g_bound)
+        # the sigmoid's slope is at most 1/4
+        assert torch.all((gate.double() - torch.sigmoid(g_exact)).abs() <= 0.25 * g_bound + 4 * 2.0 ** -24), "shared gate"
+    pn, got = p.cpu().numpy(), ids.cpu().numpy()
+    order = np.argsort(-pn, axis=1, kind="stable")[:, :k]
+    for t in range(n):
+        if list(got[t]) != list(order[t]):
+            # only where two probabilities are closer than 32-bit arithmetic can tell may the choice differ
+            a, b = sorted(set(got[t]) ^ set(order[t]))[:2] if set(got[t]) != set(order[t]) else (got[t][0], got[t][0])
+            assert abs(pn[t, a] - pn[t, b]) <= 1e-6 * pn[t].max() or sorted(got[t]) == sorted(order[t]), (t, got[t], order[t])
+        if e > 5:
+            assert not (5 in got[t] and 2 not in got[t])
