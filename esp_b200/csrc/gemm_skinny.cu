@@ -222,11 +222,12 @@ int launch_variant(const SkinnyParams& p, int groups, int tiles, cudaStream_t st
 template <int NBLK, bool SWIGLU, typename TC>
 int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
     const int tiles = SWIGLU ? (p.N + 7) / 8 : (p.N + 15) / 16;
-    // warps wanted: about one per warp slot of the machine.  The fewer tiles there are, the more warps share one.
+    // warps wanted: about a dozen per SM.  The fewer tiles there are, the more warps share one.
     const long long spread = (long long)tiles * (p.group_offsets ? (groups < p.M ? groups : p.M) : 1);
-    if (spread >= 148 * 8) return launch_variant<NBLK, SWIGLU, TC, 1>(p, groups, tiles, stream);
-    if (spread * 2 >= 148 * 8) return launch_variant<NBLK, SWIGLU, TC, 2>(p, groups, tiles, stream);
-    if (spread * 4 >= 148 * 8) return launch_variant<NBLK, SWIGLU, TC, 4>(p, groups, tiles, stream);
+    constexpr int SLOTS = 12;      // measured: 8 and 16 were slower at batch 8, 24 slower at batch 1
+    if (spread >= 148 * SLOTS) return launch_variant<NBLK, SWIGLU, TC, 1>(p, groups, tiles, stream);
+    if (spread * 2 >= 148 * SLOTS) return launch_variant<NBLK, SWIGLU, TC, 2>(p, groups, tiles, stream);
+    if (spread * 4 >= 148 * SLOTS) return launch_variant<NBLK, SWIGLU, TC, 4>(p, groups, tiles, stream);
     return launch_variant<NBLK, SWIGLU, TC, 8>(p, groups, tiles, stream);
 }
 }  // namespace
