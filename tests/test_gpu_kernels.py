@@ -466,9 +466,9 @@ def test_gemm_skinny_dense(m, n, k):
     assert torch.equal(c1[0], c[m - 1])
 
 
-@pytest.mark.parametrize("n", [6000, 12000])
+@pytest.mark.parametrize("n", [8000, 16000])
 def test_gemm_skinny_two_and_four_warps_per_tile(n):
-    """Between few tiles (eight warps share one) and many (one each): 375 tiles -> four, 750 -> two."""
+    """Between few tiles (eight warps share one) and many (one each): 500 tiles -> four, 1000 -> two."""
     m, k = 7, 200
     a, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1)
     c = torch.empty(m, n, device=DEV)
@@ -484,13 +484,13 @@ def test_gemm_skinny_two_and_four_warps_per_tile(n):
 def test_gemm_skinny_many_tiles_one_tile_per_warp():
     """With enough tiles of weight rows each warp takes a tile of its own and walks all of K: dense,
     fused SwiGLU and grouped with a ragged last tile."""
-    m, n, k = 5, 19001, 72
+    m, n, k = 5, 30001, 72
     a, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1)
     scale = rnd(m, seed=2)
     c = torch.empty(m, n, device=DEV)
     ops.gemm_skinny(a, w, c, row_scale=scale)
     close(c, (a.double() @ w.double().t()) * scale.double()[:, None], torch.float32, "one tile per warp, dense", k=k)
-    inter = 9500
+    inter = 15000
     w2 = rnd(2 * inter, k, dtype=torch.bfloat16, seed=3, scale=0.3)
     act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
     ops.gemm_skinny(a, w2, act, swiglu=True)
