@@ -289,16 +289,19 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const unsigned c_span = (unsigned)(pos - key_first);
                 const unsigned s_addr = tm_s + s * BN + lane_sel + side * 64;
                 float mx = -INFINITY;                                     // of the raw scores: the scale is positive
+                float sv[2][32];                                          // this thread's 64 scores: read from TMEM once
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    float v[32];
-                    tc_ld32(s_addr + c * 32, v);
+                    tc_ld32(s_addr + c * 32, sv[c]);
                     if (edge) {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) mx = fmaxf(mx, (unsigned)(c * 32 + i - c_lo) <= c_span ? v[i] : -INFINITY);
+                        for (int i = 0; i < 32; i++) {
+                            sv[c][i] = (unsigned)(c * 32 + i - c_lo) <= c_span ? sv[c][i] : -INFINITY;
+                            mx = fmaxf(mx, sv[c][i]);
+                        }
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) mx = fmaxf(mx, v[i]);
+                        for (int i = 0; i < 32; i++) mx = fmaxf(mx, sv[c][i]);
                     }
                 }
                 float* xm = xchg + (g & 1) * 256;                         // [2 blocks in turn][side][row]
@@ -318,26 +321,13 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 float l_add = 0.f;
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    float v[32];
-                    tc_ld32(s_addr + c * 32, v);
                     unsigned packed[16];
-                    if (edge) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float p0 = (unsigned)(c * 32 + i - c_lo) <= c_span ? fast_exp2(fmaf(v[i], sc, -m_use)) : 0.f;
-                            const float p1 = (unsigned)(c * 32 + i + 1 - c_lo) <= c_span ? fast_exp2(fmaf(v[i + 1], sc, -m_use)) : 0.f;
-                            l_add += p0 + p1;
-                            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                            packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float p0 = fast_exp2(fmaf(v[i], sc, -m_use)), p1 = fast_exp2(fmaf(v[i + 1], sc, -m_use));
-                            l_add += p0 + p1;
-                            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                            packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
-                        }
+                    for (int i = 0; i < 32; i += 2) {                     // a masked score is -inf: its weight is 0
+                        const float p0 = fast_exp2(fmaf(sv[c][i], sc, -m_use)), p1 = fast_exp2(fmaf(sv[c][i + 1], sc, -m_use));
+                        l_add += p0 + p1;
+                        __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
                     }
                     // 32 keys = 64 bytes = four 16-byte pieces of this row's 128-byte line in the slice of this side
 #pragma unroll
