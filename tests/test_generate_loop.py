@@ -206,3 +206,25 @@ def test_one_step_ahead_gives_the_same_results(case):
     extra = sum(len(c[1]) for c in ahead.calls if c[0] == "decode") - sum(len(c[1]) for c in plain.calls if c[0] == "decode")
     ended_early = sum(r.finish_reason in ("stop", "cancelled") for r in want)
     assert 0 <= extra <= ended_early
+
+
+def test_one_step_ahead_waits_when_the_cache_cannot_take_the_step_launched_ahead():
+    """A step launched ahead may ask for a page for a row that turns out not to be needed.  When the cache
+    refuses it, the loop reads the tokens first and launches the step for those that really go on."""
+    from esp_b200.errors import CacheFull
+
+    class Tight(AheadBackend):
+        refused = 0
+
+        def decode_async(self, slots, earlier, places):
+            if not earlier.read and len(slots) > 1:        # no room for every row that might go on
+                self.refused += 1
+                raise CacheFull("no page for a step launched ahead")
+            return super().decode_async(slots, earlier, places)
+
+    reqs = [SequenceRequest([10], max_tokens=6, stop_token_ids=(12,)), SequenceRequest([20], max_tokens=6)]
+    want = loop(ScriptedBackend()).run(reqs)
+    be = Tight()
+    got = loop(be).run(reqs)
+    assert [(r.token_ids, r.finish_reason) for r in got] == [(r.token_ids, r.finish_reason) for r in want]
+    assert be.refused > 0 and not be.held
