@@ -449,6 +449,105 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
     }
 }
 
+// The same for many pairs: every warp of the one block counts into a table of its own, so that an expert
+// that takes most of the tokens is not one address that a thousand threads add to in turn; a scan over
+// the warps gives every warp its first row in every expert's range, and the warp places its pairs there.
+// shared memory: [32 warps][n_experts] counts, then [n_experts + 1] offsets.
+__global__ void __launch_bounds__(1024)
+moe_permute_wide_kernel(const int* __restrict__ topk_ids, const float* __restrict__ topk_w, int n_pairs, int n_experts,
+                        int* __restrict__ offsets, int* __restrict__ perm_token, float* __restrict__ perm_weight,
+                        int* __restrict__ inverse, int top_k, int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                        int* __restrict__ tile_count, int* __restrict__ n_tiles, int tile_rows, int max_tiles,
+                        int* __restrict__ status) {
+    extern __shared__ int sm[];
+    int* hist = sm;                                  // [32][n_experts]: counts, later each warp's next row
+    int* offs = sm + 32 * n_experts;                 // [n_experts + 1]
+    const int tid = threadIdx.x, warp = tid >> 5;
+    for (int i = tid; i < 32 * n_experts; i += 1024) hist[i] = 0;
+    __syncthreads();
+    int* mine = hist + warp * n_experts;
+    // pair i belongs to warp (i / 32) % 32 in both passes.  A thread's first PER pairs stay in registers: their loads
+    // go out together (one trip to memory, not one per pair) and the second pass does not load them again.
+    constexpr int PER = 8;
+    int held[PER];
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = tid + j * 1024;
+        held[j] = i < n_pairs ? topk_ids[i] : -2;
+    }
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        if (held[j] == -2) continue;
+        if (held[j] >= 0 && held[j] < n_experts) atomicAdd(&mine[held[j]], 1);
+        else atomicOr(status, ESP_STATUS_BAD_INDEX);
+    }
+    for (int i = tid + PER * 1024; i < n_pairs; i += 1024) {
+        const int e = topk_ids[i];
+        if (e >= 0 && e < n_experts) atomicAdd(&mine[e], 1);
+        else atomicOr(status, ESP_STATUS_BAD_INDEX);
+    }
+    __syncthreads();
+    // thread e: the expert's total, and every warp's count turned into its share's first row within the expert
+    for (int e = tid; e < n_experts; e += 1024) {
+        int run = 0;
+        for (int w = 0; w < 32; w++) {
+            const int c = hist[w * n_experts + e];
+            hist[w * n_experts + e] = run;
+            run += c;
+        }
+        offs[e + 1] = run;                           // the total, for the scan below
+    }
+    __syncthreads();
+    if (tid == 0) {                                  // exclusive scan in place: offs[e + 1] holds expert e's total until
+        int run = 0;                                 // turn e reads it; turn e + 1 overwrites it with expert e + 1's start
+        for (int e = 0; e < n_experts; e++) {
+            const int c = offs[e + 1];
+            offs[e] = run;
+            offsets[e] = run;
+            run += c;
+        }
+        offs[n_experts] = run;
+        offsets[n_experts] = run;
+    }
+    __syncthreads();
+    if (tile_group && tid == 0) {                    // row tiles of the grouped products: a tile never mixes two experts
+        int t = 0;
+        for (int e = 0; e < n_experts; e++) {
+            const int lo = offs[e], cnt = offs[e + 1] - lo;
+            for (int r = 0; r < cnt && t < max_tiles; r += tile_rows, t++) {
+                tile_group[t] = e;
+                tile_row0[t] = lo + r;
+                tile_count[t] = min(tile_rows, cnt - r);
+            }
+        }
+        *n_tiles = t;
+    }
+    float wheld[PER];
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = tid + j * 1024;
+        wheld[j] = i < n_pairs ? topk_w[i] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = tid + j * 1024, e = held[j];
+        if (e == -2) continue;
+        if (e < 0 || e >= n_experts) { inverse[i] = -1; continue; }
+        const int row = offs[e] + atomicAdd(&mine[e], 1);
+        perm_token[row] = i / top_k;
+        perm_weight[row] = wheld[j];
+        inverse[i] = row;
+    }
+    for (int i = tid + PER * 1024; i < n_pairs; i += 1024) {
+        const int e = topk_ids[i];
+        if (e < 0 || e >= n_experts) { inverse[i] = -1; continue; }
+        const int row = offs[e] + atomicAdd(&mine[e], 1);
+        perm_token[row] = i / top_k;
+        perm_weight[row] = topk_w[i];
+        inverse[i] = row;
+    }
+}
+
 // One block.  counts -> exclusive offsets -> placement of every (token, rank)
 // pair into its expert's range.  Which row of its expert's range a pair lands
 // in is left to the atomics; a row's arithmetic never depends on where it sits.
@@ -717,6 +816,13 @@ ESP_API int esp_moe_permute(const int* topk_ids, const float* topk_w, int n_toke
     if (n_tokens <= 0) return 0;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const size_t smem_wide = (size_t)(33 * n_experts + 1) * sizeof(int);
+    if (n_tokens * top_k >= 2048 && smem_wide <= 48 * 1024) {
+        moe_permute_wide_kernel<<<1, 1024, smem_wide, stream>>>(topk_ids, topk_w, n_tokens * top_k, n_experts, offsets,
+                                                                perm_token, perm_weight, inverse, top_k, tile_group, tile_row0,
+                                                                tile_count, n_tiles, tile_rows, max_tiles, status);
+        return esp_launch_status();
+    }
     moe_permute_kernel<<<1, 1024, smem, stream>>>(topk_ids, topk_w, n_tokens * top_k, n_experts, offsets, perm_token,
                                                   perm_weight, inverse, top_k, tile_group, tile_row0, tile_count, n_tiles,
                                                   tile_rows, max_tiles, status);

@@ -808,3 +808,37 @@ def test_router_on_tensor_cores_keeps_32_bit_precision(n, width, e, k, with_gate
             assert abs(pn[t, a] - pn[t, b]) <= 1e-6 * pn[t].max() or sorted(got[t]) == sorted(order[t]), (t, got[t], order[t])
         if e > 5:
             assert not (5 in got[t] and 2 not in got[t])
+
+
+@pytest.mark.parametrize("n, k, e", [(1500, 3, 60), (700, 4, 7), (4096, 2, 64)])
+def test_moe_permute_many_pairs_with_uneven_routing(n, k, e):
+    """From 2,048 (token, expert) pairs on the permutation counts per warp; most tokens go to a few experts here
+    and some experts get none.  Every pair must land exactly once inside its expert's range, and the tile list
+    must cover the ranges without mixing experts."""
+    rng = np.random.default_rng(n)
+    p = rng.dirichlet(np.ones(e) * 0.15)
+    ids_np = np.stack([rng.choice(e, size=k, replace=False, p=p / p.sum()) if np.count_nonzero(p) >= k else rng.permutation(e)[:k]
+                       for _ in range(n)]).astype(np.int32)
+    ids = torch.tensor(ids_np, device=DEV)
+    wts = rnd(n, k).abs() + 0.01
+    i32 = lambda *shape: torch.empty(*shape, dtype=torch.int32, device=DEV)
+    offsets, perm_token, inverse = i32(e + 1), i32(n * k), i32(n, k)
+    perm_weight = torch.empty(n * k, device=DEV)
+    tile = ops.TC05_TILE_ROWS
+    max_tiles = (n * k + tile - 1) // tile + e
+    tiles = (i32(max_tiles), i32(max_tiles), i32(max_tiles), i32(1))
+    st = status()
+    ops.moe_permute(ids, wts, e, offsets, perm_token, perm_weight, inverse, st, tiles=tiles)
+    assert st.item() == 0
+    off = offsets.cpu().numpy()
+    assert list(off) == list(np.concatenate([[0], np.cumsum(np.bincount(ids_np.reshape(-1), minlength=e))]))
+    inv, pt, pw, w_np = inverse.cpu().numpy(), perm_token.cpu().numpy(), perm_weight.cpu().numpy(), wts.cpu().numpy()
+    assert sorted(inv.reshape(-1)) == list(range(n * k)), "a row was given twice or not at all"
+    rows = inv.reshape(-1)
+    ex = ids_np.reshape(-1)
+    assert np.all((off[ex] <= rows) & (rows < off[ex + 1])), "a pair outside its expert's range"
+    assert np.array_equal(pt[rows], np.repeat(np.arange(n), k)) and np.array_equal(pw[rows], w_np.reshape(-1))
+    n_tiles = tiles[3].item()
+    tg, tr, tc = (t.cpu().numpy()[:n_tiles] for t in tiles[:3])
+    assert n_tiles == sum((off[i + 1] - off[i] + tile - 1) // tile for i in range(e)) and sum(tc) == n * k
+    assert all(off[g] <= r and r + c <= off[g + 1] and 0 < c <= tile for g, r, c in zip(tg, tr, tc))
