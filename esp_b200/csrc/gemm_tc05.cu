@@ -422,10 +422,9 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
     if (rc) return rc;
     Tc05Params p{tile_group, tile_row0, tile_rows, n_tiles, row_scale, C, ldc, M, N, K, status};
     // ``tile_max``: the most rows a tile of the list has, 128 or 256 (with 256 an expert's weights pass once
-    // for up to 256 of its rows); dense products cut tiles of 256 rows with SwiGLU (MMAs of N = 256 run at
-    // the full rate) and of 128 without (more tiles to spread over the SMs)
+    // for up to 256 of its rows); dense products cut tiles of 256 rows (MMAs of N = 256 run at the full rate)
     if (tile_group && tile_max != 128 && tile_max != 256) return (int)cudaErrorInvalidValue;
-    const int max_tok = tile_group ? tile_max : (swiglu ? 256 : 128);
+    const int max_tok = tile_group ? tile_max : 256;
     const int token_tiles = tile_group ? max_tiles : (M + max_tok - 1) / max_tok;     // upper bound when grouped
     if (token_tiles <= 0) return 0;
     const int feats = swiglu ? BF / 2 : BF;
