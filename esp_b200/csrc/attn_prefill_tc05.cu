@@ -14,9 +14,10 @@
 //   O  = O * exp2(m_old - m_new) + PV        in registers of the row's thread; O / l at the end
 //
 // Warp 0 loads (TMA: queries once, then keys and values page by page into two-stage rings of their own:
-// a key stage is free as soon as S is done, before its block's PV), warp 1 issues the MMAs, warps 2..9
-// are the row threads, two to a row (each half of the keys of a block and half of the head's columns:
-// with one warp per scheduler the chain multiply, exp2, add, round would run at its latency).  S and PV have two TMEM buffers each (4 x 128 = all 512 columns), so S of the
+// a key stage is free as soon as S is done, before its block's PV), warp 1 issues the MMAs, the other
+// warps are the row threads, two to a row (four can be chosen; each takes a share of the keys of a
+// block and of the head's columns: with one warp per scheduler the chain multiply, exp2, add, round would
+// run at its latency).  S and PV have two TMEM buffers each (4 x 128 = all 512 columns), so S of the
 // next block runs while the row threads work on this one.  Every wait is bounded.
 //
 // Head sizes 64 and 128.  The page size is 64.  Rows of the tile beyond the sequence's new tokens are
@@ -25,7 +26,7 @@
 
 namespace {
 using namespace tc05;
-constexpr int BM = 128, BN = 128, PAGE = 64, THREADS = 320;   // warps: 0 loads, 1 MMA, 2..9 row threads
+constexpr int BM = 128, BN = 128, PAGE = 64;   // warps: 0 loads, 1 MMA, then 4 * ROWT warps of row threads
 constexpr int ATOM_BYTES = 128 * 128;           // 128 rows of 128 bytes: one 64-wide slice of a 128-row operand
 
 struct AttnParams {
@@ -62,16 +63,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
-// the 64 threads that meet at named barrier ``id`` learn whether all of them are well
-__device__ __forceinline__ bool pair_agree(bool ok, int id) {
+// the ``count`` threads that meet at named barrier ``id`` learn whether all of them are well
+__device__ __forceinline__ bool pair_agree(bool ok, int id, int count) {
     unsigned all;
     asm volatile(
         "{\n.reg .pred p, q;\n"
         "setp.ne.u32 p, %1, 0;\n"
-        "bar.red.and.pred q, %2, 64, p;\n"
+        "bar.red.and.pred q, %2, %3, p;\n"
         "selp.u32 %0, 1, 0, q;\n}\n"
-        : "=r"(all) : "r"(ok ? 1u : 0u), "r"(id) : "memory");
+        : "=r"(all) : "r"(ok ? 1u : 0u), "r"(id), "r"(count) : "memory");
     return all != 0;
+}
+__device__ __forceinline__ void named_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory");
 }
 
 // the tile of 128 query rows and the head that a block works on
@@ -99,8 +103,9 @@ __device__ __forceinline__ Item load_item(const AttnParams& p, int item) {
 // b, 2G-1-b, 2G+b, 4G-1-b, ... (G blocks), so that a long item is followed by a short one.  Every role
 // derives the same run of items, and the counters of key blocks (g) and items (n_items_done) that choose
 // the stage, the TMEM buffer and the phase of each mbarrier run on from one item to the next.
-template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+// ROWT: threads that share a query row (2 or 4): each takes 128 / ROWT keys of a block and HD / ROWT columns of O.
+template <int HD, int ROWT>
+__global__ void __launch_bounds__(64 + ROWT * 128, 1)
 attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, AttnParams p) {
     constexpr int HALVES = HD / 64;                       // 64-column slices of a head
@@ -126,12 +131,12 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned long long* p_ready = bars + 14;              // [1]
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* xchg = reinterpret_cast<float*>(bars) + 64;                  // [2][2][128] maxima, [2][128] sums of the row threads
+    float* xchg = reinterpret_cast<float*>(bars) + 64;                  // [2][ROWT][128] maxima, [ROWT][128] sums of the row threads
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < 14; i++) mbar_init(&bars[i], 1);
-        mbar_init(p_ready, 8);                                           // one arrival per warp of row threads
+        mbar_init(p_ready, 4 * ROWT);                                    // one arrival per warp of row threads
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -256,14 +261,17 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     } else {
-        // ---- row threads: TMEM lane = query row of the tile; two threads a row.  The warps w and w + 4 may read
-        // the same 32 lanes; the first takes keys 0..63 of a block and the lower half of the head's columns, the
-        // second keys 64..127 and the upper half.  They exchange their maxima of a block through shared memory
-        // and meet at a named barrier of their own; their sums stay apart until the end.
+        // ---- row threads: TMEM lane = query row of the tile; ROWT threads a row.  The warps w, w + 4, w + 8 .. may
+        // read the same 32 lanes; thread ``side`` of a row takes the keys side * CW .. of a block and the columns
+        // side * OW .. of the head.  They exchange their maxima of a block through shared memory and meet at a
+        // named barrier of their own; their sums stay apart until the end.
         const int quad = warp & 3, r = quad * 32 + lane, side = (warp - 2) >> 2;
         const unsigned lane_sel = (unsigned)(quad * 32) << 16;
         const float sc = 1.4426950408889634f / sqrtf((float)HD);
-        constexpr int OW = HD / 2;                                       // columns of O that this thread keeps
+        constexpr int CW = BN / ROWT;                                    // keys of a block that this thread takes
+        constexpr int OW = HD / ROWT;                                    // columns of O that this thread keeps
+        constexpr int MATES = ROWT * 32;                                 // threads at the row's named barrier
+        static_assert(CW % 32 == 0 && OW % 32 == 0, "a thread reads TMEM 32 columns at a time");
         bool ok = true;
         int g = 0;
         for (int round = 0; ok; round++) {
@@ -279,19 +287,19 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int j = 0; j < t.nb; j++, g++) {
                 const int s = g & 1, key0 = (t.blk_lo + j) * BN;
                 ok = !*abort_flag && mbar_wait(&s_full[s], (g >> 1) & 1);
-                ok = pair_agree(ok, 1 + quad);                            // the two warps of a row go on or leave together
+                ok = pair_agree(ok, 1 + quad, MATES);                            // the two warps of a row go on or leave together
                 if (!ok) break;
                 tc_fence_after();
                 // does any (row of the tile, key of the block) pair need the mask?
                 const bool edge = key0 + BN - 1 > t.pos0 || (p.window > 0 && key0 < t.pos0 + BM - 1 - p.window + 1);
                 // live columns of this row: c_lo .. c_lo + c_span; one unsigned comparison per element, no branch
-                const int c_lo = key_first - key0 - side * 64;
+                const int c_lo = key_first - key0 - side * CW;
                 const unsigned c_span = (unsigned)(pos - key_first);
-                const unsigned s_addr = tm_s + s * BN + lane_sel + side * 64;
+                const unsigned s_addr = tm_s + s * BN + lane_sel + side * CW;
                 float mx = -INFINITY;                                     // of the raw scores: the scale is positive
-                float sv[2][32];                                          // this thread's 64 scores: read from TMEM once
+                float sv[CW / 32][32];                                    // this thread's scores: read from TMEM once
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
+                for (int c = 0; c < CW / 32; c++) {
                     tc_ld32(s_addr + c * 32, sv[c]);
                     if (edge) {
 #pragma unroll
@@ -304,23 +312,25 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         for (int i = 0; i < 32; i++) mx = fmaxf(mx, sv[c][i]);
                     }
                 }
-                float* xm = xchg + (g & 1) * 256;                         // [2 blocks in turn][side][row]
+                float* xm = xchg + (g & 1) * (ROWT * 128);                // [2 blocks in turn][side][row]
                 xm[side * 128 + r] = mx;
-                asm volatile("bar.sync %0, 64;\n" ::"r"(1 + quad) : "memory");
-                mx = fmaxf(mx, xm[(side ^ 1) * 128 + r]) * sc;
+                named_sync(1 + quad, MATES);
+#pragma unroll
+                for (int o2 = 0; o2 < ROWT; o2++) mx = fmaxf(mx, xm[o2 * 128 + r]);
+                mx *= sc;
                 const float m_new = fmaxf(m_run, mx);
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = fast_exp2(m_run - m_use);             // m_run = -inf gives 0
                 m_run = m_new;
                 if (j > 0) {                                              // the last PV is done: P may be overwritten
                     ok = mbar_wait(&pv_full[s ^ 1], ((g - 1) >> 1) & 1);
-                    ok = pair_agree(ok, 1 + quad);
+                    ok = pair_agree(ok, 1 + quad, MATES);
                     if (!ok) break;
                     tc_fence_after();
                 }
                 float l_add = 0.f;
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
+                for (int c = 0; c < CW / 32; c++) {
                     unsigned packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {                     // a masked score is -inf: its weight is 0
@@ -329,11 +339,12 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
                         packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
                     }
-                    // 32 keys = 64 bytes = four 16-byte pieces of this row's 128-byte line in the slice of this side
+                    // 32 keys = 64 bytes = four 16-byte pieces of this row's 128-byte line in the slice of these keys
 #pragma unroll
                     for (int q4 = 0; q4 < 4; q4++) {
-                        const int piece = c * 4 + q4;
-                        unsigned char* dst = p_s + side * ATOM_BYTES + r * 128 + ((piece ^ (r & 7)) << 4);
+                        const int key = side * CW + c * 32;               // first key of these 32 within the block
+                        const int piece = ((key & 63) >> 3) + q4;
+                        unsigned char* dst = p_s + (key >> 6) * ATOM_BYTES + r * 128 + ((piece ^ (r & 7)) << 4);
                         *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                     }
                 }
@@ -356,7 +367,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (!ok) break;
             const int s = (g - 1) & 1;                                    // the item's last block
             ok = mbar_wait(&pv_full[s], ((g - 1) >> 1) & 1);
-            ok = pair_agree(ok, 1 + quad);
+            ok = pair_agree(ok, 1 + quad, MATES);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
@@ -367,10 +378,12 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
             }
             tc_fence_before();
-            float* xl = xchg + 512;                                       // the two sums of a row
+            float* xl = xchg + 2 * ROWT * 128;                            // the sums of a row's threads
             xl[side * 128 + r] = l_run;
-            asm volatile("bar.sync %0, 64;\n" ::"r"(1 + quad) : "memory");
-            const float l_all = side == 0 ? l_run + xl[128 + r] : xl[r] + l_run;     // keys in ascending order
+            named_sync(1 + quad, MATES);
+            float l_all = 0.f;
+#pragma unroll
+            for (int o2 = 0; o2 < ROWT; o2++) l_all += xl[o2 * 128 + r];  // keys in ascending order
             if (r < t.rows) {
                 const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
                 bf16* orow = p.out + ((size_t)(t.row0 + r) * p.nh + t.h) * HD + side * OW;
@@ -426,10 +439,11 @@ int make_map2d(CUtensorMap* map, const void* base, unsigned long long cols, unsi
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int n_tiles,
            cudaStream_t stream) {
-    const size_t smem = (size_t)(HD / 64) * ATOM_BYTES * 5 + 2 * ATOM_BYTES + 1024 + 256 + 768 * 4;
+    constexpr int ROWT = 2;      // four threads a row were measured too: the same time (the row threads are not the limit)
+    const size_t smem = (size_t)(HD / 64) * ATOM_BYTES * 5 + 2 * ATOM_BYTES + 1024 + 256 + 3 * ROWT * 128 * 4;
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc05_kernel<HD, ROWT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
@@ -444,7 +458,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     // with more items than SMs, blocks take pairs (a long item and a short one): as many blocks as halve the list
     long long grid = items <= sm_count ? items : (items + 1) / 2;
     if (grid > sm_count) grid = sm_count;
-    attn_prefill_tc05_kernel<HD><<<(int)grid, THREADS, smem, stream>>>(mq, mk, mv, p);
+    attn_prefill_tc05_kernel<HD, ROWT><<<(int)grid, 64 + ROWT * 128, smem, stream>>>(mq, mk, mv, p);
     return esp_launch_status();
 }
 }  // namespace
