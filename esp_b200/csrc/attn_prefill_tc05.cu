@@ -7,18 +7,20 @@
 // see in blocks of 128 (two pages of 64):
 //
 //   S  = Q K^T       tcgen05.mma, M = 128 queries, N = 128 keys, K = head size; float accumulator in TMEM
-//   P  = exp2(S * log2(e) / sqrt(hd) - m)   in 32-bit, by the thread that owns the row (TMEM lane = row,
-//        so the row's maximum and sum need no exchange between threads); rounded to bfloat16 into shared
-//        memory in the layout the tensor core reads (rows of 128 bytes, 128-byte swizzle)
+//   P  = exp2(S * log2(e) / sqrt(hd) - m)   in 32-bit, by the threads that own the row (TMEM lane = row);
+//        rounded to bfloat16 and written back over S in tensor memory (two keys to a 32-bit column), where
+//        the next product reads it as its A operand: P never passes through shared memory
 //   PV = P V         tcgen05.mma, N = head size, K = 128 keys, a fresh accumulator per block of keys
 //   O  = O * exp2(m_old - m_new) + PV        in registers of the row's thread; O / l at the end
 //
-// Warp 0 loads (TMA: queries once, then keys and values page by page into two-stage rings of their own:
-// a key stage is free as soon as S is done, before its block's PV), warp 1 issues the MMAs, the other
+// Warp 0 loads (TMA: queries once, then keys and values page by page into three-stage rings of their own:
+// a key stage is free as soon as S is done, before its block's PV; a load takes longer to land than a
+// block of keys takes to work through, so two blocks have to be in flight), warp 1 issues the MMAs, the other
 // warps are the row threads, two to a row (four can be chosen; each takes a share of the keys of a
 // block and of the head's columns: with one warp per scheduler the chain multiply, exp2, add, round would
 // run at its latency).  S and PV have two TMEM buffers each (4 x 128 = all 512 columns), so S of the
-// next block runs while the row threads work on this one.  Every wait is bounded.
+// next block runs while the row threads work on this one, and the row threads wait for a PV only when they
+// add it to O, a block later.  Every wait is bounded.
 //
 // Head sizes 64 and 128.  The page size is 64.  Rows of the tile beyond the sequence's new tokens are
 // computed and not stored; keys beyond a row's position are masked before the maximum is taken.
@@ -28,6 +30,7 @@ namespace {
 using namespace tc05;
 constexpr int BM = 128, BN = 128, PAGE = 64;   // warps: 0 loads, 1 MMA, then 4 * ROWT warps of row threads
 constexpr int ATOM_BYTES = 128 * 128;           // 128 rows of 128 bytes: one 64-wide slice of a 128-row operand
+constexpr int STAGES = 3;                       // blocks of keys (and of values) in shared memory
 
 struct AttnParams {
     bf16* out;
@@ -36,7 +39,7 @@ struct AttnParams {
     const int* seq_start;
     const int* seq_past;
     const int* block_table;
-    int table_stride, n_pages, nh, nkv, window, kv_rows, n_tiles;
+    int table_stride, n_pages, nh, nkv, window, kv_rows, n_tiles, smem_bytes;
     int* status;
 };
 
@@ -109,34 +112,40 @@ __global__ void __launch_bounds__(64 + ROWT * 128, 1)
 attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, AttnParams p) {
     constexpr int HALVES = HD / 64;                       // 64-column slices of a head
-    constexpr int Q_BYTES = HALVES * ATOM_BYTES, KV_BYTES = HALVES * ATOM_BYTES, P_BYTES = 2 * ATOM_BYTES;
+    constexpr int Q_BYTES = HALVES * ATOM_BYTES, KV_BYTES = HALVES * ATOM_BYTES;
     const int n_items = p.n_tiles * p.nh, G = gridDim.x;
     auto item_of = [&](int round) { return round * G + ((round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x); };
 
-    extern __shared__ unsigned char smem_raw[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
-    unsigned char* k_s = q_s + Q_BYTES;                   // [2 stages]
-    unsigned char* v_s = k_s + 2 * KV_BYTES;              // [2 stages]
-    unsigned char* p_s = v_s + 2 * KV_BYTES;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + P_BYTES);
+    unsigned char* k_s = q_s + Q_BYTES;                   // [STAGES]
+    unsigned char* v_s = k_s + STAGES * KV_BYTES;         // [STAGES]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(v_s + STAGES * KV_BYTES);
+    constexpr int N_BARS = 7 + 4 * STAGES;
     unsigned long long* q_full = bars;                    // [1]
-    unsigned long long* k_full = bars + 1;                // [2]
-    unsigned long long* k_empty = bars + 3;               // [2]
-    unsigned long long* v_full = bars + 5;                // [2]
-    unsigned long long* v_empty = bars + 7;               // [2]
-    unsigned long long* s_full = bars + 9;                // [2]
-    unsigned long long* pv_full = bars + 11;              // [2]
-    unsigned long long* q_empty = bars + 13;              // [1]
-    unsigned long long* p_ready = bars + 14;              // [1]
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
+    unsigned long long* q_empty = bars + 1;               // [1]
+    unsigned long long* p_ready = bars + 2;               // [1]
+    unsigned long long* s_full = bars + 3;                // [2]
+    unsigned long long* pv_full = bars + 5;               // [2]
+    unsigned long long* k_full = bars + 7;                // [STAGES]
+    unsigned long long* k_empty = k_full + STAGES;        // [STAGES]
+    unsigned long long* v_full = k_empty + STAGES;        // [STAGES]
+    unsigned long long* v_empty = v_full + STAGES;        // [STAGES]
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* xchg = reinterpret_cast<float*>(bars) + 64;                  // [2][ROWT][128] maxima, [ROWT][128] sums of the row threads
+    static_assert(N_BARS * 8 + 8 <= 256, "the barriers and the two words after them take 256 bytes");
+    float* xchg = reinterpret_cast<float*>(bars) + 64;    // [ROWT][128]: the row threads' maxima of a block, their sums at the end
+    // where shared memory is too short for the slack that rounding up to 1024 bytes needs, its start has to
+    // be aligned already; the block refuses to run otherwise
+    if (smem + Q_BYTES + 2 * STAGES * KV_BYTES + 256 + ROWT * 128 * 4 > smem_raw + p.smem_bytes) {
+        if (threadIdx.x == 0) atomicOr(p.status, ESP_STATUS_SMEM_LAYOUT);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 14; i++) mbar_init(&bars[i], 1);
-        mbar_init(p_ready, 4 * ROWT);                                    // one arrival per warp of row threads
+        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], i == 2 ? 4 * ROWT : 1);   // p_ready: one arrival per warp of row threads
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -168,7 +177,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (lane < HALVES) tma_load_2d(q_s + lane * ATOM_BYTES, &map_q, t.h * HD + lane * 64, t.row0, q_full);
             issued_q = round + 1;
             for (int j = 0; j < t.nb && ok; j++, g++) {
-                const int s = g & 1;
+                const int s = g % STAGES, ph = (g / STAGES) & 1;
                 // the page of this lane's box; a page past the tile's last key is read as zeros (a row past the cache)
                 int box_row = p.kv_rows;
                 if (lane < 2 * HALVES) {
@@ -180,7 +189,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                 }
                 if (lane == 0) {
-                    ok = !*abort_flag && mbar_wait(&k_empty[s], ((g >> 1) & 1) ^ 1);
+                    ok = !*abort_flag && mbar_wait(&k_empty[s], ph ^ 1);
                     if (ok) mbar_expect_tx(&k_full[s], KV_BYTES);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -189,7 +198,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     tma_load_2d(k_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_k, half * 64, box_row, &k_full[s]);
                 issued_k = g + 1;
                 if (lane == 0) {
-                    ok = !*abort_flag && mbar_wait(&v_empty[s], ((g >> 1) & 1) ^ 1);
+                    ok = !*abort_flag && mbar_wait(&v_empty[s], ph ^ 1);
                     if (ok) mbar_expect_tx(&v_full[s], KV_BYTES);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -204,28 +213,28 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             *abort_flag = 1;
             // let this CTA's own copies land before its shared memory is given up
             if (issued_q > 0) mbar_wait(q_full, (issued_q - 1) & 1);
-            for (int j = max(0, issued_k - 2); j < issued_k; j++) mbar_wait(&k_full[j & 1], (j >> 1) & 1);
-            for (int j = max(0, issued_v - 2); j < issued_v; j++) mbar_wait(&v_full[j & 1], (j >> 1) & 1);
+            for (int j = max(0, issued_k - STAGES); j < issued_k; j++) mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1);
+            for (int j = max(0, issued_v - STAGES); j < issued_v; j++) mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const unsigned idesc_s = idesc_attn(BN, false), idesc_pv = idesc_attn(HD, true);
-            const unsigned long long dq = smem_desc(q_s), dk = smem_desc(k_s), dp = smem_desc(p_s);
+            const unsigned long long dq = smem_desc(q_s), dk = smem_desc(k_s);
             const unsigned long long dv = smem_desc_mn(v_s, ATOM_BYTES);
             bool ok = true;
             int g = 0;
             auto issue_s = [&](int gg, bool last_of_item) {               // S = Q K^T of key block gg into S buffer gg % 2
-                const int s = gg & 1;
-                if (!mbar_wait(&k_full[s], (gg >> 1) & 1)) return false;
+                const int st = gg % STAGES;
+                if (!mbar_wait(&k_full[st], (gg / STAGES) & 1)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; kk++) {
                     const unsigned off = ((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4;
-                    tc_mma(tm_s + s * BN, dq + off, dk + ((s * KV_BYTES) >> 4) + off, idesc_s, kk > 0 ? 1u : 0u);
+                    tc_mma(tm_s + (gg & 1) * BN, dq + off, dk + ((st * KV_BYTES) >> 4) + off, idesc_s, kk > 0 ? 1u : 0u);
                 }
-                tc_commit(&k_empty[s]);                                   // the keys are free once S is done
+                tc_commit(&k_empty[st]);                                  // the keys are free once S is done
                 if (last_of_item) tc_commit(q_empty);                     // and so are the queries after the item's last S
-                tc_commit(&s_full[s]);
+                tc_commit(&s_full[gg & 1]);
                 return true;
             };
             for (int round = 0; ok && !*abort_flag; round++) {
@@ -235,23 +244,23 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 ok = mbar_wait(q_full, round & 1);
                 if (ok) ok = issue_s(g, t.nb == 1);
                 for (int j = 0; j < t.nb && ok && !*abort_flag; j++, g++) {
-                    const int s = g & 1;
+                    const int s = g & 1, st = g % STAGES;
                     if (j + 1 < t.nb) ok = issue_s(g + 1, j + 2 == t.nb);  // runs while the row threads work on this block
                     if (!ok) break;
-                    // P is in shared memory (and with that: S of this block and PV of two blocks ago have been
-                    // read), the values have landed
-                    if (!mbar_wait(p_ready, g & 1) || !mbar_wait(&v_full[s], (g >> 1) & 1)) {
+                    // P stands where S of this block stood (and with that: PV of two blocks ago has been read),
+                    // the values have landed.  S of the block after next goes to the same columns: the tensor
+                    // core runs one thread's products in the order in which they were issued
+                    if (!mbar_wait(p_ready, g & 1) || !mbar_wait(&v_full[st], (g / STAGES) & 1)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < BN / 16; kk++) {
-                        const unsigned a_off = ((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4;
-                        const unsigned b_off = (s * KV_BYTES + kk * 16 * 128) >> 4;
-                        tc_mma(tm_pv + s * BN, dp + a_off, dv + b_off, idesc_pv, kk > 0 ? 1u : 0u);
+                        const unsigned b_off = (st * KV_BYTES + kk * 16 * 128) >> 4;
+                        tc_mma_ta(tm_pv + s * BN, tm_s + s * BN + kk * 8, dv + b_off, idesc_pv, kk > 0 ? 1u : 0u);
                     }
-                    tc_commit(&v_empty[s]);
+                    tc_commit(&v_empty[st]);
                     tc_commit(&pv_full[s]);
                 }
             }
@@ -264,7 +273,8 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // ---- row threads: TMEM lane = query row of the tile; ROWT threads a row.  The warps w, w + 4, w + 8 .. may
         // read the same 32 lanes; thread ``side`` of a row takes the keys side * CW .. of a block and the columns
         // side * OW .. of the head.  They exchange their maxima of a block through shared memory and meet at a
-        // named barrier of their own; their sums stay apart until the end.
+        // named barrier of their own (once when all have written, once when all have read); their sums stay
+        // apart until the end.
         const int quad = warp & 3, r = quad * 32 + lane, side = (warp - 2) >> 2;
         const unsigned lane_sel = (unsigned)(quad * 32) << 16;
         const float sc = 1.4426950408889634f / sqrtf((float)HD);
@@ -312,48 +322,43 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         for (int i = 0; i < 32; i++) mx = fmaxf(mx, sv[c][i]);
                     }
                 }
-                float* xm = xchg + (g & 1) * (ROWT * 128);                // [2 blocks in turn][side][row]
-                xm[side * 128 + r] = mx;
+                xchg[side * 128 + r] = mx;
                 named_sync(1 + quad, MATES);
 #pragma unroll
-                for (int o2 = 0; o2 < ROWT; o2++) mx = fmaxf(mx, xm[o2 * 128 + r]);
+                for (int o2 = 0; o2 < ROWT; o2++) mx = fmaxf(mx, xchg[o2 * 128 + r]);
+                named_sync(1 + quad, MATES);                              // all have read: the next block may write
                 mx *= sc;
                 const float m_new = fmaxf(m_run, mx);
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = fast_exp2(m_run - m_use);             // m_run = -inf gives 0
                 m_run = m_new;
-                if (j > 0) {                                              // the last PV is done: P may be overwritten
-                    ok = mbar_wait(&pv_full[s ^ 1], ((g - 1) >> 1) & 1);
-                    ok = pair_agree(ok, 1 + quad, MATES);
-                    if (!ok) break;
-                    tc_fence_after();
-                }
+                // every thread of the row holds its scores in registers by now, so P may go where S stood: the
+                // weights of keys 2c and 2c + 1 of the block into column c of the S buffer
                 float l_add = 0.f;
+                unsigned packed[CW / 2];
 #pragma unroll
                 for (int c = 0; c < CW / 32; c++) {
-                    unsigned packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {                     // a masked score is -inf: its weight is 0
                         const float p0 = fast_exp2(fmaf(sv[c][i], sc, -m_use)), p1 = fast_exp2(fmaf(sv[c][i + 1], sc, -m_use));
                         l_add += p0 + p1;
                         __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<unsigned*>(&b);
-                    }
-                    // 32 keys = 64 bytes = four 16-byte pieces of this row's 128-byte line in the slice of these keys
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; q4++) {
-                        const int key = side * CW + c * 32;               // first key of these 32 within the block
-                        const int piece = ((key & 63) >> 3) + q4;
-                        unsigned char* dst = p_s + (key >> 6) * ATOM_BYTES + r * 128 + ((piece ^ (r & 7)) << 4);
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                        packed[c * 16 + (i >> 1)] = *reinterpret_cast<unsigned*>(&b);
                     }
                 }
+                const unsigned p_addr = tm_s + s * BN + lane_sel + side * (CW / 2);
+                if constexpr (CW == 64) tc_st32(p_addr, packed);
+                else tc_st16(p_addr, packed);
+                tc_wait_st();
                 l_run = l_run * alpha + l_add;
-                fence_async_smem();                                       // P: visible to the tensor core's reads
-                tc_fence_before();                                        // S of this block has been read
+                tc_fence_before();                                        // S of this block has been read, P written
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_ready);
                 if (j > 0) {                                              // O = O * factor + PV of the block before
+                    ok = mbar_wait(&pv_full[s ^ 1], ((g - 1) >> 1) & 1);
+                    ok = pair_agree(ok, 1 + quad, MATES);
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < OW / 32; c++) {
                         float v[32];
@@ -378,12 +383,12 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
             }
             tc_fence_before();
-            float* xl = xchg + 2 * ROWT * 128;                            // the sums of a row's threads
-            xl[side * 128 + r] = l_run;
+            xchg[side * 128 + r] = l_run;                                 // the sums of a row's threads
             named_sync(1 + quad, MATES);
             float l_all = 0.f;
 #pragma unroll
-            for (int o2 = 0; o2 < ROWT; o2++) l_all += xl[o2 * 128 + r];  // keys in ascending order
+            for (int o2 = 0; o2 < ROWT; o2++) l_all += xchg[o2 * 128 + r];  // keys in ascending order
+            named_sync(1 + quad, MATES);
             if (r < t.rows) {
                 const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
                 bf16* orow = p.out + ((size_t)(t.row0 + r) * p.nh + t.h) * HD + side * OW;
@@ -439,8 +444,11 @@ int make_map2d(CUtensorMap* map, const void* base, unsigned long long cols, unsi
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int n_tiles,
            cudaStream_t stream) {
-    constexpr int ROWT = 2;      // four threads a row were measured too: the same time (the row threads are not the limit)
-    const size_t smem = (size_t)(HD / 64) * ATOM_BYTES * 5 + 2 * ATOM_BYTES + 1024 + 256 + 3 * ROWT * 128 * 4;
+    constexpr int ROWT = HD >= 128 ? 4 : 2;   // threads that share a query row
+    // queries, STAGES blocks of keys and of values, barriers, the row threads' exchange; and 1024 bytes to round
+    // the start up with, where the 227 KB of a block have room for them
+    size_t smem = (size_t)(HD / 64) * ATOM_BYTES * (1 + 2 * STAGES) + 256 + ROWT * 128 * 4;
+    if (smem + 1024 <= 232448) smem += 1024;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc05_kernel<HD, ROWT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -458,7 +466,9 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     // with more items than SMs, blocks take pairs (a long item and a short one): as many blocks as halve the list
     long long grid = items <= sm_count ? items : (items + 1) / 2;
     if (grid > sm_count) grid = sm_count;
-    attn_prefill_tc05_kernel<HD, ROWT><<<(int)grid, 64 + ROWT * 128, smem, stream>>>(mq, mk, mv, p);
+    AttnParams pp = p;
+    pp.smem_bytes = (int)smem;
+    attn_prefill_tc05_kernel<HD, ROWT><<<(int)grid, 64 + ROWT * 128, smem, stream>>>(mq, mk, mv, pp);
     return esp_launch_status();
 }
 }  // namespace
@@ -483,7 +493,7 @@ ESP_API int esp_attn_prefill_tc05(const void* q, long long n_tokens, const void*
     rc = make_map2d(&mv, v_cache, (unsigned long long)hd, kv_rows, PAGE);
     if (rc) return rc;
     AttnParams p{(bf16*)out, tile_seq, tile_first, seq_start, seq_past, block_table, table_stride, n_pages, nh, nkv,
-                 window, (int)kv_rows, n_tiles, status};
+                 window, (int)kv_rows, n_tiles, 0, status};
     if (hd == 64) return launch<64>(mq, mk, mv, p, n_tiles, stream);
     return launch<128>(mq, mk, mv, p, n_tiles, stream);
 }

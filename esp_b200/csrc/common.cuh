@@ -12,6 +12,7 @@ enum : int {
     ESP_STATUS_LOGITS_NONFINITE = 2,   // a logits row holds a NaN or an infinity
     ESP_STATUS_WAIT_EXPIRED = 4,       // a bounded wait inside a kernel ran out
     ESP_STATUS_BAD_INDEX = 8,          // an index read from device memory was out of range and was skipped
+    ESP_STATUS_SMEM_LAYOUT = 16,       // a block's shared memory did not start where its layout needs it: it did not run
 };
 
 typedef __nv_bfloat16 bf16;

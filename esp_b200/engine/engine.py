@@ -344,7 +344,8 @@ class Engine:
         code = self.read_status()
         if code:
             names = {1: "non-finite router probabilities", 2: "non-finite logits", 4: "a bounded wait ran out",
-                     8: "an index on the device was out of range"}
+                     8: "an index on the device was out of range",
+                     16: "a kernel's shared memory was not aligned as its layout needs"}
             what = ", ".join(v for k, v in names.items() if code & k)
             self.rt.status.zero_()
             raise Backend(f"the device reported: {what}")
