@@ -31,6 +31,7 @@ using namespace tc05;
 constexpr int BM = 128, BN = 128, PAGE = 64;   // warps: 0 loads, 1 MMA, then 4 * ROWT warps of row threads
 constexpr int ATOM_BYTES = 128 * 128;           // 128 rows of 128 bytes: one 64-wide slice of a 128-row operand
 constexpr int STAGES = 3;                       // blocks of keys (and of values) in shared memory
+constexpr int GROUPS = 2;                       // groups of row threads: they take an item's key blocks in turn
 
 struct AttnParams {
     bf16* out;
@@ -104,11 +105,12 @@ __device__ __forceinline__ Item load_item(const AttnParams& p, int item) {
 
 // Persistent: the (tile, head) items are listed with the most keys first; block b takes the items
 // b, 2G-1-b, 2G+b, 4G-1-b, ... (G blocks), so that a long item is followed by a short one.  Every role
-// derives the same run of items, and the counters of key blocks (g) and items (n_items_done) that choose
-// the stage, the TMEM buffer and the phase of each mbarrier run on from one item to the next.
-// ROWT: threads that share a query row (2 or 4): each takes 128 / ROWT keys of a block and HD / ROWT columns of O.
+// derives the same run of items, and the counters of key blocks (g), of items and of each group's blocks that
+// choose the stage, the TMEM buffer and the phase of each mbarrier run on from one item to the next.
+// ROWT: threads of a group that share a query row: each takes 128 / ROWT keys of a block and HD / ROWT columns of
+// the group's O when it has to be rescaled.
 template <int HD, int ROWT>
-__global__ void __launch_bounds__(64 + ROWT * 128, 1)
+__global__ void __launch_bounds__(96 + GROUPS * ROWT * 128, 1)
 attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, AttnParams p) {
     constexpr int HALVES = HD / 64;                       // 64-column slices of a head
@@ -122,30 +124,33 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char* k_s = q_s + Q_BYTES;                   // [STAGES]
     unsigned char* v_s = k_s + STAGES * KV_BYTES;         // [STAGES]
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(v_s + STAGES * KV_BYTES);
-    constexpr int N_BARS = 7 + 4 * STAGES;
+    constexpr int N_BARS = 8 + 4 * STAGES;
     unsigned long long* q_full = bars;                    // [1]
     unsigned long long* q_empty = bars + 1;               // [1]
-    unsigned long long* p_ready = bars + 2;               // [1]
-    unsigned long long* s_full = bars + 3;                // [2]
-    unsigned long long* pv_full = bars + 5;               // [2]
-    unsigned long long* k_full = bars + 7;                // [STAGES]
+    unsigned long long* o_full = bars + 2;                // [1] every product of the item is done
+    unsigned long long* o_free = bars + 3;                // [1] the row threads have read the item's O
+    unsigned long long* s_full = bars + 4;                // [GROUPS]
+    unsigned long long* p_ready = bars + 6;               // [GROUPS]
+    unsigned long long* k_full = bars + 8;                // [STAGES]
     unsigned long long* k_empty = k_full + STAGES;        // [STAGES]
     unsigned long long* v_full = k_empty + STAGES;        // [STAGES]
     unsigned long long* v_empty = v_full + STAGES;        // [STAGES]
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     static_assert(N_BARS * 8 + 8 <= 256, "the barriers and the two words after them take 256 bytes");
-    float* xchg = reinterpret_cast<float*>(bars) + 64;    // [ROWT][128]: the row threads' maxima of a block, their sums at the end
+    float* xchg = reinterpret_cast<float*>(bars) + 64;    // [GROUPS][ROWT][128]: maxima of a block; sums and maxima at the end
     // where shared memory is too short for the slack that rounding up to 1024 bytes needs, its start has to
     // be aligned already; the block refuses to run otherwise
-    if (smem + Q_BYTES + 2 * STAGES * KV_BYTES + 256 + ROWT * 128 * 4 > smem_raw + p.smem_bytes) {
+    if (smem + Q_BYTES + 2 * STAGES * KV_BYTES + 256 + GROUPS * ROWT * 128 * 4 > smem_raw + p.smem_bytes) {
         if (threadIdx.x == 0) atomicOr(p.status, ESP_STATUS_SMEM_LAYOUT);
         return;
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int V_WARP = 2 + GROUPS * ROWT * 4;                        // warps: 0 keys, 1 MMA, row threads, values
     if (threadIdx.x == 0) {
-        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], i == 2 ? 4 * ROWT : 1);   // p_ready: one arrival per warp of row threads
+        // o_free: one arrival per warp of row threads; p_ready: one per warp of the group; the others one
+        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], i == 3 ? GROUPS * ROWT * 4 : (i == 6 || i == 7) ? ROWT * 4 : 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -157,64 +162,66 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
-    const unsigned tm_s = tmem_base, tm_pv = tmem_base + 256;          // S buffers at columns 0 and 128, PV at 256 and 384
+    const unsigned tm_s = tmem_base, tm_o = tmem_base + 256;           // S of the groups at columns 0 and 128, O at 256 and 384
 
-    if (warp == 0) {
-        // ---- loads: lanes 0..HALVES-1 the queries; then per block of keys, lane = (page of the block, slice)
+    if (warp == 0 || warp == V_WARP) {
+        // ---- loads.  Warp 0: the queries (lanes 0..HALVES-1) and the keys; the last warp: the values.  Each works
+        // through the same blocks of keys with a ring and barriers of its own, so neither waits for the other's
+        // stages.  A lane's box: (page of the block, 64-column slice); the pages of 16 blocks are read from the
+        // block table at once, one per lane, and handed out by shuffle.
+        const bool is_k = warp == 0;
+        unsigned char* ring = is_k ? k_s : v_s;
+        unsigned long long* full = is_k ? k_full : v_full;
+        unsigned long long* empty = is_k ? k_empty : v_empty;
+        const CUtensorMap* map = is_k ? &map_k : &map_v;
         bool ok = true;
         const int pg_in_blk = lane / HALVES, half = lane % HALVES;      // lanes 0..2*HALVES-1 issue boxes
-        int g = 0, issued_q = 0, issued_k = 0, issued_v = 0;
+        int g = 0, issued_q = 0, issued = 0;
         for (int round = 0; ok; round++) {
             const int item = item_of(round);
             if (item >= n_items) break;
             const Item t = load_item(p, item);
-            if (lane == 0) {                                             // the last item's S products have read its queries
-                ok = !*abort_flag && mbar_wait(q_empty, (round & 1) ^ 1);
-                if (ok) mbar_expect_tx(q_full, Q_BYTES);
+            if (is_k) {
+                if (lane == 0) {                                         // the last item's S products have read its queries
+                    ok = !*abort_flag && mbar_wait(q_empty, (round & 1) ^ 1);
+                    if (ok) mbar_expect_tx(q_full, Q_BYTES);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (lane < HALVES) tma_load_2d(q_s + lane * ATOM_BYTES, &map_q, t.h * HD + lane * 64, t.row0, q_full);
+                issued_q = round + 1;
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (lane < HALVES) tma_load_2d(q_s + lane * ATOM_BYTES, &map_q, t.h * HD + lane * 64, t.row0, q_full);
-            issued_q = round + 1;
+            int rows16 = p.kv_rows;                                      // this lane's page of the 16 blocks at hand
             for (int j = 0; j < t.nb && ok; j++, g++) {
                 const int s = g % STAGES, ph = (g / STAGES) & 1;
-                // the page of this lane's box; a page past the tile's last key is read as zeros (a row past the cache)
-                int box_row = p.kv_rows;
-                if (lane < 2 * HALVES) {
-                    const int page_idx = (t.blk_lo + j) * 2 + pg_in_blk;
+                if ((j & 15) == 0) {
+                    // a page past the tile's last key is read as zeros (a row past the cache)
+                    rows16 = p.kv_rows;
+                    const int page_idx = (t.blk_lo + j) * 2 + lane;
                     if (page_idx <= t.pos_last / PAGE) {
                         const int pg = p.block_table[(size_t)t.seq * p.table_stride + page_idx];
-                        if (pg >= 0 && pg < p.n_pages) box_row = (pg * p.nkv + t.kvh) * PAGE;
+                        if (pg >= 0 && pg < p.n_pages) rows16 = (pg * p.nkv + t.kvh) * PAGE;
                         else atomicOr(p.status, ESP_STATUS_BAD_INDEX);
                     }
                 }
+                const int box_row = __shfl_sync(0xffffffffu, rows16, ((j & 15) * 2 + pg_in_blk) & 31);
                 if (lane == 0) {
-                    ok = !*abort_flag && mbar_wait(&k_empty[s], ph ^ 1);
-                    if (ok) mbar_expect_tx(&k_full[s], KV_BYTES);
+                    ok = !*abort_flag && mbar_wait(&empty[s], ph ^ 1);
+                    if (ok) mbar_expect_tx(&full[s], KV_BYTES);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 if (lane < 2 * HALVES)
-                    tma_load_2d(k_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_k, half * 64, box_row, &k_full[s]);
-                issued_k = g + 1;
-                if (lane == 0) {
-                    ok = !*abort_flag && mbar_wait(&v_empty[s], ph ^ 1);
-                    if (ok) mbar_expect_tx(&v_full[s], KV_BYTES);
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                if (lane < 2 * HALVES)
-                    tma_load_2d(v_s + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), &map_v, half * 64, box_row, &v_full[s]);
-                issued_v = g + 1;
+                    tma_load_2d(ring + s * KV_BYTES + half * ATOM_BYTES + pg_in_blk * (PAGE * 128), map, half * 64, box_row, &full[s]);
+                issued = g + 1;
             }
         }
         if (lane == 0 && (!ok || *abort_flag)) {
             atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
             *abort_flag = 1;
-            // let this CTA's own copies land before its shared memory is given up
+            // let this warp's own copies land before the block's shared memory is given up
             if (issued_q > 0) mbar_wait(q_full, (issued_q - 1) & 1);
-            for (int j = max(0, issued_k - STAGES); j < issued_k; j++) mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1);
-            for (int j = max(0, issued_v - STAGES); j < issued_v; j++) mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1);
+            for (int j = max(0, issued - STAGES); j < issued; j++) mbar_wait(&full[j % STAGES], (j / STAGES) & 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -222,47 +229,55 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const unsigned long long dq = smem_desc(q_s), dk = smem_desc(k_s);
             const unsigned long long dv = smem_desc_mn(v_s, ATOM_BYTES);
             bool ok = true;
-            int g = 0;
-            auto issue_s = [&](int gg, bool last_of_item) {               // S = Q K^T of key block gg into S buffer gg % 2
-                const int st = gg % STAGES;
-                if (!mbar_wait(&k_full[st], (gg / STAGES) & 1)) return false;
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < HD / 16; kk++) {
-                    const unsigned off = ((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4;
-                    tc_mma(tm_s + (gg & 1) * BN, dq + off, dk + ((st * KV_BYTES) >> 4) + off, idesc_s, kk > 0 ? 1u : 0u);
-                }
-                tc_commit(&k_empty[st]);                                  // the keys are free once S is done
-                if (last_of_item) tc_commit(q_empty);                     // and so are the queries after the item's last S
-                tc_commit(&s_full[gg & 1]);
-                return true;
-            };
+            int g0 = 0;                                                   // key blocks before this item
+            int n_p0 = 0, n_p1 = 0;                                       // blocks of each group so far: the phase of p_ready
             for (int round = 0; ok && !*abort_flag; round++) {
                 const int item = item_of(round);
                 if (item >= n_items) break;
                 const Item t = load_item(p, item);
+                // S = Q K^T of the item's key block j, for the group j % 2, over where the group's last P stood: the
+                // tensor core runs one thread's products in the order in which they were issued
+                auto issue_s = [&](int j) {
+                    const int gg = g0 + j, st = gg % STAGES, b = j & 1;
+                    if (!mbar_wait(&k_full[st], (gg / STAGES) & 1)) return false;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; kk++) {
+                        const unsigned off = ((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4;
+                        tc_mma(tm_s + b * BN, dq + off, dk + ((st * KV_BYTES) >> 4) + off, idesc_s, kk > 0 ? 1u : 0u);
+                    }
+                    tc_commit(&k_empty[st]);                              // the keys are free once S is done
+                    if (j + 1 == t.nb) tc_commit(q_empty);                // and so are the queries after the item's last S
+                    tc_commit(&s_full[b]);
+                    return true;
+                };
                 ok = mbar_wait(q_full, round & 1);
-                if (ok) ok = issue_s(g, t.nb == 1);
-                for (int j = 0; j < t.nb && ok && !*abort_flag; j++, g++) {
-                    const int s = g & 1, st = g % STAGES;
-                    if (j + 1 < t.nb) ok = issue_s(g + 1, j + 2 == t.nb);  // runs while the row threads work on this block
-                    if (!ok) break;
-                    // P stands where S of this block stood (and with that: PV of two blocks ago has been read),
-                    // the values have landed.  S of the block after next goes to the same columns: the tensor
-                    // core runs one thread's products in the order in which they were issued
-                    if (!mbar_wait(p_ready, g & 1) || !mbar_wait(&v_full[st], (g / STAGES) & 1)) {
+                if (ok) ok = issue_s(0);
+                if (ok && t.nb > 1) ok = issue_s(1);
+                // the row threads have read the O of the item before
+                if (ok) ok = mbar_wait(o_free, (round & 1) ^ 1);
+                for (int j = 0; j < t.nb && ok && !*abort_flag; j++) {
+                    const int gg = g0 + j, st = gg % STAGES, b = j & 1;
+                    // the group's P stands where its S stood (and its O has been rescaled if it had to be), the
+                    // values have landed
+                    const int n_p = b ? n_p1 : n_p0;
+                    if (!mbar_wait(&p_ready[b], n_p & 1) || !mbar_wait(&v_full[st], (gg / STAGES) & 1)) {
                         ok = false;
                         break;
                     }
+                    if (b) n_p1++;
+                    else n_p0++;
                     tc_fence_after();
 #pragma unroll
-                    for (int kk = 0; kk < BN / 16; kk++) {
+                    for (int kk = 0; kk < BN / 16; kk++) {                // O of the group += P V; its first block starts it
                         const unsigned b_off = (st * KV_BYTES + kk * 16 * 128) >> 4;
-                        tc_mma_ta(tm_pv + s * BN, tm_s + s * BN + kk * 8, dv + b_off, idesc_pv, kk > 0 ? 1u : 0u);
+                        tc_mma_ta(tm_o + b * BN, tm_s + b * BN + kk * 8, dv + b_off, idesc_pv, (j >= GROUPS || kk > 0) ? 1u : 0u);
                     }
                     tc_commit(&v_empty[st]);
-                    tc_commit(&pv_full[s]);
+                    if (j + 1 == t.nb) tc_commit(o_full);                 // all of the item's products
+                    if (j + GROUPS < t.nb) ok = issue_s(j + GROUPS);      // the group's next block
                 }
+                g0 += t.nb;
             }
             if (!ok) {
                 atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
@@ -270,42 +285,46 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     } else {
-        // ---- row threads: TMEM lane = query row of the tile; ROWT threads a row.  The warps w, w + 4, w + 8 .. may
-        // read the same 32 lanes; thread ``side`` of a row takes the keys side * CW .. of a block and the columns
-        // side * OW .. of the head.  They exchange their maxima of a block through shared memory and meet at a
-        // named barrier of their own (once when all have written, once when all have read); their sums stay
-        // apart until the end.
-        const int quad = warp & 3, r = quad * 32 + lane, side = (warp - 2) >> 2;
+        // ---- row threads: TMEM lane = query row of the tile.  Two groups take the item's key blocks in turn (group
+        // 0 the even ones), each with a softmax of its own (maximum, sum, O in tensor memory) that are merged at the
+        // item's end: while one group turns its scores into weights, the other reads, compares and waits, so the
+        // special function unit and the tensor core both stay busy.  ROWT threads of a group share a row: thread
+        // ``side`` takes the keys side * CW .. of a block; they exchange their maxima through shared memory and
+        // meet at a named barrier of their own (once when all have written, once when all have read).
+        const int quad = warp & 3, r = quad * 32 + lane, grp = (warp - 2) / (4 * ROWT), side = ((warp - 2) >> 2) % ROWT;
         const unsigned lane_sel = (unsigned)(quad * 32) << 16;
         const float sc = 1.4426950408889634f / sqrtf((float)HD);
         constexpr int CW = BN / ROWT;                                    // keys of a block that this thread takes
-        constexpr int OW = HD / ROWT;                                    // columns of O that this thread keeps
-        constexpr int MATES = ROWT * 32;                                 // threads at the row's named barrier
-        static_assert(CW % 32 == 0 && OW % 32 == 0, "a thread reads TMEM 32 columns at a time");
+        constexpr int OW = HD / ROWT;                                    // columns of the group's O that this thread rescales
+        constexpr int FW = HD / (GROUPS * ROWT);                         // columns of the result that this thread writes
+        constexpr int MATES = ROWT * 32, ROW_ALL = GROUPS * ROWT * 32;   // threads at the group's and at the row's barrier
+        constexpr float LAZY = 8.f;                                      // O is rescaled when the maximum grew by more (log2)
+        static_assert(CW % 32 == 0, "a thread reads its scores 32 columns at a time");
+        static_assert(OW % 32 == 0 && (FW == 16 || FW == 32), "columns are read 32 or 16 at a time");
+        const int bar_grp = 1 + grp * 4 + quad, bar_row = 1 + GROUPS * 4 + quad;
+        float* xg = xchg + grp * (ROWT * 128);                            // the group's [side][row]
         bool ok = true;
-        int g = 0;
+        int n_b = 0;                                                      // blocks of this group so far
         for (int round = 0; ok; round++) {
             const int item = item_of(round);
             if (item >= n_items) break;
             const Item t = load_item(p, item);
             const int pos = t.pos0 + r;
             const int key_first = p.window > 0 ? pos - p.window + 1 : 0; // the keys this row sees: key_first .. pos
-            float o[OW];
-#pragma unroll
-            for (int i = 0; i < OW; i++) o[i] = 0.f;
-            float m_run = -INFINITY, l_run = 0.f, pending = 0.f;         // pending: the factor O takes before the last PV is added
-            for (int j = 0; j < t.nb; j++, g++) {
-                const int s = g & 1, key0 = (t.blk_lo + j) * BN;
-                ok = !*abort_flag && mbar_wait(&s_full[s], (g >> 1) & 1);
-                ok = pair_agree(ok, 1 + quad, MATES);                            // the two warps of a row go on or leave together
+            float m_ref = -INFINITY, l_run = 0.f;                         // the maximum that O and l_run are scaled by
+            for (int j = grp; j < t.nb && ok; j += GROUPS, n_b++) {
+                const int key0 = (t.blk_lo + j) * BN;
+                ok = !*abort_flag && mbar_wait(&s_full[grp], n_b & 1);
+                ok = pair_agree(ok, bar_grp, MATES);                      // the threads of a row go on or leave together
                 if (!ok) break;
+                // S is done, and so are the products issued before it: the group's O holds its blocks so far
                 tc_fence_after();
                 // does any (row of the tile, key of the block) pair need the mask?
                 const bool edge = key0 + BN - 1 > t.pos0 || (p.window > 0 && key0 < t.pos0 + BM - 1 - p.window + 1);
                 // live columns of this row: c_lo .. c_lo + c_span; one unsigned comparison per element, no branch
                 const int c_lo = key_first - key0 - side * CW;
                 const unsigned c_span = (unsigned)(pos - key_first);
-                const unsigned s_addr = tm_s + s * BN + lane_sel + side * CW;
+                const unsigned s_addr = tm_s + grp * BN + lane_sel + side * CW;
                 float mx = -INFINITY;                                     // of the raw scores: the scale is positive
                 float sv[CW / 32][32];                                    // this thread's scores: read from TMEM once
 #pragma unroll
@@ -322,78 +341,103 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         for (int i = 0; i < 32; i++) mx = fmaxf(mx, sv[c][i]);
                     }
                 }
-                xchg[side * 128 + r] = mx;
-                named_sync(1 + quad, MATES);
+                xg[side * 128 + r] = mx;
+                named_sync(bar_grp, MATES);
 #pragma unroll
-                for (int o2 = 0; o2 < ROWT; o2++) mx = fmaxf(mx, xchg[o2 * 128 + r]);
-                named_sync(1 + quad, MATES);                              // all have read: the next block may write
-                mx *= sc;
-                const float m_new = fmaxf(m_run, mx);
-                const float m_use = m_new == -INFINITY ? 0.f : m_new;
-                const float alpha = fast_exp2(m_run - m_use);             // m_run = -inf gives 0
-                m_run = m_new;
+                for (int o2 = 0; o2 < ROWT; o2++) mx = fmaxf(mx, xg[o2 * 128 + r]);
+                named_sync(bar_grp, MATES);                               // all have read: the next block may write
+                const float m_new = fmaxf(m_ref, mx * sc);
+                // The weights are exp2(score - m_ref) with a maximum that may lag behind by up to LAZY: they stay
+                // below 2^LAZY, and sum and O stay consistent.  A row that outgrows that is brought up to date:
+                // the sum here, O in tensor memory, which the warp reads and writes as a whole (the other rows
+                // take the factor 1, so no row's result depends on its neighbours).  The group's first block has
+                // nothing to rescale.
+                const bool grew = m_new > m_ref + LAZY;                   // the same for all threads of the row
+                if (j < GROUPS) {
+                    m_ref = m_new;
+                } else if (__any_sync(0xffffffffu, grew)) {
+                    const float alpha = grew ? fast_exp2(m_ref - m_new) : 1.f;   // m_ref = -inf gives 0
+                    if (grew) m_ref = m_new;
+                    l_run *= alpha;
+#pragma unroll
+                    for (int c = 0; c < OW / 16; c++) {                   // in small pieces: the scores stay in registers
+                        const unsigned o_addr = tm_o + grp * BN + lane_sel + side * OW + c * 16;
+                        float v[16];
+                        unsigned w[16];
+                        tc_ld16(o_addr, v);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) w[i] = __float_as_uint(v[i] * alpha);
+                        tc_st16(o_addr, w);
+                    }
+                }
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
                 // every thread of the row holds its scores in registers by now, so P may go where S stood: the
-                // weights of keys 2c and 2c + 1 of the block into column c of the S buffer
+                // weights of keys 2c and 2c + 1 of the block into column c of the group's S buffer
                 float l_add = 0.f;
-                unsigned packed[CW / 2];
+                const unsigned p_addr = tm_s + grp * BN + lane_sel + side * (CW / 2);
 #pragma unroll
                 for (int c = 0; c < CW / 32; c++) {
+                    unsigned packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {                     // a masked score is -inf: its weight is 0
                         const float p0 = fast_exp2(fmaf(sv[c][i], sc, -m_use)), p1 = fast_exp2(fmaf(sv[c][i + 1], sc, -m_use));
                         l_add += p0 + p1;
-                        __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                        packed[c * 16 + (i >> 1)] = *reinterpret_cast<unsigned*>(&b);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<unsigned*>(&b2);
                     }
+                    tc_st16(p_addr + c * 16, packed);
                 }
-                const unsigned p_addr = tm_s + s * BN + lane_sel + side * (CW / 2);
-                if constexpr (CW == 64) tc_st32(p_addr, packed);
-                else tc_st16(p_addr, packed);
                 tc_wait_st();
-                l_run = l_run * alpha + l_add;
-                tc_fence_before();                                        // S of this block has been read, P written
+                l_run += l_add;
+                tc_fence_before();                                        // S has been read, P and O written
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_ready);
-                if (j > 0) {                                              // O = O * factor + PV of the block before
-                    ok = mbar_wait(&pv_full[s ^ 1], ((g - 1) >> 1) & 1);
-                    ok = pair_agree(ok, 1 + quad, MATES);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < OW / 32; c++) {
-                        float v[32];
-                        tc_ld32(tm_pv + (s ^ 1) * BN + lane_sel + side * OW + c * 32, v);
-#pragma unroll
-                        for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
-                    }
-                }
-                pending = alpha;
+                if (lane == 0) mbar_arrive(&p_ready[grp]);
             }
-            if (!ok) break;
-            const int s = (g - 1) & 1;                                    // the item's last block
-            ok = mbar_wait(&pv_full[s], ((g - 1) >> 1) & 1);
-            ok = pair_agree(ok, 1 + quad, MATES);
+            // ---- the item's end: the sum of the group's threads, then (sum, maximum) of every group to all the
+            // row's threads, who wait for the last products and each write HD / (GROUPS * ROWT) columns
+            xg[side * 128 + r] = l_run;
+            named_sync(bar_grp, MATES);
+            float l_grp = 0.f;
+#pragma unroll
+            for (int o2 = 0; o2 < ROWT; o2++) l_grp += xg[o2 * 128 + r];  // keys in ascending order
+            named_sync(bar_grp, MATES);
+            if (side == 0) xg[r] = l_grp;
+            if (side == 1) xg[128 + r] = m_ref;
+            if (ok) ok = !*abort_flag && mbar_wait(o_full, round & 1);
+            ok = pair_agree(ok, bar_row, ROW_ALL);                        // all threads of the row: written, and well
             if (!ok) break;
             tc_fence_after();
+            float m_all = -INFINITY, f[GROUPS], l_all = 0.f;
 #pragma unroll
-            for (int c = 0; c < OW / 32; c++) {
-                float v[32];
-                tc_ld32(tm_pv + s * BN + lane_sel + side * OW + c * 32, v);
+            for (int b = 0; b < GROUPS; b++) m_all = fmaxf(m_all, xchg[b * (ROWT * 128) + 128 + r]);
 #pragma unroll
-                for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * pending + v[i];
+            for (int b = 0; b < GROUPS; b++) {                            // a group without a key for this row counts 0
+                const float m_b = xchg[b * (ROWT * 128) + 128 + r];
+                f[b] = m_b == -INFINITY ? 0.f : fast_exp2(m_b - m_all);
+                l_all += f[b] * xchg[b * (ROWT * 128) + r];
+            }
+            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+            const int col0 = (grp * ROWT + side) * FW;
+            float o[FW];
+#pragma unroll
+            for (int i = 0; i < FW; i++) o[i] = 0.f;
+#pragma unroll
+            for (int b = 0; b < GROUPS; b++) {
+                if (b < t.nb) {                                           // an item of one block has nothing from the second group
+                    float v[FW];
+                    if constexpr (FW == 32) tc_ld32(tm_o + b * BN + lane_sel + col0, v);
+                    else tc_ld16(tm_o + b * BN + lane_sel + col0, v);
+#pragma unroll
+                    for (int i = 0; i < FW; i++) o[i] += f[b] * v[i];
+                }
             }
             tc_fence_before();
-            xchg[side * 128 + r] = l_run;                                 // the sums of a row's threads
-            named_sync(1 + quad, MATES);
-            float l_all = 0.f;
-#pragma unroll
-            for (int o2 = 0; o2 < ROWT; o2++) l_all += xchg[o2 * 128 + r];  // keys in ascending order
-            named_sync(1 + quad, MATES);
+            named_sync(bar_row, ROW_ALL);                                 // all have read the sums: the next item may write
+            if (lane == 0) mbar_arrive(o_free);
             if (r < t.rows) {
-                const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
-                bf16* orow = p.out + ((size_t)(t.row0 + r) * p.nh + t.h) * HD + side * OW;
+                bf16* orow = p.out + ((size_t)(t.row0 + r) * p.nh + t.h) * HD + col0;
 #pragma unroll
-                for (int i = 0; i < OW; i += 8) {
+                for (int i = 0; i < FW; i += 8) {
                     __nv_bfloat162 b0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
                     __nv_bfloat162 b1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
                     __nv_bfloat162 b2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
@@ -444,10 +488,10 @@ int make_map2d(CUtensorMap* map, const void* base, unsigned long long cols, unsi
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int n_tiles,
            cudaStream_t stream) {
-    constexpr int ROWT = HD >= 128 ? 4 : 2;   // threads that share a query row
+    constexpr int ROWT = 2;      // threads of a group that share a query row
     // queries, STAGES blocks of keys and of values, barriers, the row threads' exchange; and 1024 bytes to round
     // the start up with, where the 227 KB of a block have room for them
-    size_t smem = (size_t)(HD / 64) * ATOM_BYTES * (1 + 2 * STAGES) + 256 + ROWT * 128 * 4;
+    size_t smem = (size_t)(HD / 64) * ATOM_BYTES * (1 + 2 * STAGES) + 256 + GROUPS * ROWT * 128 * 4;
     if (smem + 1024 <= 232448) smem += 1024;
     static bool raised = false;
     if (!raised) {
@@ -468,7 +512,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     if (grid > sm_count) grid = sm_count;
     AttnParams pp = p;
     pp.smem_bytes = (int)smem;
-    attn_prefill_tc05_kernel<HD, ROWT><<<(int)grid, 64 + ROWT * 128, smem, stream>>>(mq, mk, mv, pp);
+    attn_prefill_tc05_kernel<HD, ROWT><<<(int)grid, 96 + GROUPS * ROWT * 128, smem, stream>>>(mq, mk, mv, pp);
     return esp_launch_status();
 }
 }  // namespace
