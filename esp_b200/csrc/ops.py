@@ -385,6 +385,9 @@ def attn_prefill(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_
         _ptr(status, torch.int32), _stream()), "attn_prefill")
 
 
+ATTN_TC05_TILE_ROWS = 256      # new tokens of a sequence to a tile of attn_prefill_tc05
+
+
 def attn_prefill_tc05_fits(hd, page) -> bool:
     """Head sizes and page size that the tensor-memory prefill attention takes."""
     return hd in (64, 128) and page == 64
@@ -393,8 +396,9 @@ def attn_prefill_tc05_fits(hd, page) -> bool:
 def attn_prefill_tc05(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,
                       window, status):
     """Prefill attention on tcgen05 with accumulators in tensor memory (bfloat16; head size 64 or 128; pages
-    of 64 positions).  Same arguments as attn_prefill, but tile_seq / tile_first list tiles of 128 new
-    tokens, best with the tiles that see the most keys first (the order only matters for the balance)."""
+    of 64 positions).  Same arguments as attn_prefill, but tile_seq / tile_first list tiles of
+    ATTN_TC05_TILE_ROWS new tokens, best with the tiles that see the most keys first (the order only matters
+    for the balance)."""
     if not attn_prefill_tc05_fits(hd, page):
         raise Backend(f"attn_prefill_tc05: head size {hd} / page {page} not taken (64 or 128; page 64)")
     if not q.is_contiguous() or q.numel() != q.shape[0] * nh * hd:

@@ -252,9 +252,10 @@ class Engine:
             tables = [np.asarray(g.table_rows(slots, stride), dtype=np.int32).reshape(b, stride)
                       for g in book.groups]
             tiles = [(i, first) for i, t in enumerate(news) for first in range(0, t, 64)]
-            # tiles of 128 rows for the tensor-memory attention, those that see the most keys first
-            wide = sorted(((i, first) for i, t in enumerate(news) for first in range(0, t, 128)),
-                          key=lambda sf: -(pasts[sf[0]] + min(sf[1] + 128, news[sf[0]])))
+            # wider tiles for the tensor-memory attention, those that see the most keys first
+            wide_rows = ops.ATTN_TC05_TILE_ROWS
+            wide = sorted(((i, first) for i, t in enumerate(news) for first in range(0, t, wide_rows)),
+                          key=lambda sf: -(pasts[sf[0]] + min(sf[1] + wide_rows, news[sf[0]])))
             arrays = [tok_ids, tok_seq, tok_pos, np.asarray(slots, dtype=np.int32),
                       np.asarray(starts, dtype=np.int32), np.asarray(pasts, dtype=np.int32),
                       np.asarray(want_rows, dtype=np.int32), np.asarray([t[0] for t in tiles], dtype=np.int32),

@@ -170,5 +170,5 @@ class StepContext:
     block_tables: list               # per layer group: [B, stride] page ids
     host: dict                       # the same lists on the host (slots, starts, pasts, news)
     aux: dict
-    q_wide_seq: Optional[torch.Tensor] = None     # [tiles] the same for tiles of 128 new tokens, those that see the
+    q_wide_seq: Optional[torch.Tensor] = None     # [tiles] the same for the wider tiles of the tensor-memory attention, those that see the
     q_wide_first: Optional[torch.Tensor] = None   # most keys first (None: the step did not list them)

@@ -610,16 +610,16 @@ def test_attn_prefill_against_reference(nh, nkv, hd, window):
                                                  (2, 2, 128, 300)])
 def test_attn_prefill_tc05_against_reference(nh, nkv, hd, window):
     """The same runs through the kernel that keeps scores and weighted values in tensor memory."""
-    check_attn_prefill(ops.attn_prefill_tc05, nh, nkv, hd, window, tile=128)
+    check_attn_prefill(ops.attn_prefill_tc05, nh, nkv, hd, window, tile=ops.ATTN_TC05_TILE_ROWS)
 
 
 def check_attn_prefill(fn, nh, nkv, hd, window, tile=64):
     torch.manual_seed(3)
     dtype = torch.bfloat16
     group = nh // nkv
-    runs = [(0, 200), (130, 70), (0, 1), (63, 66), (300, 129)]        # (past, new)
+    runs = [(0, 200), (130, 70), (0, 1), (63, 66), (300, 129), (10, 420)]        # (past, new)
     lens = [p + n for p, n in runs]
-    tables = [[5 * i + s for i in range(7)] for s in range(5)]
+    tables = [[6 * i + s for i in range(7)] for s in range(6)]
     ks = [torch.randn(n, nkv, hd) * 0.3 for n in lens]
     vs = [torch.randn(n, nkv, hd) for n in lens]
     qs = [torch.randn(n, nh, hd) * 0.3 for _p, n in runs]
@@ -633,7 +633,7 @@ def check_attn_prefill(fn, nh, nkv, hd, window, tile=64):
             for h in range(nh):
                 ks[s][target, h // group] = ks[s][target, h // group] / ks[s][target, h // group].norm() * 6.0
                 qs[s][i, h] = ks[s][target, h // group] * (np.sqrt(hd) * 3.0 / 6.0)
-    kc, vc = paged(ks, vs, tables, 35, nkv, hd, dtype)
+    kc, vc = paged(ks, vs, tables, 42, nkv, hd, dtype)
     q = torch.cat(qs).to(dtype)
     n = q.shape[0]
     out = torch.full((n, nh * hd), float("nan"), dtype=dtype, device=DEV)
