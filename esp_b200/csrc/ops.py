@@ -385,7 +385,7 @@ def attn_prefill(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_
         _ptr(status, torch.int32), _stream()), "attn_prefill")
 
 
-ATTN_TC05_TILE_ROWS = 256      # new tokens of a sequence to a tile of attn_prefill_tc05
+ATTN_TC05_TILE_ROWS = 128      # new tokens of a sequence to a tile of attn_prefill_tc05
 
 
 def attn_prefill_tc05_fits(hd, page) -> bool:
