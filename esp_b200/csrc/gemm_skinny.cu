@@ -32,6 +32,7 @@ struct SkinnyParams {
     void* C;
     long long ldc;
     int M, N, K;
+    int groups;                     // grouped form: how many groups there are (the grid's y may be smaller)
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -58,16 +59,29 @@ gemm_skinny_kernel(SkinnyParams p) {
     bf16* a_s = reinterpret_cast<bf16*>(smem_raw);                   // [8*NBLK][a_stride]
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)8 * NBLK * a_stride * sizeof(bf16));   // [WARPS][NBLK][32][4]
 
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
     int m_begin = 0, m_end = p.M;
     const bf16* W = p.W;
     if (p.group_offsets) {
-        m_begin = p.group_offsets[blockIdx.y];
-        m_end = p.group_offsets[blockIdx.y + 1];
-        W += (size_t)blockIdx.y * p.w_group_stride;
+        int group = blockIdx.y;
+        if ((int)gridDim.y < p.groups) {
+            // fewer rows than groups (a decode step of one sequence names a few experts of many): the grid has
+            // one y per row, and y takes the group whose first row is row y; the other blocks leave at once
+            int* found = reinterpret_cast<int*>(smem_raw);            // read by all before the first rows are staged there
+            if (tid == 0) *found = -1;
+            __syncthreads();
+            for (int e = tid; e < p.groups; e += WARPS * 32)
+                if (p.group_offsets[e] == (int)blockIdx.y && p.group_offsets[e + 1] > (int)blockIdx.y) *found = e;
+            __syncthreads();
+            group = *found;
+            if (group < 0) return;
+        }
+        m_begin = p.group_offsets[group];
+        m_end = p.group_offsets[group + 1];
+        W += (size_t)group * p.w_group_stride;
     }
     if (m_begin >= m_end) return;
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
     // the two weight rows this lane streams
     int row_a, row_b;
     bool ok_a, ok_b;
@@ -214,7 +228,7 @@ int launch_variant(const SkinnyParams& p, int groups, int tiles, cudaStream_t st
         raised = true;
     }
     constexpr int TILES = WARPS / KS;
-    dim3 grid((tiles + TILES - 1) / TILES, groups);
+    dim3 grid((tiles + TILES - 1) / TILES, p.group_offsets && p.M < groups ? p.M : groups);   // every group that has rows starts below M
     gemm_skinny_kernel<NBLK, SWIGLU, TC, KS><<<grid, WARPS * 32, smem, stream>>>(p);
     return esp_launch_status();
 }
@@ -240,7 +254,7 @@ ESP_API int esp_gemm_skinny(const void* A, long long lda, const int* a_rows, con
                             int groups, int M, int N, int K, int max_rows, int swiglu, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K % 8 != 0 || lda % 8 != 0 || groups > 65535) return (int)cudaErrorInvalidValue;
-    SkinnyParams p{(const bf16*)W, w_group_stride, (const bf16*)A, lda, a_rows, group_offsets, row_scale, C, ldc, M, N, K};
+    SkinnyParams p{(const bf16*)W, w_group_stride, (const bf16*)A, lda, a_rows, group_offsets, row_scale, C, ldc, M, N, K, groups};
     const int g = group_offsets ? groups : 1;
     const bool two = max_rows > 8 && (size_t)16 * (K + 32) * 2 + WARPS * 2 * 512 <= 227 * 1024;
 #define ESP_GO(NB, SW, TC) return launch<NB, SW, TC>(p, g, stream)

@@ -552,6 +552,36 @@ def test_gemm_skinny_grouped_gather_scale_and_chunks():
             row += 1
 
 
+@pytest.mark.parametrize("counts_at", [{0: 1, 17: 2, 59: 1}, {59: 4}, {3: 1, 4: 1, 5: 1, 58: 1}, {0: 5}])
+def test_gemm_skinny_grouped_fewer_rows_than_groups(counts_at):
+    """A decode step of one sequence names a few experts of many: the grid then has one row per (token,
+    expert) pair and finds each pair's group; the first and the last group, neighbours, one group with
+    every row."""
+    g, n, k, inter = 60, 50, 136, 24
+    counts = [counts_at.get(e, 0) for e in range(g)]
+    offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+    total = sum(counts)
+    assert total < g
+    src = rnd(7, k, dtype=torch.bfloat16)
+    a_rows = torch.tensor(np.random.default_rng(2).integers(0, 7, total), dtype=torch.int32, device=DEV)
+    w = rnd(g, n, k, dtype=torch.bfloat16, seed=1)
+    scale = rnd(total, seed=2)
+    c = torch.full((total + 1, n), 7.0, device=DEV)
+    ops.gemm_skinny(src, w, c, a_rows=a_rows, row_scale=scale, group_offsets=offsets, rows=total, max_rows=8)
+    w2 = rnd(g, 2 * inter, k, dtype=torch.bfloat16, seed=3, scale=0.3)
+    act = torch.full((total + 1, inter), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(src, w2, act, swiglu=True, a_rows=a_rows, group_offsets=offsets, rows=total, max_rows=8)
+    row = 0
+    for e, cnt in enumerate(counts):
+        for _ in range(cnt):
+            x = src[a_rows[row].long()].double()
+            close(c[row], (x @ w[e].double().t()) * scale[row].double(), torch.float32, f"group {e} row {row}")
+            gg, uu = x @ w2[e, :inter].double().t(), x @ w2[e, inter:].double().t()
+            close(act[row], gg / (1 + torch.exp(-gg)) * uu, torch.bfloat16, f"swiglu group {e} row {row}")
+            row += 1
+    assert torch.all(c[total:] == 7.0) and torch.all(act[total:] == 7.0)
+
+
 @pytest.mark.parametrize("split", [256, 512])
 @pytest.mark.parametrize("nh, nkv, hd, window", [(4, 4, 128, None), (6, 2, 64, None), (7, 1, 128, 100), (8, 1, 192, None),
                                                  (4, 2, 256, 300), (16, 16, 128, 65)])
