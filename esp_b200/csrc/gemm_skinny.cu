@@ -106,6 +106,21 @@ gemm_skinny_kernel(SkinnyParams p) {
     const int k_lo = min(K, kslice * per_warp * 32);
     const int k_hi = min(K, (kslice + 1) * per_warp * 32);
 
+    // The first pieces of the weight rows are asked for before the activation rows are staged: the two trips to
+    // memory (rows from L2, weights from DRAM) then run side by side, which is most of what a short product
+    // (K / KS of a few hundred) takes.
+    uint4 wa[UNROLL], wb[UNROLL];
+    auto load_weights = [&](int k0) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const int k = k0 + u * 32 + tg * 8;
+            const bool in = k < k_hi;                                 // K is a multiple of 8: a piece is whole or absent
+            wa[u] = (in && ok_a) ? load_stream(wa_ptr + k) : make_uint4(0, 0, 0, 0);
+            wb[u] = (in && ok_b) ? load_stream(wb_ptr + k) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    load_weights(k_lo);
+
     for (int m0 = m_begin; m0 < m_end; m0 += 8 * NBLK) {
         const int cnt = min(8 * NBLK, m_end - m0);
         __syncthreads();                                              // the previous chunk's readers are done
@@ -129,14 +144,7 @@ gemm_skinny_kernel(SkinnyParams p) {
             for (int i = 0; i < 4; i++) acc[nb][i] = 0.f;
 
         for (int k0 = k_lo; k0 < k_hi; k0 += 32 * UNROLL) {
-            uint4 wa[UNROLL], wb[UNROLL];
-#pragma unroll
-            for (int u = 0; u < UNROLL; u++) {
-                const int k = k0 + u * 32 + tg * 8;
-                const bool in = k < k_hi;                             // K is a multiple of 8: a piece is whole or absent
-                wa[u] = (in && ok_a) ? load_stream(wa_ptr + k) : make_uint4(0, 0, 0, 0);
-                wb[u] = (in && ok_b) ? load_stream(wb_ptr + k) : make_uint4(0, 0, 0, 0);
-            }
+            if (k0 != k_lo || m0 != m_begin) load_weights(k0);        // the very first pieces are on their way already
 #pragma unroll
             for (int u = 0; u < UNROLL; u++) {
                 const int k = k0 + u * 32 + tg * 8;
