@@ -247,7 +247,9 @@ int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
     // warps wanted: about a dozen per SM.  The fewer tiles there are, the more warps share one.
     const long long spread = (long long)tiles * (p.group_offsets ? (groups < p.M ? groups : p.M) : 1);
     constexpr int SLOTS = 12;      // measured: 8 and 16 were slower at batch 8, 24 slower at batch 1
-    if (spread >= 148 * SLOTS) return launch_variant<NBLK, SWIGLU, TC, 1>(p, groups, tiles, stream);
+    // a warp takes a tile all by itself only with several waves of tiles (measured: batch 1 gains 4 % over a
+    // limit of 12, batch 8 and 64 are the same)
+    if (spread >= 148 * 48) return launch_variant<NBLK, SWIGLU, TC, 1>(p, groups, tiles, stream);
     if (spread * 2 >= 148 * SLOTS) return launch_variant<NBLK, SWIGLU, TC, 2>(p, groups, tiles, stream);
     if (spread * 4 >= 148 * SLOTS) return launch_variant<NBLK, SWIGLU, TC, 4>(p, groups, tiles, stream);
     return launch_variant<NBLK, SWIGLU, TC, 8>(p, groups, tiles, stream);

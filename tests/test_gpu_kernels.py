@@ -484,19 +484,19 @@ def test_gemm_skinny_two_and_four_warps_per_tile(n):
 def test_gemm_skinny_many_tiles_one_tile_per_warp():
     """With enough tiles of weight rows each warp takes a tile of its own and walks all of K: dense,
     fused SwiGLU and grouped with a ragged last tile."""
-    m, n, k = 5, 30001, 72
+    m, n, k = 5, 120001, 72
     a, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1)
     scale = rnd(m, seed=2)
     c = torch.empty(m, n, device=DEV)
     ops.gemm_skinny(a, w, c, row_scale=scale)
     close(c, (a.double() @ w.double().t()) * scale.double()[:, None], torch.float32, "one tile per warp, dense", k=k)
-    inter = 15000
+    inter = 60000
     w2 = rnd(2 * inter, k, dtype=torch.bfloat16, seed=3, scale=0.3)
     act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
     ops.gemm_skinny(a, w2, act, swiglu=True)
     g, u = a.double() @ w2[:inter].double().t(), a.double() @ w2[inter:].double().t()
     close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "one tile per warp, swiglu")
-    groups, n3 = 40, 500
+    groups, n3 = 40, 2900
     counts = [(3 * i) % 5 for i in range(groups)]
     offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
     total = sum(counts)
