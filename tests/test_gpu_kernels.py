@@ -709,6 +709,14 @@ def test_gemm_tc05_swiglu(m, inter, k):
     close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "tcgen05 swiglu")
 
 
+def check_tile_cover(first_rows, counts, rows, tile):
+    """Every permuted row lies in exactly one tile."""
+    seen = np.zeros(rows, dtype=np.int64)
+    for r, c in zip(first_rows, counts):
+        seen[r:r + c] += 1
+    assert np.all(seen == 1), "a row outside every tile or in two"
+
+
 def test_gemm_tc05_grouped_through_the_permutation():
     """Router output -> permutation and tile list -> gathered rows -> grouped SwiGLU product -> grouped
     down product with the routing weight; experts with no rows, one row and several tiles of rows."""
@@ -732,7 +740,7 @@ def test_gemm_tc05_grouped_through_the_permutation():
     assert n_tiles == sum((off[i + 1] - off[i] + tile - 1) // tile for i in range(e))
     tg, tr, tc = (t.cpu().numpy()[:n_tiles] for t in tiles[:3])
     assert all(off[g] <= r and r + c <= off[g + 1] and 0 < c <= tile for g, r, c in zip(tg, tr, tc))
-    assert sum(tc) == rows
+    check_tile_cover(tr, tc, rows, tile)
     h = rnd(n_tok, width, dtype=torch.bfloat16, seed=5)
     h_perm = torch.empty(rows, width, dtype=torch.bfloat16, device=DEV)
     ops.gather_rows(h, perm_token, h_perm)
@@ -872,3 +880,4 @@ def test_moe_permute_many_pairs_with_uneven_routing(n, k, e):
     tg, tr, tc = (t.cpu().numpy()[:n_tiles] for t in tiles[:3])
     assert n_tiles == sum((off[i + 1] - off[i] + tile - 1) // tile for i in range(e)) and sum(tc) == n * k
     assert all(off[g] <= r and r + c <= off[g + 1] and 0 < c <= tile for g, r, c in zip(tg, tr, tc))
+    check_tile_cover(tr, tc, n * k, tile)
