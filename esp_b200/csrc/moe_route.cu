@@ -232,6 +232,7 @@ router_logits_mma_kernel(const float* __restrict__ h, const bf16* __restrict__ w
     // the MMA's k index may be any fixed rearrangement of the columns as long as both operands use it: of a run
     // of 32 columns this lane takes the 8 from tg * 8 on, four in each of two MMAs, so that its loads are 16 bytes
     const int share = width / KW;                                 // width is a multiple of KW * 32
+#pragma unroll 2                                               // the loads of two steps are on their way together
     for (int k0 = warp * share; k0 < (warp + 1) * share; k0 += 32) {
 #pragma unroll
         for (int s = 0; s < 2; s++) {
