@@ -22,10 +22,11 @@
 // accumulator of n_tok columns holds them (lanes 0..63 gate, 64..127 up).  A
 // tcgen05.mma with M = 128 keeps its issuing thread for about 83 cycles at any
 // N up to 128 and for 128 cycles at N = 256 (measured), so few wide MMAs beat many
-// narrow ones: token tiles reach 256 rows.  Warp 0 issues the TMA loads, warp 1
-// owns TMEM and issues the MMAs, warps 2..5 are the epilogue (each reads the 32
-// TMEM lanes that its position in the warpgroup may touch).  A ring of
-// shared-memory stages is handed back and forth with mbarriers.  Every wait is
+// narrow ones: token tiles reach 256 rows.  Warps 0 and 6 issue the TMA loads (the
+// k steps in turn, each into a ring of its own), warp 1 owns TMEM and issues the
+// MMAs, warps 2..5 and 7..10 are the epilogue (each reads the 32 TMEM lanes that its
+// position in the warpgroup may touch; the two sets take alternate runs of 32 tokens).  The
+// rings' stages are handed back and forth with mbarriers.  Every wait is
 // bounded: if one runs out the kernel raises ESP_STATUS_WAIT_EXPIRED in the
 // status word, stops issuing work, lets its own copies land, frees its TMEM and
 // returns.
