@@ -93,15 +93,29 @@ class GroupBook:
         lo = self.first_needed(old_len) // PAGE
         return [i for i in range(lo, hi) if i >= len(table) or table[i] < 0]
 
-    def reserve(self, slot: int, old_len: int, new_len: int) -> None:
+    def reserve(self, slot: int, old_len: int, new_len: int) -> tuple:
+        """Takes the pages the step needs.  Returns what ``cancel`` needs to undo it."""
         need = self.missing(slot, old_len, new_len)
         got = self.pool.take(len(need))
         table = self.tables.setdefault(slot, [])
+        before = len(table)
         hi = pages_for(new_len)
         while len(table) < hi:
             table.append(-1)
         for i, page in zip(need, got):
             table[i] = page
+        return slot, before, need
+
+    def cancel(self, receipt: tuple) -> None:
+        """Gives back the pages of a reservation whose step did not run to its end."""
+        slot, before, need = receipt
+        table = self.tables.get(slot)
+        if table is None:
+            return
+        self.pool.give_back([table[i] for i in need])
+        for i in need:
+            table[i] = -1
+        del table[before:]
 
     def trim(self, slot: int, length: int) -> None:
         """Give back pages that no later query of the slot can see."""
@@ -169,11 +183,22 @@ class CacheBook:
                 raise CacheFull(f"the step needs {need} more cache pages of {PAGE} tokens, "
                                 f"{g.pool.available} of {g.pool.n} are free")
 
-    def reserve(self, growth: dict) -> None:
+    def reserve(self, growth: dict) -> list:
+        """Takes the pages of a step (all of them or, with CacheFull, none).  The
+        result goes to ``commit`` once the step has run, or to ``cancel`` if it
+        has not."""
         self.check_step(growth)
+        receipts = []
         for g in self.groups:
             for slot, n_new in growth.items():
-                g.reserve(slot, self.lengths[slot], self.lengths[slot] + n_new)
+                receipts.append((g, g.reserve(slot, self.lengths[slot], self.lengths[slot] + n_new)))
+        return receipts
+
+    def cancel(self, receipts: list) -> None:
+        """Undoes ``reserve``: the step failed, its sequences keep their old
+        lengths and hold no page more than before."""
+        for g, receipt in reversed(receipts):
+            g.cancel(receipt)
 
     def commit(self, growth: dict) -> None:
         for slot, n_new in growth.items():

@@ -12,9 +12,7 @@ from .book import PAGE, CacheBook, KvLayout
 
 # words of the engine's own per-sequence state (int64 each)
 STATE_RNG = 0          # splitmix64 state of the sequence's sampler
-STATE_DRAWS = 1        # draws taken so far
-STATE_LAST_TOKEN = 2   # last token chosen on the device
-STATE_WORDS = 4
+STATE_WORDS = 4        # a row is 32 bytes; the other words are free
 
 
 @dataclass(frozen=True)

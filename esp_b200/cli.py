@@ -17,19 +17,33 @@ def _ids(text: str) -> list:
 
 
 def cmd_generate(a) -> int:
-    from .provider import DecoderProvider, GenerationRequest
-    prov = DecoderProvider.load(a.model, dtype=a.dtype, device=a.device, max_batch=a.max_batch,
-                                max_context=a.max_context)
+    from .config import config_from_json
+    from .provider import DecoderProvider, GenerationRequest, cache_tokens_for, load_tokenizer
     reqs = []
     for ids in a.prompt_ids or []:
         reqs.append(GenerationRequest(prompt_ids=_ids(ids), max_tokens=a.max_tokens, temperature=a.temperature,
                                       top_p=a.top_p, seed=a.seed, stop=a.stop or [], stop_token_ids=a.stop_token_id or []))
-    for text in a.prompt or []:
-        reqs.append(GenerationRequest(prompt=text, max_tokens=a.max_tokens, temperature=a.temperature, top_p=a.top_p,
-                                      seed=a.seed, stop=a.stop or [], stop_token_ids=a.stop_token_id or []))
+    if a.prompt:
+        tok = load_tokenizer(a.model)
+        if tok is None:
+            print("text prompts need tokenizer.json in the model folder (and the tokenizers package); "
+                  "give --prompt-ids", file=sys.stderr)
+            return 2
+        for text in a.prompt:
+            reqs.append(GenerationRequest(prompt_ids=tok.encode(text, add_special_tokens=True).ids,
+                                          max_tokens=a.max_tokens, temperature=a.temperature, top_p=a.top_p,
+                                          seed=a.seed, stop=a.stop or [], stop_token_ids=a.stop_token_id or []))
     if not reqs:
         print("give at least one --prompt-ids or --prompt", file=sys.stderr)
         return 2
+    # the cache is sized for the requests at hand (prompt + what each may generate, in whole pages),
+    # not for the most the model could ever hold
+    window = config_from_json(a.model).plan().max_positions
+    if a.max_context is not None:
+        window = min(window, a.max_context)
+    cache_tokens = a.cache_tokens or cache_tokens_for([len(r.prompt_ids) for r in reqs], a.max_tokens, window, a.max_batch)
+    prov = DecoderProvider.load(a.model, dtype=a.dtype, device=a.device, max_batch=a.max_batch,
+                                max_context=a.max_context, max_tokens=cache_tokens)
     for i, g in enumerate(prov.generate(reqs)):
         print(json.dumps({"request": i, "token_ids": g.token_ids, "text": g.text, "finish_reason": g.finish_reason,
                           "prompt_tokens": g.prompt_tokens, "seed": g.seed}))
@@ -69,6 +83,8 @@ def main(argv=None) -> int:
     g.add_argument("--stop-token-id", type=int, action="append")
     g.add_argument("--max-batch", type=int, default=64)
     g.add_argument("--max-context", type=int, default=None)
+    g.add_argument("--cache-tokens", type=int, default=None,
+                   help="cache size in tokens (default: what these requests need)")
     g.set_defaults(fn=cmd_generate)
     r = sub.add_parser("random-model", help="write a model folder with random weights from a config.json and a seed")
     r.add_argument("--config", required=True)

@@ -30,6 +30,36 @@ class PositionSpec:
 
 
 @dataclass(frozen=True)
+class AttentionNames:
+    """Tensor names of an attention layer, after the spec's prefix.  An architecture whose checkpoint
+    names them otherwise passes its own table; the part knows no name by itself."""
+    q: str = "q_proj"
+    k: str = "k_proj"
+    v: str = "v_proj"
+    o: str = "o_proj"
+    weight: str = ".weight"
+    bias: str = ".bias"
+
+
+@dataclass(frozen=True)
+class SwiGluNames:
+    """Tensor names of a SwiGLU MLP, after its prefix."""
+    gate: str = "gate_proj.weight"
+    up: str = "up_proj.weight"
+    down: str = "down_proj.weight"
+
+
+@dataclass(frozen=True)
+class MoeNames:
+    """Tensor names of a sparse block, after the spec's prefix; ``expert`` is a template over the expert's index."""
+    router: str = "gate.weight"
+    shared_gate: str = "shared_expert_gate.weight"
+    shared: str = "shared_expert."
+    expert: str = "experts.{e}."
+    mlp: SwiGluNames = SwiGluNames()
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Softmax attention over cached keys and values with grouped query heads."""
     hidden: int
@@ -42,6 +72,7 @@ class AttentionSpec:
     position: Optional[PositionSpec]
     prefix: str                      # tensor-name prefix, e.g. "model.layers.3.self_attn."
     kind: str = "attention"
+    names: AttentionNames = AttentionNames()
 
 
 @dataclass(frozen=True)
@@ -50,6 +81,7 @@ class DenseFfnSpec:
     intermediate: int
     prefix: str
     kind: str = "swiglu"
+    names: SwiGluNames = SwiGluNames()
 
 
 @dataclass(frozen=True)
@@ -64,6 +96,7 @@ class MoeFfnSpec:
     shared_intermediate: int
     prefix: str
     kind: str = "moe_swiglu_shared"
+    names: MoeNames = MoeNames()
 
 
 @dataclass(frozen=True)
@@ -99,3 +132,7 @@ class ModelPlan:
     # tensor names that a checkpoint may hold although nothing reads them
     tolerated_suffixes: tuple = ()
     extra: dict = field(default_factory=dict)
+    # the two ends of the model, as far as they are more than a lookup and a product:
+    embed_scale: float = 1.0                 # the table's rows are multiplied by this as they enter the residual stream
+    logit_softcap: Optional[float] = None    # logits = cap * tanh(logits / cap)
+    tied_head_name: Optional[str] = None     # with head_weight None: a checkpoint may still carry the head under this name

@@ -10,7 +10,7 @@ from dataclasses import dataclass, field
 from typing import Optional
 
 from ..errors import InvalidConfig, Unsupported
-from .plan import (AttentionSpec, BlockSpec, DenseFfnSpec, ModelPlan, MoeFfnSpec, NormSpec,
+from .plan import (AttentionNames, AttentionSpec, BlockSpec, MoeNames, SwiGluNames, DenseFfnSpec, ModelPlan, MoeFfnSpec, NormSpec,
                    PositionSpec, ScheduleEntry)
 from .registry import register_architecture
 
@@ -248,12 +248,14 @@ class Qwen2MoeConfig:
         for i in range(self.num_hidden_layers):
             p = f"model.layers.{i}."
             mixer = AttentionSpec(self.hidden_size, self.num_attention_heads, self.kv_heads, hd,
-                                  self.qkv_bias, self.output_bias, self.layer_window(i), pos, p + "self_attn.")
+                                  self.qkv_bias, self.output_bias, self.layer_window(i), pos, p + "self_attn.",
+                                  names=ATTENTION_NAMES)
             if self.layer_is_moe(i):
                 ffn = MoeFfnSpec(self.hidden_size, self.num_experts, self.num_experts_per_tok, self.norm_topk_prob,
-                                 self.moe_intermediate_size, self.shared_expert_intermediate_size, p + "mlp.")
+                                 self.moe_intermediate_size, self.shared_expert_intermediate_size, p + "mlp.",
+                                 names=MOE_NAMES)
             else:
-                ffn = DenseFfnSpec(self.hidden_size, self.intermediate_size, p + "mlp.")
+                ffn = DenseFfnSpec(self.hidden_size, self.intermediate_size, p + "mlp.", names=MLP_NAMES)
             blocks.append(BlockSpec(
                 mixer, ffn,
                 NormSpec("rmsnorm", self.hidden_size, self.rms_norm_eps, p + "input_layernorm.weight"),
@@ -267,7 +269,15 @@ class Qwen2MoeConfig:
             head_weight=None if self.tie_word_embeddings else "lm_head.weight",
             stop_token_ids=self.stop_token_ids(),
             tolerated_suffixes=(".rotary_emb.inv_freq",),   # loader.rs:253-255
+            # a tied checkpoint may still store the head; it is used if present (loader.rs:441-449)
+            tied_head_name="lm_head.weight",
         )
 
+
+# the checkpoint's tensor names below "model.layers.{i}." (loader.rs:87-91, :212-245, :512-556)
+ATTENTION_NAMES = AttentionNames(q="q_proj", k="k_proj", v="v_proj", o="o_proj", weight=".weight", bias=".bias")
+MLP_NAMES = SwiGluNames(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight")
+MOE_NAMES = MoeNames(router="gate.weight", shared_gate="shared_expert_gate.weight", shared="shared_expert.",
+                     expert="experts.{e}.", mlp=MLP_NAMES)
 
 register_architecture(ARCHITECTURE, MODEL_TYPE, Qwen2MoeConfig)

@@ -244,11 +244,22 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         if (tid == 0 && issued < n_items) issue(issued++);
     }
     if (failed) {
+        // A wait ran out: flag it, let the copies in flight land, and still take part in the row's count below
+        // with an empty partial (maximum -inf, sum 0), so that the counter returns to zero and the row's last
+        // block finishes.  The row's output is then incomplete, which the status word tells the host.
         if (tid == 0) {
             atomicOr(status, ESP_STATUS_WAIT_EXPIRED);
             for (int it = max(0, issued - RING); it < issued; it++) mbar_wait(&full_bar[it % RING], (it / RING) & 1);
         }
-        return;
+        if (tid < heads) {
+            m_s[tid] = -INFINITY;
+            l_s[tid] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < NBW; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) o[i][j] = 0.f;
+        __syncthreads();
     }
     // ---- partial results: rows g8 and g8+8, this warp's columns
 #pragma unroll
@@ -336,11 +347,13 @@ int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, flo
     rc = make_cache_map(&map_v, v, rows, HD);
     if (rc) return rc;
     const size_t dyn = (size_t)RING * PAGE_KEYS * HD * sizeof(bf16) + 1024;
-    static bool raised = false;
-    if (!raised) {
+    static bool raised[64] = {false};              // per device: the attribute belongs to the device's context
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+    if (!raised[device]) {
         cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel<HD, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
         if (e != cudaSuccess) return (int)e;
-        raised = true;
+        raised[device] = true;
     }
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + MMA_HEADS - 1) / MMA_HEADS), n_splits);

@@ -21,8 +21,11 @@
 // Sharing: all calls on a device use the same array.  It keeps whatever the last call left there.  The
 // kernel writes every partial result it later reads, so that part needs no clearing; the counters at
 // the array's end must be zero when a call starts: they are zero when the library is loaded and each
-// call puts them back to zero before it ends.  Two calls whose kernels can overlap on the GPU (different
-// streams, no ordering between them) race on the array: order them.
+// call puts them back to zero before it ends, also when one of its bounded waits runs out (such a block
+// still takes part in its row's count, with an empty partial result, and the status word says so).  Two
+// calls whose kernels can overlap on the GPU (different streams, no ordering between them) race on the
+// array: order them.  On the host the entry point keeps its per-device address table without a lock:
+// make the first call on each device from one thread.
 //
 // Arguments and result are those of esp_attn_decode without the two scratch pointers; the return value
 // is 0, a cudaError_t, or ESP_NOALLOC_TOO_LARGE.

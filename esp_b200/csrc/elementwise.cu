@@ -3,10 +3,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// x[n, :] = float(table[ids[n], :]); the residual stream is 32-bit in every mode.
+// x[n, :] = scale * float(table[ids[n], :]); the residual stream is 32-bit in every mode.  ``scale`` is 1 for
+// models that feed the table rows as they are (multiplying by 1 changes no bit).
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
-                                    int n_tokens, int width, int vocab, int* __restrict__ status) {
+                                    int n_tokens, int width, int vocab, float scale, int* __restrict__ status) {
     const int n = blockIdx.x;
     if (n >= n_tokens) return;
     int id = ids[n];
@@ -16,16 +17,18 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
     }
     const TW* row = table + (size_t)id * width;
     float* out = x + (size_t)n * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = scale * to_f32(row[i]);
 }
 
 ESP_API int esp_embed_gather(const void* table, int table_is_bf16, const int* ids, float* x, int n_tokens, int width,
-                             int vocab, int* status, cudaStream_t stream) {
+                             int vocab, float scale, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (table_is_bf16)
-        embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>((const bf16*)table, ids, x, n_tokens, width, vocab, status);
+        embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>((const bf16*)table, ids, x, n_tokens, width, vocab, scale,
+                                                                status);
     else
-        embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, x, n_tokens, width, vocab, status);
+        embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, x, n_tokens, width, vocab, scale,
+                                                                 status);
     return esp_launch_status();
 }
 
@@ -212,6 +215,22 @@ ESP_API int esp_finite_check(const float* v, long long count, int* status, cudaS
     long long blocks = (count + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     finite_check_kernel<<<(int)blocks, 256, 0, stream>>>(v, count, status);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- logit soft-cap
+// v = cap * tanh(v / cap), in place, for heads that bound their logits this way.
+__global__ void softcap_kernel(float* __restrict__ v, long long count, float cap) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+        v[i] = cap * tanhf(v[i] / cap);
+}
+
+ESP_API int esp_softcap(float* v, long long count, float cap, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    softcap_kernel<<<(int)blocks, 256, 0, stream>>>(v, count, cap);
     return esp_launch_status();
 }
 

@@ -456,3 +456,23 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
     if (which == 3) gemm_tc05_kernel<true, 256><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
     return esp_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// A probe of the bounded wait that every kernel of this library relies on: one thread waits, for at most
+// ``polls`` tries, on an mbarrier that nothing will ever complete (no copy is in flight, nobody arrives),
+// then reports ESP_STATUS_WAIT_EXPIRED and returns.  It shows that a wait that runs out ends the kernel in an
+// orderly way and leaves the device usable.  ``polls`` is clamped to 2^20.
+__global__ void wait_probe_kernel(unsigned polls, int* __restrict__ status) {
+    __shared__ __align__(8) unsigned long long bar;
+    if (threadIdx.x == 0) {
+        tc05::mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        if (!tc05::mbar_wait_limited(&bar, 0, polls)) atomicOr(status, ESP_STATUS_WAIT_EXPIRED);
+    }
+}
+
+ESP_API int esp_wait_probe(int polls, int* status, cudaStream_t stream) {
+    if (polls <= 0) return (int)cudaErrorInvalidValue;
+    wait_probe_kernel<<<1, 32, 0, stream>>>((unsigned)(polls > (1 << 20) ? (1 << 20) : polls), status);
+    return esp_launch_status();
+}

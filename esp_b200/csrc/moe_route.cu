@@ -365,7 +365,8 @@ __global__ void __launch_bounds__(256)
 route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids, float* __restrict__ topk_w,
                    float* __restrict__ gate, float* __restrict__ probs_out, int n_tokens, int n_experts, int top_k,
                    int norm_topk, int has_gate, int* __restrict__ offsets, int* __restrict__ perm_token,
-                   float* __restrict__ perm_weight, int* __restrict__ inverse, int* __restrict__ status) {
+                   float* __restrict__ perm_weight, int* __restrict__ inverse, int* __restrict__ status,
+                   unsigned long long* __restrict__ distinct) {
     extern __shared__ float sm_f[];
     float* ps_all = sm_f;                                      // [8 warps][n_experts]
     int* counts = reinterpret_cast<int*>(sm_f + 8 * n_experts); // [n_experts]
@@ -430,14 +431,16 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
     }
     __syncthreads();
     if (tid == 0) {
-        int run = 0;
+        int run = 0, used = 0;
         for (int e = 0; e < n_experts; e++) {
             cursor[e] = run;
             offsets[e] = run;
             run += counts[e];
+            used += counts[e] > 0;
         }
         cursor[n_experts] = run;
         offsets[n_experts] = run;
+        if (distinct) atomicAdd(distinct, (unsigned long long)used);     // experts that this step reads
     }
     __syncthreads();
     const int n_pairs = n_tokens * top_k;
@@ -459,7 +462,7 @@ moe_permute_wide_kernel(const int* __restrict__ topk_ids, const float* __restric
                         int* __restrict__ offsets, int* __restrict__ perm_token, float* __restrict__ perm_weight,
                         int* __restrict__ inverse, int top_k, int* __restrict__ tile_group, int* __restrict__ tile_row0,
                         int* __restrict__ tile_count, int* __restrict__ n_tiles, int tile_rows, int max_tiles,
-                        int* __restrict__ status) {
+                        int* __restrict__ status, unsigned long long* __restrict__ distinct) {
     extern __shared__ int sm[];
     int* hist = sm;                                  // [32][n_experts]: counts, later each warp's next row
     int* offs = sm + 32 * n_experts;                 // [n_experts + 1]
@@ -500,15 +503,17 @@ moe_permute_wide_kernel(const int* __restrict__ topk_ids, const float* __restric
     }
     __syncthreads();
     if (tid == 0) {                                  // exclusive scan in place: offs[e + 1] holds expert e's total until
-        int run = 0;                                 // turn e reads it; turn e + 1 overwrites it with expert e + 1's start
+        int run = 0, used = 0;                       // turn e reads it; turn e + 1 overwrites it with expert e + 1's start
         for (int e = 0; e < n_experts; e++) {
             const int c = offs[e + 1];
             offs[e] = run;
             offsets[e] = run;
             run += c;
+            used += c > 0;
         }
         offs[n_experts] = run;
         offsets[n_experts] = run;
+        if (distinct) atomicAdd(distinct, (unsigned long long)used);
     }
     __syncthreads();
     if (tile_group && tid == 0) {                    // row tiles of the grouped products: a tile never mixes two experts
@@ -557,7 +562,7 @@ moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ t
                    int* __restrict__ offsets, int* __restrict__ perm_token, float* __restrict__ perm_weight,
                    int* __restrict__ inverse, int top_k, int* __restrict__ tile_group, int* __restrict__ tile_row0,
                    int* __restrict__ tile_count, int* __restrict__ n_tiles, int tile_rows, int max_tiles,
-                   int* __restrict__ status) {
+                   int* __restrict__ status, unsigned long long* __restrict__ distinct) {
     extern __shared__ int sm[];
     int* counts = sm;                      // [n_experts]
     int* cursor = sm + n_experts;          // [n_experts + 1]
@@ -570,14 +575,16 @@ moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ t
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int run = 0;
+        int run = 0, used = 0;
         for (int e = 0; e < n_experts; e++) {
             cursor[e] = run;
             offsets[e] = run;
             run += counts[e];
+            used += counts[e] > 0;
         }
         cursor[n_experts] = run;
         offsets[n_experts] = run;
+        if (distinct) atomicAdd(distinct, (unsigned long long)used);
         // row tiles of the grouped products: a tile never mixes two experts
         if (tile_group) {
             int t = 0;
@@ -786,7 +793,8 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
 ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, const void* w_gate, int w_is_bf16,
                             float* logits, int* topk_ids, float* topk_w, float* gate, float* probs_out, int n_tokens,
                             int width, int n_experts, int top_k, int norm_topk, int* offsets, int* perm_token,
-                            float* perm_weight, int* inverse, int* status, cudaStream_t stream) {
+                            float* perm_weight, int* inverse, int* status, unsigned long long* distinct,
+                            cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts || n_tokens > 32) return (int)cudaErrorInvalidValue;
     const size_t smem_a = (size_t)width * sizeof(float);
@@ -803,17 +811,18 @@ ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, 
 #undef ESP_LOGITS
     route_small_kernel<<<1, 256, smem_b, stream>>>(logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k,
                                                    norm_topk, w_gate ? 1 : 0, offsets, perm_token, perm_weight, inverse,
-                                                   status);
+                                                   status, distinct);
     return esp_launch_status();
 }
 
+// ``distinct`` (may be null): a 64-bit counter to which the number of experts with at least one row is added.
 // tile_group / tile_row0 / tile_count / n_tiles (may be null): the list of row tiles of at most
 // ``tile_rows`` rows each (group, first row, rows), at most ``max_tiles`` of them (pass at least
 // ceil(pairs / tile_rows) + n_experts).
 ESP_API int esp_moe_permute(const int* topk_ids, const float* topk_w, int n_tokens, int top_k, int n_experts,
                             int* offsets, int* perm_token, float* perm_weight, int* inverse, int* tile_group,
                             int* tile_row0, int* tile_count, int* n_tiles, int tile_rows, int max_tiles, int* status,
-                            cudaStream_t stream) {
+                            unsigned long long* distinct, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
@@ -821,12 +830,12 @@ ESP_API int esp_moe_permute(const int* topk_ids, const float* topk_w, int n_toke
     if (n_tokens * top_k >= 2048 && smem_wide <= 48 * 1024) {
         moe_permute_wide_kernel<<<1, 1024, smem_wide, stream>>>(topk_ids, topk_w, n_tokens * top_k, n_experts, offsets,
                                                                 perm_token, perm_weight, inverse, top_k, tile_group, tile_row0,
-                                                                tile_count, n_tiles, tile_rows, max_tiles, status);
+                                                                tile_count, n_tiles, tile_rows, max_tiles, status, distinct);
         return esp_launch_status();
     }
     moe_permute_kernel<<<1, 1024, smem, stream>>>(topk_ids, topk_w, n_tokens * top_k, n_experts, offsets, perm_token,
                                                   perm_weight, inverse, top_k, tile_group, tile_row0, tile_count, n_tiles,
-                                                  tile_rows, max_tiles, status);
+                                                  tile_rows, max_tiles, status, distinct);
     return esp_launch_status();
 }
 

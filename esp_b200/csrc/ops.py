@@ -18,7 +18,8 @@ from .build import load_library
 P = c_void_p
 
 _SIGNATURES = {
-    "esp_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, P, P],
+    "esp_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, c_float, P, P],
+    "esp_softcap": [P, c_longlong, c_float, P],
     "esp_feed_tokens": [P, P, P, c_int, P],
     "esp_add_rmsnorm": [P, P, P, P, P, c_int, P, c_int, c_int, c_float, c_int, P],
     "esp_swiglu": [P, P, c_int, c_longlong, c_int, P],
@@ -29,11 +30,12 @@ _SIGNATURES = {
                          c_int, c_int, P, P],
     "esp_attn_simt": [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
-    "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P],
+    "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
-    "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P],
+    "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P],
     "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                       P, P],
+    "esp_wait_probe": [c_int, P, P],
     "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
     "esp_moe_combine_add_rmsnorm": [P, P, P, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, c_int, P],
@@ -110,12 +112,21 @@ def _is_bf16(t) -> int:
 
 # ---------------------------------------------------------------------------
 
-def embed_gather(table, ids, x, status):
-    """x[n] = float(table[ids[n]]); ids int32 [N], x float32 [N, H]."""
+def embed_gather(table, ids, x, status, scale: float = 1.0):
+    """x[n] = scale * float(table[ids[n]]); ids int32 [N], x float32 [N, H]."""
     n, width = x.shape
     _check(_fn("core", "esp_embed_gather")(
         _ptr(table, FLOATS, "embedding table"), _is_bf16(table), _ptr(ids, torch.int32, "ids"),
-        _ptr(x, torch.float32, "x"), n, width, table.shape[0], _ptr(status, torch.int32), _stream()), "embed_gather")
+        _ptr(x, torch.float32, "x"), n, width, table.shape[0], float(scale), _ptr(status, torch.int32), _stream()),
+        "embed_gather")
+
+
+def softcap(values, cap: float):
+    """values = cap * tanh(values / cap), in place (float32)."""
+    if not cap > 0:
+        raise Backend(f"softcap: the cap must be positive, got {cap}")
+    _check(_fn("core", "esp_softcap")(_ptr(values, torch.float32, "values"), values.numel(), float(cap), _stream()),
+           "softcap")
 
 
 def feed_tokens(ids, picks, src):
@@ -238,9 +249,10 @@ def route_small_fits(width: int, n_experts: int) -> bool:
 
 
 def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm_topk, offsets, perm_token,
-                perm_weight, inverse, status, probs_out=None):
+                perm_weight, inverse, status, probs_out=None, distinct=None):
     """Router and permutation for at most ROUTE_SMALL_TOKENS tokens: logits over many blocks, then one
-    block for softmax, top-k and the permutation.  ``logits``: float32 scratch [N, E + 1]."""
+    block for softmax, top-k and the permutation.  ``logits``: float32 scratch [N, E + 1].  ``distinct``:
+    an int64 tensor of one element to which the number of experts with at least one token is added."""
     n, width = h.shape
     n_experts = w_router.shape[0]
     if n > ROUTE_SMALL_TOKENS or top_k > 32 or not route_small_fits(width, n_experts):
@@ -250,11 +262,12 @@ def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm
         _ptr(logits, torch.float32), _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32),
         _ptr(gate, torch.float32), _ptr(probs_out, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
         _ptr(offsets, torch.int32), _ptr(perm_token, torch.int32), _ptr(perm_weight, torch.float32),
-        _ptr(inverse, torch.int32), _ptr(status, torch.int32), _stream()), "route_small")
+        _ptr(inverse, torch.int32), _ptr(status, torch.int32), _ptr(distinct, torch.int64), _stream()), "route_small")
 
 
-def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, inverse, status, tiles=None):
-    """``tiles``: optional (tile_group, tile_row0, tile_count, n_tiles) int32 tensors that receive the
+def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, inverse, status, tiles=None,
+                distinct=None):
+    """``distinct``: as for route_small.  ``tiles``: optional (tile_group, tile_row0, tile_count, n_tiles) int32 tensors that receive the
     list of row tiles (of at most TC05_TILE_ROWS rows) for the grouped tensor-core products."""
     n, top_k = topk_ids.shape
     if (2 * n_experts + 1) * 4 > 48 * 1024:
@@ -264,8 +277,8 @@ def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, i
         _ptr(perm_token, torch.int32), _ptr(perm_weight, torch.float32), _ptr(inverse, torch.int32),
         _ptr(tiles[0], torch.int32) if tiles else None, _ptr(tiles[1], torch.int32) if tiles else None,
         _ptr(tiles[2], torch.int32) if tiles else None, _ptr(tiles[3], torch.int32) if tiles else None,
-        TC05_TILE_ROWS if tiles else 0, tiles[0].shape[0] if tiles else 0, _ptr(status, torch.int32), _stream()),
-        "moe_permute")
+        TC05_TILE_ROWS if tiles else 0, tiles[0].shape[0] if tiles else 0, _ptr(status, torch.int32),
+        _ptr(distinct, torch.int64), _stream()), "moe_permute")
 
 
 def moe_combine(expert_out, topk_ids, inverse, gate, shared, y):
@@ -450,3 +463,9 @@ def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=No
         tile_rows if grouped else 0, m, n, k,
         1 if swiglu else 0, _ptr(status, torch.int32), _stream())
     _check(code, "gemm_tc05")
+
+
+def wait_probe(polls: int, status):
+    """Runs the library's bounded wait on a barrier that nothing completes: after ``polls`` tries the
+    kernel sets the wait-expired bit of ``status`` and returns."""
+    _check(_fn("tc05", "esp_wait_probe")(int(polls), _ptr(status, torch.int32, "status"), _stream()), "wait_probe")

@@ -16,6 +16,20 @@ __device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
 __device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// Bounded wait for the phase with the given parity: at most ``limit`` polls; false if they ran out.
+__device__ __forceinline__ bool mbar_wait_limited(void* bar, unsigned parity, unsigned limit) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned i = 0; i < limit; i++) {
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
 // Bounded wait for the phase with the given parity; false if the limit ran out.
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
     const unsigned addr = smem_u32(bar);

@@ -8,6 +8,7 @@ token rows are packed back to back and every kernel works on rows.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Optional
@@ -20,8 +21,9 @@ from ..cache.storage import STATE_RNG, STATE_WORDS
 from ..csrc import ops
 from ..sampling import as_signed64
 from ..config import config_from_json
-from ..errors import Backend, InvalidRequest
+from ..errors import Backend, InvalidRequest, NonFiniteScores
 from ..parts import Runtime, StepContext
+from ..parts.base import StepHost
 from ..weights import FolderSource, InitSpec, RandomSource, load_into
 from .model import DecoderModel
 
@@ -61,8 +63,11 @@ class StepEntry:
 
 class Engine:
     def __init__(self, config, source_factory, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
-                 max_slots: Optional[int] = None):
-        """``source_factory(specs) -> source``: gives the loader its tensors."""
+                 max_slots: Optional[int] = None, shrink_to_fit: bool = False):
+        """``source_factory(specs) -> source``: gives the loader its tensors.
+        ``max_tokens`` sizes the cache; it is refused if weights and cache do not
+        fit the device's free memory, or, with ``shrink_to_fit``, made as small
+        as fits (``self.max_tokens`` tells what it became)."""
         self.config = config
         self.plan = config.plan()
         self.dtype = parse_dtype(dtype)
@@ -74,13 +79,32 @@ class Engine:
         with torch.cuda.device(self.rt.device):
             self.model = DecoderModel(self.plan, self.rt)
             specs = [s for part in self.model.all_parts() for s in part.param_specs()]
-            load_into(self.model, source_factory(specs), self.rt)
+            source = source_factory(specs)
+            self.memory_plan = self._check_memory(specs, source, max_tokens, shrink_to_fit)
+            max_tokens = self.memory_plan["cache_tokens"]
+            self.max_tokens = max_tokens
+            load_into(self.model, source, self.rt)
             n_pages = (max_tokens + 63) // 64
             if max_slots is None:
                 max_slots = max(1, min(n_pages, 4096))
             self.max_slots = max_slots
             self.cache = Cache(self.model.cache_requests(), max_tokens, max_slots, self.plan.max_positions,
                                self.dtype, self.rt.device)
+        parts = self.model.all_parts()
+        # a decode step is replayed from a captured graph only if every part says that it may be
+        self._parts_graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
+        self._array_makers, seen = [], set()
+        for p in parts:
+            key = p.step_arrays_key()
+            if key is not None and key not in seen:
+                seen.add(key)
+                self._array_makers.append(p)
+        self._host_counters = {"steps": 0, "tokens": 0, "kv_bytes_read": 0}
+        # testing aid: the index of a wanted logits row that is overwritten with NaN before the finite
+        # check, to exercise what follows a failed check without a faulty model; ``poison_steps`` says for
+        # how many more forward passes (None: until the row is set back to None)
+        self.poison_logits_row: Optional[int] = None
+        self.poison_steps: Optional[int] = None
         self._pinned = None
         self._pinned_event = None
         self._copy_stream = None
@@ -93,6 +117,40 @@ class Engine:
         self._graphs: dict = {}
         self._graph_seen: dict = {}
         self.graph_replays = 0
+
+    def _check_memory(self, specs, source, max_tokens: int, shrink: bool) -> dict:
+        """Bytes of weights and cache that this engine is about to allocate against
+        the device's free memory; refuses with the numbers instead of dying inside
+        an allocation.  ``ESP_B200_MEMORY_HEADROOM`` (bytes, default 2 GiB) is kept
+        for scratch buffers and the CUDA context."""
+        el = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2}
+        have = set(source.names())
+        weights = 0
+        for sp in specs:
+            if sp.name not in have:
+                continue
+            count = int(np.prod(sp.shape)) if sp.shape else 1
+            kept = self.rt.matrix_dtype([source.dtype(sp.name)]) if sp.role == "matrix" else torch.float32
+            weights += count * el.get(kept, 4)
+        tokens = (max_tokens + 63) // 64 * 64
+        per_token = 0
+        for layout, _state, cache_of in self.model.cache_requests():
+            if layout is not None and cache_of is None:
+                per_token += 2 * layout.num_kv_heads * layout.head_dim * el[self.dtype]
+        cache = per_token * tokens
+        free, total = torch.cuda.mem_get_info(self.rt.device)
+        headroom = int(os.environ.get("ESP_B200_MEMORY_HEADROOM", 2 << 30))
+        if shrink and weights + cache + headroom > free and per_token > 0:
+            tokens = max(0, (free - weights - headroom) // per_token) // 64 * 64
+            cache = per_token * tokens
+        plan = {"weights_bytes": weights, "cache_bytes": cache, "cache_tokens": tokens, "free_bytes": free,
+                "total_bytes": total}
+        if weights + cache + headroom > free or tokens <= 0:
+            gb = lambda v: f"{v / 1e9:.1f} GB"
+            raise Backend(f"the model does not fit the device: weights {gb(weights)} + a cache of {tokens} tokens "
+                          f"{gb(cache)} + {gb(headroom)} of headroom exceed the {gb(free)} that are free "
+                          f"(of {gb(total)}); ask for a smaller cache (max_tokens) or fewer sequences")
+        return plan
 
     # -- construction ---------------------------------------------------------
     @classmethod
@@ -239,50 +297,90 @@ class Engine:
         with torch.cuda.device(self.rt.device):
             slots, news, pasts, starts, want_rows, growth = self.plan_step(entries)
             book = self.cache.book
-            book.reserve(growth)
-            b, n = len(entries), starts[-1]
-            decode = n == b
-            tok_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-            tok_seq = np.repeat(np.arange(b, dtype=np.int32), news)
-            tok_pos = np.concatenate([np.arange(p, p + t, dtype=np.int32) for p, t in zip(pasts, news)])
-            stride = self.cache.max_table_stride(slots, growth)
-            graphable = decode and self.use_graphs and not self.rt.record_routing and aux is None
-            if graphable:
-                stride = (stride + GRAPH_STRIDE_PAGES - 1) // GRAPH_STRIDE_PAGES * GRAPH_STRIDE_PAGES
-            tables = [np.asarray(g.table_rows(slots, stride), dtype=np.int32).reshape(b, stride)
-                      for g in book.groups]
-            tiles = [(i, first) for i, t in enumerate(news) for first in range(0, t, 64)]
-            # wider tiles for the tensor-memory attention, those that see the most keys first
-            wide_rows = ops.ATTN_TC05_TILE_ROWS
-            wide = sorted(((i, first) for i, t in enumerate(news) for first in range(0, t, wide_rows)),
-                          key=lambda sf: -(pasts[sf[0]] + min(sf[1] + wide_rows, news[sf[0]])))
-            arrays = [tok_ids, tok_seq, tok_pos, np.asarray(slots, dtype=np.int32),
-                      np.asarray(starts, dtype=np.int32), np.asarray(pasts, dtype=np.int32),
-                      np.asarray(want_rows, dtype=np.int32), np.asarray([t[0] for t in tiles], dtype=np.int32),
-                      np.asarray([t[1] for t in tiles], dtype=np.int32), np.asarray([t[0] for t in wide], dtype=np.int32),
-                      np.asarray([t[1] for t in wide], dtype=np.int32), *tables, *extra_arrays]
-            dev = self._stage(arrays)
-            nt = 11 + len(tables)
-            if feed is not None:                      # token ids from the earlier step's choices, on the device
-                ops.feed_tokens(dev[0], feed, dev[-1])
-            ctx = StepContext(
-                n_tokens=n, n_seqs=b, max_new=max(news), max_len=max(p + t for p, t in zip(pasts, news)),
-                tok_ids=dev[0], tok_seq=dev[1], tok_pos=dev[2], seq_slot=dev[3], seq_start=dev[4], seq_past=dev[5],
-                want_rows=dev[6], q_tile_seq=dev[7], q_tile_first=dev[8], q_wide_seq=dev[9], q_wide_first=dev[10],
-                block_tables=list(dev[11:nt]),
-                host={"slots": slots, "news": news, "pasts": pasts, "starts": starts, "want_rows": want_rows},
-                aux=aux if aux is not None else {})
-            extra = dev[nt:]
-            if graphable:
-                result = self._run_decode_graph(ctx, extra, pick, (b, stride, pick, tuple(want_rows)))
-            else:
-                result = self._forward(ctx, extra, pick)
+            receipts = book.reserve(growth)
+            try:
+                result = self._run_reserved(entries, aux, extra_arrays, pick, feed, slots, news, pasts, starts, want_rows,
+                                            growth)
+            except BaseException:
+                book.cancel(receipts)              # the step did not run: its pages go back, lengths stay
+                raise
             book.commit(growth)
             self.steps_run += 1
             return result
 
+    def _run_reserved(self, entries, aux, extra_arrays, pick, feed, slots, news, pasts, starts, want_rows, growth):
+        book = self.cache.book
+        b, n = len(entries), starts[-1]
+        decode = n == b
+        tok_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        tok_seq = np.repeat(np.arange(b, dtype=np.int32), news)
+        tok_pos = np.concatenate([np.arange(p, p + t, dtype=np.int32) for p, t in zip(pasts, news)])
+        stride = self.cache.max_table_stride(slots, growth)
+        graphable = (decode and self.use_graphs and self._parts_graph_safe and not self.rt.record_routing
+                     and aux is None and self.poison_logits_row is None)
+        if graphable:
+            stride = (stride + GRAPH_STRIDE_PAGES - 1) // GRAPH_STRIDE_PAGES * GRAPH_STRIDE_PAGES
+        tables = [np.asarray(g.table_rows(slots, stride), dtype=np.int32).reshape(b, stride)
+                  for g in book.groups]
+        # the lists that the model's parts want on the device for this step (the engine knows none of them)
+        host = StepHost(tuple(slots), tuple(news), tuple(pasts), tuple(starts))
+        named = {}
+        for part in self._array_makers:
+            for name, arr in part.step_arrays(host).items():
+                named.setdefault(name, np.ascontiguousarray(arr, dtype=np.int32))
+        names = sorted(named)
+        fixed = [tok_ids, tok_seq, tok_pos, np.asarray(slots, dtype=np.int32), np.asarray(starts, dtype=np.int32),
+                 np.asarray(pasts, dtype=np.int32), np.asarray(want_rows, dtype=np.int32)]
+        dev = self._stage([*fixed, *tables, *[named[k] for k in names], *extra_arrays])
+        nf, nt = len(fixed), len(fixed) + len(tables)
+        if feed is not None:                      # token ids from the earlier step's choices, on the device
+            ops.feed_tokens(dev[0], feed, dev[-1])
+        ctx = StepContext(
+            n_tokens=n, n_seqs=b, max_new=max(news), max_len=max(p + t for p, t in zip(pasts, news)),
+            tok_ids=dev[0], tok_seq=dev[1], tok_pos=dev[2], seq_slot=dev[3], seq_start=dev[4], seq_past=dev[5],
+            want_rows=dev[6], block_tables=list(dev[nf:nt]),
+            host={"slots": slots, "news": news, "pasts": pasts, "starts": starts, "want_rows": want_rows},
+            aux=aux if aux is not None else {}, arrays=dict(zip(names, dev[nt:nt + len(names)])))
+        extra = dev[nt + len(names):]
+        self._count_step(news, pasts)
+        if graphable:
+            key = (b, stride, pick, tuple(want_rows), tuple((k, named[k].size) for k in names))
+            return self._run_decode_graph(ctx, extra, pick, key)
+        return self._forward(ctx, extra, pick)
+
+    def _count_step(self, news, pasts) -> None:
+        """Host-side counters of the work a step asks for (what the kernels must read of the cache follows
+        from lengths and windows alone)."""
+        c = self._host_counters
+        c["steps"] += 1
+        c["tokens"] += sum(news)
+        el = torch.empty((), dtype=self.dtype).element_size()
+        for layout, members in zip(self.cache.layouts, self.cache.members):
+            per_key = 2 * len(members) * layout.num_kv_heads * layout.head_dim * el
+            seen = 0
+            for p, t in zip(pasts, news):
+                # the keys the sequence's last new token sees: every kernel streams a sequence's visible keys once
+                last = p + t
+                seen += last if layout.window is None else min(last, layout.window + t - 1)
+            c["kv_bytes_read"] += seen * per_key
+
+    def counters(self) -> dict:
+        """Work done since the engine was made: ``steps``, ``tokens``, ``kv_bytes_read`` (bytes of keys and
+        values that the steps' attention had to read), and what the parts counted on the device
+        (``expert_reads``: experts with at least one token, summed over sparse layers and steps).  Reading
+        waits for the device."""
+        out = dict(self._host_counters)
+        out.update(self.rt.read_counters())
+        return out
+
     def _forward(self, ctx, extra, pick: bool):
         logits = self.model.forward(ctx, self.cache)
+        if self.poison_logits_row is not None and logits.shape[0] > self.poison_logits_row:
+            logits[self.poison_logits_row].fill_(float("nan"))
+            if self.poison_steps is not None:
+                self.poison_steps -= 1
+                if self.poison_steps <= 0:
+                    self.poison_logits_row = self.poison_steps = None
         if not pick:
             return logits, None
         b = ctx.n_seqs
@@ -349,4 +447,12 @@ class Engine:
                      16: "a kernel's shared memory was not aligned as its layout needs"}
             what = ", ".join(v for k, v in names.items() if code & k)
             self.rt.status.zero_()
+            if code == 2:
+                raise NonFiniteScores(f"the device reported: {what}")
             raise Backend(f"the device reported: {what}")
+
+    def settle(self) -> None:
+        """Waits for everything launched so far and clears the status word: what a
+        caller does before it runs a failed step's work again."""
+        torch.cuda.synchronize(self.rt.device)
+        self.rt.status.zero_()

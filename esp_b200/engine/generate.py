@@ -21,7 +21,8 @@ from dataclasses import dataclass, field
 from typing import Callable, Optional
 
 from ..cache.book import PAGE
-from ..errors import CacheFull, InvalidRequest, PromptTooLong
+from ..errors import Backend, CacheFull, InvalidRequest, NonFiniteScores, PromptTooLong
+from ..sampling.sampler import skip_draws
 from ..sampling import SamplingParams
 
 
@@ -40,6 +41,17 @@ class SequenceResult:
     finish_reason: str            # "stop" (stop token), "length" (budget) or "cancelled" (callback)
     prompt_tokens: int
     seed: Optional[int] = None    # the seed the stream was started from (sampled requests)
+
+
+@dataclass
+class ScoreHealth:
+    """What the loop saw of the logits' health, as the reference counts it
+    (crates/esp/src/infer/decoder/provider.rs:34-60).  The device checks a step's
+    rows together, so ``invalid_steps`` counts steps, not rows."""
+    checked_rows: int = 0
+    invalid_steps: int = 0
+    prefix_recomputations: int = 0
+    failed_recoveries: int = 0
 
 
 def budget(prompt_len: int, max_tokens: int, window: int) -> int:
@@ -88,16 +100,52 @@ class GenerationLoop:
     device with each slot's own sampling options; this class only decides what
     runs next and what is kept."""
 
-    def __init__(self, backend, window: int, max_batch: int, max_tokens: int, default_stop_ids=()):
+    def __init__(self, backend, window: int, max_batch: int, max_tokens: int, default_stop_ids=(),
+                 health: Optional[ScoreHealth] = None):
         self.backend = backend
         self.window = window
         self.max_batch = max_batch
         self.max_tokens = max_tokens
         self.default_stop_ids = tuple(default_stop_ids)
+        self.health = health if health is not None else ScoreHealth()
+        self._recovery_used = False
+
+    # A corrupt row of scores must never become a token.  When the backend reports non-finite
+    # scores (NonFiniteScores), the tokens of that step are thrown away and the committed prefix of
+    # every live sequence (prompt + tokens kept so far) is run again from fresh slots, once per
+    # ``run`` call; if scores are bad again, or a second time later in the call, the call fails with
+    # Backend (crates/esp/src/infer/decoder/provider.rs:219-240, :763-803).  Each sequence's sampling
+    # stream restarts where it stood before the failed step, so draws are unchanged.
+    def _recover(self, live, slots, seeds, outs, requests, launch):
+        """Closes the live sequences' slots, opens fresh ones and returns
+        ``launch(slots, prefixes)``: the re-run of the committed prefixes."""
+        self.health.invalid_steps += 1
+        if self._recovery_used:
+            self.health.failed_recoveries += 1
+            raise Backend("non-finite model scores after numerical recovery was already used")
+        self._recovery_used = True
+        self.health.prefix_recomputations += 1
+        if hasattr(self.backend, "settle"):
+            self.backend.settle()
+        for i in live:
+            self.backend.close(slots.pop(i))
+        for i in live:
+            seed = seeds[i]
+            if seed is not None:
+                seed = skip_draws(seed, len(outs[i]))        # one draw per kept token went before
+            slots[i] = self.backend.open(requests[i].sampling, seed)
+        prefixes = [list(requests[i].prompt_ids) + list(outs[i]) for i in live]
+        try:
+            return launch([slots[i] for i in live], prefixes)
+        except NonFiniteScores:
+            self.health.invalid_steps += 1
+            self.health.failed_recoveries += 1
+            raise Backend("recomputed model scores are non-finite") from None
 
     def run(self, requests: list, on_token: Optional[Callable] = None) -> list:
         """``on_token(request_index, token) -> bool``: a true return value
         stops that sequence after the token is kept."""
+        self._recovery_used = False
         budgets = []
         for r in requests:
             r.sampling.validate()
@@ -120,7 +168,11 @@ class GenerationLoop:
                 slots[i] = self.backend.open(requests[i].sampling, seed)
                 outs[i] = []
                 live.append(i)
-            tokens = self.backend.prefill([slots[i] for i in live], [list(requests[i].prompt_ids) for i in live])
+            try:
+                tokens = self.backend.prefill([slots[i] for i in live], [list(requests[i].prompt_ids) for i in live])
+            except NonFiniteScores:
+                tokens = self._recover(live, slots, seeds, outs, requests, self.backend.prefill)
+            self.health.checked_rows += len(live)
             while live:
                 nxt, feed = [], []
                 for i, tok in zip(live, tokens):
@@ -143,7 +195,12 @@ class GenerationLoop:
                         self.backend.close(slots.pop(i))
                 live = nxt
                 if live:
-                    tokens = self.backend.decode([slots[i] for i in live], feed)
+                    try:
+                        tokens = self.backend.decode([slots[i] for i in live], feed)
+                    except NonFiniteScores:
+                        # the fed tokens were kept already: they are part of the prefix that runs again
+                        tokens = self._recover(live, slots, seeds, outs, requests, self.backend.prefill)
+                    self.health.checked_rows += len(live)
         finally:
             for s in slots.values():      # only reached with slots left over when something raised
                 self.backend.close(s)
@@ -185,7 +242,20 @@ class GenerationLoop:
                         nxt = self.backend.decode_async([slots[i] for i in ahead], handle, [order.index(i) for i in ahead])
                     except CacheFull:
                         nxt = None                       # a page for a row that may not be needed: decide after the tokens
-                tokens = handle.result()
+                try:
+                    tokens = handle.result()
+                except NonFiniteScores:
+                    # the step launched ahead took its tokens from the bad step: it is dropped with it
+                    order = [i for i in order if i in slots]
+                    handle = self._recover(order, slots, seeds, outs, requests, self.backend.prefill_async)
+                    try:
+                        tokens = handle.result()
+                    except NonFiniteScores:
+                        self.health.invalid_steps += 1
+                        self.health.failed_recoveries += 1
+                        raise Backend("recomputed model scores are non-finite") from None
+                    nxt = None
+                self.health.checked_rows += len(order)
                 for i, tok in zip(order, tokens):
                     if i not in slots:
                         continue                         # ended a step ago: this row was computed for nothing

@@ -6,10 +6,17 @@ import torch
 
 from ..csrc import ops
 from ..parts import ParamSpec, Part, build, walk
+from ..parts.base import plain_delta
 from ..parts.linear import linear
 
 
 class DecoderModel(Part):
+    """Embedding (rows times ``plan.embed_scale``), the blocks in the order of
+    the schedule, the final norm and the head on the wanted rows (with
+    ``plan.logit_softcap`` if the plan has one)."""
+
+    graph_safe = True
+
     def __init__(self, plan, rt):
         self.plan = plan
         self.rt = rt
@@ -30,18 +37,17 @@ class DecoderModel(Part):
         specs = [ParamSpec(p.embed_weight, (p.vocab, p.hidden), "matrix")]
         if p.head_weight is not None:
             specs.append(ParamSpec(p.head_weight, (p.vocab, p.hidden), "matrix"))
-        else:
+        elif p.tied_head_name is not None:
             # a tied model may still carry an explicit head; it is used if present
-            # (crates/esp/src/infer/decoder/loader.rs:441-449)
-            specs.append(ParamSpec("lm_head.weight", (p.vocab, p.hidden), "matrix", optional=True))
+            specs.append(ParamSpec(p.tied_head_name, (p.vocab, p.hidden), "matrix", optional=True))
         return specs
 
     def allocate(self, stored, rt):
         p = self.plan
         self.embed = torch.empty((p.vocab, p.hidden), dtype=rt.matrix_dtype([stored[p.embed_weight]]), device=rt.device)
         views = {p.embed_weight: self.embed}
-        head_name = p.head_weight or "lm_head.weight"
-        if head_name in stored:
+        head_name = p.head_weight or p.tied_head_name
+        if head_name is not None and head_name in stored:
             self.head = torch.empty((p.vocab, p.hidden), dtype=rt.matrix_dtype([stored[head_name]]), device=rt.device)
             views[head_name] = self.head
         else:
@@ -67,7 +73,7 @@ class DecoderModel(Part):
         rt, p = self.rt, self.plan
         n = ctx.n_tokens
         x = rt.ws.get("residual", (n, p.hidden), torch.float32)
-        ops.embed_gather(self.embed, ctx.tok_ids, x, rt.status)
+        ops.embed_gather(self.embed, ctx.tok_ids, x, rt.status, scale=p.embed_scale)
         pending = None
         for idx, entry in enumerate(p.schedule):
             pending = self.blocks[entry.layer].forward(x, pending, ctx, cache.layers[idx])
@@ -76,6 +82,8 @@ class DecoderModel(Part):
         if r == 0:
             return logits
         h = rt.ws.get("head_in", (r, p.hidden), rt.dtype)
-        self.final_norm.forward(x, pending, h, rows=ctx.want_rows, write_x=False)
+        self.final_norm.forward(x, plain_delta(self.final_norm, pending), h, rows=ctx.want_rows, write_x=False)
         linear(rt, h, self.head, logits)
+        if p.logit_softcap is not None:
+            ops.softcap(logits, p.logit_softcap)
         return logits

@@ -40,3 +40,7 @@ class CacheFull(InferError):
 
 class Backend(InferError):
     """The device or the compiled kernels failed or are missing."""
+
+
+class NonFiniteScores(Backend):
+    """A step's logits held a NaN or an infinity: no token may be decided from them."""

@@ -1,9 +1,11 @@
 """Softmax attention over the paged cache with grouped query heads."""
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache import KvLayout
+from ..cache.book import PAGE
 from ..csrc import ops
 from ..errors import Unsupported
 from .base import ParamSpec, Part, build, register
@@ -19,6 +21,8 @@ class Attention(Part):
     causal (optionally windowed) softmax attention, output projection
     (crates/esp/src/infer/decoder/attention.rs:292-404).  Query head i reads
     key/value head i // (num_heads / num_kv_heads)."""
+
+    graph_safe = True
 
     def __init__(self, spec, rt):
         self.spec = spec
@@ -43,38 +47,73 @@ class Attention(Part):
         return [self.position]
 
     # -- parameters ----------------------------------------------------------
+    def _name(self, which: str, bias: bool = False) -> str:
+        n = self.spec.names
+        return self.spec.prefix + getattr(n, which) + (n.bias if bias else n.weight)
+
     def param_specs(self):
-        s, p = self.spec, self.spec.prefix
-        specs = [ParamSpec(p + "q_proj.weight", (self.q_width, s.hidden), "matrix"),
-                 ParamSpec(p + "k_proj.weight", (self.kv_width, s.hidden), "matrix"),
-                 ParamSpec(p + "v_proj.weight", (self.kv_width, s.hidden), "matrix"),
-                 ParamSpec(p + "o_proj.weight", (s.hidden, self.q_width), "matrix")]
+        s = self.spec
+        specs = [ParamSpec(self._name("q"), (self.q_width, s.hidden), "matrix"),
+                 ParamSpec(self._name("k"), (self.kv_width, s.hidden), "matrix"),
+                 ParamSpec(self._name("v"), (self.kv_width, s.hidden), "matrix"),
+                 ParamSpec(self._name("o"), (s.hidden, self.q_width), "matrix")]
         if s.qkv_bias:
-            specs += [ParamSpec(p + "q_proj.bias", (self.q_width,), "bias"),
-                      ParamSpec(p + "k_proj.bias", (self.kv_width,), "bias"),
-                      ParamSpec(p + "v_proj.bias", (self.kv_width,), "bias")]
+            specs += [ParamSpec(self._name("q", True), (self.q_width,), "bias"),
+                      ParamSpec(self._name("k", True), (self.kv_width,), "bias"),
+                      ParamSpec(self._name("v", True), (self.kv_width,), "bias")]
         if s.out_bias:
-            specs.append(ParamSpec(p + "o_proj.bias", (s.hidden,), "bias"))
+            specs.append(ParamSpec(self._name("o", True), (s.hidden,), "bias"))
         return specs
 
     def allocate(self, stored, rt):
-        s, p = self.spec, self.spec.prefix
-        names = [p + "q_proj.weight", p + "k_proj.weight", p + "v_proj.weight"]
+        s = self.spec
+        names = [self._name("q"), self._name("k"), self._name("v")]
         dt = rt.matrix_dtype([stored[n] for n in names])
         self.w_qkv = torch.empty((self.qkv_width, s.hidden), dtype=dt, device=rt.device)
-        self.w_o = torch.empty((s.hidden, self.q_width), dtype=rt.matrix_dtype([stored[p + "o_proj.weight"]]),
+        self.w_o = torch.empty((s.hidden, self.q_width), dtype=rt.matrix_dtype([stored[self._name("o")]]),
                                device=rt.device)
         a, b = self.q_width, self.q_width + self.kv_width
         views = {names[0]: self.w_qkv[:a], names[1]: self.w_qkv[a:b], names[2]: self.w_qkv[b:],
-                 p + "o_proj.weight": self.w_o}
+                 self._name("o"): self.w_o}
         if s.qkv_bias:
             self.b_qkv = torch.empty(self.qkv_width, dtype=torch.float32, device=rt.device)
-            views.update({p + "q_proj.bias": self.b_qkv[:a], p + "k_proj.bias": self.b_qkv[a:b],
-                          p + "v_proj.bias": self.b_qkv[b:]})
+            views.update({self._name("q", True): self.b_qkv[:a], self._name("k", True): self.b_qkv[a:b],
+                          self._name("v", True): self.b_qkv[b:]})
         if s.out_bias:
             self.b_o = torch.empty(s.hidden, dtype=torch.float32, device=rt.device)
-            views[p + "o_proj.bias"] = self.b_o
+            views[self._name("o", True)] = self.b_o
         return views
+
+    # -- which kernel a step of n token rows gets, and the index lists it needs ----------
+    def kernel_for(self, n: int, page: int = PAGE) -> str:
+        s, rt = self.spec, self.rt
+        if rt.dtype == torch.bfloat16:
+            if s.head_dim in (64, 128, 192, 256) and n <= DECODE_ROWS and page == PAGE:
+                return "split"         # few rows: split the keys over blocks so that the cache streams at full width
+            if ops.attn_prefill_tc05_fits(s.head_dim, page):
+                return "tc05"          # many rows, head size 64 or 128: scores and weighted values in tensor memory
+            if s.head_dim <= 128 and page == 64:
+                return "flash"
+        return "plain"
+
+    def step_arrays_key(self):
+        return ("attention", self.rt.dtype, self.spec.head_dim)
+
+    def step_arrays(self, step):
+        """Tiles of new tokens for the two prefill kernels: (sequence, first new token) per tile; for the
+        tensor-memory kernel the tiles that see the most keys come first (its blocks take them in order)."""
+        kind = self.kernel_for(step.n_tokens)
+        if kind == "tc05":
+            rows = ops.ATTN_TC05_TILE_ROWS
+            tiles = sorted(((i, f) for i, t in enumerate(step.news) for f in range(0, t, rows)),
+                           key=lambda sf: -(step.pasts[sf[0]] + min(sf[1] + rows, step.news[sf[0]])))
+        elif kind == "flash":
+            rows = 64
+            tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, rows)]
+        else:
+            return {}
+        return {f"attention.tiles{rows}.seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
+                f"attention.tiles{rows}.first": np.asarray([t[1] for t in tiles], dtype=np.int32)}
 
     # -- what it keeps per sequence ------------------------------------------------
     def kv_layout(self):
@@ -104,8 +143,13 @@ class Attention(Part):
         s, rt = self.spec, self.rt
         table = ctx.block_tables[layer.group]
         n = q.shape[0]
-        if rt.dtype == torch.bfloat16 and s.head_dim in (64, 128, 192, 256) and n <= DECODE_ROWS:
-            # few rows: split the keys over blocks so that the cache streams at full width
+        kind = self.kernel_for(n, layer.page)
+        if kind in ("tc05", "flash"):
+            rows = ops.ATTN_TC05_TILE_ROWS if kind == "tc05" else 64
+            tile_seq, tile_first = ctx.arrays.get(f"attention.tiles{rows}.seq"), ctx.arrays.get(f"attention.tiles{rows}.first")
+            if tile_seq is None:
+                kind = "plain"         # a step made without this part's lists (a caller that built its own context)
+        if kind == "split":
             positions = table.shape[1] * layer.page
             group = s.num_heads // s.num_kv_heads
             kv_blocks = s.num_kv_heads * ((group + 15) // 16)
@@ -117,18 +161,15 @@ class Attention(Part):
                 rt.attn_counters = torch.zeros(ops.ATTN_DECODE_COUNTERS, dtype=torch.int32, device=rt.device)
             ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, rt.attn_counters, ctx.tok_seq, ctx.tok_pos, table, layer.page,
                             s.num_heads, s.num_kv_heads, s.head_dim, s.window, split, n_splits, rt.status)
-            return
-        if rt.dtype == torch.bfloat16 and ops.attn_prefill_tc05_fits(s.head_dim, layer.page) and ctx.q_wide_seq is not None:
-            # many rows, head size 64 or 128: scores and weighted values in tensor memory (tcgen05)
-            ops.attn_prefill_tc05(q, layer.k, layer.v, o, ctx.q_wide_seq, ctx.q_wide_first, ctx.seq_start, ctx.seq_past,
+        elif kind == "tc05":
+            ops.attn_prefill_tc05(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past,
                                   table, layer.page, s.num_heads, s.num_kv_heads, s.head_dim, s.window, rt.status)
-            return
-        if rt.dtype == torch.bfloat16 and s.head_dim <= 128 and layer.page == 64:
-            ops.attn_prefill(q, layer.k, layer.v, o, ctx.q_tile_seq, ctx.q_tile_first, ctx.seq_start, ctx.seq_past,
+        elif kind == "flash":
+            ops.attn_prefill(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past,
                              table, layer.page, s.num_heads, s.num_kv_heads, s.head_dim, s.window, rt.status)
-            return
-        ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, table, layer.page, s.num_heads,
-                      s.num_kv_heads, s.head_dim, s.window, rt.status)
+        else:
+            ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, table, layer.page, s.num_heads,
+                          s.num_kv_heads, s.head_dim, s.window, rt.status)
 
 
 register("mixer", "attention", Attention)

@@ -17,10 +17,24 @@ Interfaces (all tensors live on the GPU; N = tokens of the step, H = width):
 * position:  ``rotate_and_store(qkv, bias, ctx, q_out, layer, nh, nkv, hd)``: encodes the new queries and
              keys (float32 in ``qkv``) and stores keys and values in the cache.
 * block:     ``forward(x, pending, ctx, layer) -> pending``: runs its parts in its arrangement.
+
+Per-step index lists.  A part that needs lists of its own on the device (tiles
+of new tokens for an attention kernel, chunk boundaries for a scan) returns them
+from ``step_arrays(step)`` as named int32 numpy arrays, made from the host-side
+description of the step; the engine copies them to the device with the rest of
+the step's metadata and hands them back as ``ctx.arrays[name]``.  The engine
+itself knows none of these lists.
+
+Captured steps.  A decode step is replayed from a CUDA graph only if every part
+of the model has ``graph_safe = True``.  A graph-safe part does the same
+launches with the same addresses for every step of the same shape (number of
+sequences, page-table stride, sizes of its step arrays): it reads nothing from
+``ctx.host`` while it runs, never syncs with the host, and takes slots,
+positions and page tables from the device tensors of the context.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Callable, Optional
 
 import torch
@@ -36,12 +50,44 @@ class ParamSpec:
     optional: bool = False
 
 
+@dataclass(frozen=True)
+class StepHost:
+    """What a step is, on the host: one entry per sequence of the batch."""
+    slots: tuple       # cache slot of every sequence
+    news: tuple        # tokens each brings in this step
+    pasts: tuple       # tokens each had cached before
+    starts: tuple      # [B + 1] offsets of the sequences among the step's token rows
+
+    @property
+    def n_tokens(self) -> int:
+        return self.starts[-1]
+
+    @property
+    def n_seqs(self) -> int:
+        return len(self.slots)
+
+
 class Part:
     """Base of every part.  ``params`` maps tensor name -> the view the loader
     fills; it exists after ``allocate``."""
 
+    # True: the part may run inside a captured step (see the module's text); parts from outside the
+    # library are taken to be unsafe until they say otherwise
+    graph_safe = False
+
     def param_specs(self) -> list:
         return []
+
+    def step_arrays(self, step: "StepHost") -> dict:
+        """name -> int32 numpy array that this part wants on the device for this
+        step.  Names are global: parts that return the same name must mean the
+        same list (the first one is kept)."""
+        return {}
+
+    def step_arrays_key(self):
+        """Parts with equal keys would return the same lists; only one of them
+        is asked.  None: this part has no lists."""
+        return None
 
     def allocate(self, stored: dict, rt: "Runtime") -> dict:
         """``stored``: tensor name -> dtype in the checkpoint (only names that
@@ -54,6 +100,16 @@ class Part:
 
     def children(self) -> list:
         return []
+
+
+def plain_delta(norm, delta):
+    """What a norm is given as ``delta``.  A producer may hand on a deferred
+    output (an object with ``materialize()`` that also knows how to fold its
+    last step into an add + norm); only a norm that says ``takes_deferred =
+    True`` sees it, every other norm gets the plain tensor."""
+    if hasattr(delta, "materialize") and not getattr(norm, "takes_deferred", False):
+        return delta.materialize()
+    return delta
 
 
 def walk(part: Part):
@@ -136,6 +192,34 @@ class Runtime:
             self.side_stream = torch.cuda.Stream(device=self.device)     # for work that may run beside the main stream
         self.ffn_chunk_tokens = ffn_chunk_tokens
         self.record_routing = False       # debugging aid: MoE parts put their choices into ctx.aux
+        # named 64-bit counters that kernels add to on the device (read with ``read_counters``: that waits)
+        self._counter_names: list = []
+        self.counters = None
+        if self.device is not None:
+            self.counters = torch.zeros(self.MAX_COUNTERS, dtype=torch.int64, device=self.device)
+
+    MAX_COUNTERS = 1024
+
+    def new_counter(self, name: str):
+        """A one-element int64 view that a part's kernels may add to; None on a
+        runtime without a device."""
+        if self.counters is None:
+            return None
+        if len(self._counter_names) >= self.MAX_COUNTERS:
+            raise Backend(f"more than {self.MAX_COUNTERS} device counters were asked for")
+        self._counter_names.append(name)
+        i = len(self._counter_names) - 1
+        return self.counters[i:i + 1]
+
+    def read_counters(self) -> dict:
+        """name -> value; names given more than once are summed."""
+        if self.counters is None:
+            return {}
+        host = self.counters[:len(self._counter_names)].tolist()
+        out: dict = {}
+        for name, v in zip(self._counter_names, host):
+            out[name] = out.get(name, 0) + int(v)
+        return out
 
     @property
     def full_precision(self) -> bool:
@@ -165,10 +249,7 @@ class StepContext:
     seq_start: torch.Tensor          # [B+1] offsets of the sequences in the token rows
     seq_past: torch.Tensor           # [B] cached length before the step
     want_rows: torch.Tensor          # [R] token rows whose logits are wanted
-    q_tile_seq: torch.Tensor         # [tiles] sequence of every tile of 64 new tokens
-    q_tile_first: torch.Tensor       # [tiles] index of the tile's first token among its sequence's new tokens
     block_tables: list               # per layer group: [B, stride] page ids
-    host: dict                       # the same lists on the host (slots, starts, pasts, news)
+    host: dict                       # the same lists on the host (slots, starts, pasts, news); not for graph-safe parts
     aux: dict
-    q_wide_seq: Optional[torch.Tensor] = None     # [tiles] the same for the wider tiles of the tensor-memory attention, those that see the
-    q_wide_first: Optional[torch.Tensor] = None   # most keys first (None: the step did not list them)
+    arrays: dict = field(default_factory=dict)    # name -> device tensor of every list the parts asked for (step_arrays)

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Part, build, register
+from .base import Part, build, plain_delta, register
 
 
 class PreNormResidualBlock(Part):
@@ -11,6 +11,8 @@ class PreNormResidualBlock(Part):
     (crates/esp/src/infer/decoder/layer.rs:115-153).  The residual adds are
     folded into the norm that follows them: a part's output travels as
     ``pending`` until the next norm adds it to the 32-bit residual stream."""
+
+    graph_safe = True
 
     def __init__(self, spec, rt):
         self.spec = spec
@@ -26,12 +28,12 @@ class PreNormResidualBlock(Part):
     def forward(self, x, pending, ctx, layer):
         rt = self.rt
         h = rt.ws.get("block_h", tuple(x.shape), rt.dtype)
-        self.mixer_norm.forward(x, pending, h)
+        self.mixer_norm.forward(x, plain_delta(self.mixer_norm, pending), h)
         delta = self.mixer.forward(h, ctx, layer)
         h32 = None
         if rt.dtype != torch.float32 and getattr(self.ffn, "wants_f32_input", False):
             h32 = rt.ws.get("block_h32", tuple(x.shape), torch.float32)
-        self.ffn_norm.forward(x, delta, h, h32=h32)
+        self.ffn_norm.forward(x, plain_delta(self.ffn_norm, delta), h, h32=h32)
         return self.ffn.forward(h, ctx, h32=h32)
 
 

@@ -45,25 +45,27 @@ class DenseSwiGlu(Part):
     """y = W_d(silu(W_g h) * (W_u h)), no biases
     (crates/esp/src/infer/decoder/moe.rs:87-89, :143-148)."""
 
+    graph_safe = True
+
     def __init__(self, spec, rt):
         self.spec = spec
         self.rt = rt
         self.w_gate_up = self.w_down = None
 
     def param_specs(self):
-        s, p = self.spec, self.spec.prefix
-        return [ParamSpec(p + "gate_proj.weight", (s.intermediate, s.hidden), "matrix"),
-                ParamSpec(p + "up_proj.weight", (s.intermediate, s.hidden), "matrix"),
-                ParamSpec(p + "down_proj.weight", (s.hidden, s.intermediate), "matrix")]
+        s, p, n = self.spec, self.spec.prefix, self.spec.names
+        return [ParamSpec(p + n.gate, (s.intermediate, s.hidden), "matrix"),
+                ParamSpec(p + n.up, (s.intermediate, s.hidden), "matrix"),
+                ParamSpec(p + n.down, (s.hidden, s.intermediate), "matrix")]
 
     def allocate(self, stored, rt):
-        s, p = self.spec, self.spec.prefix
-        dt = rt.matrix_dtype([stored[p + "gate_proj.weight"], stored[p + "up_proj.weight"]])
+        s, p, n = self.spec, self.spec.prefix, self.spec.names
+        dt = rt.matrix_dtype([stored[p + n.gate], stored[p + n.up]])
         self.w_gate_up = torch.empty((2 * s.intermediate, s.hidden), dtype=dt, device=rt.device)
-        self.w_down = torch.empty((s.hidden, s.intermediate), dtype=rt.matrix_dtype([stored[p + "down_proj.weight"]]),
+        self.w_down = torch.empty((s.hidden, s.intermediate), dtype=rt.matrix_dtype([stored[p + n.down]]),
                                   device=rt.device)
-        return {p + "gate_proj.weight": self.w_gate_up[:s.intermediate],
-                p + "up_proj.weight": self.w_gate_up[s.intermediate:], p + "down_proj.weight": self.w_down}
+        return {p + n.gate: self.w_gate_up[:s.intermediate], p + n.up: self.w_gate_up[s.intermediate:],
+                p + n.down: self.w_down}
 
     def forward(self, h, ctx, h32=None):
         rt = self.rt
@@ -83,51 +85,59 @@ class MoeSwiGluShared(Part):
     SwiGLU expert scaled by sigmoid(h . w_shared_gate)
     (crates/esp/src/infer/decoder/moe.rs:135-256)."""
 
+    graph_safe = True
+
     def __init__(self, spec, rt):
         self.spec = spec
         self.rt = rt
         self.w_router = self.w_shared_gate = None
         self.w_gate_up = self.w_down = None            # [E, 2Im, H], [E, H, Im]
         self.w_shared_gate_up = self.w_shared_down = None
+        # experts with at least one token, summed over this block's calls (a device counter; nothing waits for it)
+        self.expert_reads = rt.new_counter("expert_reads")
+
+    def _names(self):
+        """(router, shared gate, shared (gate, up, down), [per expert (gate, up, down)])"""
+        s, p, n = self.spec, self.spec.prefix, self.spec.names
+        mlp = lambda q: (q + n.mlp.gate, q + n.mlp.up, q + n.mlp.down)
+        return (p + n.router, p + n.shared_gate, mlp(p + n.shared),
+                [mlp(p + n.expert.format(e=e)) for e in range(s.num_experts)])
 
     def param_specs(self):
-        s, p = self.spec, self.spec.prefix
-        specs = [ParamSpec(p + "gate.weight", (s.num_experts, s.hidden), "matrix"),
-                 ParamSpec(p + "shared_expert_gate.weight", (1, s.hidden), "matrix"),
-                 ParamSpec(p + "shared_expert.gate_proj.weight", (s.shared_intermediate, s.hidden), "matrix"),
-                 ParamSpec(p + "shared_expert.up_proj.weight", (s.shared_intermediate, s.hidden), "matrix"),
-                 ParamSpec(p + "shared_expert.down_proj.weight", (s.hidden, s.shared_intermediate), "matrix")]
-        for e in range(s.num_experts):
-            q = f"{p}experts.{e}."
-            specs += [ParamSpec(q + "gate_proj.weight", (s.expert_intermediate, s.hidden), "matrix"),
-                      ParamSpec(q + "up_proj.weight", (s.expert_intermediate, s.hidden), "matrix"),
-                      ParamSpec(q + "down_proj.weight", (s.hidden, s.expert_intermediate), "matrix")]
+        s = self.spec
+        router, shared_gate, shared, experts = self._names()
+        specs = [ParamSpec(router, (s.num_experts, s.hidden), "matrix"),
+                 ParamSpec(shared_gate, (1, s.hidden), "matrix"),
+                 ParamSpec(shared[0], (s.shared_intermediate, s.hidden), "matrix"),
+                 ParamSpec(shared[1], (s.shared_intermediate, s.hidden), "matrix"),
+                 ParamSpec(shared[2], (s.hidden, s.shared_intermediate), "matrix")]
+        for gate, up, down in experts:
+            specs += [ParamSpec(gate, (s.expert_intermediate, s.hidden), "matrix"),
+                      ParamSpec(up, (s.expert_intermediate, s.hidden), "matrix"),
+                      ParamSpec(down, (s.hidden, s.expert_intermediate), "matrix")]
         return specs
 
     def allocate(self, stored, rt):
-        s, p = self.spec, self.spec.prefix
+        s = self.spec
         dev = rt.device
         E, Im, Is, H = s.num_experts, s.expert_intermediate, s.shared_intermediate, s.hidden
-        rdt = rt.matrix_dtype([stored[p + "gate.weight"], stored[p + "shared_expert_gate.weight"]])
+        router, shared_gate, shared, experts = self._names()
+        rdt = rt.matrix_dtype([stored[router], stored[shared_gate]])
         self.w_router = torch.empty((E, H), dtype=rdt, device=dev)
         self.w_shared_gate = torch.empty((1, H), dtype=rdt, device=dev)
-        gu_names = [f"{p}experts.{e}.{k}_proj.weight" for e in range(E) for k in ("gate", "up")]
-        self.w_gate_up = torch.empty((E, 2 * Im, H), dtype=rt.matrix_dtype([stored[n] for n in gu_names]), device=dev)
-        d_names = [f"{p}experts.{e}.down_proj.weight" for e in range(E)]
-        self.w_down = torch.empty((E, H, Im), dtype=rt.matrix_dtype([stored[n] for n in d_names]), device=dev)
-        sdt = rt.matrix_dtype([stored[p + "shared_expert.gate_proj.weight"], stored[p + "shared_expert.up_proj.weight"]])
+        gu_dt = rt.matrix_dtype([stored[n] for g, u, _d in experts for n in (g, u)])
+        self.w_gate_up = torch.empty((E, 2 * Im, H), dtype=gu_dt, device=dev)
+        self.w_down = torch.empty((E, H, Im), dtype=rt.matrix_dtype([stored[d] for _g, _u, d in experts]), device=dev)
+        sdt = rt.matrix_dtype([stored[shared[0]], stored[shared[1]]])
         self.w_shared_gate_up = torch.empty((2 * Is, H), dtype=sdt, device=dev)
-        self.w_shared_down = torch.empty((H, Is), dtype=rt.matrix_dtype([stored[p + "shared_expert.down_proj.weight"]]),
-                                         device=dev)
-        views = {p + "gate.weight": self.w_router, p + "shared_expert_gate.weight": self.w_shared_gate,
-                 p + "shared_expert.gate_proj.weight": self.w_shared_gate_up[:Is],
-                 p + "shared_expert.up_proj.weight": self.w_shared_gate_up[Is:],
-                 p + "shared_expert.down_proj.weight": self.w_shared_down}
-        for e in range(E):
-            q = f"{p}experts.{e}."
-            views[q + "gate_proj.weight"] = self.w_gate_up[e, :Im]
-            views[q + "up_proj.weight"] = self.w_gate_up[e, Im:]
-            views[q + "down_proj.weight"] = self.w_down[e]
+        self.w_shared_down = torch.empty((H, Is), dtype=rt.matrix_dtype([stored[shared[2]]]), device=dev)
+        views = {router: self.w_router, shared_gate: self.w_shared_gate,
+                 shared[0]: self.w_shared_gate_up[:Is], shared[1]: self.w_shared_gate_up[Is:],
+                 shared[2]: self.w_shared_down}
+        for e, (gate, up, down) in enumerate(experts):
+            views[gate] = self.w_gate_up[e, :Im]
+            views[up] = self.w_gate_up[e, Im:]
+            views[down] = self.w_down[e]
         return views
 
     wants_f32_input = True      # the router works from unrounded rows
@@ -164,7 +174,7 @@ class MoeSwiGluShared(Part):
             # few tokens: router and permutation in two short launches
             logits = ws.get("moe_logits", (n, E + 1), torch.float32)
             ops.route_small(router_in, self.w_router, self.w_shared_gate, logits, ids, wts, gate, k, s.norm_topk,
-                            offsets, perm_token, perm_weight, inverse, rt.status, probs)
+                            offsets, perm_token, perm_weight, inverse, rt.status, probs, distinct=self.expert_reads)
         else:
             ops.router_topk(router_in, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status,
                             probs, logits=ws.get("moe_logits", (n, E + 1), torch.float32))
@@ -173,7 +183,8 @@ class MoeSwiGluShared(Part):
                 tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32),
                          ws.get("moe_tile_row0", (max_tiles,), torch.int32),
                          ws.get("moe_tile_count", (max_tiles,), torch.int32), ws.get("moe_n_tiles", (1,), torch.int32))
-            ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles)
+            ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles,
+                            distinct=self.expert_reads)
         if rt.record_routing:
             ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
         shared = ws.get("moe_shared_out", (n, H), torch.float32)

@@ -11,6 +11,9 @@ class RmsNorm(Part):
     """h = (x + delta) * rsqrt(mean((x + delta)^2) + eps) * weight, in 32-bit
     (crates/esp/src/infer/decoder/layer.rs:27-33)."""
 
+    graph_safe = True
+    takes_deferred = True      # a deferred expert sum is added and normalised here in one launch
+
     def __init__(self, spec, rt):
         self.spec = spec
         self.rt = rt

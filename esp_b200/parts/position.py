@@ -15,6 +15,8 @@ class RopeSplitHalf(Part):
     in 32-bit on the host once (crates/esp/src/infer/decoder/attention.rs:58-95)
     and kept as cos/sin tables [max_positions, rotary_dim/2]."""
 
+    graph_safe = True
+
     def __init__(self, spec, rt):
         self.spec = spec
         self.rt = rt
@@ -39,6 +41,8 @@ class RopeSplitHalf(Part):
 
 class NoPosition(Part):
     """No encoding: queries and keys are stored as projected."""
+
+    graph_safe = True
 
     def __init__(self, spec, rt):
         self.spec = spec

@@ -18,7 +18,7 @@ from typing import Callable, Optional, Union
 import torch
 
 from .engine import Engine, StepEntry
-from .engine.generate import GenerationLoop, SequenceRequest
+from .engine.generate import GenerationLoop, ScoreHealth, SequenceRequest
 from .errors import Backend, InvalidRequest, Unsupported
 from .sampling import SamplingParams
 
@@ -70,6 +70,9 @@ class _EngineBackend:
         self.options.pop(slot, None)
         self.engine.close(slot)
 
+    def settle(self):
+        self.engine.settle()
+
     def _pick(self, entries):
         temps = [self.options[e.slot].temperature for e in entries]
         tops = [self.options[e.slot].top_p for e in entries]
@@ -119,35 +122,33 @@ class DecoderProvider:
         self.tokenizer = tokenizer
         self.max_batch = max_batch
         self._backend = _EngineBackend(engine)
+        self.score_health = ScoreHealth()      # counts over this provider's generate calls
 
     # -- construction -----------------------------------------------------------
     @classmethod
     def load(cls, model_dir, dtype="bfloat16", device="cuda:0", max_batch: int = 64, max_context: Optional[int] = None,
              max_tokens: Optional[int] = None) -> "DecoderProvider":
         """``max_context``: longest sequence to make room for (default: the
-        model's).  ``max_tokens``: cache size in tokens (default: max_batch
-        sequences of max_context, capped at 1M tokens)."""
+        model's).  ``max_tokens``: cache size in tokens; refused if it does not
+        fit the device.  Default: room for max_batch sequences of max_context,
+        at most 1M tokens and at most what the device's free memory holds
+        beside the weights."""
         model_dir = Path(model_dir)
         from .config import config_from_json
         config = config_from_json(model_dir)
+        fit = max_tokens is None
         max_tokens = cls._cache_tokens(config, max_batch, max_context, max_tokens)
-        engine = Engine.from_folder(model_dir, dtype=dtype, device=device, max_tokens=max_tokens)
-        tok = None
-        if (model_dir / "tokenizer.json").is_file():
-            try:
-                from tokenizers import Tokenizer
-                tok = Tokenizer.from_file(str(model_dir / "tokenizer.json"))
-            except ImportError:
-                tok = None
-        return cls(engine, tok, max_batch)
+        engine = Engine.from_folder(model_dir, dtype=dtype, device=device, max_tokens=max_tokens, shrink_to_fit=fit)
+        return cls(engine, load_tokenizer(model_dir), max_batch)
 
     @classmethod
     def from_random(cls, config, seed: int = 0, init=None, dtype="bfloat16", device="cuda:0", max_batch: int = 64,
                     max_context: Optional[int] = None, max_tokens: Optional[int] = None) -> "DecoderProvider":
         from .weights import InitSpec
+        fit = max_tokens is None
         max_tokens = cls._cache_tokens(config, max_batch, max_context, max_tokens)
         engine = Engine.from_random(config, seed, init or InitSpec(), dtype=dtype, device=device,
-                                    max_tokens=max_tokens)
+                                    max_tokens=max_tokens, shrink_to_fit=fit)
         return cls(engine, None, max_batch)
 
     @staticmethod
@@ -186,7 +187,8 @@ class DecoderProvider:
                                         tuple(r.stop_token_ids)))
         hooks = self._stop_string_hook(reqs, on_token)
         loop = GenerationLoop(self._backend, self.engine.plan.max_positions, self.max_batch,
-                              self.engine.cache.book.n_pages * 64, self.engine.plan.stop_token_ids)
+                              self.engine.cache.book.n_pages * 64, self.engine.plan.stop_token_ids,
+                              health=self.score_health)
         results = loop.run(seqs, hooks)
         outs = []
         for r, res in zip(reqs, results):
@@ -229,6 +231,29 @@ class DecoderProvider:
             return logits[0]
         finally:
             self.engine.close(slot)
+
+
+def load_tokenizer(model_dir):
+    """The folder's tokenizer, or None if it has no tokenizer.json or the
+    ``tokenizers`` package is missing (requests then carry token ids)."""
+    path = Path(model_dir) / "tokenizer.json"
+    if not path.is_file():
+        return None
+    try:
+        from tokenizers import Tokenizer
+    except ImportError:
+        return None
+    return Tokenizer.from_file(str(path))
+
+
+def cache_tokens_for(prompt_lengths: list, max_tokens: int, window: int, max_batch: int) -> int:
+    """Cache size, in tokens, that serves these requests in batches of at most
+    ``max_batch``: the largest batch's prompts plus what each may generate,
+    every sequence rounded up to whole pages."""
+    from .engine.generate import reserved_tokens
+    need = [reserved_tokens(n, max(1, min(max_tokens, window - n))) for n in prompt_lengths]
+    batches = [sum(need[i:i + max_batch]) for i in range(0, len(need), max_batch)]
+    return max(batches, default=64)
 
 
 def load(model_dir, **kw) -> DecoderProvider:

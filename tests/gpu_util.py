@@ -23,11 +23,13 @@ ROUTE_MARGIN = {"float32": 1e-5, "bfloat16": 2e-2}
 _engines = {}
 
 
-def engine_for(folder, dtype, max_tokens=2048):
-    key = (str(folder), dtype, max_tokens)
+def engine_for(folder, dtype, max_tokens=2048, record_routing=True):
+    """``record_routing``: the engine notes its expert choices for the comparison with the plain
+    implementation; that keeps decode steps out of captured graphs, so tests of the graphs turn it off."""
+    key = (str(folder), dtype, max_tokens, record_routing)
     if key not in _engines:
         eng = Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens)
-        eng.rt.record_routing = True
+        eng.rt.record_routing = record_routing
         _engines[key] = eng
     return _engines[key]
 
@@ -133,21 +135,29 @@ def steps_batches(requests, batches, prompt_lens):
     return steps
 
 
-def check_against_plain(folder, dtype, requests, recorder, what):
-    c, w = plain_model(str(folder))
+def check_against_plain(folder, dtype, requests, recorder, what, positions=None):
+    """``folder``: a model folder, or a loaded plain model (config, weights).  ``positions``: request id ->
+    the positions to compare (default: all of them)."""
+    c, w = folder if isinstance(folder, tuple) else plain_model(str(folder))
     k = c["num_experts_per_tok"]
     for rid, toks in requests.items():
         forced = recorder.forced(rid, len(toks))
         record = {}
         ref = plain.forward_logits(c, w, toks, forced_routing=forced, routing_record=record)
-        got = recorder.logits_of(rid, range(len(toks)))
+        at = list(range(len(toks))) if positions is None else list(positions[rid])
+        got = recorder.logits_of(rid, at)
+        ref = ref[at]
         scale = max(1e-6, float(np.abs(ref).max()))
         err = float(np.abs(got - ref).max())
-        first_bad = int(np.argmax(np.abs(got - ref).max(axis=1) > REL_TOL[dtype] * scale))
+        first_bad = at[int(np.argmax(np.abs(got - ref).max(axis=1) > REL_TOL[dtype] * scale))]
         assert err <= REL_TOL[dtype] * scale, (
             f"{what}, request {rid} ({len(toks)} tokens, {dtype}): max |engine - plain| = {err:.3e} > "
             f"{REL_TOL[dtype] * scale:.3e}; first wrong position {first_bad}")
-        # the engine's expert choices are the plain ones up to rounding of near ties
+        # the engine's expert choices are the plain ones up to rounding of near ties (an engine that recorded
+        # none ran with the plain implementation's own choices: only sound where every expert is chosen)
+        if not forced:
+            assert k == c["num_experts"], "without the engine's expert choices only top-k = all experts can be compared"
+            continue
         for layer, (ids_plain, p) in record.items():
             mine = forced[layer]
             for t in range(len(toks)):

@@ -54,9 +54,13 @@ def read_safetensors(path) -> dict[str, np.ndarray]:
 
 
 def read_config(path) -> dict:
-    """config.json with the reference's defaults filled in
+    return read_config_dict(json.loads(Path(path).read_text()))
+
+
+def read_config_dict(c: dict) -> dict:
+    """config.json's keys with the reference's defaults filled in
     (crates/esp/src/infer/decoder/config.rs:36-51, :322-386, :434-446)."""
-    c = json.loads(Path(path).read_text())
+    c = dict(c)
     c.setdefault("num_key_value_heads", c["num_attention_heads"])
     if c.get("head_dim") is None:
         c["head_dim"] = c["hidden_size"] // c["num_attention_heads"]
@@ -69,6 +73,7 @@ def read_config(path) -> dict:
     c.setdefault("use_sliding_window", None)
     c.setdefault("sliding_window", None)
     c.setdefault("max_window_layers", 28)
+    c.setdefault("layer_types", None)
     return c
 
 
@@ -78,12 +83,19 @@ def load_model(folder) -> tuple[dict, dict[str, np.ndarray]]:
 
 
 def layer_is_moe(c: dict, i: int) -> bool:
-    """crates/esp/src/infer/decoder/config.rs:460-464"""
+    """crates/esp/src/infer/decoder/config.rs:460-464.  A configuration without experts (the reference's
+    dense ``qwen2`` checkpoint, which shares the attention code and is used here to pin the window) has
+    dense layers only."""
+    if not c.get("num_experts"):
+        return False
     return i not in c["mlp_only_layers"] and (i + 1) % c["decoder_sparse_step"] == 0
 
 
 def layer_window(c: dict, i: int):
-    """crates/esp/src/infer/decoder/config.rs:466-485 (the qwen2_moe branch)."""
+    """crates/esp/src/infer/decoder/config.rs:466-485: ``layer_types``, when present, decides layer by
+    layer; else ``use_sliding_window`` and ``max_window_layers`` (the qwen2 / qwen2_moe branch)."""
+    if c.get("layer_types") is not None:
+        return c["sliding_window"] if c["layer_types"][i] == "sliding_attention" else None
     if c["use_sliding_window"] is False or c["use_sliding_window"] is None:
         return None
     if c["use_sliding_window"] is True and i >= c["max_window_layers"]:
@@ -233,7 +245,7 @@ def forward_logits(c, w, ids, dtype=np.float32, forced_routing=None, routing_rec
     (crates/esp/src/infer/decoder/model.rs:468-473, :541-666).  ``forced_routing``
     maps layer index -> ids [T,k]; ``routing_record`` (a dict) receives, per MoE
     layer, (ids, probabilities)."""
-    w = {k: v.astype(dtype) for k, v in w.items()}
+    w = {k: v.astype(dtype, copy=False) for k, v in w.items()}
     x = w["model.embed_tokens.weight"][np.asarray(ids)]
     for i in range(c["num_hidden_layers"]):
         rec = None

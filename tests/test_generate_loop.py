@@ -228,3 +228,110 @@ def test_one_step_ahead_waits_when_the_cache_cannot_take_the_step_launched_ahead
     got = loop(be).run(reqs)
     assert [(r.token_ids, r.finish_reason) for r in got] == [(r.token_ids, r.finish_reason) for r in want]
     assert be.refused > 0 and not be.held
+
+
+# ---------------------------------------------------------------------------
+# non-finite scores: the committed prefix runs again once, then the call fails
+# (crates/esp/src/infer/decoder/provider.rs:219-240, :763-803, tests :944-1020)
+# ---------------------------------------------------------------------------
+class Counting(ScriptedBackend):
+    """Every sequence continues its last token: [.., t] -> t + 1, whether the prefix comes as a prompt or
+    token by token.  ``bad_calls``: indices (over prefill and decode calls together) whose scores are
+    reported as non-finite after the step has run."""
+
+    def __init__(self, bad_calls=(), **kw):
+        super().__init__(**kw)
+        self.bad_calls = set(bad_calls)
+        self.n_calls = 0
+        self.settled = 0
+
+    def _maybe_fail(self):
+        from esp_b200.errors import NonFiniteScores
+        self.n_calls += 1
+        if self.n_calls - 1 in self.bad_calls:
+            raise NonFiniteScores("the device reported: non-finite logits")
+
+    def settle(self):
+        self.settled += 1
+
+    def prefill(self, slots, prompts):
+        self.calls.append(("prefill", tuple(slots), tuple(len(p) for p in prompts)))
+        for s, p in zip(slots, prompts):
+            self.held[s] = p[-1] + 1
+        self._maybe_fail()
+        return [self.held[s] for s in slots]
+
+    def decode(self, slots, tokens):
+        self.calls.append(("decode", tuple(slots), tuple(tokens)))
+        for s, t in zip(slots, tokens):
+            assert self.held[s] == t
+            self.held[s] = t + 1
+        self._maybe_fail()
+        return [self.held[s] for s in slots]
+
+
+class CountingAhead(Counting):
+    class Handle:
+        def __init__(self, tokens, error):
+            self.tokens, self.error, self.read = tokens, error, False
+
+        def result(self):
+            self.read = True
+            if self.error is not None:
+                raise self.error
+            return list(self.tokens)
+
+    def _handle(self, fn, *args):
+        from esp_b200.errors import NonFiniteScores
+        try:
+            return self.Handle(fn(*args), None)
+        except NonFiniteScores as e:                     # the step ran; its bad scores show when the tokens are read
+            return self.Handle([self.held[s] for s in args[0]], e)
+
+    def prefill_async(self, slots, prompts):
+        return self._handle(self.prefill, slots, prompts)
+
+    def decode_async(self, slots, earlier, places):
+        return self._handle(self.decode, slots, [earlier.tokens[p] for p in places])
+
+
+def _recovery_requests():
+    return [SequenceRequest([10], max_tokens=6, sampling=SamplingParams(0.7, None, 1234)),
+            SequenceRequest([20, 21], max_tokens=3),
+            SequenceRequest([30], max_tokens=8, stop_token_ids=(35,))]
+
+
+@pytest.mark.parametrize("backend_class", [Counting, CountingAhead])
+@pytest.mark.parametrize("bad_call", [0, 1, 3])
+def test_bad_scores_once_run_the_committed_prefix_again(backend_class, bad_call):
+    from esp_b200.engine.generate import ScoreHealth
+    want = loop(backend_class()).run(_recovery_requests())
+    be = backend_class(bad_calls=[bad_call])
+    health = ScoreHealth()
+    got = loop(be, health=health).run(_recovery_requests())
+    assert [(r.token_ids, r.finish_reason) for r in got] == [(r.token_ids, r.finish_reason) for r in want]
+    assert (health.invalid_steps, health.prefix_recomputations, health.failed_recoveries) == (1, 1, 0)
+    assert be.settled == 1 and not be.held and sorted(be.free) == list(range(4))
+    # the sampled sequence's stream restarts where it stood: its seed moved on by one draw per kept token
+    reopened = [c for c in be.calls if c[0] == "open" and c[2] is not None][1:]
+    for c in reopened:
+        assert c[2] in [skip_draws(1234, n) for n in range(0, 7)], "the reopened stream is not a continuation"
+    # the prefix that ran again is prompt + kept tokens: one prefill more than a clean run, of longer prompts
+    prefills = [c for c in be.calls if c[0] == "prefill"]
+    assert len(prefills) == 2 and all(a >= b for a, b in zip(prefills[1][2], prefills[0][2][-len(prefills[1][2]):]))
+
+
+# with the loop one step ahead, call 2 is the step launched before call 1's bad scores were read; it is dropped
+# with them, and the re-run of the prefix is call 3
+@pytest.mark.parametrize("backend_class, bad_calls, message", [
+    (Counting, (1, 4), "already used"), (Counting, (1, 2), "recomputed"),
+    (CountingAhead, (1, 4), "already used"), (CountingAhead, (1, 3), "recomputed")])
+def test_bad_scores_again_fail_the_call_and_free_every_slot(backend_class, bad_calls, message):
+    from esp_b200.engine.generate import ScoreHealth
+    from esp_b200.errors import Backend
+    be = backend_class(bad_calls=bad_calls)
+    health = ScoreHealth()
+    with pytest.raises(Backend, match=message):
+        loop(be, health=health).run(_recovery_requests())
+    assert health.prefix_recomputations == 1 and health.failed_recoveries == 1 and health.invalid_steps == 2
+    assert not be.held and sorted(be.free) == list(range(4))

@@ -143,3 +143,65 @@ def test_waiting_and_one_step_ahead_agree_bfloat16(folders):
     assert [(r.token_ids, r.finish_reason) for r in got] == [(r.token_ids, r.finish_reason) for r in want]
     assert want[0].finish_reason == "stop" and len(want[0].token_ids) <= 2
     assert prov.engine.cache.book.slots.available == prov.engine.max_slots
+
+
+def _poison_after(engine, steps_before, row=1, steps=1):
+    """Arms the engine's testing aid so that the logits row ``row`` of the step number ``steps_before``
+    (counted from now) is overwritten with NaN, and the same for ``steps`` steps in a row (None: for good)."""
+    seen = {"n": 0}
+    run_reserved = engine._run_reserved
+
+    def counted(*args, **kw):
+        if seen["n"] == steps_before:
+            engine.poison_logits_row, engine.poison_steps = row, steps
+        seen["n"] += 1
+        return run_reserved(*args, **kw)
+
+    engine._run_reserved = counted
+    return lambda: setattr(engine, "_run_reserved", run_reserved)
+
+
+@pytest.mark.parametrize("at", [0, 3])
+def test_non_finite_logits_once_are_recomputed_and_change_nothing(folders, at):
+    """A logits row turns NaN in one step (the prompts' step, or the third decode step): no token is taken
+    from that step, the committed prefixes run again in fresh slots, and the tokens are those of a clean
+    run, with seeded sampling too (the streams restart where they stood)."""
+    prov = DecoderProvider.load(folders["B"], dtype="float32", max_batch=4)
+    ps = prompts("B", PROMPTS_B, seed=21)
+    reqs = [GenerationRequest(prompt_ids=p, max_tokens=9, temperature=0.0 if i % 2 else 0.8, seed=7 + i)
+            for i, p in enumerate(ps)]
+    clean = prov.generate(reqs)
+    restore = _poison_after(prov.engine, at)
+    try:
+        again = prov.generate(reqs)
+    finally:
+        restore()
+    assert [o.token_ids for o in again] == [o.token_ids for o in clean]
+    h = prov.score_health
+    assert (h.invalid_steps, h.prefix_recomputations, h.failed_recoveries) == (1, 1, 0) and h.checked_rows > 0
+    assert prov.engine.cache.book.slots.available == prov.engine.max_slots
+    assert all(g.pool.available == g.pool.n for g in prov.engine.cache.book.groups)
+    assert prov.engine.read_status() == 0
+
+
+def test_non_finite_logits_that_stay_fail_the_call_closed(folders):
+    """Scores that are still bad after the one recomputation end the call with a Backend error that names
+    them; no token of the bad steps is handed out, every slot and page goes back."""
+    from esp_b200.errors import Backend
+    prov = DecoderProvider.load(folders["A"], dtype="bfloat16", max_batch=4)
+    ps = prompts("A", PROMPTS_A, seed=22)
+    seen = []
+    restore = _poison_after(prov.engine, 2, row=0, steps=None)
+    try:
+        with pytest.raises(Backend, match="non-finite"):
+            prov.generate([GenerationRequest(prompt_ids=p, max_tokens=8) for p in ps], lambda i, t: seen.append((i, t)) and False)
+    finally:
+        restore()
+        prov.engine.poison_logits_row = prov.engine.poison_steps = None
+    assert max(sum(1 for i, _t in seen if i == r) for r in range(3)) <= 2, "tokens were taken from a step with bad scores"
+    assert prov.score_health.failed_recoveries == 1
+    assert prov.engine.cache.book.slots.available == prov.engine.max_slots
+    assert all(g.pool.available == g.pool.n for g in prov.engine.cache.book.groups)
+    prov.engine.settle()
+    ok = prov.generate(GenerationRequest(prompt_ids=ps[0], max_tokens=3))      # the provider is still usable
+    assert len(ok.token_ids) == 3

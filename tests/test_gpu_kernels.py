@@ -643,13 +643,14 @@ def test_attn_prefill_tc05_against_reference(nh, nkv, hd, window):
     check_attn_prefill(ops.attn_prefill_tc05, nh, nkv, hd, window, tile=ops.ATTN_TC05_TILE_ROWS)
 
 
-def check_attn_prefill(fn, nh, nkv, hd, window, tile=64):
+def check_attn_prefill(fn, nh, nkv, hd, window, tile=64, runs=None):
     torch.manual_seed(3)
     dtype = torch.bfloat16
     group = nh // nkv
-    runs = [(0, 200), (130, 70), (0, 1), (63, 66), (300, 129), (10, 420)]        # (past, new)
+    runs = runs or [(0, 200), (130, 70), (0, 1), (63, 66), (300, 129), (10, 420)]        # (past, new)
     lens = [p + n for p, n in runs]
-    tables = [[6 * i + s for i in range(7)] for s in range(6)]
+    n_seq, per_seq = len(runs), (max(lens) + 63) // 64
+    tables = [[n_seq * i + s for i in range(per_seq)] for s in range(n_seq)]
     ks = [torch.randn(n, nkv, hd) * 0.3 for n in lens]
     vs = [torch.randn(n, nkv, hd) for n in lens]
     qs = [torch.randn(n, nh, hd) * 0.3 for _p, n in runs]
@@ -663,7 +664,7 @@ def check_attn_prefill(fn, nh, nkv, hd, window, tile=64):
             for h in range(nh):
                 ks[s][target, h // group] = ks[s][target, h // group] / ks[s][target, h // group].norm() * 6.0
                 qs[s][i, h] = ks[s][target, h // group] * (np.sqrt(hd) * 3.0 / 6.0)
-    kc, vc = paged(ks, vs, tables, 42, nkv, hd, dtype)
+    kc, vc = paged(ks, vs, tables, n_seq * per_seq, nkv, hd, dtype)
     q = torch.cat(qs).to(dtype)
     n = q.shape[0]
     out = torch.full((n, nh * hd), float("nan"), dtype=dtype, device=DEV)
@@ -881,3 +882,24 @@ def test_moe_permute_many_pairs_with_uneven_routing(n, k, e):
     assert n_tiles == sum((off[i + 1] - off[i] + tile - 1) // tile for i in range(e)) and sum(tc) == n * k
     assert all(off[g] <= r and r + c <= off[g + 1] and 0 < c <= tile for g, r, c in zip(tg, tr, tc))
     check_tile_cover(tr, tc, n * k, tile)
+
+
+def test_a_bounded_wait_that_runs_out_sets_the_status_and_leaves_the_device_usable():
+    """The waits inside the kernels poll a limited number of times.  Here one waits on a barrier that
+    nothing completes, with a limit of a few thousand polls: the kernel reports it and returns, the
+    engine turns the word into an error, and the next kernel runs as ever."""
+    st = status()
+    ops.wait_probe(4000, st)
+    torch.cuda.synchronize()
+    assert st.item() == 4
+    x = torch.empty(3, 200, device=DEV)
+    ok = status()
+    ops.embed_gather(rnd(10, 200), torch.tensor([1, 2, 3], dtype=torch.int32, device=DEV), x, ok)
+    assert ok.item() == 0 and torch.isfinite(x).all()
+
+
+def test_attn_prefill_tc05_with_more_items_than_the_gpu_has_sms():
+    """More (tile, head) items than the GPU has SMs, so that every persistent block of the tensor-memory
+    prefill attention takes a second and third item with its rings and phases carried over."""
+    check_attn_prefill(ops.attn_prefill_tc05, 24, 8, 128, None, tile=ops.ATTN_TC05_TILE_ROWS, runs=[
+        (0, 900), (130, 700), (0, 1), (63, 66), (300, 129), (10, 420), (0, 384), (5, 250)])

@@ -33,8 +33,9 @@ def make(family, spec, dtype, seed=3, init=InitSpec(0.08, 0.05, 0.05)):
     return rt, part, weights
 
 
-def context(rt, cache, runs):
-    """runs: [(slot, past, new)] -> a StepContext with pages reserved."""
+def context(rt, cache, runs, part=None):
+    """runs: [(slot, past, new)] -> a StepContext with pages reserved and the index lists ``part`` asks for."""
+    from esp_b200.parts.base import StepHost
     growth = {s: n for s, _p, n in runs}
     cache.book.reserve(growth)
     slots = [s for s, _, _ in runs]
@@ -47,10 +48,13 @@ def context(rt, cache, runs):
     ctx = StepContext(n_tokens=len(seq), n_seqs=len(runs), max_new=max(n for _, _, n in runs),
                       max_len=max(p + n for _, p, n in runs), tok_ids=t(np.zeros(len(seq))), tok_seq=t(seq),
                       tok_pos=t(pos), seq_slot=t(slots), seq_start=t(starts), seq_past=t([p for _, p, _ in runs]),
-                      want_rows=t([]), q_tile_seq=t([i for i, (_s, _p, n) in enumerate(runs) for _ in range(0, n, 64)]),
-                      q_tile_first=t([f for _s, _p, n in runs for f in range(0, n, 64)]), block_tables=tables,
+                      want_rows=t([]), block_tables=tables,
                       host={"slots": slots, "news": [n for _, _, n in runs], "pasts": [p for _, p, _ in runs],
                             "starts": list(starts)}, aux={})
+    if part is not None:
+        host = StepHost(tuple(slots), tuple(n for _, _, n in runs), tuple(p for _, p, _ in runs),
+                        tuple(int(v) for v in starts))
+        ctx.arrays = {name: t(a) for name, a in part.step_arrays(host).items()}
     return ctx, growth
 
 
@@ -87,13 +91,13 @@ def test_attention_part_with_cache_across_steps(dtype, nh, nkv, hd, window, thet
     got = [[], []]
     # both sequences start together with unequal prompts, then go on one token at a time
     cuts = [lens[0] - 20, lens[1] - 20]
-    ctx, growth = context(rt, cache, [(slots[0], 0, cuts[0]), (slots[1], 0, cuts[1])])
+    ctx, growth = context(rt, cache, [(slots[0], 0, cuts[0]), (slots[1], 0, cuts[1])], attn)
     h = torch.cat([xs[0][:cuts[0]], xs[1][:cuts[1]]]).to(dtype).to(DEV)
     y = attn.forward(h, ctx, cache.layers[0]).clone()
     cache.book.commit(growth)
     got[0].append(y[:cuts[0]]), got[1].append(y[cuts[0]:])
     for i in range(20):
-        ctx, growth = context(rt, cache, [(slots[0], cuts[0] + i, 1), (slots[1], cuts[1] + i, 1)])
+        ctx, growth = context(rt, cache, [(slots[0], cuts[0] + i, 1), (slots[1], cuts[1] + i, 1)], attn)
         h = torch.stack([xs[0][cuts[0] + i], xs[1][cuts[1] + i]]).to(dtype).to(DEV)
         y = attn.forward(h, ctx, cache.layers[0]).clone()
         cache.book.commit(growth)
@@ -167,7 +171,13 @@ class RunningMeanSpec:
 class RunningMean(Part):
     """delta_t = W * mean(h_0 .. h_t): needs the sum of the sequence's earlier
     rows, which it keeps as per-sequence state of fixed size [hidden + 1]
-    (the sum and the count).  No keys, no values, no pages."""
+    (the sum and the count).  No keys, no values, no pages.
+
+    It may run inside a captured step: it reads nothing from ``ctx.host``; which
+    state row a sequence owns comes from ``ctx.seq_slot`` on the device, and the
+    runs of rows of a sequence from ``ctx.tok_seq``."""
+
+    graph_safe = True
 
     def __init__(self, spec, rt):
         self.spec, self.rt, self.w = spec, rt, None
@@ -186,15 +196,20 @@ class RunningMean(Part):
         return StateSpec((self.spec.hidden + 1,), torch.float32)
 
     def forward(self, h, ctx, layer):
-        out = torch.empty(h.shape[0], self.spec.hidden, dtype=torch.float32, device=h.device)
-        for b, slot in enumerate(ctx.host["slots"]):
-            a, e = ctx.host["starts"][b], ctx.host["starts"][b + 1]
-            state = layer.state[slot]
-            sums = state[:-1] + torch.cumsum(h[a:e].float(), 0)
-            counts = state[-1] + torch.arange(1, e - a + 1, device=h.device, dtype=torch.float32)
-            out[a:e] = (sums / counts[:, None]) @ self.w.t()
-            state[:-1] = sums[-1]
-            state[-1] = counts[-1]
+        n, b = h.shape[0], ctx.n_seqs
+        seq = ctx.tok_seq.long()                                     # [N] sequence of every row
+        slot = ctx.seq_slot.long()                                   # [B] state row of every sequence
+        x = h.float()
+        # sums of a sequence's rows up to each row: a cumulative sum over all rows minus what came before the sequence
+        total = torch.cumsum(x, 0)
+        start = ctx.seq_start.long()[:b]                             # first row of every sequence
+        before = torch.where(start[:, None] > 0, total[(start - 1).clamp(min=0)], torch.zeros_like(total[:1]))
+        state = layer.state[slot]                                    # [B, hidden + 1]
+        sums = total - before[seq] + state[seq, :-1]
+        counts = (torch.arange(n, device=h.device) - start[seq] + 1).float() + state[seq, -1]
+        out = (sums / counts[:, None]) @ self.w.t()
+        last = ctx.seq_start.long()[1:b + 1] - 1                     # last row of every sequence
+        layer.state.index_copy_(0, slot, torch.cat([sums[last], counts[last, None]], 1))
         return out
 
 
@@ -248,6 +263,60 @@ def test_toy_mixer_with_its_own_state_runs_through_the_engine():
         x = x + plain.dense_mlp(w, p + "mlp.", h)
     ref = plain.rms_norm(x, w["toy.norm.weight"], 1e-6) @ w["toy.embed.weight"].T
     assert np.abs(whole - ref).max() <= 2e-5 * np.abs(ref).max()
+
+
+def test_toy_mixer_decodes_from_a_graph_in_another_slot_than_the_one_it_was_captured_in():
+    """The graph of a decode step is captured while the sequence sits in one slot and replayed for a
+    sequence in another: a part that took its slot from the host when the graph was made would read the
+    wrong state on replay."""
+    register("mixer", "toy_running_mean", RunningMean)
+    eng = Engine.from_random(ToyConfig(), seed=2, init=InitSpec(0.3, 0.0, 0.0), dtype="float32", max_tokens=512)
+    assert eng._parts_graph_safe
+    rng = np.random.default_rng(3)
+    toks = [int(t) for t in rng.integers(0, 100, 30)]
+    s = eng.open()
+    whole = eng.step([StepEntry(s, toks, list(range(30)))]).cpu().numpy()
+    eng.close(s)
+
+    def prompt_then_decode(slot):
+        rows = [eng.step([StepEntry(slot, toks[:6], list(range(6)))]).cpu().numpy()]
+        rows += [eng.step([StepEntry(slot, [t], [0])]).cpu().numpy() for t in toks[6:]]
+        return np.concatenate(rows)
+
+    first = eng.open()
+    a = prompt_then_decode(first)                  # eager step, capture, replays: all in this slot
+    replays = eng.graph_replays
+    assert replays > 10, "the decode steps were meant to replay a captured graph"
+    spare = eng.open()                             # holds the slot that ``first`` would get back
+    eng.close(first)
+    other = eng.open()
+    filler = eng.open()
+    assert other != first or filler != first
+    eng.close(other)
+    second = filler                                # a slot that the captured steps never saw
+    assert second != first
+    b = prompt_then_decode(second)
+    assert eng.graph_replays > replays + 10
+    eng.close(second), eng.close(spare)
+    for got in (a, b):
+        assert np.abs(got - whole).max() <= 1e-5 * np.abs(whole).max()
+
+
+def test_a_part_that_is_not_graph_safe_keeps_the_engine_from_capturing():
+    class HostReading(RunningMean):
+        graph_safe = False
+
+    register("mixer", "toy_running_mean", HostReading)
+    try:
+        eng = Engine.from_random(ToyConfig(), seed=2, init=InitSpec(0.3, 0.0, 0.0), dtype="float32", max_tokens=256)
+        s = eng.open()
+        eng.step([StepEntry(s, [1, 2, 3], [2])])
+        for t in range(8):
+            eng.step([StepEntry(s, [t], [0])])
+        eng.close(s)
+        assert eng.graph_replays == 0 and not eng._graphs
+    finally:
+        register("mixer", "toy_running_mean", RunningMean)
 
 
 def eng_tensor(eng, name):
@@ -390,3 +459,162 @@ def test_toy_position_encoding_and_toy_routed_ffn_run_through_the_engine():
     a = eng.step([StepEntry(s, [5, 7, 7], [1, 2])]).cpu().numpy()
     eng.close(s)
     assert np.abs(a[0] - a[1]).max() > 1e-4
+
+
+# ---------------------------------------------------------------------------
+# a toy norm behind a sparse layer, and the model's two ends
+# ---------------------------------------------------------------------------
+class CenteredNorm(Part):
+    """h = (v - mean(v)) / sqrt(var(v) + eps) * weight with v = x + delta: a norm that knows nothing of
+    deferred expert sums, so it must be handed plain tensors."""
+
+    graph_safe = True
+    seen_delta_types = set()
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt, self.weight = spec, rt, None
+
+    def param_specs(self):
+        return [ParamSpec(self.spec.weight, (self.spec.width,), "norm_scale")]
+
+    def allocate(self, stored, rt):
+        self.weight = torch.empty(self.spec.width, dtype=torch.float32, device=rt.device)
+        return {self.spec.weight: self.weight}
+
+    def forward(self, x, delta, h, rows=None, write_x=True, h32=None):
+        CenteredNorm.seen_delta_types.add(type(delta))
+        v = x if delta is None else x + delta
+        if delta is not None and write_x:
+            x.copy_(v)
+        if rows is not None:
+            v = v[rows.long()]
+        c = v - v.mean(-1, keepdim=True)
+        out = c / torch.sqrt((c * c).mean(-1, keepdim=True) + self.spec.eps) * self.weight
+        h.copy_(out)
+        if h32 is not None:
+            h32.copy_(out)
+        return h
+
+
+def test_a_toy_norm_after_a_sparse_layer_gets_plain_tensors():
+    """The sparse block hands on a deferred sum that only the library's own norm folds into its launch;
+    a norm from outside must see an ordinary tensor, in the blocks and at the model's end."""
+    import dataclasses
+    from esp_b200.config import config_from_dict
+    from tiny import TINY_A
+
+    class Renormed:
+        def __init__(self):
+            self.inner = config_from_dict(TINY_A)
+
+        def plan(self):
+            plan = self.inner.plan()
+            swap = lambda n: dataclasses.replace(n, kind="toy_centered_norm")
+            plan.blocks = [dataclasses.replace(b, mixer_norm=swap(b.mixer_norm), ffn_norm=swap(b.ffn_norm))
+                           for b in plan.blocks]
+            plan.final_norm = swap(plan.final_norm)
+            return plan
+
+    register("norm", "toy_centered_norm", CenteredNorm)
+    CenteredNorm.seen_delta_types = set()
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_random(Renormed(), seed=6, init=InitSpec(0.05, 0.02, 0.01), dtype=dtype, max_tokens=256)
+        toks = [int(t) for t in np.random.default_rng(2).integers(0, 256, 50)]
+        s = eng.open()
+        whole = eng.step([StepEntry(s, toks, list(range(50)))]).cpu().numpy()
+        eng.close(s)
+        s = eng.open()
+        rows = [eng.step([StepEntry(s, toks[:20], list(range(20)))]).cpu().numpy()]
+        rows += [eng.step([StepEntry(s, [t], [0])]).cpu().numpy() for t in toks[20:]]
+        eng.close(s)
+        assert np.isfinite(whole).all() and eng.read_status() == 0
+        tol = 1e-5 if dtype == "float32" else 4 * 2.0 ** -8
+        assert np.abs(np.concatenate(rows) - whole).max() <= tol * np.abs(whole).max()
+    assert CenteredNorm.seen_delta_types <= {torch.Tensor, type(None)}, CenteredNorm.seen_delta_types
+
+
+def test_embedding_scale_and_logit_softcap_of_a_plan():
+    """The model's two ends take a scale and a cap from the plan: the scaled model equals the unscaled one
+    whose table was multiplied beforehand, and the cap is cap * tanh(logits / cap)."""
+    scale, cap = 3.0, 0.25
+
+    class Ends(ToyAttentionConfig):
+        def __init__(self, with_ends):
+            self.with_ends = with_ends
+
+        def plan(self):
+            plan = super().plan()
+            plan.head_weight = "t.head.weight"
+            if self.with_ends:
+                plan.embed_scale, plan.logit_softcap = scale, cap
+            return plan
+
+    register("position", "toy_scaled_position", ScaledPosition)
+    register("ffn", "toy_top1_ffn", Top1Ffn)
+    toks = [int(t) for t in np.random.default_rng(4).integers(0, 90, 25)]
+    outs = []
+    for with_ends in (False, True):
+        eng = Engine.from_random(Ends(with_ends), seed=3, init=InitSpec(0.2, 0.05, 0.0), dtype="float32", max_tokens=256)
+        if not with_ends:
+            eng.model.embed.mul_(scale)
+        s = eng.open()
+        outs.append(eng.step([StepEntry(s, toks, list(range(25)))]).cpu().numpy())
+        eng.close(s)
+        assert eng.read_status() == 0
+    want = cap * np.tanh(outs[0].astype(np.float64) / cap)
+    assert np.abs(outs[0]).max() > cap, "the cap is meant to bite"
+    assert np.abs(outs[1] - want).max() <= 2e-6 * cap
+
+
+# ---------------------------------------------------------------------------
+# two probes of the attention part (crates/esp/src/infer/decoder/attention.rs:518-627)
+# ---------------------------------------------------------------------------
+def run_attention(attn, rt, dtype, x, cut):
+    """The part's output for the rows of ``x``: the first ``cut`` rows as one step, the rest one by one."""
+    cache = Cache([(attn.kv_layout(), None, None)], 1024, 2, 600, dtype, rt.device)
+    slot = cache.open()
+    outs = []
+    for a, b in [(0, cut)] + [(i, i + 1) for i in range(cut, x.shape[0])]:
+        ctx, growth = context(rt, cache, [(slot, a, b - a)], attn)
+        outs.append(attn.forward(x[a:b].to(dtype).to(DEV), ctx, cache.layers[0]).clone())
+        cache.book.commit(growth)
+    assert rt.status.item() == 0
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd, rows, cut", [(24, 40, 33), (128, 200, 200), (128, 150, 140), (64, 70, 64)])
+def test_changing_the_last_token_changes_no_earlier_row(dtype, hd, rows, cut):
+    """The causal-mask probe: with only the last token moved, every earlier row's output keeps its bits (a
+    missing or inverted mask, or a kernel whose rows share a reduction, would show), and the last row's
+    output changes."""
+    hidden = 96
+    spec = AttentionSpec(hidden, 4, 2, hd, True, False, None, PositionSpec("rope_split_half", hd, 1e4, 600), "a.")
+    rt, attn, _w = make("mixer", spec, dtype)
+    x = torch.randn(rows, hidden, generator=torch.Generator().manual_seed(5)) * 0.5
+    moved = x.clone()
+    moved[-1] += 1.0
+    a, b = run_attention(attn, rt, dtype, x, cut), run_attention(attn, rt, dtype, moved, cut)
+    assert torch.equal(a[:-1], b[:-1]), "an earlier position changed when only the last token moved"
+    assert (a[-1] - b[-1]).abs().max() > 1e-3, "the moved position itself must change"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd, rows, cut", [(24, 40, 33), (128, 200, 190), (64, 140, 130)])
+def test_grouped_heads_equal_full_heads_with_duplicated_key_value_blocks(dtype, hd, rows, cut):
+    """Attention with 2 key/value heads for 4 query heads equals attention with 4 key/value heads whose k and
+    v weights (and biases) repeat each block once per group: query head i reads key/value head i // 2."""
+    hidden, nh, nkv = 96, 4, 2
+    pos = PositionSpec("rope_split_half", hd, 1e4, 600)
+    rt, gqa, _w = make("mixer", AttentionSpec(hidden, nh, nkv, hd, True, False, None, pos, "a."), dtype)
+    rt2, mha, _w2 = make("mixer", AttentionSpec(hidden, nh, nh, hd, True, False, None, pos, "a."), dtype, seed=8)
+    q_rows, kv_rows = nh * hd, nkv * hd
+    dup = lambda t: t.reshape(nkv, hd, *t.shape[1:]).repeat_interleave(nh // nkv, 0).reshape(nh * hd, *t.shape[1:])
+    for src, dst in ((gqa.w_qkv, mha.w_qkv), (gqa.b_qkv, mha.b_qkv)):
+        dst[:q_rows].copy_(src[:q_rows])
+        dst[q_rows:q_rows + nh * hd].copy_(dup(src[q_rows:q_rows + kv_rows]))
+        dst[q_rows + nh * hd:].copy_(dup(src[q_rows + kv_rows:]))
+    mha.w_o.copy_(gqa.w_o)
+    x = torch.randn(rows, hidden, generator=torch.Generator().manual_seed(6)) * 0.5
+    a, b = run_attention(gqa, rt, dtype, x, cut), run_attention(mha, rt2, dtype, x, cut)
+    assert torch.equal(a, b), f"grouped and duplicated heads differ by {(a - b).abs().max().item():.3e}"

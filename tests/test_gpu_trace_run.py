@@ -103,6 +103,35 @@ def test_three_cuttings_through_the_program(tmp_path, case, dtype):
                   f"{(np.abs(got[0] - ref[rid]).max(axis=1) <= REL_TOL[dtype] * scale).mean():.0%}")
 
 
+@pytest.mark.parametrize("case", ["A", "B"])
+def test_three_cuttings_through_the_program_in_bfloat16_every_row(tmp_path, case):
+    """The same in bfloat16 on the model with every expert chosen for every token, where no near tie of the
+    router can move a row: every row of every cutting against the plain implementation.  The decode steps
+    of the program are replayed from captured graphs."""
+    raw = dict(CASES[case][0])
+    folder = make_folder(tmp_path, case, num_experts_per_tok=raw["num_experts"])
+    rng = np.random.default_rng(12)
+    lengths = [90, 40, 33, 64] if case == "A" else [150, 40, 65, 33]
+    reqs = {f"q{i}": random_ids(rng, n, raw["vocab_size"]) for i, n in enumerate(lengths)}
+    prompt_lens = {"q0": lengths[0] - 32, "q1": lengths[1] - 3, "q2": 1, "q3": lengths[3]}
+    whole, tail = steps_whole(reqs), steps_tail(reqs, 32)
+    batches = steps_batches(reqs, [["q0", "q1"], ["q2", "q3"]], prompt_lens)
+    need = max(sum((len(reqs[r]) + 63) // 64 * 64 for r in b) for b in (["q0", "q1"], ["q2", "q3"]))
+    out = tmp_path / "out"
+    wanted = replay(folder, "bfloat16", whole + tail + batches, out, need)
+    c, w = plain.load_model(folder)
+    offset = 0
+    for part in (whole, tail, batches):
+        rows = collect(part, out, raw["vocab_size"], wanted[offset:offset + len(part)], offset)
+        offset += len(part)
+        for rid, toks in reqs.items():
+            ref = plain.forward_logits(c, w, toks)
+            got = np.stack([rows[rid][p] for p in range(len(toks))])
+            err = np.abs(got - ref).max(axis=1)
+            bound = REL_TOL["bfloat16"] * max(1e-6, float(np.abs(ref).max()))
+            assert (err <= bound).all(), (rid, int(np.argmax(err > bound)), float(err.max()), bound)
+
+
 def test_rows_positions_helper_counts_unwanted_tokens(tmp_path):
     """A step that wants nothing writes no file and still advances the request."""
     folder = make_folder(tmp_path, "A")

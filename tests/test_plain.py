@@ -25,6 +25,28 @@ def test_recorded_logits_and_greedy_ids(name, dtype):
     assert ids == case["generated_ids"]
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_recorded_outputs_of_the_windowed_checkpoint_pin_the_mask(dtype):
+    """The reference's dense ``qwen2`` checkpoint runs the same attention code with q/k/v bias, one key/value
+    head for two query heads, ``layer_types`` [full, sliding] and a window of 3 over a prompt of 9 tokens:
+    its recorded logits pin the window's mask (a query sees itself and two predecessors), which layer is
+    windowed, and the decode steps behind the window.  Every layer is dense here."""
+    case = CASES["qwen2"]
+    c, w = plain.load_model(GOLDEN / "qwen2")
+    assert [plain.layer_window(c, i) for i in range(2)] == [None, 3]
+    logits = plain.forward_logits(c, w, case["input_ids"], dtype)
+    err = np.abs(logits[-1] - np.asarray(case["last_logits"], dtype=np.float32)).max()
+    assert err < (2e-6 if dtype is np.float32 else 5e-7), err
+    assert plain.generate(c, w, case["input_ids"], 4, dtype=dtype) == case["generated_ids"]
+    # the recorded numbers do depend on the window: with one key more or one key fewer they are missed
+    for other in (2, 4, None):
+        wrong = dict(c, sliding_window=other) if other else dict(c, layer_types=None, use_sliding_window=False)
+        off = np.abs(plain.forward_logits(wrong, w, case["input_ids"], dtype)[-1] - np.asarray(case["last_logits"])).max()
+        assert off > 1e-4, (other, off)
+    # without layer_types, use_sliding_window + max_window_layers 1 name the same layer
+    assert [plain.layer_window(dict(c, layer_types=None), i) for i in range(2)] == [None, 3]
+
+
 def test_splitmix64_known_values():
     # first outputs of splitmix64 from seed 0 (public test vector of the generator)
     r = plain.SplitMix64(0)
