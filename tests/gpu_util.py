@@ -90,9 +90,10 @@ def run_steps(engine, steps, recorder):
             meta.append((rid, pos[rid], len(tokens), want))
             pos[rid] += len(tokens)
         if es:
-            aux = {}
+            # a step that is asked to record is never replayed from a graph: ask only where the engine records
+            aux = {} if engine.rt.record_routing else None
             logits = engine.step(es, aux)
-            recorder.take(meta, None, logits, aux)
+            recorder.take(meta, None, logits, aux or {})
         for rid in end:
             engine.close(slots.pop(rid))
     assert not slots, "the trace left requests open"
