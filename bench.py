@@ -120,7 +120,9 @@ def model_numbers(cfg, layers):
     flops_token = layers * 2 * (attn_w + E * H + H + 3 * H * Is + k * expert_w)
     return {"layer_fixed_bytes": 2 * layer_fixed, "expert_bytes": 2 * expert_w, "head_bytes": 2 * V * H,
             "flops_token": flops_token, "attn_flops_per_key": layers * 4 * nh * hd,
-            "kv_bytes_token": layers * 2 * nkv * hd * 2, "head_flops_row": 2 * V * H}
+            "kv_bytes_token": layers * 2 * nkv * hd * 2, "head_flops_row": 2 * V * H,
+            "dense_flops_token_layer": 2 * (attn_w + E * H + H + 3 * H * Is), "expert_flops_token_layer": 2 * k * expert_w,
+            "n_experts": E}
 
 
 def timed_steps(torch, fn, warmup, steps):
@@ -139,7 +141,7 @@ def timed_steps(torch, fn, warmup, steps):
 def decode_run(torch, engine, batch, context, warmup, steps, vocab, seed):
     """Prefills ``batch`` prompts so that warmup + steps decode steps end at
     ``context``, then times the decode steps on the device.  Returns
-    (ms per step, distinct experts per layer, slots)."""
+    (ms per step, distinct experts per sparse layer averaged over the timed steps, slots, prompt length)."""
     import numpy as np
     from esp_b200.engine import StepEntry
     rng = np.random.default_rng(seed)
@@ -155,13 +157,193 @@ def decode_run(torch, engine, batch, context, warmup, steps, vocab, seed):
         toks = rng.integers(0, vocab, batch).tolist()
         engine.step_and_pick([StepEntry(s, [t], [0]) for s, t in zip(slots, toks)], temps, tops)
 
-    engine.rt.record_routing = True
-    aux = {}
-    engine.step([StepEntry(s, [int(t)], [0]) for s, t in zip(slots, rng.integers(0, vocab, batch))], aux)
-    engine.rt.record_routing = False
-    distinct = [int(torch.unique(ids).numel()) for _p, _r, ids, _w, _pr in aux.get("routing", [])]
-    ms = timed_steps(torch, one, warmup, steps)
-    return ms, (sum(distinct) / len(distinct) if distinct else 0.0), slots, prompt_len
+    for _ in range(warmup):              # the steps that size scratch, load kernels and capture the graph
+        one()
+    before = engine.counters()
+    ms = timed_steps(torch, one, 0, steps)
+    after = engine.counters()
+    sparse_layers = sum(1 for b in engine.plan.blocks if getattr(b.ffn, "kind", "") == "moe_swiglu_shared")
+    reads = after.get("expert_reads", 0) - before.get("expert_reads", 0)
+    distinct = reads / (steps * sparse_layers) if sparse_layers else 0.0
+    return ms, distinct, slots, prompt_len
+
+
+def decode_roofline(nums, layers, batch, context, steps, distinct, ms, pk):
+    """Bytes a decode step has to read (every weight it uses once, and the cache of the live requests)
+    against the HBM peak."""
+    ctx_mean = context - (steps + 1) / 2
+    step_bytes = (layers * (nums["layer_fixed_bytes"] + distinct * nums["expert_bytes"]) + nums["head_bytes"]
+                  + batch * ctx_mean * nums["kv_bytes_token"])
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+            "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
+
+
+def prefill_numbers(nums, layers, T, ms, pk):
+    """``frac``: all FLOPs of the step over the tensor-core peak.  ``frac_of_bound``: against the sum over the
+    step's products of max(FLOPs / peak, weight bytes / HBM peak): at one prompt of 2,048 tokens the routed
+    experts are bound by streaming their weights, not by arithmetic."""
+    flops = nums["flops_token"] * T + nums["attn_flops_per_key"] * T * (T + 1) / 2 + nums["head_flops_row"]
+    peak_f, peak_b = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    dense = max(nums["dense_flops_token_layer"] * T / peak_f, nums["layer_fixed_bytes"] / peak_b)
+    routed = max(nums["expert_flops_token_layer"] * T / peak_f, nums["n_experts"] * nums["expert_bytes"] / peak_b)
+    attn = nums["attn_flops_per_key"] * T * (T + 1) / 2 / peak_f
+    head = max(nums["head_flops_row"] / peak_f, nums["head_bytes"] / peak_b)
+    bound_ms = (layers * (dense + routed) + attn + head) * 1e3
+    return {"value": round(T / ms * 1e3, 1), "tokens": T, "ms": round(ms, 3),
+            "frac": round(flops / (ms * 1e-3) / peak_f, 4), "bound_ms": round(bound_ms, 3),
+            "frac_of_bound": round(bound_ms / ms, 4)}
+
+
+def measure_shape(torch, raw, layers, batch, context, steps, warmup, pk, points=(1, 64), e2e=True, prefill=True,
+                  clocks=None):
+    """Builds the model with random weights and measures prefill, decode at ``batch``, the same through the
+    entry point, and decode at ``points``.  Returns a dict of results; the engine is freed before returning."""
+    import gc
+    import numpy as np
+    from esp_b200.config import config_from_dict
+    from esp_b200.csrc import ops
+    from esp_b200.engine import Engine, StepEntry
+    from esp_b200.provider import DecoderProvider, GenerationRequest
+    from esp_b200.weights import InitSpec
+
+    cfg = config_from_dict(dict(raw, num_hidden_layers=layers))
+    nums = model_numbers(raw, layers)
+    vocab = raw["vocab_size"]
+    biggest = max([batch, *points])
+    engine = Engine.from_random(cfg, seed=0, init=InitSpec(0.02, 0.02, 0.0), dtype="bfloat16",
+                                max_tokens=biggest * (context + 64), max_slots=biggest + 2)
+    torch.cuda.synchronize()
+    out = {}
+    rng = np.random.default_rng(1)
+    T = 2048
+
+    def prefill_once():
+        s = engine.open()
+        engine.step([StepEntry(s, rng.integers(0, vocab, T).tolist(), [T - 1])])
+        engine.close(s)
+
+    if prefill:
+        out["prefill"] = prefill_numbers(nums, layers, T, timed_steps(torch, prefill_once, 3, 5), pk)
+
+    launches_before = ops.launch_count()
+    if clocks is not None:
+        with clocks:
+            ms_step, distinct, slots, prompt_len = decode_run(torch, engine, batch, context, warmup, steps, vocab, 2)
+    else:
+        ms_step, distinct, slots, prompt_len = decode_run(torch, engine, batch, context, warmup, steps, vocab, 2)
+    out["gpu_launches"] = ops.launch_count() - launches_before
+    for s in slots:
+        engine.close(s)
+    out.update(ms_per_step=ms_step, value=batch / ms_step * 1e3, distinct=distinct, prompt_len=prompt_len,
+               roofline=decode_roofline(nums, layers, batch, context, steps, distinct, ms_step, pk))
+
+    if e2e:
+        prov = DecoderProvider(engine, None, max_batch=batch)
+        n_new = warmup + steps + 1
+        reqs = [GenerationRequest(prompt_ids=rng.integers(0, vocab, context - n_new).tolist(), max_tokens=n_new)
+                for _ in range(batch)]
+        marks = {}
+
+        def on_token(i, tok):
+            if i == batch - 1:            # the last sequence of a step: the step's tokens are on the host
+                marks[len(marks)] = time.perf_counter()
+            return False
+
+        prov.generate(reqs, on_token)
+        t0, t1 = marks[warmup], marks[warmup + steps]
+        h2d = engine.staged_bytes         # the last step's staged arrays: ids, positions, page tables, sampling options
+        out["e2e"] = {"value": round(batch * steps / (t1 - t0), 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                      "d2h_bytes_per_step": 4 * (batch + 1)}
+
+    out["points"], out["points_detail"] = {}, {}
+    for b in points:
+        n = max(8, steps // 2)
+        ms_b, d_b, sl, _p = decode_run(torch, engine, b, context, warmup, n, vocab, 3 + b)
+        for s in sl:
+            engine.close(s)
+        out["points"][f"decode_b{b}"] = round(b / ms_b * 1e3, 1)
+        out["points_detail"][f"decode_b{b}"] = {
+            "ms": round(ms_b, 4), "distinct_experts_per_layer": round(d_b, 1),
+            "hbm_frac": decode_roofline(nums, layers, b, context, n, d_b, ms_b, pk)["frac"]}
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def fp32_cuttings(torch, raw, layers, n_prompts=16, longest=1024, decoded=64, seed=7):
+    """The true 32-bit path at the headline layer sizes: ``n_prompts`` requests with prompt lengths uniform in
+    [1, longest] and ``decoded`` further given tokens each, run three ways: every request alone and whole; its
+    prompt, then its tokens one by one; all prompts as one batch, then one token of each per step.  The logits
+    at the last ``decoded`` + 1 positions of every request are compared on the device, bit for bit."""
+    import gc
+    import numpy as np
+    from esp_b200.config import config_from_dict
+    from esp_b200.engine import Engine, StepEntry
+    from esp_b200.weights import InitSpec
+
+    t_start = time.perf_counter()
+    cfg = config_from_dict(dict(raw, num_hidden_layers=layers))
+    rng = np.random.default_rng(seed)
+    vocab = raw["vocab_size"]
+    plens = [int(n) for n in rng.integers(1, longest + 1, n_prompts)]
+    reqs = [rng.integers(0, vocab, n + decoded).tolist() for n in plens]
+    tokens = sum((len(r) + 63) // 64 * 64 for r in reqs)
+    engine = Engine.from_random(cfg, seed=0, init=InitSpec(0.02, 0.02, 0.0), dtype="float32", stored_dtype="bfloat16",
+                                max_tokens=tokens + 64, max_slots=n_prompts + 1)
+    torch.cuda.synchronize()
+    t_built = time.perf_counter()
+
+    def whole():
+        rows = []
+        for r, n in zip(reqs, plens):
+            s = engine.open()
+            rows.append(engine.step([StepEntry(s, r, list(range(n - 1, len(r))))]))
+            engine.close(s)
+        return rows
+
+    def one_by_one():
+        rows = []
+        for r, n in zip(reqs, plens):
+            s = engine.open()
+            got = [engine.step([StepEntry(s, r[:n], [n - 1])])]
+            got += [engine.step([StepEntry(s, [t], [0])]) for t in r[n:]]
+            engine.close(s)
+            rows.append(torch.cat(got))
+        return rows
+
+    def batched():
+        slots = [engine.open() for _ in reqs]
+        first = engine.step([StepEntry(s, r[:n], [n - 1]) for s, r, n in zip(slots, reqs, plens)])
+        steps = [first]
+        for j in range(decoded):
+            steps.append(engine.step([StepEntry(s, [r[n + j]], [0]) for s, r, n in zip(slots, reqs, plens)]))
+        for s in slots:
+            engine.close(s)
+        stacked = torch.stack(steps, 1)             # [request, step, vocab]
+        return [stacked[i] for i in range(len(reqs))]
+
+    times, results = {}, {}
+    for name, fn in (("whole", whole), ("one_by_one", one_by_one), ("batched", batched)):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        results[name] = fn()
+        torch.cuda.synchronize()
+        times[name] = round(time.perf_counter() - t0, 2)
+    equal = all(torch.equal(a, b) and torch.equal(a, c)
+                for a, b, c in zip(results["whole"], results["one_by_one"], results["batched"]))
+    finite = all(bool(torch.isfinite(a).all()) for a in results["whole"])
+    status = engine.read_status()
+    out = {"fp32_cuttings_equal": bool(equal and finite and status == 0), "layers": layers, "prompts": n_prompts,
+           "prompt_tokens": sum(plens), "decoded_each": decoded, "rows_compared": n_prompts * (decoded + 1),
+           "seconds": times, "build_seconds": round(t_built - t_start, 1),
+           "weights_gb": round(engine.memory_plan["weights_bytes"] / 1e9, 1),
+           "prefill_tok_s": round(sum(plens) / max(times["batched"], 1e-9), 1)}
+    del engine, results
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
 
 
 def main() -> int:
@@ -177,6 +359,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement (for profiling decode)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the 32-bit cuttings check at the headline sizes and the Qwen2-57B-A14B shape")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -189,104 +373,56 @@ def main() -> int:
         return 2
     a.warmup = max(a.warmup, 3)
 
-    import numpy as np
     import torch
-    from esp_b200.config import config_from_dict
-    from esp_b200.csrc import ops
-    from esp_b200.engine import Engine, StepEntry
-    from esp_b200.provider import DecoderProvider, GenerationRequest
-    from esp_b200.weights import InitSpec
 
     pk = peaks()
-    shape, shape_name = SHAPES[a.shape]
-    full_layers = shape["num_hidden_layers"]
+    raw, shape_name = SHAPES[a.shape]
+    full_layers = raw["num_hidden_layers"]
     if a.layers is None:
         a.layers = full_layers
-    raw = dict(shape, num_hidden_layers=a.layers)
-    cfg = config_from_dict(raw)
-    nums = model_numbers(raw, a.layers)
-    vocab = raw["vocab_size"]
-    biggest = max(a.batch, 1 if a.no_points else 64)
-    engine = Engine.from_random(cfg, seed=0, init=InitSpec(0.02, 0.02, 0.0), dtype="bfloat16",
-                                max_tokens=biggest * (a.context + 64), max_slots=biggest + 2)
-    torch.cuda.synchronize()
+    clocks = ClockSampler()
+    m = measure_shape(torch, raw, a.layers, a.batch, a.context, a.steps, a.warmup, pk,
+                      points=() if a.no_points else (1, 64), e2e=not a.no_e2e, prefill=not a.no_prefill, clocks=clocks)
 
-    # ---- prefill of one 2,048-token prompt --------------------------------------
-    rng = np.random.default_rng(1)
-    T = 2048
-
-    def prefill_once():
-        s = engine.open()
-        engine.step([StepEntry(s, rng.integers(0, vocab, T).tolist(), [T - 1])])
-        engine.close(s)
-
-    prefill = None
-    if not a.no_prefill:
-        ms_prefill = timed_steps(torch, prefill_once, 3, 5)
-        prefill_flops = nums["flops_token"] * T + nums["attn_flops_per_key"] * T * (T + 1) / 2 + nums["head_flops_row"]
-        prefill = {"value": round(T / ms_prefill * 1e3, 1), "tokens": T, "ms": round(ms_prefill, 3),
-                   "frac": round(prefill_flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
-
-    # ---- decode at the headline batch ---------------------------------------------
-    launches_before = ops.launch_count()
-    with ClockSampler() as clocks:
-        ms_step, distinct, slots, prompt_len = decode_run(torch, engine, a.batch, a.context, a.warmup, a.steps, vocab, 2)
-    launches = ops.launch_count() - launches_before
-    for s in slots:
-        engine.close(s)
-    ctx_mean = a.context - (a.steps + 1) / 2
-    step_bytes = (a.layers * (nums["layer_fixed_bytes"] + distinct * nums["expert_bytes"]) + nums["head_bytes"]
-                  + a.batch * ctx_mean * nums["kv_bytes_token"])
-    achieved = step_bytes / (ms_step * 1e-3) / 1e9
-    value = a.batch / ms_step * 1e3
-
-    # ---- the same through the Python entry point ------------------------------------
-    e2e = None
-    if not a.no_e2e:
-        prov = DecoderProvider(engine, None, max_batch=a.batch)
-        n_new = a.warmup + a.steps + 1
-        reqs = [GenerationRequest(prompt_ids=rng.integers(0, vocab, a.context - n_new).tolist(), max_tokens=n_new)
-                for _ in range(a.batch)]
-        marks = {}
-
-        def on_token(i, tok):
-            if i == a.batch - 1:          # the last sequence of a step: the step's tokens are on the host
-                marks[len(marks)] = time.perf_counter()
-            return False
-
-        prov.generate(reqs, on_token)
-        t0, t1 = marks[a.warmup], marks[a.warmup + a.steps]
-        h2d = engine.staged_bytes         # the last step's staged arrays: ids, positions, page tables, sampling options
-        e2e = {"value": round(a.batch * a.steps / (t1 - t0), 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": 4 * (a.batch + 1)}
-
-    # ---- decode at batch 1 and 64 --------------------------------------------------------
-    points = {}
-    if not a.no_points:
-        for b in (1, 64):
-            ms_b, _d, sl, _p = decode_run(torch, engine, b, a.context, a.warmup, max(8, a.steps // 2), vocab, 3 + b)
-            for s in sl:
-                engine.close(s)
-            points[f"decode_b{b}"] = round(b / ms_b * 1e3, 1)
+    extras = {}
+    if not a.no_extras and a.shape == "a2.7b":
+        # BASELINE's other two configurations, each guarded: a failure there must not lose the headline
+        try:
+            extras["fp32_path"] = fp32_cuttings(torch, raw, a.layers)
+        except Exception as e:                                   # noqa: BLE001
+            extras["fp32_path"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        try:
+            big, big_name = SHAPES["57b-a14b"]
+            q = measure_shape(torch, big, big["num_hidden_layers"], a.batch, 8192, max(8, a.steps // 2), a.warmup, pk,
+                              points=(1, 64), e2e=False, prefill=True)
+            extras["shape_57b_a14b"] = {
+                "model": big_name, "layers": big["num_hidden_layers"], "context": 8192,
+                "decode_b8": round(q["value"], 1), "decode_b8_ms": round(q["ms_per_step"], 3),
+                "decode_b8_hbm_frac": q["roofline"]["frac"], "distinct_b8": round(q["distinct"], 1),
+                **q["points"], "points_detail": q["points_detail"], "prefill": q["prefill"]}
+        except Exception as e:                                   # noqa: BLE001
+            extras["shape_57b_a14b"] = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     line = {
-        "metric": f"decode tok/s at batch {a.batch}", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
-        "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "metric": f"decode tok/s at batch {a.batch}", "value": round(m["value"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(m["ms_per_step"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights N(0,0.02)",
         "impl": "esp_b200",
         "config": {"model": shape_name, "layers": a.layers, "layers_of_model": full_layers,
                    "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"],
-                   "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"], "vocab": vocab,
+                   "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"], "vocab": raw["vocab_size"],
                    "experts": raw["num_experts"], "top_k": raw["num_experts_per_tok"],
                    "moe_intermediate": raw["moe_intermediate_size"],
                    "shared_intermediate": raw["shared_expert_intermediate_size"], "global_batch": a.batch,
-                   "seq_len": a.context, "prompt_len": prompt_len, "parallelism": "1 GPU",
-                   "l2": "inputs larger than L2 (a step reads >10 GB)", "distinct_experts_per_layer": round(distinct, 1)},
-        "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(), "prefill": prefill,
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
-        "points": points,
+                   "seq_len": a.context, "prompt_len": m["prompt_len"], "parallelism": "1 GPU",
+                   "l2": "inputs larger than L2 (a step reads >10 GB)",
+                   "distinct_experts_per_layer": round(m["distinct"], 1)},
+        "e2e": m.get("e2e"), "gpu_launches": m["gpu_launches"], "clocks": clocks.summary(), "prefill": m.get("prefill"),
+        "roofline": m["roofline"], "points": m["points"], "points_detail": m["points_detail"],
     }
+    if "fp32_path" in extras:
+        line["fp32_cuttings_equal"] = extras["fp32_path"].get("fp32_cuttings_equal")
+    line.update(extras)
     print(json.dumps(line))
     return 0
 
