@@ -91,6 +91,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                       int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv,
                       int window, int n_splits, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int ITEM = PAGE_KEYS * HD;
     constexpr int NBW = HD / 32;                   // 8-column blocks of the head that one warp accumulates
     constexpr int PLD = PAGE_KEYS + 8;             // row stride of the probabilities (bfloat16)
@@ -357,7 +359,7 @@ int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, flo
     }
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + MMA_HEADS - 1) / MMA_HEADS), n_splits);
-    attn_split_mma_kernel<HD, SPLIT><<<grid, THREADS, dyn, stream>>>(map_k, map_v, q, out, po, pml, counters, tok_seq, tok_pos,
+    esp_launch_pdl(ESP_PDL_ATTENTION, attn_split_mma_kernel<HD, SPLIT>, dim3(grid), dim3(THREADS), dyn, stream, map_k, map_v, q, out, po, pml, counters, tok_seq, tok_pos,
                                                                      table, stride, n_pages, page, nh, nkv, window, n_splits,
                                                                      status);
     return esp_launch_status();

@@ -38,6 +38,9 @@ LIBRARIES = {
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+# further flags for a one-off build (e.g. -D switches of a kernel's tuning constants); part of the stamp, so a
+# changed value rebuilds; use ESP_B200_BUILD_DIR to keep such a build apart from the ordinary one
+NVCC_FLAGS += os.environ.get("ESP_B200_NVCC_FLAGS", "").split()
 
 _loaded: dict = {}
 _lock = threading.Lock()

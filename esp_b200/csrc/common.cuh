@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define ESP_API extern "C" __attribute__((visibility("default")))
 
@@ -70,3 +71,46 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 // Launch-error helper: the C entry points return cudaGetLastError() as an int.
 static inline int esp_launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------
+// A decode step is a chain of short kernels.  A kernel launched with esp_launch_pdl may be set up on the SMs
+// while the kernel before it in the stream is still running: its blocks start, do what needs nothing of the
+// predecessor (index arithmetic, the first loads of weights, which no kernel ever writes), and call pdl_wait()
+// before they read anything the predecessor wrote and before they write anything at all (the predecessor, or
+// the kernels before it, may still read what this kernel would overwrite).  pdl_wait() returns once the
+// predecessor has finished and its writes are visible; as the predecessor itself has waited for its own
+// predecessor, everything earlier in the stream is finished as well.  pdl_trigger() tells the scheduler that the
+// next kernel may be set up; it is called at the top, so that the next kernel's set-up overlaps as much as it can.
+// In a kernel launched the ordinary way both calls do nothing.  ESP_B200_PDL=0 turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+#define ESP_PDL_DEFAULT_MASK 9
+// classes of kernels, so that the attribute can be tried class by class: ESP_B200_PDL is a bit mask
+enum : int { ESP_PDL_DENSE = 1, ESP_PDL_GROUPED = 2, ESP_PDL_ATTENTION = 4, ESP_PDL_SMALL = 8 };
+static inline bool esp_pdl_enabled(int kind) {
+    static int mask = -1;
+    if (mask < 0) {
+        const char* e = getenv("ESP_B200_PDL");
+        mask = e ? atoi(e) : ESP_PDL_DEFAULT_MASK;
+    }
+    return (mask & kind) != 0;
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...) with the attribute that lets the kernel be set up before its
+// predecessor in the stream has finished.  Only for kernels that call pdl_wait() as described above.
+template <typename... KArgs, typename... Args>
+static inline void esp_launch_pdl(int kind, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = esp_pdl_enabled(kind) ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

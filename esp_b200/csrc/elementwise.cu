@@ -8,6 +8,8 @@
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
                                     int n_tokens, int width, int vocab, float scale, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     const int n = blockIdx.x;
     if (n >= n_tokens) return;
     int id = ids[n];
@@ -24,10 +26,10 @@ ESP_API int esp_embed_gather(const void* table, int table_is_bf16, const int* id
                              int vocab, float scale, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (table_is_bf16)
-        embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>((const bf16*)table, ids, x, n_tokens, width, vocab, scale,
+        esp_launch_pdl(ESP_PDL_SMALL, embed_gather_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)table, ids, x, n_tokens, width, vocab, scale,
                                                                 status);
     else
-        embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, x, n_tokens, width, vocab, scale,
+        esp_launch_pdl(ESP_PDL_SMALL, embed_gather_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)table, ids, x, n_tokens, width, vocab, scale,
                                                                  status);
     return esp_launch_status();
 }
@@ -36,13 +38,15 @@ ESP_API int esp_embed_gather(const void* table, int table_is_bf16, const int* id
 // ids[j] = picks[src[j]] where src[j] >= 0: a step that follows a step can take its tokens from the device,
 // before the host has seen them.
 __global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ picks, const int* __restrict__ src, int n) {
+    pdl_trigger();
+    pdl_wait();
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j < n && src[j] >= 0) ids[j] = picks[src[j]];
 }
 
 ESP_API int esp_feed_tokens(int* ids, const int* picks, const int* src, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    feed_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, picks, src, n);
+    esp_launch_pdl(ESP_PDL_SMALL, feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, picks, src, n);
     return esp_launch_status();
 }
 
@@ -58,6 +62,8 @@ template <typename TH>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma,
                                    const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
                                    float eps, int write_x) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
@@ -93,6 +99,8 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma,
                         const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width, float eps,
                         int write_x) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
@@ -142,16 +150,16 @@ ESP_API int esp_add_rmsnorm(float* x, const float* y, const float* gamma, const 
         // blocks, more rows in flight per SM.
         if (width / 4 <= 1024 && !(h_is_bf16 && n_rows >= 256)) threads = (width / 4 + 31) / 32 * 32;
         if (h_is_bf16)
-            add_rmsnorm_rows_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
+            esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_rows_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
         else
-            add_rmsnorm_rows_kernel<float><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (float*)h, h32, width, eps, write_x);
+            esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma, rows, (float*)h, h32, width, eps, write_x);
         return esp_launch_status();
     }
     const int threads = width >= 1024 ? 256 : 128;
     if (h_is_bf16)
-        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
+        esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
     else
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, y, gamma, rows, (float*)h, h32, width, eps, write_x);
+        esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma, rows, (float*)h, h32, width, eps, write_x);
     return esp_launch_status();
 }
 
@@ -204,6 +212,8 @@ ESP_API int esp_gather_rows(const void* src, const int* rows, void* out, int n_r
 
 // ---------------------------------------------------------------- finite check
 __global__ void finite_check_kernel(const float* __restrict__ v, long long count, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     bool bad = false;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
         bad |= !isfinite(v[i]);
@@ -214,7 +224,7 @@ ESP_API int esp_finite_check(const float* v, long long count, int* status, cudaS
     if (count <= 0) return 0;
     long long blocks = (count + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    finite_check_kernel<<<(int)blocks, 256, 0, stream>>>(v, count, status);
+    esp_launch_pdl(ESP_PDL_SMALL, finite_check_kernel, dim3((int)blocks), dim3(256), 0, stream, v, count, status);
     return esp_launch_status();
 }
 

@@ -19,7 +19,13 @@
 
 namespace {
 constexpr int WARPS = 8;
-constexpr int UNROLL = 4;
+#ifndef ESP_SKINNY_UNROLL
+#define ESP_SKINNY_UNROLL 4
+#endif
+#ifndef ESP_SKINNY_BLOCKS
+#define ESP_SKINNY_BLOCKS 3
+#endif
+constexpr int UNROLL = ESP_SKINNY_UNROLL;
 
 struct SkinnyParams {
     const bf16* W;
@@ -51,7 +57,7 @@ __device__ __forceinline__ uint4 load_stream(const bf16* p) {
 // tiles per block).  Few tiles: KS = 8, so that every SM still gets work; many tiles: KS = 1, each warp
 // walks all of K of its own tile (longer streams per warp, no reduction between warps); 2 and 4 lie between.
 template <int NBLK, bool SWIGLU, typename TC, int KS>
-__global__ void __launch_bounds__(WARPS * 32, 3)
+__global__ void __launch_bounds__(WARPS * 32, ESP_SKINNY_BLOCKS)
 gemm_skinny_kernel(SkinnyParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K = p.K;
@@ -62,7 +68,9 @@ gemm_skinny_kernel(SkinnyParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
     int m_begin = 0, m_end = p.M;
     const bf16* W = p.W;
+    pdl_trigger();
     if (p.group_offsets) {
+        pdl_wait();                                                   // which group a block takes was written by the kernel before
         int group = blockIdx.y;
         if ((int)gridDim.y < p.groups) {
             // fewer rows than groups (a decode step of one sequence names a few experts of many): the grid has
@@ -120,6 +128,17 @@ gemm_skinny_kernel(SkinnyParams p) {
         }
     };
     load_weights(k_lo);
+    if (!p.group_offsets) {
+        // The dense form knows its weights without the kernel before it: besides the first pieces, the lines
+        // that follow them (up to 1 KB of each row) are asked into L2, so that the weight stream is under way
+        // while the predecessor finishes; then wait for the predecessor, whose output the rows below are.
+        const int pre_hi = min(k_hi, k_lo + 32 * UNROLL + 512);
+        for (int k = k_lo + 32 * UNROLL + tg * 64; k < pre_hi; k += 256) {
+            if (ok_a) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wa_ptr + k));
+            if (ok_b) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wb_ptr + k));
+        }
+        pdl_wait();
+    }
 
     for (int m0 = m_begin; m0 < m_end; m0 += 8 * NBLK) {
         const int cnt = min(8 * NBLK, m_end - m0);
@@ -237,7 +256,7 @@ int launch_variant(const SkinnyParams& p, int groups, int tiles, cudaStream_t st
     }
     constexpr int TILES = WARPS / KS;
     dim3 grid((tiles + TILES - 1) / TILES, p.group_offsets && p.M < groups ? p.M : groups);   // every group that has rows starts below M
-    gemm_skinny_kernel<NBLK, SWIGLU, TC, KS><<<grid, WARPS * 32, smem, stream>>>(p);
+    esp_launch_pdl(p.group_offsets ? ESP_PDL_GROUPED : ESP_PDL_DENSE, gemm_skinny_kernel<NBLK, SWIGLU, TC, KS>, grid, dim3(WARPS * 32), smem, stream, p);
     return esp_launch_status();
 }
 

@@ -345,6 +345,8 @@ template <typename TH, typename TW>
 __global__ void __launch_bounds__(256)
 router_logits_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, const TW* __restrict__ w_gate,
                      float* __restrict__ logits, int width, int n_experts) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float hs[];
     const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rows = n_experts + (w_gate ? 1 : 0);
@@ -367,6 +369,8 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
                    int norm_topk, int has_gate, int* __restrict__ offsets, int* __restrict__ perm_token,
                    float* __restrict__ perm_weight, int* __restrict__ inverse, int* __restrict__ status,
                    unsigned long long* __restrict__ distinct) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float sm_f[];
     float* ps_all = sm_f;                                      // [8 warps][n_experts]
     int* counts = reinterpret_cast<int*>(sm_f + 8 * n_experts); // [n_experts]
@@ -614,6 +618,8 @@ moe_permute_kernel(const int* __restrict__ topk_ids, const float* __restrict__ t
 __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const int* __restrict__ topk_ids,
                                    const int* __restrict__ inverse, const float* __restrict__ gate,
                                    const float* __restrict__ shared, float* __restrict__ y, int width, int top_k) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ int order[MAX_TOPK];
     const int t = blockIdx.x;
     if (threadIdx.x == 0) {
@@ -670,6 +676,8 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
                                const float* __restrict__ shared, float* __restrict__ x, const float* __restrict__ gamma,
                                const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
                                int top_k, float eps, int write_x) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ int order[MAX_TOPK];
     __shared__ float scratch[33];
     const int r = blockIdx.x;
@@ -802,14 +810,14 @@ ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, 
     if (smem_a > 48 * 1024 || smem_b > 48 * 1024) return (int)cudaErrorInvalidValue;
     const dim3 grid(n_tokens, (n_experts + 1 + 7) / 8);
 #define ESP_LOGITS(TH, TW)                                                                                        \
-    router_logits_kernel<TH, TW><<<grid, 256, smem_a, stream>>>((const TH*)h, (const TW*)w_router, (const TW*)w_gate, \
+    esp_launch_pdl(ESP_PDL_SMALL, router_logits_kernel<TH, TW>, dim3(grid), dim3(256), smem_a, stream, (const TH*)h, (const TW*)w_router, (const TW*)w_gate, \
                                                                 logits, width, n_experts)
     if (h_is_bf16 && w_is_bf16) ESP_LOGITS(bf16, bf16);
     else if (h_is_bf16) ESP_LOGITS(bf16, float);
     else if (w_is_bf16) ESP_LOGITS(float, bf16);
     else ESP_LOGITS(float, float);
 #undef ESP_LOGITS
-    route_small_kernel<<<1, 256, smem_b, stream>>>(logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k,
+    esp_launch_pdl(ESP_PDL_SMALL, route_small_kernel, dim3(1), dim3(256), smem_b, stream, logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k,
                                                    norm_topk, w_gate ? 1 : 0, offsets, perm_token, perm_weight, inverse,
                                                    status, distinct);
     return esp_launch_status();
@@ -843,7 +851,7 @@ ESP_API int esp_moe_combine(const float* expert_out, const int* topk_ids, const 
                             const float* shared, float* y, int n_tokens, int width, int top_k, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK) return (int)cudaErrorInvalidValue;
-    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(expert_out, topk_ids, inverse, gate, shared, y, width, top_k);
+    esp_launch_pdl(ESP_PDL_SMALL, moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, expert_out, topk_ids, inverse, gate, shared, y, width, top_k);
     return esp_launch_status();
 }
 
@@ -859,10 +867,10 @@ ESP_API int esp_moe_combine_add_rmsnorm(const float* expert_out, const int* topk
     // more rows in flight per SM.
     if (width / 4 <= 1024 && !(h_is_bf16 && n_rows >= 256)) threads = (width / 4 + 31) / 32 * 32;
     if (h_is_bf16)
-        moe_combine_add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(expert_out, topk_ids, inverse, gate, shared, x, gamma,
+        esp_launch_pdl(ESP_PDL_SMALL, moe_combine_add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, expert_out, topk_ids, inverse, gate, shared, x, gamma,
                                                                             rows, (bf16*)h, h32, width, top_k, eps, write_x);
     else
-        moe_combine_add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(expert_out, topk_ids, inverse, gate, shared, x,
+        esp_launch_pdl(ESP_PDL_SMALL, moe_combine_add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, expert_out, topk_ids, inverse, gate, shared, x,
                                                                              gamma, rows, (float*)h, h32, width, top_k, eps,
                                                                              write_x);
     return esp_launch_status();

@@ -21,6 +21,8 @@ __global__ void rope_kvwrite_kernel(const float* __restrict__ qkv, const float* 
                                     T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ block_table,
                                     int table_stride, int n_pages, int page, int nh, int nkv, int hd, int write_kv,
                                     int heads_per_block, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     const int n = blockIdx.x;
     const int pos = tok_pos[n];
     const int seq = tok_seq[n];
@@ -94,6 +96,8 @@ rope_kvwrite_vec_kernel(const float* __restrict__ qkv, const float* __restrict__
                         int max_pos, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv,
                         int hd, int write_kv, int heads_per_block, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     const int n = blockIdx.x;
     const int pos = tok_pos[n], seq = tok_seq[n];
     const int half = hd / 2, quads = half / 4, heads = nh + 2 * nkv;
@@ -160,12 +164,12 @@ ESP_API int esp_rope_kvwrite(const float* qkv, const float* bias, const int* tok
         const int hpb = 64;
         const dim3 vgrid(n_tokens, (nh + 2 * nkv + hpb - 1) / hpb);
         if (is_bf16)
-            rope_kvwrite_vec_kernel<bf16><<<vgrid, 256, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, max_pos,
+            esp_launch_pdl(ESP_PDL_SMALL, rope_kvwrite_vec_kernel<bf16>, dim3(vgrid), dim3(256), 0, stream, qkv, bias, tok_seq, tok_pos, cos_t, sin_t, max_pos,
                                                                     (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache,
                                                                     block_table, table_stride, n_pages, page, nh, nkv, hd,
                                                                     write_kv, hpb, status);
         else
-            rope_kvwrite_vec_kernel<float><<<vgrid, 256, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, max_pos,
+            esp_launch_pdl(ESP_PDL_SMALL, rope_kvwrite_vec_kernel<float>, dim3(vgrid), dim3(256), 0, stream, qkv, bias, tok_seq, tok_pos, cos_t, sin_t, max_pos,
                                                                      (float*)q_out, (float*)k_cache, (float*)v_cache,
                                                                      block_table, table_stride, n_pages, page, nh, nkv,
                                                                      hd, write_kv, hpb, status);
@@ -175,11 +179,11 @@ ESP_API int esp_rope_kvwrite(const float* qkv, const float* bias, const int* tok
     const dim3 grid(n_tokens, (nh + 2 * nkv + heads_per_block - 1) / heads_per_block);
     const int threads = heads_per_block == 1 ? (hd >= 128 ? 128 : (hd + 31) / 32 * 32) : 256;
     if (is_bf16)
-        rope_kvwrite_kernel<bf16><<<grid, threads, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
+        esp_launch_pdl(ESP_PDL_SMALL, rope_kvwrite_kernel<bf16>, dim3(grid), dim3(threads), 0, stream, qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
                                                                (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, block_table,
                                                                table_stride, n_pages, page, nh, nkv, hd, write_kv, heads_per_block, status);
     else
-        rope_kvwrite_kernel<float><<<grid, threads, 0, stream>>>(qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
+        esp_launch_pdl(ESP_PDL_SMALL, rope_kvwrite_kernel<float>, dim3(grid), dim3(threads), 0, stream, qkv, bias, tok_seq, tok_pos, cos_t, sin_t, rot, max_pos,
                                                                 (float*)q_out, (float*)k_cache, (float*)v_cache,
                                                                 block_table, table_stride, n_pages, page, nh, nkv, hd,
                                                                 write_kv, heads_per_block, status);

@@ -84,6 +84,8 @@ __global__ void __launch_bounds__(PICK_THREADS)
 pick_tokens_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                    const float* __restrict__ top_p, unsigned long long* __restrict__ rng_state,
                    const int* __restrict__ row_slot, int* __restrict__ tokens) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float best_v[PICK_THREADS / 32];
     __shared__ int best_i[PICK_THREADS / 32];
     __shared__ unsigned long long hist[256];
@@ -161,6 +163,6 @@ pick_tokens_kernel(const float* __restrict__ logits, int vocab, const float* __r
 ESP_API int esp_pick_tokens(const float* logits, int n_rows, int vocab, const float* temperature, const float* top_p,
                             unsigned long long* rng_state, const int* row_slot, int* tokens, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    pick_tokens_kernel<<<n_rows, PICK_THREADS, 0, stream>>>(logits, vocab, temperature, top_p, rng_state, row_slot, tokens);
+    esp_launch_pdl(ESP_PDL_SMALL, pick_tokens_kernel, dim3(n_rows), dim3(PICK_THREADS), 0, stream, logits, vocab, temperature, top_p, rng_state, row_slot, tokens);
     return esp_launch_status();
 }
