@@ -1,6 +1,9 @@
 // Weight-streaming matrix product for a handful of rows (decode):
 //   C[m, n] = scale[m] * sum_k A[row(m), k] * W[g][n, k]          (PLAIN)
 //   act[m, j] = silu(A W_gate[j]) * (A W_up[j])                   (SWIGLU; W = [gate rows; up rows])
+//   q / k / v of a decode step: the packed q/k/v projection whose epilogue adds the bias, rotates queries and
+//   keys by the token's position (split-half pairs (i, i + hd/2)) and writes the keys and values into the
+//   paged cache                                                  (ROPE; a tile holds 8 pairs)
 // bfloat16 operands, float accumulation on the tensor cores (mma.sync
 // m16n8k16 with the weight rows as the 16-row operand and up to 8 tokens as the
 // 8-column operand, so a step with few rows wastes no tensor work and every
@@ -19,13 +22,10 @@
 
 namespace {
 constexpr int WARPS = 8;
-#ifndef ESP_SKINNY_UNROLL
-#define ESP_SKINNY_UNROLL 4
-#endif
-#ifndef ESP_SKINNY_BLOCKS
+// 16-byte pieces of each of its two weight rows that a lane has in flight, and blocks per SM.  Measured on the
+// 24-layer decode step: 4 pieces and 3 blocks beat 8 and 2, 6 and 2, 2 and 4 at batch 1 and at batch 8.
+constexpr int UNROLL = 4;
 #define ESP_SKINNY_BLOCKS 3
-#endif
-constexpr int UNROLL = ESP_SKINNY_UNROLL;
 
 struct SkinnyParams {
     const bf16* W;
@@ -39,7 +39,60 @@ struct SkinnyParams {
     long long ldc;
     int M, N, K;
     int groups;                     // grouped form: how many groups there are (the grid's y may be smaller)
+    // ROPE form only: N counts pairs (i, i + hd/2) over the nh + 2 nkv heads of the packed projection
+    const float* bias;              // [(nh + 2 nkv) * hd] or null
+    const int* tok_seq;
+    const int* tok_pos;
+    const float* cos_t;             // [max_pos, hd / 2]
+    const float* sin_t;
+    void* q_out;                    // [M, nh * hd] bfloat16
+    void* k_cache;                  // [pages, nkv, page, hd] bfloat16
+    void* v_cache;
+    const int* block_table;
+    int table_stride, n_pages, page, nh, nkv, hd, max_pos, write_kv;
+    int* status;
 };
+
+enum : int { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_ROPE = 2 };
+
+// One pair (x[i], x[i + hd/2]) of head ``head`` of token row m: bias, rotation in float with the same
+// operations in the same order as the separate kernel (rope_kv.cu), then the query row or the cache.
+__device__ __forceinline__ void emit_rope_pair(const SkinnyParams& p, int m, int pair, float lo, float hi) {
+    const int half = p.hd / 2, head = pair / half, i = pair - head * half;
+    if (p.bias) {
+        lo += p.bias[(size_t)head * p.hd + i];
+        hi += p.bias[(size_t)head * p.hd + i + half];
+    }
+    const int pos = p.tok_pos[m];
+    if (pos < 0 || pos >= p.max_pos) {
+        atomicOr(p.status, ESP_STATUS_BAD_INDEX);
+        return;
+    }
+    float ol = lo, oh = hi;
+    if (head < p.nh + p.nkv) {                       // queries and keys rotate, values do not
+        const float c = p.cos_t[(size_t)pos * half + i], sn = p.sin_t[(size_t)pos * half + i];
+        ol = lo * c - hi * sn;
+        oh = hi * c + lo * sn;
+    }
+    bf16* dst = nullptr;
+    if (head < p.nh) {
+        dst = reinterpret_cast<bf16*>(p.q_out) + ((size_t)m * p.nh + head) * p.hd;
+    } else if (p.write_kv) {
+        const int page_id = p.block_table[(size_t)p.tok_seq[m] * p.table_stride + pos / p.page];
+        if (page_id < 0 || page_id >= p.n_pages) {
+            atomicOr(p.status, ESP_STATUS_BAD_INDEX);
+            return;
+        }
+        const bool is_k = head < p.nh + p.nkv;
+        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+        dst = reinterpret_cast<bf16*>(is_k ? p.k_cache : p.v_cache) +
+              (((size_t)page_id * p.nkv + kvh) * p.page + pos % p.page) * p.hd;
+    }
+    if (dst) {
+        dst[i] = __float2bfloat16_rn(ol);
+        dst[i + half] = __float2bfloat16_rn(oh);
+    }
+}
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                          unsigned b1) {
@@ -56,9 +109,10 @@ __device__ __forceinline__ uint4 load_stream(const bf16* p) {
 // KS: how many of the block's 8 warps share one tile of weight rows, each with its own slice of K (8 / KS
 // tiles per block).  Few tiles: KS = 8, so that every SM still gets work; many tiles: KS = 1, each warp
 // walks all of K of its own tile (longer streams per warp, no reduction between warps); 2 and 4 lie between.
-template <int NBLK, bool SWIGLU, typename TC, int KS>
+template <int NBLK, int MODE, typename TC, int KS>
 __global__ void __launch_bounds__(WARPS * 32, ESP_SKINNY_BLOCKS)
 gemm_skinny_kernel(SkinnyParams p) {
+    constexpr bool SWIGLU = MODE == MODE_SWIGLU, ROPE = MODE == MODE_ROPE, PAIRS = SWIGLU || ROPE;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K = p.K;
     const int a_stride = K + 32;                                    // elements; 64 bytes of padding per row
@@ -95,7 +149,13 @@ gemm_skinny_kernel(SkinnyParams p) {
     bool ok_a, ok_b;
     constexpr int TILES = WARPS / KS;              // tiles of weight rows per block
     const int tile = blockIdx.x * TILES + warp / KS, kslice = warp % KS;
-    if (SWIGLU) {
+    if (ROPE) {
+        // pair j of the packed projection: feature i of head ``head`` and its partner half a head further
+        const int j = tile * 8 + g, half = p.hd / 2, head = j / half;
+        ok_a = ok_b = j < p.N;
+        row_a = head * p.hd + (j - head * half);
+        row_b = row_a + half;
+    } else if (SWIGLU) {
         const int j = tile * 8 + g;
         ok_a = ok_b = j < p.N;
         row_a = j;
@@ -186,7 +246,10 @@ gemm_skinny_kernel(SkinnyParams p) {
                 for (int i = 0; i < 2; i++) {
                     const int tok = nb * 8 + tg * 2 + i;
                     if (tok >= cnt) continue;
-                    if (SWIGLU) {
+                    if (ROPE) {
+                        const int j = tile * 8 + g;
+                        if (j < p.N) emit_rope_pair(p, m0 + tok, j, acc[nb][i], acc[nb][2 + i]);
+                    } else if (SWIGLU) {
                         const int j = tile * 8 + g;
                         if (j < p.N) {
                             const float gate = acc[nb][i], up = acc[nb][2 + i];
@@ -208,7 +271,7 @@ gemm_skinny_kernel(SkinnyParams p) {
             *reinterpret_cast<float4*>(red + (((size_t)warp * NBLK + nb) * 32 + lane) * 4) =
                 make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
         __syncthreads();
-        if (SWIGLU) {
+        if (PAIRS) {
             for (int e = tid; e < TILES * NBLK * 64; e += WARPS * 32) {
                 const int tl = e / (NBLK * 64), rem = e % (NBLK * 64);
                 const int nb = rem / 64, ln = (rem % 64) / 2, i = rem & 1;
@@ -220,8 +283,12 @@ gemm_skinny_kernel(SkinnyParams p) {
                 }
                 const int tok = nb * 8 + (ln & 3) * 2 + i, j = (blockIdx.x * TILES + tl) * 8 + (ln >> 2);
                 if (tok < cnt && j < p.N) {
-                    const float v = gate / (1.0f + expf(-gate)) * up;
-                    reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + j] = from_f32<TC>(v);
+                    if (ROPE) {
+                        emit_rope_pair(p, m0 + tok, j, gate, up);
+                    } else {
+                        const float v = gate / (1.0f + expf(-gate)) * up;
+                        reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + j] = from_f32<TC>(v);
+                    }
                 }
             }
         } else {
@@ -243,35 +310,35 @@ gemm_skinny_kernel(SkinnyParams p) {
     }
 }
 
-template <int NBLK, bool SWIGLU, typename TC, int KS>
+template <int NBLK, int MODE, typename TC, int KS>
 int launch_variant(const SkinnyParams& p, int groups, int tiles, cudaStream_t stream) {
     const size_t smem = (size_t)8 * NBLK * (p.K + 32) * sizeof(bf16) + (size_t)WARPS * NBLK * 32 * 4 * sizeof(float);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
     static bool raised = false;        // per instantiation
     if (smem > 48 * 1024 && !raised) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NBLK, SWIGLU, TC, KS>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NBLK, MODE, TC, KS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
     constexpr int TILES = WARPS / KS;
     dim3 grid((tiles + TILES - 1) / TILES, p.group_offsets && p.M < groups ? p.M : groups);   // every group that has rows starts below M
-    esp_launch_pdl(p.group_offsets ? ESP_PDL_GROUPED : ESP_PDL_DENSE, gemm_skinny_kernel<NBLK, SWIGLU, TC, KS>, grid, dim3(WARPS * 32), smem, stream, p);
+    esp_launch_pdl(p.group_offsets ? ESP_PDL_GROUPED : ESP_PDL_DENSE, gemm_skinny_kernel<NBLK, MODE, TC, KS>, grid, dim3(WARPS * 32), smem, stream, p);
     return esp_launch_status();
 }
 
-template <int NBLK, bool SWIGLU, typename TC>
+template <int NBLK, int MODE, typename TC>
 int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
-    const int tiles = SWIGLU ? (p.N + 7) / 8 : (p.N + 15) / 16;
+    const int tiles = MODE != MODE_PLAIN ? (p.N + 7) / 8 : (p.N + 15) / 16;
     // warps wanted: about a dozen per SM.  The fewer tiles there are, the more warps share one.
     const long long spread = (long long)tiles * (p.group_offsets ? (groups < p.M ? groups : p.M) : 1);
     constexpr int SLOTS = 12;      // measured: 8 and 16 were slower at batch 8, 24 slower at batch 1
     // a warp takes a tile all by itself only with several waves of tiles (measured: batch 1 gains 4 % over a
     // limit of 12, batch 8 and 64 are the same)
-    if (spread >= 148 * 48) return launch_variant<NBLK, SWIGLU, TC, 1>(p, groups, tiles, stream);
-    if (spread * 2 >= 148 * SLOTS) return launch_variant<NBLK, SWIGLU, TC, 2>(p, groups, tiles, stream);
-    if (spread * 4 >= 148 * SLOTS) return launch_variant<NBLK, SWIGLU, TC, 4>(p, groups, tiles, stream);
-    return launch_variant<NBLK, SWIGLU, TC, 8>(p, groups, tiles, stream);
+    if (spread >= 148 * 48) return launch_variant<NBLK, MODE, TC, 1>(p, groups, tiles, stream);
+    if (spread * 2 >= 148 * SLOTS) return launch_variant<NBLK, MODE, TC, 2>(p, groups, tiles, stream);
+    if (spread * 4 >= 148 * SLOTS) return launch_variant<NBLK, MODE, TC, 4>(p, groups, tiles, stream);
+    return launch_variant<NBLK, MODE, TC, 8>(p, groups, tiles, stream);
 }
 }  // namespace
 
@@ -283,17 +350,44 @@ ESP_API int esp_gemm_skinny(const void* A, long long lda, const int* a_rows, con
                             int groups, int M, int N, int K, int max_rows, int swiglu, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K % 8 != 0 || lda % 8 != 0 || groups > 65535) return (int)cudaErrorInvalidValue;
-    SkinnyParams p{(const bf16*)W, w_group_stride, (const bf16*)A, lda, a_rows, group_offsets, row_scale, C, ldc, M, N, K, groups};
+    SkinnyParams p{};
+    p.W = (const bf16*)W; p.w_group_stride = w_group_stride; p.A = (const bf16*)A; p.lda = lda; p.a_rows = a_rows;
+    p.group_offsets = group_offsets; p.row_scale = row_scale; p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+    p.groups = groups;
     const int g = group_offsets ? groups : 1;
     const bool two = max_rows > 8 && (size_t)16 * (K + 32) * 2 + WARPS * 2 * 512 <= 227 * 1024;
 #define ESP_GO(NB, SW, TC) return launch<NB, SW, TC>(p, g, stream)
     if (swiglu) {
-        if (c_dtype == 1) { if (two) ESP_GO(2, true, bf16); else ESP_GO(1, true, bf16); }
-        else { if (two) ESP_GO(2, true, float); else ESP_GO(1, true, float); }
+        if (c_dtype == 1) { if (two) ESP_GO(2, MODE_SWIGLU, bf16); else ESP_GO(1, MODE_SWIGLU, bf16); }
+        else { if (two) ESP_GO(2, MODE_SWIGLU, float); else ESP_GO(1, MODE_SWIGLU, float); }
     } else {
-        if (c_dtype == 1) { if (two) ESP_GO(2, false, bf16); else ESP_GO(1, false, bf16); }
-        else { if (two) ESP_GO(2, false, float); else ESP_GO(1, false, float); }
+        if (c_dtype == 1) { if (two) ESP_GO(2, MODE_PLAIN, bf16); else ESP_GO(1, MODE_PLAIN, bf16); }
+        else { if (two) ESP_GO(2, MODE_PLAIN, float); else ESP_GO(1, MODE_PLAIN, float); }
     }
+    return (int)cudaErrorInvalidValue;
+}
+
+// The packed q/k/v projection of a step of few rows with the position encoding and the cache write in its
+// epilogue: out = A W^T (+ bias), heads [nh queries | nkv keys | nkv values] of width hd; queries and keys
+// are rotated by their token's position (full split-half rotation, cos/sin tables [max_pos, hd / 2]), queries
+// go to q_out [M, nh * hd], keys and values into the paged cache (all bfloat16).  Same arithmetic as
+// esp_gemm_skinny followed by esp_rope_kvwrite, without the float intermediate.  hd a multiple of 16.
+ESP_API int esp_qkv_rope_skinny(const void* A, long long lda, const void* W, const float* bias, const int* tok_seq,
+                                const int* tok_pos, const float* cos_t, const float* sin_t, int max_pos, void* q_out,
+                                void* k_cache, void* v_cache, const int* block_table, int table_stride, int n_pages, int page,
+                                int M, int K, int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (K % 8 != 0 || lda % 8 != 0 || hd % 16 != 0 || hd <= 0 || nh <= 0 || nkv <= 0 || page <= 0 || M > 16)
+        return (int)cudaErrorInvalidValue;
+    SkinnyParams p{};
+    p.W = (const bf16*)W; p.A = (const bf16*)A; p.lda = lda; p.M = M; p.N = (nh + 2 * nkv) * (hd / 2); p.K = K; p.groups = 1;
+    p.bias = bias; p.tok_seq = tok_seq; p.tok_pos = tok_pos; p.cos_t = cos_t; p.sin_t = sin_t; p.q_out = q_out;
+    p.k_cache = k_cache; p.v_cache = v_cache; p.block_table = block_table; p.table_stride = table_stride;
+    p.n_pages = n_pages; p.page = page; p.nh = nh; p.nkv = nkv; p.hd = hd; p.max_pos = max_pos; p.write_kv = write_kv;
+    p.status = status;
+    const int g = 1;
+    const bool two = M > 8 && (size_t)16 * (K + 32) * 2 + WARPS * 2 * 512 <= 227 * 1024;
+    if (two) ESP_GO(2, MODE_ROPE, bf16); else ESP_GO(1, MODE_ROPE, bf16);
 #undef ESP_GO
     return (int)cudaErrorInvalidValue;
 }

@@ -41,6 +41,8 @@ _SIGNATURES = {
     "esp_moe_combine_add_rmsnorm": [P, P, P, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, c_int, P],
     "esp_gemm_skinny": [P, c_longlong, P, P, c_longlong, P, P, c_int, c_longlong, P, c_int, c_int, c_int, c_int, c_int,
                         c_int, P],
+    "esp_qkv_rope_skinny": [P, c_longlong, P, P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_int, c_int, c_int, P, P],
     "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_attn_prefill_tc05": [P, c_longlong, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               P, P],
@@ -352,9 +354,35 @@ def gemm_skinny(a, w, c, swiglu=False, row_scale=None, a_rows=None, group_offset
     _check(code, "gemm_skinny")
 
 
+def qkv_rope_skinny_fits(rows: int, k: int, hd: int) -> bool:
+    return rows <= 16 and hd % 16 == 0 and skinny_fits(k)
+
+
+def qkv_rope_skinny(a, w_qkv, bias, tok_seq, tok_pos, cos, sin, q_out, k_cache, v_cache, block_table, page, nh, nkv, hd,
+                    write_kv, status):
+    """The packed q/k/v projection of at most 16 rows with bias, full split-half rotation of queries and keys
+    and the cache write in one kernel (bfloat16): what gemm_skinny followed by rope_kvwrite computes."""
+    m, k = a.shape
+    if w_qkv.shape != ((nh + 2 * nkv) * hd, k) or not qkv_rope_skinny_fits(m, k, hd):
+        raise Backend(f"qkv_rope_skinny: sizes not taken: a {tuple(a.shape)}, w {tuple(w_qkv.shape)}, head size {hd}")
+    if cos.shape[1] != hd // 2:
+        raise Backend("qkv_rope_skinny rotates the whole head: the tables must be [positions, head size / 2]")
+    if a.stride(-1) != 1 or a.stride(0) % 8 != 0 or a.data_ptr() % 16 != 0:
+        raise Backend("qkv_rope_skinny: the rows must be 16-byte aligned")
+    _check(_fn("bf16", "esp_qkv_rope_skinny")(
+        _ptr(a, torch.bfloat16, "a") if a.is_contiguous() else a.data_ptr(), a.stride(0), _ptr(w_qkv, torch.bfloat16, "w_qkv"),
+        _ptr(bias, torch.float32, "bias"), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32),
+        _ptr(cos, torch.float32, "cos"), _ptr(sin, torch.float32, "sin"), cos.shape[0], _ptr(q_out, torch.bfloat16, "q_out"),
+        _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16), _ptr(block_table, torch.int32),
+        block_table.shape[1], k_cache.shape[0], page, m, k, nh, nkv, hd, 1 if write_kv else 0,
+        _ptr(status, torch.int32), _stream()), "qkv_rope_skinny")
+
+
 def attn_decode_split(n_rows: int, nkv_blocks: int, positions: int) -> int:
-    """Key positions per block: 256 while that still gives few blocks (so that every SM has work at
+    """Key positions per block: 128 or 256 while that still gives few blocks (so that every SM has work at
     batch 1), 512 once there are plenty (fewer partial results to combine)."""
+    if n_rows * nkv_blocks * ((positions + 127) // 128) <= 1024:
+        return 128
     return 256 if n_rows * nkv_blocks * ((positions + 255) // 256) <= 1024 else 512
 
 
@@ -369,8 +397,8 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, to
     N * nh words, all zero (the kernel leaves them zero)."""
     if counters.numel() < q.shape[0] * nh:
         raise Backend("attn_decode: too few counters for this many rows and heads")
-    if split not in (256, 512):
-        raise Backend(f"attn_decode: split {split} is not 256 or 512")
+    if split not in (128, 256, 512):
+        raise Backend(f"attn_decode: split {split} is not 128, 256 or 512")
     if hd not in (64, 128, 192, 256):
         raise Backend(f"attn_decode: head size {hd} is not one of 64, 128, 192, 256")
     n = q.shape[0]

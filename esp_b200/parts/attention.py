@@ -126,11 +126,14 @@ class Attention(Part):
     def forward(self, h, ctx, layer):
         s, rt = self.spec, self.rt
         n = h.shape[0]
-        qkv = rt.ws.get("attn_qkv", (n, self.qkv_width), torch.float32)
-        linear(rt, h, self.w_qkv, qkv)
         q = rt.ws.get("attn_q", (n, self.q_width), rt.dtype)
-        self.position.rotate_and_store(qkv, self.b_qkv, ctx, q, layer, s.num_heads, s.num_kv_heads, s.head_dim,
-                                       rt.status)
+        fused = getattr(self.position, "project_rotate_store", None)
+        if fused is None or not fused(h, self.w_qkv, self.b_qkv, ctx, q, layer, s.num_heads, s.num_kv_heads, s.head_dim,
+                                      rt.status):
+            qkv = rt.ws.get("attn_qkv", (n, self.qkv_width), torch.float32)
+            linear(rt, h, self.w_qkv, qkv)
+            self.position.rotate_and_store(qkv, self.b_qkv, ctx, q, layer, s.num_heads, s.num_kv_heads, s.head_dim,
+                                           rt.status)
         o = rt.ws.get("attn_o", (n, self.q_width), rt.dtype)
         self.attend(q, o, ctx, layer)
         y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)

@@ -14,8 +14,10 @@ Interfaces (all tensors live on the GPU; N = tokens of the step, H = width):
              what it keeps per sequence (``layer`` is a ``cache.LayerCache``).
 * ffn:       ``forward(h, ctx, h32=None) -> delta`` float32 [N,H]; a part with ``wants_f32_input = True``
              also gets the normed rows unrounded (float32) when the activation dtype is narrower.
-* position:  ``rotate_and_store(qkv, bias, ctx, q_out, layer, nh, nkv, hd)``: encodes the new queries and
-             keys (float32 in ``qkv``) and stores keys and values in the cache.
+* position:  ``rotate_and_store(qkv, bias, ctx, q_out, layer, nh, nkv, hd, status)``: encodes the new queries and
+             keys (float32 in ``qkv``) and stores keys and values in the cache.  Optional:
+             ``project_rotate_store(h, w_qkv, bias, ctx, q_out, layer, nh, nkv, hd, status) -> bool`` does the
+             packed projection as well, in one kernel, where the part has one for the sizes at hand.
 * block:     ``forward(x, pending, ctx, layer) -> pending``: runs its parts in its arrangement.
 
 Per-step index lists.  A part that needs lists of its own on the device (tiles

@@ -38,6 +38,16 @@ class RopeSplitHalf(Part):
         ops.rope_kvwrite(qkv, bias, ctx.tok_seq, ctx.tok_pos, self.cos, self.sin, self.spec.rotary_dim, q_out,
                          layer.k, layer.v, table, layer.page, nh, nkv, hd, layer.writes, status)
 
+    def project_rotate_store(self, h, w_qkv, bias, ctx, q_out, layer, nh, nkv, hd, status) -> bool:
+        """Optional short cut of a position part: the packed projection, this encoding and the cache write
+        in one kernel.  False: not for these sizes; the caller projects and calls ``rotate_and_store``."""
+        if (h.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16 or self.spec.rotary_dim != hd
+                or layer.group is None or not ops.qkv_rope_skinny_fits(h.shape[0], h.shape[1], hd)):
+            return False
+        ops.qkv_rope_skinny(h, w_qkv, bias, ctx.tok_seq, ctx.tok_pos, self.cos, self.sin, q_out, layer.k, layer.v,
+                            ctx.block_tables[layer.group], layer.page, nh, nkv, hd, layer.writes, status)
+        return True
+
 
 class NoPosition(Part):
     """No encoding: queries and keys are stored as projected."""

@@ -582,7 +582,7 @@ def test_gemm_skinny_grouped_fewer_rows_than_groups(counts_at):
     assert torch.all(c[total:] == 7.0) and torch.all(act[total:] == 7.0)
 
 
-@pytest.mark.parametrize("split", [256, 512])
+@pytest.mark.parametrize("split", [128, 256, 512])
 @pytest.mark.parametrize("nh, nkv, hd, window", [(4, 4, 128, None), (6, 2, 64, None), (7, 1, 128, 100), (8, 1, 192, None),
                                                  (4, 2, 256, 300), (16, 16, 128, 65)])
 def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window, split):
@@ -903,3 +903,43 @@ def test_attn_prefill_tc05_with_more_items_than_the_gpu_has_sms():
     prefill attention takes a second and third item with its rings and phases carried over."""
     check_attn_prefill(ops.attn_prefill_tc05, 24, 8, 128, None, tile=ops.ATTN_TC05_TILE_ROWS, runs=[
         (0, 900), (130, 700), (0, 1), (63, 66), (300, 129), (10, 420), (0, 384), (5, 250)])
+
+
+@pytest.mark.parametrize("m, nh, nkv, hd, k", [(1, 4, 2, 128, 512), (8, 16, 16, 128, 2048), (13, 6, 3, 64, 384), (16, 7, 1, 32, 200)])
+def test_qkv_projection_with_rotation_and_cache_write_in_one_kernel(m, nh, nkv, hd, k):
+    """The fused kernel against the two kernels it replaces (same arithmetic in the same order: equal bits)
+    and against a float64 restatement."""
+    torch.manual_seed(4)
+    width = (nh + 2 * nkv) * hd
+    a = rnd(m, k, dtype=torch.bfloat16, scale=0.5)
+    w = rnd(width, k, dtype=torch.bfloat16, scale=0.05, seed=1)
+    bias = rnd(width, scale=0.1, seed=2)
+    max_pos, n_pages, half = 300, 9, hd // 2
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] / (1e4 ** (torch.arange(half, dtype=torch.float64) * 2 / hd))[None, :]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    seqs = torch.arange(m, dtype=torch.int32, device=DEV) % 3
+    pos = torch.tensor([(37 * i + 5) % max_pos for i in range(m)], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[3 * p + s_ for p in range(5)] for s_ in range(3)], dtype=torch.int32, device=DEV) % n_pages
+    table = torch.tensor([[0, 3, 6, 1, 4], [7, 2, 5, 8, 0], [4, 1, 8, 3, 6]], dtype=torch.int32, device=DEV)
+    outs = []
+    for fused in (False, True):
+        q = torch.zeros(m, nh * hd, dtype=torch.bfloat16, device=DEV)
+        kc = torch.zeros(n_pages, nkv, 64, hd, dtype=torch.bfloat16, device=DEV)
+        vc = torch.zeros_like(kc)
+        st = status()
+        if fused:
+            ops.qkv_rope_skinny(a, w, bias, seqs, pos, cos, sin, q, kc, vc, table, 64, nh, nkv, hd, True, st)
+        else:
+            qkv = torch.empty(m, width, device=DEV)
+            ops.gemm_skinny(a, w, qkv)
+            ops.rope_kvwrite(qkv, bias, seqs, pos, cos, sin, hd, q, kc, vc, table, 64, nh, nkv, hd, True, st)
+        assert st.item() == 0
+        outs.append((q, kc, vc))
+    for x, y in zip(*outs):
+        assert torch.equal(x, y)
+    # float64: projection, bias, rotation of queries
+    ref = a.double() @ w.double().t() + bias.double()
+    qr = ref[:, :nh * hd].reshape(m, nh, hd)
+    c, s_ = torch.cos(ang).to(DEV)[pos.long()][:, None, :], torch.sin(ang).to(DEV)[pos.long()][:, None, :]
+    rot = torch.cat([qr[..., :half] * c - qr[..., half:] * s_, qr[..., half:] * c + qr[..., :half] * s_], -1)
+    close(outs[1][0].view(m, nh, hd), rot, torch.bfloat16, "rotated queries", k=k)
