@@ -211,20 +211,49 @@ ESP_API int esp_gather_rows(const void* src, const int* rows, void* out, int n_r
 }
 
 // ---------------------------------------------------------------- finite check
-__global__ void finite_check_kernel(const float* __restrict__ v, long long count, int* __restrict__ status) {
+// ORs ``bit`` into *status if any value is a NaN or an infinity.  bfloat16 values are tested on their bits
+// (an exponent of all ones), 16 bytes at a time where the count allows.
+template <typename T>
+__global__ void finite_check_kernel(const T* __restrict__ v, long long count, int* __restrict__ status, int bit) {
     pdl_trigger();
     pdl_wait();
     bool bad = false;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
-        bad |= !isfinite(v[i]);
-    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, ESP_STATUS_LOGITS_NONFINITE);
+        bad |= !isfinite(to_f32(v[i]));
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, bit);
 }
 
-ESP_API int esp_finite_check(const float* v, long long count, int* status, cudaStream_t stream) {
+__global__ void finite_check_bf16x8_kernel(const uint4* __restrict__ v, long long pieces, int* __restrict__ status, int bit) {
+    bool bad = false;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < pieces; i += (long long)gridDim.x * blockDim.x) {
+        const uint4 q = v[i];
+        const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            bad |= ((w[j] & 0x7F80u) == 0x7F80u) || ((w[j] & 0x7F800000u) == 0x7F800000u);
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, bit);
+}
+
+ESP_API int esp_finite_check(const void* v, int is_bf16, long long count, int* status, int bit, cudaStream_t stream) {
     if (count <= 0) return 0;
+    if (is_bf16) {
+        const long long pieces = ((uintptr_t)v & 15) ? 0 : count / 8;
+        if (pieces > 0) {
+            long long blocks = (pieces + 255) / 256;
+            if (blocks > 148 * 16) blocks = 148 * 16;
+            finite_check_bf16x8_kernel<<<(int)blocks, 256, 0, stream>>>((const uint4*)v, pieces, status, bit);
+        }
+        const long long rest = count - pieces * 8;
+        if (rest > 0)
+            finite_check_kernel<bf16><<<(int)((rest + 255) / 256 > 1184 ? 1184 : (rest + 255) / 256), 256, 0, stream>>>(
+                (const bf16*)v + pieces * 8, rest, status, bit);
+        return esp_launch_status();
+    }
     long long blocks = (count + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    esp_launch_pdl(ESP_PDL_SMALL, finite_check_kernel, dim3((int)blocks), dim3(256), 0, stream, v, count, status);
+    esp_launch_pdl(ESP_PDL_SMALL, finite_check_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)v, count, status,
+                   bit);
     return esp_launch_status();
 }
 

@@ -23,7 +23,7 @@ _SIGNATURES = {
     "esp_feed_tokens": [P, P, P, c_int, P],
     "esp_add_rmsnorm": [P, P, P, P, P, c_int, P, c_int, c_int, c_float, c_int, P],
     "esp_swiglu": [P, P, c_int, c_longlong, c_int, P],
-    "esp_finite_check": [P, c_longlong, P, P],
+    "esp_finite_check": [P, c_int, c_longlong, P, c_int, P],
     "esp_normal_fill": [P, c_int, c_longlong, c_ulonglong, c_float, c_float, P],
     "esp_gemm_simt": [P, c_int, P, P, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, P],
     "esp_rope_kvwrite": [P, P, P, P, P, P, c_int, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -161,9 +161,13 @@ def swiglu(gu, act):
                                      inter, _stream()), "swiglu")
 
 
-def finite_check(values, status):
-    _check(_fn("core", "esp_finite_check")(_ptr(values, torch.float32, "values"), values.numel(),
-                                           _ptr(status, torch.int32), _stream()), "finite_check")
+STATUS_LOGITS_NONFINITE = 2
+
+
+def finite_check(values, status, bit: int = STATUS_LOGITS_NONFINITE):
+    """ORs ``bit`` into status[0] if ``values`` (float32 or bfloat16, contiguous) hold a NaN or an infinity."""
+    _check(_fn("core", "esp_finite_check")(_ptr(values, FLOATS, "values"), _is_bf16(values), values.numel(),
+                                           _ptr(status, torch.int32), int(bit), _stream()), "finite_check")
 
 
 def normal_fill(out, key: int, mean: float, std: float):

@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 import torch
 
+from esp_b200.engine import Engine
 from gpu_util import (Recorder, check_against_plain, engine_for, plain_model, run_steps, steps_batches, steps_tail,
                       steps_whole)
 from tiny import CASES, make_folder, random_ids
@@ -123,3 +124,40 @@ def test_step_refuses_what_cannot_run_and_changes_nothing(folders):
     eng.close(t)
     with pytest.raises(InvalidRequest):
         eng.close(t)
+
+
+def test_checkpoint_streams_to_the_device_in_chunks_and_refuses_non_finite_values(folders, tmp_path):
+    """The loader reads a tensor in chunks through pinned buffers; with chunks of 1,000 bytes (no multiple of an
+    element) the model's logits are those of the ordinary load.  A NaN or an infinity anywhere in a tensor is
+    found on the device and named."""
+    import shutil
+    from esp_b200.engine import StepEntry
+    from esp_b200.errors import InvalidWeights
+    from esp_b200.weights import FolderSource
+    from esp_b200.weights.safetensors_io import open_model_folder, read_tensor, write_safetensors
+    toks = requests_for("B")["r1"]
+    want = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(folders["B"], dtype=dtype, max_tokens=256)
+        s = eng.open()
+        want[dtype] = eng.step([StepEntry(s, toks, [len(toks) - 1])]).cpu()
+    chunk = FolderSource.CHUNK_BYTES
+    FolderSource.CHUNK_BYTES = 1000
+    try:
+        for dtype in ("float32", "bfloat16"):
+            eng = Engine.from_folder(folders["B"], dtype=dtype, max_tokens=256)
+            s = eng.open()
+            assert torch.equal(eng.step([StepEntry(s, toks, [len(toks) - 1])]).cpu(), want[dtype])
+    finally:
+        FolderSource.CHUNK_BYTES = chunk
+    # one bad value in the middle of a tensor, one at the very end of another
+    bad = tmp_path / "bad"
+    shutil.copytree(folders["B"], bad)
+    tensors = {n: read_tensor(m) for n, m in open_model_folder(bad).items()}
+    tensors["model.layers.1.mlp.experts.2.up_proj.weight"].view(-1)[1234] = float("nan")
+    tensors["model.norm.weight"].view(-1)[-1] = float("inf")
+    write_safetensors(bad / "model.safetensors", tensors)
+    for dtype in ("float32", "bfloat16"):
+        with pytest.raises(InvalidWeights) as e:
+            Engine.from_folder(bad, dtype=dtype, max_tokens=256)
+        assert "experts.2.up_proj" in str(e.value) and "model.norm.weight" in str(e.value) and "not finite" in str(e.value)
