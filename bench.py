@@ -338,12 +338,52 @@ def fp32_cuttings(torch, raw, layers, n_prompts=16, longest=1024, decoded=64, se
     out = {"fp32_cuttings_equal": bool(equal and finite and status == 0), "layers": layers, "prompts": n_prompts,
            "prompt_tokens": sum(plens), "decoded_each": decoded, "rows_compared": n_prompts * (decoded + 1),
            "seconds": times, "build_seconds": round(t_built - t_start, 1),
-           "weights_gb": round(engine.memory_plan["weights_bytes"] / 1e9, 1),
-           "prefill_tok_s": round(sum(plens) / max(times["batched"], 1e-9), 1)}
+           "weights_gb": round(engine.memory_plan["weights_bytes"] / 1e9, 1)}
     del engine, results
     gc.collect()
     torch.cuda.empty_cache()
     return out
+
+
+def dense_products(torch, raw, tokens=2048):
+    """Times the plain dense products of a prefill step (q/k/v, o, shared down) and the fused shared gate/up
+    through this library's TMA + tcgen05 kernel (one CTA per tile, and pairs of CTAs) and through cuBLAS."""
+    from esp_b200.csrc import ops
+    H, nh, nkv, hd, Is = (raw["hidden_size"], raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"],
+                          raw["shared_expert_intermediate_size"])
+    dev = "cuda:0"
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.05).bfloat16()
+
+    def time_us(fn):
+        return timed_steps(torch, fn, 3, 20) * 1e3
+
+    rows = []
+    for name, n, k in (("q/k/v", (nh + 2 * nkv) * hd, H), ("o", H, nh * hd), ("shared down", H, Is)):
+        a, w, c = rnd(tokens, k), rnd(n, k), torch.empty(tokens, n, device=dev)
+        flops = 2.0 * tokens * n * k
+        own = time_us(lambda: ops.gemm_tc05(a, w, c, st, pair=False))
+        pair = time_us(lambda: ops.gemm_tc05(a, w, c, st, pair=True))
+        lib = time_us(lambda: torch.mm(a, w.t(), out_dtype=torch.float32, out=c))
+        rows.append({"product": name, "n": n, "k": k, "own_us": round(own, 1), "own_pair_us": round(pair, 1),
+                     "cublas_us": round(lib, 1), "own_tflops": round(flops / own / 1e6, 1),
+                     "cublas_tflops": round(flops / lib / 1e6, 1)})
+    a, w, act = rnd(tokens, H), rnd(2 * Is, H), torch.empty(tokens, Is, dtype=torch.bfloat16, device=dev)
+    gu = torch.empty(tokens, 2 * Is, device=dev)
+    flops = 2.0 * tokens * 2 * Is * H
+
+    def library_then_swiglu():
+        torch.mm(a, w.t(), out_dtype=torch.float32, out=gu)
+        ops.swiglu(gu, act)
+
+    own = time_us(lambda: ops.gemm_tc05(a, w, act, st, swiglu=True, pair=False))
+    pair = time_us(lambda: ops.gemm_tc05(a, w, act, st, swiglu=True, pair=True))
+    lib = time_us(library_then_swiglu)
+    rows.append({"product": "shared gate/up + SwiGLU", "n": 2 * Is, "k": H, "own_us": round(own, 1),
+                 "own_pair_us": round(pair, 1), "cublas_us": round(lib, 1), "own_tflops": round(flops / own / 1e6, 1),
+                 "cublas_tflops": round(flops / lib / 1e6, 1)})
+    return {"tokens": tokens, "status": int(st.item()), "rows": rows}
 
 
 def main() -> int:
@@ -361,6 +401,8 @@ def main() -> int:
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement (for profiling decode)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the 32-bit cuttings check at the headline sizes and the Qwen2-57B-A14B shape")
+    ap.add_argument("--dense-products", action="store_true",
+                    help="only time the dense products of a 2,048-token prefill, own kernel against cuBLAS, and print them")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -377,6 +419,9 @@ def main() -> int:
 
     pk = peaks()
     raw, shape_name = SHAPES[a.shape]
+    if a.dense_products:
+        print(json.dumps({"model": shape_name, **dense_products(torch, raw)}))
+        return 0
     full_layers = raw["num_hidden_layers"]
     if a.layers is None:
         a.layers = full_layers

@@ -44,6 +44,19 @@ def cmd_generate(a) -> int:
     cache_tokens = a.cache_tokens or cache_tokens_for([len(r.prompt_ids) for r in reqs], a.max_tokens, window, a.max_batch)
     prov = DecoderProvider.load(a.model, dtype=a.dtype, device=a.device, max_batch=a.max_batch,
                                 max_context=a.max_context, max_tokens=cache_tokens)
+    if a.profile:
+        # one eager prefill of the first request and one eager decode step of it, timed kernel by kernel
+        from .engine import StepEntry
+        eng = prov.engine
+        ids = list(reqs[0].prompt_ids)
+        slot = eng.open()
+        try:
+            _logits, prefill = eng.profile_step([StepEntry(slot, ids, [len(ids) - 1])])
+            _logits, decode = eng.profile_step([StepEntry(slot, [ids[-1]], [0])])
+        finally:
+            eng.close(slot)
+        print(f"prefill of {len(ids)} tokens, by kernel:\n{prefill.table()}\n\none decode step, by kernel:\n{decode.table()}",
+              file=sys.stderr)
     for i, g in enumerate(prov.generate(reqs)):
         print(json.dumps({"request": i, "token_ids": g.token_ids, "text": g.text, "finish_reason": g.finish_reason,
                           "prompt_tokens": g.prompt_tokens, "seed": g.seed}))
@@ -83,6 +96,8 @@ def main(argv=None) -> int:
     g.add_argument("--stop-token-id", type=int, action="append")
     g.add_argument("--max-batch", type=int, default=64)
     g.add_argument("--max-context", type=int, default=None)
+    g.add_argument("--profile", action="store_true",
+                   help="before generating, time one prefill and one decode step kernel by kernel (to stderr)")
     g.add_argument("--cache-tokens", type=int, default=None,
                    help="cache size in tokens (default: what these requests need)")
     g.set_defaults(fn=cmd_generate)

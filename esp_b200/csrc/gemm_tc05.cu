@@ -54,8 +54,8 @@ struct Tc05Params {
 };
 
 // Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ unsigned instr_desc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BF >> 4) << 24);
+__device__ __forceinline__ unsigned instr_desc(int n, int m = BF) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
 // Persistent form: a CTA per SM walks the list of (token tile, feature tile) pairs with stride gridDim.x.
@@ -83,10 +83,14 @@ struct TileInfo {
     int group, row0, n_rows, n_tok, f0;
 };
 
-template <int MAX_TOK, int FEATS>
-__device__ __forceinline__ TileInfo tile_info(const Tc05Params& p, int tile, int feat_tiles) {
+// PAIR: two CTAs of a cluster work on one token tile and two neighbouring feature tiles (rank 0 the even one):
+// ``feat_tiles`` then counts pairs of feature tiles, and the tile's width is a multiple of 32 so that each CTA
+// loads a half that is whole boxes.
+template <int MAX_TOK, int FEATS, bool PAIR>
+__device__ __forceinline__ TileInfo tile_info(const Tc05Params& p, int tile, int feat_tiles, int rank) {
     TileInfo t;
-    const int tt = tile / feat_tiles, ft = tile - tt * feat_tiles;     // feature tiles vary fastest: neighbours share tokens
+    const int tt = tile / feat_tiles;
+    const int ft = PAIR ? 2 * (tile - tt * feat_tiles) + rank : tile - tt * feat_tiles;   // feature tiles vary fastest: neighbours share tokens
     if (p.tile_group) {
         t.group = p.tile_group[tt];
         t.row0 = p.tile_row0[tt];
@@ -96,14 +100,56 @@ __device__ __forceinline__ TileInfo tile_info(const Tc05Params& p, int tile, int
         t.row0 = tt * MAX_TOK;
         t.n_rows = min(MAX_TOK, p.M - t.row0);
     }
-    t.n_tok = min(MAX_TOK, (max(t.n_rows, 1) + TOK_BOX - 1) / TOK_BOX * TOK_BOX);
+    constexpr int STEP = PAIR ? 2 * TOK_BOX : TOK_BOX;
+    t.n_tok = min(MAX_TOK, (max(t.n_rows, 1) + STEP - 1) / STEP * STEP);
     t.f0 = ft * FEATS;
     return t;
 }
 
+// ---- what a pair of CTAs needs (cta_group::2): one thread of the leader (rank 0) issues MMAs of 256 rows, the
+// upper 128 being the peer's weight rows; each CTA holds half of the token rows; copies of both CTAs count
+// on the leader's barriers; the leader's commits reach the barriers of both.
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the copy lands in this CTA's shared memory; its bytes are counted on the barrier at the same place in the
+// pair's first CTA (bit 24 of a shared::cluster address tells the two CTAs of a pair apart)
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, int c0, int c1, int c2, void* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tc_mma_lo_pair(unsigned tmem_d, unsigned a_lo, unsigned b_lo, unsigned hi, unsigned idesc,
+                                               unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "mov.b64 da, {%1, %3};\n"
+        "mov.b64 db, {%2, %3};\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n}\n"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the barrier at this address in both CTAs of the pair gets an arrival once the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair_addr(unsigned bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(bar_addr), "h"((unsigned short)3) : "memory");
+}
+// an arrival on the barrier at this address in the pair's first CTA
+__device__ __forceinline__ void mbar_arrive_leader(void* bar) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(bar)), "r"(0));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(remote) : "memory");
+}
+
 // MAX_TOK: token rows per tile at most (the N side of the MMA): 128 or 256.  Two accumulators of MAX_TOK
 // columns fit the 512 columns of TMEM in either case.
-template <bool SWIGLU, int MAX_TOK>
+template <bool SWIGLU, int MAX_TOK, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a64,
                  const __grid_constant__ CUtensorMap map_a128, const __grid_constant__ CUtensorMap map_w, Tc05Params p) {
@@ -125,10 +171,13 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     float* swap = reinterpret_cast<float*>(smem + PRODUCERS * RING_BYTES + BAR_BYTES);     // SWIGLU: [2 halves][2][2 pairs][2 roles][16][32]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int feat_tiles = (p.N + FEATS - 1) / FEATS;
+    const int rank = PAIR ? (int)cluster_rank() : 0;                 // this CTA within its pair
+    const int unit = PAIR ? blockIdx.x >> 1 : blockIdx.x;            // the CTA (or pair) among those of the grid
+    const int n_units = PAIR ? gridDim.x >> 1 : gridDim.x;
+    const int feat_tiles = PAIR ? ((p.N + FEATS - 1) / FEATS + 1) / 2 : (p.N + FEATS - 1) / FEATS;
     const int token_tiles = p.tile_group ? *p.n_tiles : (p.M + MAX_TOK - 1) / MAX_TOK;
     const int total_tiles = token_tiles * feat_tiles;
-    if ((int)blockIdx.x >= total_tiles) return;                      // the whole CTA leaves before any barrier exists
+    if (unit >= total_tiles) return;                                 // the whole CTA (pair) leaves before any barrier exists
     const int k_iters = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -138,17 +187,23 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&acc_full_bar[b], 1);
-            mbar_init(&acc_empty_bar[b], 8);                         // one arrival per epilogue warp
+            mbar_init(&acc_empty_bar[b], PAIR ? 16 : 8);             // one arrival per epilogue warp (of both CTAs)
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();                                    // the peer's barriers exist before anything reaches them
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
 
@@ -166,15 +221,18 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int off_kb = 0, free_kb = RING_KB;
         unsigned long long held = 0;                                 // lane 0: KB that each stage in flight holds, 8 bits a slot
         bool ok = true;
-        TileInfo next = tile_info<MAX_TOK, FEATS>(p, blockIdx.x, feat_tiles);
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TileInfo next = tile_info<MAX_TOK, FEATS, PAIR>(p, unit, feat_tiles, rank);
+        for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
             const TileInfo t = next;
-            if (tile + (int)gridDim.x < total_tiles)                  // the list entry of the next tile is fetched early
-                next = tile_info<MAX_TOK, FEATS>(p, tile + gridDim.x, feat_tiles);
-            const unsigned stage_tx = W_BYTES + t.n_tok * BK * 2;
-            const int size_kb = stage_tx >> 10;                       // n_tok is a multiple of 16: whole KB
+            if (tile + n_units < total_tiles)                         // the list entry of the next tile is fetched early
+                next = tile_info<MAX_TOK, FEATS, PAIR>(p, tile + n_units, feat_tiles, rank);
+            // token rows that this CTA loads: all of the tile, or its half of a pair's tile
+            const int my_tok = PAIR ? t.n_tok >> 1 : t.n_tok, tok0 = PAIR ? rank * my_tok : 0;
+            const unsigned my_tx = W_BYTES + my_tok * BK * 2;
+            const unsigned stage_tx = PAIR ? 2 * my_tx : my_tx;       // what the (leader's) barrier is told to expect
+            const int size_kb = my_tx >> 10;                          // my_tok is a multiple of 16: whole KB
             // this lane's box: the map, the row it starts at, the bytes into the stage
-            const int n128 = t.n_tok >> 7, n64 = (t.n_tok >> 6) & 1, n16 = (t.n_tok >> 4) & 3;
+            const int n128 = my_tok >> 7, n64 = (my_tok >> 6) & 1, n16 = (my_tok >> 4) & 3;
             const CUtensorMap* box_map = nullptr;
             int box_row = 0, box_grp = 0, box_off = 0;
             if (lane == 0) {
@@ -187,7 +245,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (j < n128) r = j * 128, box_map = &map_a128;
                 else if (j < n128 + n64) r = n128 * 128, box_map = &map_a64;
                 else if (j < n128 + n64 + n16) r = n128 * 128 + n64 * 64 + (j - n128 - n64) * TOK_BOX, box_map = &map_a;
-                if (r >= 0) box_row = t.row0 + r, box_off = W_BYTES + r * BK * 2;
+                if (r >= 0) box_row = t.row0 + tok0 + r, box_off = W_BYTES + r * BK * 2;
             }
             for (int k = 0; k < k_iters && ok; k++, it++) {
                 if (it % PRODUCERS != me) continue;
@@ -203,12 +261,15 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                     held = (held & ~(0xFFull << (8 * s))) | ((unsigned long long)need_kb << (8 * s));
                     free_kb -= need_kb;
-                    if (ok) mbar_expect_tx(&my_full[s], stage_tx);
+                    if (ok && rank == 0) mbar_expect_tx(&my_full[s], stage_tx);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 if (wrap) off_kb = 0;
-                if (box_map) tma_load_3d(ring + off_kb * 1024 + box_off, box_map, k * BK, box_row, box_grp, &my_full[s]);
+                if (box_map) {
+                    if (PAIR) tma_load_3d_pair(ring + off_kb * 1024 + box_off, box_map, k * BK, box_row, box_grp, &my_full[s]);
+                    else tma_load_3d(ring + off_kb * 1024 + box_off, box_map, k * BK, box_row, box_grp, &my_full[s]);
+                }
                 off_kb += size_kb;
                 issued++;
             }
@@ -218,10 +279,16 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             *abort_flag = 1;
             // let this warp's own copies land before the CTA's shared memory is given up: the stages not yet
             // known free may still be in flight, each on the phase of its own use of its slot
-            for (int j = tail; j < issued; j++) mbar_wait(&my_full[j % NSLOT], (j / NSLOT) & 1);
+            if (PAIR && rank != 0) {
+                // the peer's copies are counted on the leader's barriers, which it cannot wait on: give them a
+                // millisecond, far more than a copy takes
+                for (int j = 0; j < 1000; j++) __nanosleep(1000);
+            } else {
+                for (int j = tail; j < issued; j++) mbar_wait(&my_full[j % NSLOT], (j / NSLOT) & 1);
+            }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {                                // of a pair, the first CTA issues the MMAs of both
             int local = 0, ring = 0;
             int off0 = 0, off1 = 0, count0 = 0, count1 = 0;           // per ring: the next offset (KB), the stages consumed
             // descriptors differ from stage to stage and from one 16-wide k step to the next only in the
@@ -241,19 +308,27 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const unsigned t_lo = w_lo + (W_BYTES >> 4);
                 off += size_kb;
                 count++;
-                tc_mma_lo(acc, w_lo, t_lo, desc_hi, idesc, first ? 0u : 1u);
-                tc_mma_lo(acc, w_lo + 2, t_lo + 2, desc_hi, idesc, 1u);
-                tc_mma_lo(acc, w_lo + 4, t_lo + 4, desc_hi, idesc, 1u);
-                tc_mma_lo(acc, w_lo + 6, t_lo + 6, desc_hi, idesc, 1u);
-                tc_commit_addr(empty_addr + slot8);                     // the stage is free once these MMAs have read it
+                if (PAIR) {
+                    tc_mma_lo_pair(acc, w_lo, t_lo, desc_hi, idesc, first ? 0u : 1u);
+                    tc_mma_lo_pair(acc, w_lo + 2, t_lo + 2, desc_hi, idesc, 1u);
+                    tc_mma_lo_pair(acc, w_lo + 4, t_lo + 4, desc_hi, idesc, 1u);
+                    tc_mma_lo_pair(acc, w_lo + 6, t_lo + 6, desc_hi, idesc, 1u);
+                    tc_commit_pair_addr(empty_addr + slot8);            // the stage is free in both CTAs once these MMAs have read it
+                } else {
+                    tc_mma_lo(acc, w_lo, t_lo, desc_hi, idesc, first ? 0u : 1u);
+                    tc_mma_lo(acc, w_lo + 2, t_lo + 2, desc_hi, idesc, 1u);
+                    tc_mma_lo(acc, w_lo + 4, t_lo + 4, desc_hi, idesc, 1u);
+                    tc_mma_lo(acc, w_lo + 6, t_lo + 6, desc_hi, idesc, 1u);
+                    tc_commit_addr(empty_addr + slot8);                 // the stage is free once these MMAs have read it
+                }
                 return true;
             };
             static_assert(NSLOT == 8 && BK == 64, "the slot arithmetic and the four MMAs of a k step are written out");
-            TileInfo next = tile_info<MAX_TOK, FEATS>(p, blockIdx.x, feat_tiles);
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
+            TileInfo next = tile_info<MAX_TOK, FEATS, PAIR>(p, unit, feat_tiles, rank);
+            for (int tile = unit; tile < total_tiles && !*abort_flag; tile += n_units, local++) {
                 const TileInfo t = next;
-                if (tile + (int)gridDim.x < total_tiles) next = tile_info<MAX_TOK, FEATS>(p, tile + gridDim.x, feat_tiles);
-                const unsigned idesc = instr_desc(t.n_tok);
+                if (tile + n_units < total_tiles) next = tile_info<MAX_TOK, FEATS, PAIR>(p, tile + n_units, feat_tiles, rank);
+                const unsigned idesc = instr_desc(t.n_tok, PAIR ? 2 * BF : BF);
                 const int buf = local % NBUF;
                 // the epilogue must have emptied this accumulator buffer (NBUF tiles ago)
                 if (!mbar_wait(&acc_empty_bar[buf], ((local / NBUF) & 1) ^ 1)) {
@@ -262,13 +337,14 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
                 tc_fence_after();
                 const unsigned acc = tmem_base + buf * ACC_COLS;
-                const int size_kb = (W_BYTES + t.n_tok * BK * 2) >> 10;
+                const int size_kb = (W_BYTES + (PAIR ? t.n_tok >> 1 : t.n_tok) * BK * 2) >> 10;
                 for (int k = 0; k < k_iters && ok; k++, ring ^= 1) {
                     if (ring == 0) ok = k_step(std::integral_constant<int, 0>{}, off0, count0, acc, idesc, size_kb, k == 0);
                     else ok = k_step(std::integral_constant<int, 1>{}, off1, count1, acc, idesc, size_kb, k == 0);
                 }
                 if (!ok || *abort_flag) break;
-                tc_commit(&acc_full_bar[buf]);                        // the accumulator is complete once all MMAs are done
+                if (PAIR) tc_commit_pair_addr(smem_u32(&acc_full_bar[buf]));
+                else tc_commit(&acc_full_bar[buf]);                   // the accumulator is complete once all MMAs are done
             }
             if (!ok) {
                 atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
@@ -282,10 +358,10 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int quad = warp & 3;
         const int half = warp >= 7 ? 1 : 0;
         int local = 0;
-        TileInfo next = tile_info<MAX_TOK, FEATS>(p, blockIdx.x, feat_tiles);
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
+        TileInfo next = tile_info<MAX_TOK, FEATS, PAIR>(p, unit, feat_tiles, rank);
+        for (int tile = unit; tile < total_tiles; tile += n_units, local++) {
             const TileInfo t = next;
-            if (tile + (int)gridDim.x < total_tiles) next = tile_info<MAX_TOK, FEATS>(p, tile + gridDim.x, feat_tiles);
+            if (tile + n_units < total_tiles) next = tile_info<MAX_TOK, FEATS, PAIR>(p, tile + n_units, feat_tiles, rank);
             const int buf = local % NBUF;
             bool ok = !*abort_flag && mbar_wait(&acc_full_bar[buf], (local / NBUF) & 1);
             if (SWIGLU) {
@@ -357,14 +433,19 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // this warp has read its part of the buffer: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_leader(&acc_empty_bar[buf]);       // the leader's MMA thread waits for both CTAs' readers
+                else mbar_arrive(&acc_empty_bar[buf]);
+            }
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();           // neither CTA gives up its shared or tensor memory while the other may still reach it
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
 }
 
@@ -404,11 +485,12 @@ int make_map(CUtensorMap* map, const void* base, unsigned long long d0, unsigned
 // A [rows_total, K] bfloat16 (row-major, contiguous), W [G, w_rows, K] bfloat16.  Dense: tile_group = null,
 // M rows.  Grouped: the token-tile list on the device (tiles of at most ``tile_max`` rows); ``max_tiles`` bounds
 // their number.  swiglu: N is the intermediate size and w_rows = 2N.  K must be a multiple of 8, the
-// bases 16-byte aligned.
+// bases 16-byte aligned.  pair: clusters of two CTAs share a token tile (tcgen05 cta_group::2): one MMA covers
+// 256 weight rows, each CTA loads its own 128 and half of the token rows.
 ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, int groups, int w_rows,
                           const float* row_scale, void* C, long long ldc, const int* tile_group, const int* tile_row0,
                           const int* tile_rows, const int* n_tiles, int max_tiles, int tile_max, int M, int N, int K, int swiglu,
-                          int* status, cudaStream_t stream) {
+                          int pair, int* status, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || rows_total <= 0) return 0;
     if (K % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     CUtensorMap map_a, map_a64, map_a128, map_w;
@@ -438,22 +520,38 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
         if (sm_count <= 0) sm_count = 148;
     }
     const size_t smem = PRODUCERS * RING_BYTES + 1024 + BAR_BYTES + SWAP_BYTES;     // 230,656 of the 232,448 bytes a block may have
-    const int which = (swiglu ? 2 : 0) + (max_tok == 256 ? 1 : 0);
-    static bool raised[4] = {false, false, false, false};
+    const int which = (pair ? 4 : 0) + (swiglu ? 2 : 0) + (max_tok == 256 ? 1 : 0);
+    typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, Tc05Params);
+    static const Kernel kernels[8] = {
+        gemm_tc05_kernel<false, 128, false>, gemm_tc05_kernel<false, 256, false>, gemm_tc05_kernel<true, 128, false>,
+        gemm_tc05_kernel<true, 256, false>,  gemm_tc05_kernel<false, 128, true>,  gemm_tc05_kernel<false, 256, true>,
+        gemm_tc05_kernel<true, 128, true>,   gemm_tc05_kernel<true, 256, true>};
+    static bool raised[8] = {false, false, false, false, false, false, false, false};
     if (!raised[which]) {
-        cudaError_t e = cudaSuccess;
-        if (which == 0) e = cudaFuncSetAttribute(gemm_tc05_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (which == 1) e = cudaFuncSetAttribute(gemm_tc05_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (which == 2) e = cudaFuncSetAttribute(gemm_tc05_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (which == 3) e = cudaFuncSetAttribute(gemm_tc05_kernel<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kernels[which], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         raised[which] = true;
     }
-    const int grid = (int)(tiles_bound < sm_count ? tiles_bound : sm_count);
-    if (which == 0) gemm_tc05_kernel<false, 128><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
-    if (which == 1) gemm_tc05_kernel<false, 256><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
-    if (which == 2) gemm_tc05_kernel<true, 128><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
-    if (which == 3) gemm_tc05_kernel<true, 256><<<grid, THREADS, smem, stream>>>(map_a, map_a64, map_a128, map_w, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pair) {
+        // two CTAs of a cluster share a token tile: the grid is a whole number of pairs, one pair per two SMs
+        const long long pair_tiles = (long long)token_tiles * (((N + feats - 1) / feats + 1) / 2);
+        const long long pairs = pair_tiles < sm_count / 2 ? pair_tiles : sm_count / 2;
+        cfg.gridDim = dim3((unsigned)(2 * pairs));
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    } else {
+        cfg.gridDim = dim3((unsigned)(tiles_bound < sm_count ? tiles_bound : sm_count));
+    }
+    cudaLaunchKernelEx(&cfg, kernels[which], map_a, map_a64, map_a128, map_w, p);
     return esp_launch_status();
 }
 

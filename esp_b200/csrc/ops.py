@@ -8,6 +8,7 @@ these functions: without the compiled library they raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
@@ -34,7 +35,7 @@ _SIGNATURES = {
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
     "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P],
     "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-                      P, P],
+                      c_int, P, P],
     "esp_wait_probe": [c_int, P, P],
     "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
@@ -85,9 +86,55 @@ def add_launches(count: int) -> None:
     _launches += count
 
 
+class LaunchProfile:
+    """Device time by kind of kernel.  While one is active (``with LaunchProfile() as prof``) every launch made
+    through this module on the current stream is followed by a CUDA event; the time between two events is
+    charged to the later launch (so a launch's share holds the gap before it as well).  Meant for steps that
+    run eagerly on one stream: no captured graphs, nothing on a second stream."""
+
+    active = None
+
+    def __init__(self):
+        self.marks = []                      # (what, event)
+
+    def __enter__(self):
+        first = torch.cuda.Event(enable_timing=True)
+        first.record()
+        self.marks = [("start", first)]
+        LaunchProfile.active = self
+        return self
+
+    def __exit__(self, *exc):
+        LaunchProfile.active = None
+
+    def note(self, what: str) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.marks.append((what, ev))
+
+    def rows(self) -> list:
+        """[(kind, launches, microseconds)], the largest first."""
+        torch.cuda.synchronize()
+        total: dict = {}
+        for (_w0, e0), (what, e1) in zip(self.marks, self.marks[1:]):
+            n, us = total.get(what, (0, 0.0))
+            total[what] = (n + 1, us + e0.elapsed_time(e1) * 1e3)
+        return sorted(((w, n, us) for w, (n, us) in total.items()), key=lambda r: -r[2])
+
+    def table(self) -> str:
+        rows = self.rows()
+        whole = sum(us for _w, _n, us in rows) or 1.0
+        lines = [f"{'kernel':<28}{'launches':>9}{'us':>12}{'share':>8}"]
+        lines += [f"{w:<28}{n:>9}{us:>12.1f}{us / whole:>8.1%}" for w, n, us in rows]
+        lines.append(f"{'all':<28}{sum(n for _w, n, _u in rows):>9}{whole:>12.1f}{1:>8.0%}")
+        return "\n".join(lines)
+
+
 def _check(code: int, what: str) -> None:
     global _launches
     _launches += 1
+    if LaunchProfile.active is not None:
+        LaunchProfile.active.note(what)
     if code != 0:
         raise Backend(f"{what}: the launch was refused with CUDA error {code} "
                       f"(invalid value means a size this kernel does not take)")
@@ -466,7 +513,14 @@ def gather_rows(src, rows, out):
 TC05_TILE_ROWS = 256
 
 
-def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None, tile_rows=None):
+# Which tensor-memory products run on pairs of CTAs (tcgen05 cta_group::2: one MMA of 256 weight rows, each CTA of
+# the pair loads its own 128 and half of the token rows): "0" none, "grouped", "dense" or "all".  Measured at the
+# A2.7B sizes, 2,048 tokens: grouped gate/up 143.5 -> 133.8 us, grouped down 86.9 -> 82.8 us, dense fused SwiGLU
+# 78.4 -> 74.7 us, dense plain 42.3 -> 43.9 us; results are equal bit for bit.
+TC05_PAIR = os.environ.get("ESP_B200_TC05_PAIR", "all")
+
+
+def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None, tile_rows=None, pair=None):
     """TMA + tcgen05 product for many rows.  a [rows, K] bfloat16 contiguous; w [N, K] or [G, N, K]
     bfloat16.  Plain: c float32 [rows, N] = scale * a @ w[g].T.  swiglu: w rows are [gate; up] and c is
     bfloat16 [rows, I].  Grouped: ``tiles`` = (tile_group, tile_row0, tile_count, n_tiles) from moe_permute,
@@ -487,13 +541,15 @@ def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=No
         raise Backend("gemm_tc05: the plain product writes float32, the SwiGLU product bfloat16")
     grouped = tiles is not None
     tile_rows = TC05_TILE_ROWS if tile_rows is None else tile_rows
+    if pair is None:
+        pair = TC05_PAIR == "all" or TC05_PAIR == ("grouped" if grouped else "dense")
     code = _fn("tc05", "esp_gemm_tc05")(
         a.data_ptr(), m, w.data_ptr(), groups, wn, _ptr(row_scale, torch.float32, "row_scale"), c.data_ptr(),
         c.stride(0), _ptr(tiles[0], torch.int32) if grouped else None,
         _ptr(tiles[1], torch.int32) if grouped else None, _ptr(tiles[2], torch.int32) if grouped else None,
         _ptr(tiles[3], torch.int32) if grouped else None, tiles[0].shape[0] if grouped else 0,
         tile_rows if grouped else 0, m, n, k,
-        1 if swiglu else 0, _ptr(status, torch.int32), _stream())
+        1 if swiglu else 0, 1 if pair else 0, _ptr(status, torch.int32), _stream())
     _check(code, "gemm_tc05")
 
 

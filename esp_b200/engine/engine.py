@@ -364,6 +364,19 @@ class Engine:
                 seen += last if layout.window is None else min(last, layout.window + t - 1)
             c["kv_bytes_read"] += seen * per_key
 
+    def profile_step(self, entries: list):
+        """Runs one step eagerly on one stream (no captured graph, the shared expert in line) and returns
+        (logits, ``ops.LaunchProfile``): device time by kind of kernel for this step.  Library products
+        (cuBLAS) appear in the share of the kernel that follows them."""
+        graphs, side = self.use_graphs, self.rt.side_stream
+        self.use_graphs, self.rt.side_stream = False, None
+        try:
+            with torch.cuda.device(self.rt.device), ops.LaunchProfile() as prof:
+                logits = self.step(entries)
+            return logits, prof
+        finally:
+            self.use_graphs, self.rt.side_stream = graphs, side
+
     def counters(self) -> dict:
         """Work done since the engine was made: ``steps``, ``tokens``, ``kv_bytes_read`` (bytes of keys and
         values that the steps' attention had to read), and what the parts counted on the device

@@ -25,19 +25,24 @@ _M = (1 << 64) - 1
 @dataclass(frozen=True)
 class InitSpec:
     """Standard deviations: matrices N(0, weight_std); biases N(0, bias_std)
-    (0: zeros); norm scales 1 + N(0, norm_std)."""
+    (0: zeros); norm scales 1 + N(0, norm_std).  ``roles`` gives (mean, std)
+    for any further role that a part's parameters may carry."""
     weight_std: float = 0.02
     bias_std: float = 0.0
     norm_std: float = 0.0
+    roles: tuple = ()          # ((role, mean, std), ...)
 
     def mean_std(self, role: str):
+        for name, mean, std in self.roles:
+            if name == role:
+                return float(mean), float(std)
         if role == "matrix":
             return 0.0, self.weight_std
         if role == "bias":
             return 0.0, self.bias_std
         if role == "norm_scale":
             return 1.0, self.norm_std
-        raise InvalidConfig(f"no initialisation rule for parameter role {role!r}")
+        raise InvalidConfig(f"no initialisation rule for parameter role {role!r}; give one in InitSpec.roles")
 
 
 def _mix64(z: int) -> int:

@@ -3,6 +3,7 @@ greedy and seeded sampling, unequal prompts in one batch, stop tokens,
 sequences that end earlier, batches that follow one another."""
 import numpy as np
 import pytest
+import torch
 
 import plain_qwen2_moe as plain
 from esp_b200.provider import DecoderProvider, GenerationRequest
@@ -205,3 +206,26 @@ def test_non_finite_logits_that_stay_fail_the_call_closed(folders):
     prov.engine.settle()
     ok = prov.generate(GenerationRequest(prompt_ids=ps[0], max_tokens=3))      # the provider is still usable
     assert len(ok.token_ids) == 3
+
+
+def test_profile_of_a_step_names_the_kernels_and_changes_nothing(folders, capsys):
+    """``--profile`` / ``Engine.profile_step``: device time by kind of kernel for one eager step; the step's logits
+    are those of the ordinary step, and generation afterwards is as without it."""
+    from esp_b200.cli import main
+    from esp_b200.engine import Engine, StepEntry
+    eng = Engine.from_folder(folders["A"], dtype="bfloat16", max_tokens=256)
+    p = prompts("A", [40])[0]
+    s = eng.open()
+    want = eng.step([StepEntry(s, p, [len(p) - 1])]).cpu()
+    eng.close(s)
+    s = eng.open()
+    got, prof = eng.profile_step([StepEntry(s, p, [len(p) - 1])])
+    eng.close(s)
+    assert torch.equal(got.cpu(), want)
+    kinds = {w for w, _n, _us in prof.rows()}
+    assert {"embed_gather", "add_rmsnorm", "rope_kvwrite", "moe_permute"} <= kinds and all(us >= 0 for _w, _n, us in prof.rows())
+    assert eng.use_graphs and eng.rt.side_stream is not None
+    rc = main(["generate", "--model", str(folders["A"]), "--dtype", "float32", "--prompt-ids", ",".join(map(str, p[:6])),
+               "--max-tokens", "3", "--profile"])
+    out = capsys.readouterr()
+    assert rc == 0 and "one decode step, by kernel" in out.err and "gemm_simt" in out.err
