@@ -22,6 +22,13 @@ A27B_2L = {
     "decoder_sparse_step": 1, "mlp_only_layers": [], "use_sliding_window": False, "sliding_window": None,
     "tie_word_embeddings": False,
 }
+# The second shape of the reference's real-model gates, Qwen2-57B-A14B, with 1 of its 28 layers: 7 query heads per
+# key/value head, top-8 of 64 experts, a shared expert whose down-projection has rows of 20,480 values (more than the
+# weight-streaming kernel stages at once).
+Q57B_1L = dict(A27B_2L, num_hidden_layers=1, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+               max_position_embeddings=32768, intermediate_size=18944, num_experts=64, num_experts_per_tok=8,
+               moe_intermediate_size=2560, shared_expert_intermediate_size=20480)
+SHAPES = {"a2.7b": (A27B_2L, f"A2.7B sizes, {LAYERS} of {LAYERS_OF_MODEL} layers"), "57b-a14b": (Q57B_1L, "57B-A14B sizes, 1 of 28 layers")}
 LENGTHS = [200, 37, 131, 256, 9, 64]
 DECODED = [8, 8, 8, 8, 8, 0]
 
@@ -47,24 +54,27 @@ class Keeping:
         self.views[name] = view
 
 
-def make_engine(dtype, views=None):
+def make_engine(shape, dtype, views=None):
     from esp_b200.config import config_from_dict
     from esp_b200.engine import Engine
     from esp_b200.weights import InitSpec, RandomSource
     views = {} if views is None else views
     factory = lambda specs: Keeping(RandomSource(specs, 5, InitSpec(0.02, 0.02, 0.0), torch.bfloat16), views)
-    eng = Engine(config_from_dict(A27B_2L), factory, dtype=dtype, max_tokens=1024, max_slots=8)
+    eng = Engine(config_from_dict(SHAPES[shape][0]), factory, dtype=dtype, max_tokens=1024, max_slots=8)
     eng.rt.record_routing = True
     return eng, views
 
 
-@pytest.fixture(scope="module")
-def model():
-    """(config, weights) for the plain implementation: the bfloat16 values the engines hold, widened."""
-    eng, views = make_engine("bfloat16")
+@pytest.fixture(scope="module", params=["a2.7b", "57b-a14b"])
+def model(request):
+    """(shape, bfloat16 engine, (config, weights) for the plain implementation: the bfloat16 values the
+    engines hold, widened)."""
+    eng, views = make_engine(request.param, "bfloat16")
     weights = {name: v.float().cpu().numpy() for name, v in views.items()}
-    config = plain.read_config_dict(dict(A27B_2L))
-    return eng, (config, weights)
+    config = plain.read_config_dict(dict(SHAPES[request.param][0]))
+    yield request.param, eng, (config, weights)
+    del eng, weights
+    torch.cuda.empty_cache()
 
 
 def requests(seed=0):
@@ -80,11 +90,11 @@ def cuttings(reqs):
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
 def test_real_layer_sizes_three_cuttings_and_plain(model, dtype):
-    eng_bf16, plain_model = model
+    shape, eng_bf16, plain_model = model
     if dtype == "bfloat16":
         eng = eng_bf16
     else:
-        eng, _ = make_engine("float32")             # the same values (stored as bfloat16), widened exactly
+        eng, _ = make_engine(shape, "float32")      # the same values (stored as bfloat16), widened exactly
     reqs = requests()
     recs = {}
     for what, steps in cuttings(reqs).items():
@@ -93,8 +103,7 @@ def test_real_layer_sizes_three_cuttings_and_plain(model, dtype):
     # every position of the two shortest requests and the last positions of the others
     at = {rid: (range(len(t)) if len(t) <= 40 else range(len(t) - 9, len(t))) for rid, t in reqs.items()}
     for what, rec in recs.items():
-        check_against_plain(plain_model, dtype, reqs, rec, f"A2.7B sizes, {LAYERS} of {LAYERS_OF_MODEL} layers, {what}",
-                            positions=at)
+        check_against_plain(plain_model, dtype, reqs, rec, f"{SHAPES[shape][1]}, {what}", positions=at)
     # in bfloat16 each cutting is held against the plain implementation with its own expert choices (a choice
     # between nearly equal probabilities may fall differently in two cuttings); in float32 the cuttings
     # must agree bit for bit
