@@ -125,3 +125,33 @@ def test_table_rows_are_padded_for_the_device():
     assert len(rows[0]) == 4 and rows[0][3] == -1 and rows[0][2] >= 0 and rows[1][1:] == [-1, -1, -1]
     with pytest.raises(InvalidRequest):
         book.groups[0].table_rows([a], 2)
+
+
+def test_a_cancelled_reservation_gives_every_page_back_and_leaves_the_tables_as_they_were():
+    """A step whose forward pass fails: the pages it took go back, lengths and tables stay, in a group that
+    keeps everything and in one with a window whose table has gaps."""
+    rng = random.Random(3)
+    book = CacheBook([FULL, WIN], max_tokens=40 * PAGE, max_slots=4, max_positions=5000)
+    a, b = book.open(), book.open()
+    first = {a: 300, b: 70}
+    book.reserve(first)
+    book.commit(first)
+    for _ in range(200):
+        growth = {a: rng.choice([1, 1, 1, 64, 130]), b: rng.choice([1, 2, 65])}
+        free = [g.pool.available for g in book.groups]
+        tables = [{s: list(t) for s, t in g.tables.items()} for g in book.groups]
+        lengths = dict(book.lengths)
+        try:
+            receipts = book.reserve(growth)
+        except CacheFull:
+            break
+        if rng.random() < 0.5:
+            book.cancel(receipts)
+            assert [g.pool.available for g in book.groups] == free
+            assert [{s: list(t) for s, t in g.tables.items()} for g in book.groups] == tables
+            assert book.lengths == lengths
+        else:
+            book.commit(growth)
+    book.close(a)
+    book.close(b)
+    assert all(g.pool.available == g.pool.n for g in book.groups) and book.slots.available == 4

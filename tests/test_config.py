@@ -117,3 +117,35 @@ def test_hidden_act_swish_is_silu_and_round_trip(tmp_path):
     again = config_from_json(tmp_path)
     assert again == c
     assert config_from_json((tmp_path / "config.json").read_bytes()) == c
+
+
+def test_the_plan_carries_the_checkpoint_names_and_the_parts_spell_none():
+    """Tensor names are data of the plan: another name table gives other parameter names from the same parts."""
+    import dataclasses
+    import torch
+    from esp_b200.config import config_from_dict
+    from esp_b200.config.plan import AttentionNames, MoeNames, SwiGluNames
+    from esp_b200.engine.model import DecoderModel
+    from esp_b200.parts import Runtime
+    from esp_b200.weights import InitSpec
+    import sys, pathlib
+    sys.path.insert(0, str(pathlib.Path(__file__).parent))
+    from tiny import TINY_A
+    plan = config_from_dict(TINY_A).plan()
+    names = {s.name for part in DecoderModel(plan, Runtime(None, torch.float32)).all_parts() for s in part.param_specs()}
+    assert "model.layers.0.self_attn.q_proj.weight" in names and "model.layers.1.mlp.experts.3.down_proj.weight" in names
+    other_mlp = SwiGluNames("w1.weight", "w3.weight", "w2.weight")
+    plan.blocks = [dataclasses.replace(
+        b, mixer=dataclasses.replace(b.mixer, names=AttentionNames("wq", "wk", "wv", "wo", ".w", ".b")),
+        ffn=dataclasses.replace(b.ffn, names=MoeNames("router.weight", "shared_gate.weight", "shared.", "expert_{e}.", other_mlp)))
+        for b in plan.blocks]
+    renamed = {s.name for part in DecoderModel(plan, Runtime(None, torch.float32)).all_parts() for s in part.param_specs()}
+    assert {"model.layers.0.self_attn.wq.w", "model.layers.0.self_attn.wk.b", "model.layers.1.mlp.expert_3.w2.weight",
+            "model.layers.0.mlp.router.weight", "model.layers.1.mlp.shared.w1.weight"} <= renamed
+    assert len(renamed) == len(names)
+    # a role of its own gets its rule from the spec; an unknown one is refused by name
+    assert InitSpec(roles=(("decay", 0.5, 0.1),)).mean_std("decay") == (0.5, 0.1)
+    from esp_b200.errors import InvalidConfig
+    import pytest
+    with pytest.raises(InvalidConfig, match="decay"):
+        InitSpec().mean_std("decay")

@@ -335,3 +335,13 @@ def test_bad_scores_again_fail_the_call_and_free_every_slot(backend_class, bad_c
         loop(be, health=health).run(_recovery_requests())
     assert health.prefix_recomputations == 1 and health.failed_recoveries == 1 and health.invalid_steps == 2
     assert not be.held and sorted(be.free) == list(range(4))
+
+
+def test_cache_size_for_the_requests_at_hand():
+    """The command line sizes the cache from its requests: prompt plus what each may generate (the last token is
+    never fed back), in whole pages, the largest batch of at most max_batch requests."""
+    from esp_b200.provider import cache_tokens_for
+    assert cache_tokens_for([5], 16, window=4096, max_batch=8) == 64
+    assert cache_tokens_for([60, 10], 10, window=4096, max_batch=8) == 128 + 64
+    assert cache_tokens_for([100] * 5, 200, window=4096, max_batch=2) == 2 * 320       # batches of two: 299 -> 320 each
+    assert cache_tokens_for([4000], 1000, window=4096, max_batch=1) == 4096            # budget cut at the window
