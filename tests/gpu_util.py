@@ -13,9 +13,11 @@ from esp_b200.engine import Engine, StepEntry
 # Bounds on |engine - plain| per request, relative to the largest |logit| of
 # the request.  float32: the reference project accepts 2e-5 absolute on logits
 # of order 0.1 (architecture_tests.rs:237-247); different summation orders
-# give a few 1e-7.  bfloat16: activations are rounded to 8 bits of mantissa
-# (eps = 2^-8) a handful of times per layer; 4 eps bounds what that can do.
-REL_TOL = {"float32": 2e-5, "bfloat16": 4 * 2.0 ** -8}
+# give up to 1.7e-6 on the models of this suite (sums of 2,048 to 5,632 terms),
+# so 6e-6 is the bound.  bfloat16: activations are rounded to 8 bits of mantissa
+# (eps = 2^-8) a handful of times per layer; the worst request of the suite is
+# off by 1.5 eps, and 3 eps is the bound.
+REL_TOL = {"float32": 6e-6, "bfloat16": 3 * 2.0 ** -8}
 # A routing choice may differ from the plain one only between experts whose
 # probabilities are this close (relative), i.e. within rounding of a tie.
 ROUTE_MARGIN = {"float32": 1e-5, "bfloat16": 2e-2}
