@@ -75,7 +75,14 @@ __device__ __forceinline__ unsigned instr_desc(int n, int m = BF) {
 // take the k steps in turn.
 constexpr int PRODUCERS = 2;               // warps that issue the loads, taking the k steps in turn
 constexpr int RING_KB = 96, RING_BYTES = RING_KB * 1024;    // each producer's own ring
-constexpr int NSLOT = 8;                   // stages of one ring in flight at most (pairs of mbarriers)
+// GROUP consecutive k steps (one of each ring) share a pair of mbarriers: one wait before their MMAs, one commit
+// after them.  A wait on a complete barrier and a commit keep the MMA thread about 100 cycles each, as long as
+// two of a k step's four MMAs, and that thread's time is what a k step takes (measured with clock64: the
+// copies are there long before, the producers wait for room).  Wider groups were measured and lose: four k steps
+// behind one wait and one commit, or behind one wait with a commit for every two (2,048 tokens, 24 layers: 15.1
+// and 13.7 ms against 12.7), because the rings then hold too few groups for the copies to run ahead.
+constexpr int GROUP = 2;
+constexpr int NSLOT = 8;                   // groups of stages in flight at most (pairs of mbarriers)
 constexpr int BAR_BYTES = 512;             // the mbarriers and two words behind the ring
 constexpr int SWAP_BYTES = 2 * 2 * 2 * 2 * 16 * 32 * 4;   // the epilogue's exchange of gate and up halves
 
@@ -160,11 +167,12 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr int NBUF = 2;
     constexpr int TMEM_COLS = NBUF * ACC_COLS;
     static_assert(TMEM_COLS <= 512, "the accumulators do not fit");
+    static_assert(GROUP == PRODUCERS, "a ring holds one stage of a group, which fits whatever was skipped at the ring's end");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + PRODUCERS * RING_BYTES);   // [ring][slot]
-    unsigned long long* empty_bar = full_bar + PRODUCERS * NSLOT;
-    unsigned long long* acc_full_bar = empty_bar + PRODUCERS * NSLOT;   // [2]
+    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + PRODUCERS * RING_BYTES);   // [slot]
+    unsigned long long* empty_bar = full_bar + NSLOT;
+    unsigned long long* acc_full_bar = empty_bar + NSLOT;            // [2]
     unsigned long long* acc_empty_bar = acc_full_bar + 2;        // [2]
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -181,8 +189,8 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int k_iters = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PRODUCERS * NSLOT; s++) {
-            mbar_init(&full_bar[s], 1);
+        for (int s = 0; s < NSLOT; s++) {
+            mbar_init(&full_bar[s], GROUP);                          // one announcement per k step of the group
             mbar_init(&empty_bar[s], 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -214,13 +222,28 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // the token rows in boxes of 128, then 64, then 16.
         const int me = warp == 0 ? 0 : 1;
         unsigned char* ring = smem + me * RING_BYTES;
-        unsigned long long* my_full = full_bar + me * NSLOT;
-        unsigned long long* my_empty = empty_bar + me * NSLOT;
         int it = 0;                                                  // k steps of the CTA so far
-        int issued = 0, tail = 0;                                    // this ring: stages issued; the oldest not yet known free
+        int tail = 0;                                                // the oldest group whose bytes in this ring are not yet known free
         int off_kb = 0, free_kb = RING_KB;
-        unsigned long long held = 0;                                 // lane 0: KB that each stage in flight holds, 8 bits a slot
+        unsigned long long held = 0;                                 // lane 0: KB that this ring holds for each group in flight, 8 bits a slot
         bool ok = true;
+        // lane 0, before a k step's copies: the step's group has a slot (the group NSLOT before it was consumed)
+        // and the ring has room; the bytes of consumed groups come back as their barriers complete
+        auto acquire = [&](int grp, int need_kb) {
+            ok = !*abort_flag;
+            while (ok && (free_kb < need_kb || grp - tail >= NSLOT)) {
+                if (tail >= grp) {                                    // nothing older is left to come back: never wait on the step's own group
+                    ok = false;
+                    break;
+                }
+                ok = mbar_wait(&empty_bar[tail % NSLOT], (tail / NSLOT) & 1);
+                free_kb += (int)((held >> (8 * (tail % NSLOT))) & 0xFF);
+                held &= ~(0xFFull << (8 * (tail % NSLOT)));
+                tail++;
+            }
+            held += (unsigned long long)need_kb << (8 * (grp % NSLOT));
+            free_kb -= need_kb;
+        };
         TileInfo next = tile_info<MAX_TOK, FEATS, PAIR>(p, unit, feat_tiles, rank);
         for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
             const TileInfo t = next;
@@ -251,79 +274,82 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (it % PRODUCERS != me) continue;
                 const bool wrap = off_kb + size_kb > RING_KB;
                 const int need_kb = size_kb + (wrap ? RING_KB - off_kb : 0);
-                const int s = issued % NSLOT;
+                const int s = (it / GROUP) % NSLOT;
                 if (lane == 0) {
-                    ok = !*abort_flag;
-                    while (ok && (free_kb < need_kb || issued - tail == NSLOT)) {     // the oldest stages give their bytes back
-                        ok = mbar_wait(&my_empty[tail % NSLOT], (tail / NSLOT) & 1);
-                        free_kb += (int)((held >> (8 * (tail % NSLOT))) & 0xFF);
-                        tail++;
-                    }
-                    held = (held & ~(0xFFull << (8 * s))) | ((unsigned long long)need_kb << (8 * s));
-                    free_kb -= need_kb;
-                    if (ok && rank == 0) mbar_expect_tx(&my_full[s], stage_tx);
+                    acquire(it / GROUP, need_kb);
+                    if (ok && rank == 0) mbar_expect_tx(&full_bar[s], stage_tx);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 if (wrap) off_kb = 0;
                 if (box_map) {
-                    if (PAIR) tma_load_3d_pair(ring + off_kb * 1024 + box_off, box_map, k * BK, box_row, box_grp, &my_full[s]);
-                    else tma_load_3d(ring + off_kb * 1024 + box_off, box_map, k * BK, box_row, box_grp, &my_full[s]);
+                    if (PAIR) tma_load_3d_pair(ring + off_kb * 1024 + box_off, box_map, k * BK, box_row, box_grp, &full_bar[s]);
+                    else tma_load_3d(ring + off_kb * 1024 + box_off, box_map, k * BK, box_row, box_grp, &full_bar[s]);
                 }
                 off_kb += size_kb;
-                issued++;
             }
+        }
+        // the CTA's last group may be short of k steps: the barrier still wants an announcement for each
+        for (const int end = (it + GROUP - 1) / GROUP * GROUP; it < end && ok; it++) {
+            if (it % PRODUCERS != me) continue;
+            if (lane == 0) {
+                acquire(it / GROUP, 0);
+                if (ok && rank == 0) mbar_arrive(&full_bar[(it / GROUP) % NSLOT]);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
         }
         if (lane == 0 && (!ok || *abort_flag)) {
             atomicOr(p.status, ESP_STATUS_WAIT_EXPIRED);
             *abort_flag = 1;
-            // let this warp's own copies land before the CTA's shared memory is given up: the stages not yet
-            // known free may still be in flight, each on the phase of its own use of its slot
-            if (PAIR && rank != 0) {
-                // the peer's copies are counted on the leader's barriers, which it cannot wait on: give them a
-                // millisecond, far more than a copy takes
-                for (int j = 0; j < 1000; j++) __nanosleep(1000);
-            } else {
-                for (int j = tail; j < issued; j++) mbar_wait(&my_full[j % NSLOT], (j / NSLOT) & 1);
-            }
+            // let this warp's own copies land before the CTA's shared memory is given up: a millisecond, far more
+            // than a copy takes (their barriers also count the other producer's copies, which may never come)
+            for (int j = 0; j < 1000; j++) __nanosleep(1000);
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {                                // of a pair, the first CTA issues the MMAs of both
-            int local = 0, ring = 0;
-            int off0 = 0, off1 = 0, count0 = 0, count1 = 0;           // per ring: the next offset (KB), the stages consumed
+            int local = 0;
+            int off0 = 0, off1 = 0;                                   // per ring: the next offset (KB)
+            int step = 0;                                             // k steps of the CTA so far
+            const int my_steps = ((total_tiles - unit + n_units - 1) / n_units) * k_iters;
             // descriptors differ from stage to stage and from one 16-wide k step to the next only in the
             // address field (16-byte units): the low word is a base plus a constant
             const unsigned long long desc0 = smem_desc(smem);
             const unsigned desc_hi = (unsigned)(desc0 >> 32), desc_lo0 = (unsigned)desc0;
             const unsigned full_addr = smem_u32(full_bar), empty_addr = smem_u32(empty_bar);
             bool ok = true;
-            // one k step out of ring R: wait for its stage, four MMAs, hand the stage back
-            auto k_step = [&](auto ring_tag, int& off, int& count, unsigned acc, unsigned idesc, int size_kb, bool first) {
+            // One k step out of ring R: four MMAs.  The first k step of a group waits for the group's copies (of
+            // both rings), the last one hands the group's stages back: a wait and a commit keep this thread about
+            // 100 cycles each, as long as two MMAs, and this thread's time is what a k step takes.
+            auto k_step = [&](auto ring_tag, int& off, unsigned acc, unsigned idesc, int size_kb, bool first) {
                 constexpr int R = decltype(ring_tag)::value;
-                const unsigned slot8 = (unsigned)(R * NSLOT + (count & (NSLOT - 1))) << 3;
-                if (!mbar_wait_addr(full_addr + slot8, (count >> 3) & 1)) return false;
-                tc_fence_after();
+                const int grp = step / GROUP, in_grp = step - grp * GROUP;
+                const unsigned slot8 = (unsigned)(grp & (NSLOT - 1)) << 3;
+                if (in_grp == 0) {
+                    if (!mbar_wait_addr(full_addr + slot8, (grp >> 3) & 1)) return false;
+                    tc_fence_after();
+                }
                 if (off + size_kb > RING_KB) off = 0;                   // the producer's rule
                 const unsigned w_lo = desc_lo0 + (R * RING_KB + off) * (1024 >> 4);
                 const unsigned t_lo = w_lo + (W_BYTES >> 4);
                 off += size_kb;
-                count++;
+                step++;
+                const bool last = in_grp == GROUP - 1 || step == my_steps;
                 if (PAIR) {
                     tc_mma_lo_pair(acc, w_lo, t_lo, desc_hi, idesc, first ? 0u : 1u);
                     tc_mma_lo_pair(acc, w_lo + 2, t_lo + 2, desc_hi, idesc, 1u);
                     tc_mma_lo_pair(acc, w_lo + 4, t_lo + 4, desc_hi, idesc, 1u);
                     tc_mma_lo_pair(acc, w_lo + 6, t_lo + 6, desc_hi, idesc, 1u);
-                    tc_commit_pair_addr(empty_addr + slot8);            // the stage is free in both CTAs once these MMAs have read it
+                    if (last) tc_commit_pair_addr(empty_addr + slot8);  // the stages are free in both CTAs once these MMAs have read them
                 } else {
                     tc_mma_lo(acc, w_lo, t_lo, desc_hi, idesc, first ? 0u : 1u);
                     tc_mma_lo(acc, w_lo + 2, t_lo + 2, desc_hi, idesc, 1u);
                     tc_mma_lo(acc, w_lo + 4, t_lo + 4, desc_hi, idesc, 1u);
                     tc_mma_lo(acc, w_lo + 6, t_lo + 6, desc_hi, idesc, 1u);
-                    tc_commit_addr(empty_addr + slot8);                 // the stage is free once these MMAs have read it
+                    if (last) tc_commit_addr(empty_addr + slot8);       // the stages are free once these MMAs have read them
                 }
                 return true;
             };
-            static_assert(NSLOT == 8 && BK == 64, "the slot arithmetic and the four MMAs of a k step are written out");
+            static_assert(NSLOT == 8 && BK == 64 && PRODUCERS == 2, "the slot arithmetic and the four MMAs of a k step are written out");
             TileInfo next = tile_info<MAX_TOK, FEATS, PAIR>(p, unit, feat_tiles, rank);
             for (int tile = unit; tile < total_tiles && !*abort_flag; tile += n_units, local++) {
                 const TileInfo t = next;
@@ -338,9 +364,9 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tc_fence_after();
                 const unsigned acc = tmem_base + buf * ACC_COLS;
                 const int size_kb = (W_BYTES + (PAIR ? t.n_tok >> 1 : t.n_tok) * BK * 2) >> 10;
-                for (int k = 0; k < k_iters && ok; k++, ring ^= 1) {
-                    if (ring == 0) ok = k_step(std::integral_constant<int, 0>{}, off0, count0, acc, idesc, size_kb, k == 0);
-                    else ok = k_step(std::integral_constant<int, 1>{}, off1, count1, acc, idesc, size_kb, k == 0);
+                for (int k = 0; k < k_iters && ok; k++) {
+                    if ((step & 1) == 0) ok = k_step(std::integral_constant<int, 0>{}, off0, acc, idesc, size_kb, k == 0);
+                    else ok = k_step(std::integral_constant<int, 1>{}, off1, acc, idesc, size_kb, k == 0);
                 }
                 if (!ok || *abort_flag) break;
                 if (PAIR) tc_commit_pair_addr(smem_u32(&acc_full_bar[buf]));

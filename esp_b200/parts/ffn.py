@@ -170,6 +170,15 @@ class MoeSwiGluShared(Part):
         perm_weight = ws.get("moe_perm_weight", (n * k,), torch.float32)
         inverse = ws.get("moe_inverse", (n, k), torch.int32)
         tiles = None
+        shared = ws.get("moe_shared_out", (n, H), torch.float32)
+        beside = n <= SIDE_STREAM_ROWS and rt.side_stream is not None
+        if beside:
+            # few rows: the shared expert depends neither on the router nor on the routing, so it runs beside
+            # them and the routed experts on a second stream (in a captured step: a parallel branch of the graph)
+            main = torch.cuda.current_stream()
+            rt.side_stream.wait_stream(main)
+            with torch.cuda.stream(rt.side_stream):
+                _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
         if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E) and not grouped_uses_tc05(h, self.w_gate_up, n * k):
             # few tokens: router and permutation in two short launches
             logits = ws.get("moe_logits", (n, E + 1), torch.float32)
@@ -187,18 +196,10 @@ class MoeSwiGluShared(Part):
                             distinct=self.expert_reads)
         if rt.record_routing:
             ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
-        shared = ws.get("moe_shared_out", (n, H), torch.float32)
-        if n <= SIDE_STREAM_ROWS and rt.side_stream is not None:
-            # few rows: the shared expert does not depend on the routing, so it runs beside the routed
-            # experts on a second stream (in a captured step: a parallel branch of the graph)
-            main = torch.cuda.current_stream()
-            rt.side_stream.wait_stream(main)
-            with torch.cuda.stream(rt.side_stream):
-                _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
-            expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
+        expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
+        if beside:
             main.wait_stream(rt.side_stream)
         else:
-            expert_out = self.experts(h, offsets, perm_token, perm_weight, n * k, n, tiles)
             _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
         if y is None:
             return DeferredMoeCombine(rt, expert_out, ids, inverse, gate, shared, H)
