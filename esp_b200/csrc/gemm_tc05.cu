@@ -516,8 +516,9 @@ int make_map(CUtensorMap* map, const void* base, unsigned long long d0, unsigned
 ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, int groups, int w_rows,
                           const float* row_scale, void* C, long long ldc, const int* tile_group, const int* tile_row0,
                           const int* tile_rows, const int* n_tiles, int max_tiles, int tile_max, int M, int N, int K, int swiglu,
-                          int pair, int* status, cudaStream_t stream) {
+                          int pair, int max_ctas, int* status, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || rows_total <= 0) return 0;
+    if (max_ctas < 0 || (pair && max_ctas == 1)) return (int)cudaErrorInvalidValue;
     if (K % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     CUtensorMap map_a, map_a64, map_a128, map_w;
     int rc = make_map(&map_a, A, (unsigned long long)K, (unsigned long long)rows_total, 1, TOK_BOX, 3);
@@ -545,6 +546,9 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
+    // ``max_ctas`` > 0: the kernel takes at most that many SMs (its CTAs walk the tiles with the grid's stride),
+    // so that kernels of another stream find room beside it
+    const int ctas = max_ctas > 0 && max_ctas < sm_count ? max_ctas : sm_count;
     const size_t smem = PRODUCERS * RING_BYTES + 1024 + BAR_BYTES + SWAP_BYTES;     // 230,656 of the 232,448 bytes a block may have
     const int which = (pair ? 4 : 0) + (swiglu ? 2 : 0) + (max_tok == 256 ? 1 : 0);
     typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, Tc05Params);
@@ -566,7 +570,7 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
     if (pair) {
         // two CTAs of a cluster share a token tile: the grid is a whole number of pairs, one pair per two SMs
         const long long pair_tiles = (long long)token_tiles * (((N + feats - 1) / feats + 1) / 2);
-        const long long pairs = pair_tiles < sm_count / 2 ? pair_tiles : sm_count / 2;
+        const long long pairs = pair_tiles < ctas / 2 ? pair_tiles : ctas / 2;
         cfg.gridDim = dim3((unsigned)(2 * pairs));
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
@@ -575,7 +579,7 @@ ESP_API int esp_gemm_tc05(const void* A, long long rows_total, const void* W, in
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     } else {
-        cfg.gridDim = dim3((unsigned)(tiles_bound < sm_count ? tiles_bound : sm_count));
+        cfg.gridDim = dim3((unsigned)(tiles_bound < ctas ? tiles_bound : ctas));
     }
     cudaLaunchKernelEx(&cfg, kernels[which], map_a, map_a64, map_a128, map_w, p);
     return esp_launch_status();

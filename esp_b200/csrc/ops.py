@@ -35,7 +35,7 @@ _SIGNATURES = {
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
     "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P],
     "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-                      c_int, P, P],
+                      c_int, c_int, P, P],
     "esp_wait_probe": [c_int, P, P],
     "esp_moe_combine": [P, P, P, P, P, P, c_int, c_int, c_int, P],
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
@@ -522,11 +522,13 @@ TC05_TILE_ROWS = 256
 TC05_PAIR = os.environ.get("ESP_B200_TC05_PAIR", "all")
 
 
-def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None, tile_rows=None, pair=None):
+def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None, tile_rows=None, pair=None,
+              max_ctas=0):
     """TMA + tcgen05 product for many rows.  a [rows, K] bfloat16 contiguous; w [N, K] or [G, N, K]
     bfloat16.  Plain: c float32 [rows, N] = scale * a @ w[g].T.  swiglu: w rows are [gate; up] and c is
     bfloat16 [rows, I].  Grouped: ``tiles`` = (tile_group, tile_row0, tile_count, n_tiles) from moe_permute,
-    ``tile_rows`` the most rows a tile has (128 or 256; TC05_TILE_ROWS when not given)."""
+    ``tile_rows`` the most rows a tile has (128 or 256; TC05_TILE_ROWS when not given).  ``max_ctas`` > 0:
+    the kernel takes at most that many SMs, so that kernels of another stream find room beside it."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not a.is_contiguous() or not w.is_contiguous():
         raise Backend("gemm_tc05 takes contiguous bfloat16 operands")
     if w.dim() == 3:
@@ -551,7 +553,7 @@ def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=No
         _ptr(tiles[1], torch.int32) if grouped else None, _ptr(tiles[2], torch.int32) if grouped else None,
         _ptr(tiles[3], torch.int32) if grouped else None, tiles[0].shape[0] if grouped else 0,
         tile_rows if grouped else 0, m, n, k,
-        1 if swiglu else 0, 1 if pair else 0, _ptr(status, torch.int32), _stream())
+        1 if swiglu else 0, 1 if pair else 0, int(max_ctas), _ptr(status, torch.int32), _stream())
     _check(code, "gemm_tc05")
 
 

@@ -192,6 +192,7 @@ class Runtime:
             self.ws = Workspace(self.device)
             self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
             self.side_stream = torch.cuda.Stream(device=self.device)     # for work that may run beside the main stream
+            self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.ffn_chunk_tokens = ffn_chunk_tokens
         self.record_routing = False       # debugging aid: MoE parts put their choices into ctx.aux
         # named 64-bit counters that kernels add to on the device (read with ``read_counters``: that waits)

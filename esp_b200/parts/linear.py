@@ -42,16 +42,17 @@ def linear(rt, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Ten
     return out
 
 
-def swiglu_linear(rt, a, w_gate_up, act, tag):
+def swiglu_linear(rt, a, w_gate_up, act, tag, max_ctas=0):
     """act = silu(a @ w_gate.T) * (a @ w_up.T) in the activation dtype; w_gate_up
-    is [2I, K] with the gate rows first."""
+    is [2I, K] with the gate rows first.  ``max_ctas`` > 0 bounds the SMs that the
+    many-row kernel takes."""
     n = a.shape[0]
     inter = w_gate_up.shape[0] // 2
     if _both_bf16(a, w_gate_up) and n <= SKINNY_ROWS and ops.skinny_fits(a.shape[1]):
         ops.gemm_skinny(a, w_gate_up, act, swiglu=True)
         return act
     if _both_bf16(a, w_gate_up) and DENSE_GEMM in ("own", "mixed") and a.shape[1] % 8 == 0 and a.is_contiguous() and act.is_contiguous():
-        ops.gemm_tc05(a, w_gate_up, act, rt.status, swiglu=True)
+        ops.gemm_tc05(a, w_gate_up, act, rt.status, swiglu=True, max_ctas=max_ctas)
         return act
     gu = rt.ws.get(tag + "_gu", (n, 2 * inter), torch.float32)
     linear(rt, a, w_gate_up, gu)
