@@ -349,7 +349,43 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
                 return true;
             };
-            static_assert(NSLOT == 8 && BK == 64 && PRODUCERS == 2, "the slot arithmetic and the four MMAs of a k step are written out");
+            // a whole group in one piece: the two k steps of a tile that lie in one group, without a branch between them
+            auto two_steps = [&](unsigned acc, unsigned idesc, int size_kb, bool first) {
+                const int grp = step / GROUP;
+                const unsigned slot8 = (unsigned)(grp & (NSLOT - 1)) << 3;
+                if (!mbar_wait_addr(full_addr + slot8, (grp >> 3) & 1)) return false;
+                tc_fence_after();
+                if (off0 + size_kb > RING_KB) off0 = 0;
+                if (off1 + size_kb > RING_KB) off1 = 0;
+                const unsigned w0 = desc_lo0 + off0 * (1024 >> 4), t0 = w0 + (W_BYTES >> 4);
+                const unsigned w1 = desc_lo0 + (RING_KB + off1) * (1024 >> 4), t1 = w1 + (W_BYTES >> 4);
+                off0 += size_kb;
+                off1 += size_kb;
+                step += 2;
+                if (PAIR) {
+                    tc_mma_lo_pair(acc, w0, t0, desc_hi, idesc, first ? 0u : 1u);
+                    tc_mma_lo_pair(acc, w0 + 2, t0 + 2, desc_hi, idesc, 1u);
+                    tc_mma_lo_pair(acc, w0 + 4, t0 + 4, desc_hi, idesc, 1u);
+                    tc_mma_lo_pair(acc, w0 + 6, t0 + 6, desc_hi, idesc, 1u);
+                    tc_mma_lo_pair(acc, w1, t1, desc_hi, idesc, 1u);
+                    tc_mma_lo_pair(acc, w1 + 2, t1 + 2, desc_hi, idesc, 1u);
+                    tc_mma_lo_pair(acc, w1 + 4, t1 + 4, desc_hi, idesc, 1u);
+                    tc_mma_lo_pair(acc, w1 + 6, t1 + 6, desc_hi, idesc, 1u);
+                    tc_commit_pair_addr(empty_addr + slot8);
+                } else {
+                    tc_mma_lo(acc, w0, t0, desc_hi, idesc, first ? 0u : 1u);
+                    tc_mma_lo(acc, w0 + 2, t0 + 2, desc_hi, idesc, 1u);
+                    tc_mma_lo(acc, w0 + 4, t0 + 4, desc_hi, idesc, 1u);
+                    tc_mma_lo(acc, w0 + 6, t0 + 6, desc_hi, idesc, 1u);
+                    tc_mma_lo(acc, w1, t1, desc_hi, idesc, 1u);
+                    tc_mma_lo(acc, w1 + 2, t1 + 2, desc_hi, idesc, 1u);
+                    tc_mma_lo(acc, w1 + 4, t1 + 4, desc_hi, idesc, 1u);
+                    tc_mma_lo(acc, w1 + 6, t1 + 6, desc_hi, idesc, 1u);
+                    tc_commit_addr(empty_addr + slot8);
+                }
+                return true;
+            };
+            static_assert(NSLOT == 8 && BK == 64 && PRODUCERS == 2 && GROUP == 2, "the slot arithmetic and the MMAs of a group are written out");
             TileInfo next = tile_info<MAX_TOK, FEATS, PAIR>(p, unit, feat_tiles, rank);
             for (int tile = unit; tile < total_tiles && !*abort_flag; tile += n_units, local++) {
                 const TileInfo t = next;
@@ -364,10 +400,14 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tc_fence_after();
                 const unsigned acc = tmem_base + buf * ACC_COLS;
                 const int size_kb = (W_BYTES + (PAIR ? t.n_tok >> 1 : t.n_tok) * BK * 2) >> 10;
-                for (int k = 0; k < k_iters && ok; k++) {
-                    if ((step & 1) == 0) ok = k_step(std::integral_constant<int, 0>{}, off0, acc, idesc, size_kb, k == 0);
-                    else ok = k_step(std::integral_constant<int, 1>{}, off1, acc, idesc, size_kb, k == 0);
+                int k = 0;
+                if (step & 1) {                                       // the second k step of a group that the tile before began
+                    ok = k_step(std::integral_constant<int, 1>{}, off1, acc, idesc, size_kb, true);
+                    k = 1;
                 }
+                for (; k + 2 <= k_iters && ok; k += 2) ok = two_steps(acc, idesc, size_kb, k == 0);
+                if (k < k_iters && ok)                                // the first k step of a group that the next tile ends, if there is one
+                    ok = k_step(std::integral_constant<int, 0>{}, off0, acc, idesc, size_kb, k == 0);
                 if (!ok || *abort_flag) break;
                 if (PAIR) tc_commit_pair_addr(smem_u32(&acc_full_bar[buf]));
                 else tc_commit(&acc_full_bar[buf]);                   // the accumulator is complete once all MMAs are done
