@@ -31,8 +31,9 @@ class DeferredMoeCombine:
 # Steps with at least AHEAD_ROWS rows start the shared expert's first product on a second stream before the
 # router, on all SMs but ROUTING_SMS: the router and the permutation are a chain of short launches that leaves
 # the device idle, and they find room on the SMs left over (2,048 tokens, 24 layers: 12.7 -> 12.2 ms; with 4 or 16
-# SMs left over 12.6 and 12.5 ms).
-AHEAD_ROWS = 512
+# SMs left over 12.6 and 12.5 ms).  Below about 768 rows it does not pay (one prompt of 400 tokens: 7.4 -> 7.7 ms;
+# 768: even; 1,024: 8.9 -> 8.3 ms).
+AHEAD_ROWS = 768
 ROUTING_SMS = 8
 SIDE_STREAM_ROWS = 64      # steps with at most this many rows run the shared expert on a second stream
 
