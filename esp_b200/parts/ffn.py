@@ -193,7 +193,7 @@ class MoeSwiGluShared(Part):
             rt.side_stream.wait_stream(main)
             with torch.cuda.stream(rt.side_stream):
                 _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
-        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E) and not grouped_uses_tc05(h, self.w_gate_up, n * k):
+        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E) and not grouped_uses_tc05(h, self.w_gate_up, n * k, n):
             # few tokens: router and permutation in two short launches
             logits = ws.get("moe_logits", (n, E + 1), torch.float32)
             ops.route_small(router_in, self.w_router, self.w_shared_gate, logits, ids, wts, gate, k, s.norm_topk,
@@ -201,7 +201,7 @@ class MoeSwiGluShared(Part):
         else:
             ops.router_topk(router_in, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status,
                             probs, logits=ws.get("moe_logits", (n, E + 1), torch.float32))
-            if grouped_uses_tc05(h, self.w_gate_up, n * k) and Im % 8 == 0:
+            if grouped_uses_tc05(h, self.w_gate_up, n * k, n) and Im % 8 == 0:
                 max_tiles = (n * k + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
                 tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32),
                          ws.get("moe_tile_row0", (max_tiles,), torch.int32),

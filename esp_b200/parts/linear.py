@@ -19,6 +19,7 @@ import os
 
 SKINNY_ROWS = 16            # dense products with at most this many rows stream the weights once
 TC05_GROUPED_ROWS = int(os.environ.get("ESP_B200_TC05_ROWS", "128"))   # grouped products with at least this many (token, expert) rows use TMA + tcgen05
+TC05_GROUP_ROWS = int(os.environ.get("ESP_B200_TC05_GROUP_ROWS", "8"))   # ... or with a group that may have more rows than this
 # dense products with many rows: "own" = this library's TMA + tcgen05 kernel everywhere; "library" = cuBLAS
 # through torch; "mixed" = cuBLAS for plain products, this library's kernel where SwiGLU is fused into it
 DENSE_GEMM = os.environ.get("ESP_B200_DENSE_GEMM", "mixed")
@@ -60,8 +61,14 @@ def swiglu_linear(rt, a, w_gate_up, act, tag, max_ctas=0):
     return act
 
 
-def grouped_uses_tc05(a, w, rows) -> bool:
-    return _both_bf16(a, w) and rows >= TC05_GROUPED_ROWS and a.shape[1] % 8 == 0 and w.shape[1] % 16 == 0
+def grouped_uses_tc05(a, w, rows, max_rows=None) -> bool:
+    """Whether a grouped product of ``rows`` (token, expert) rows, at most ``max_rows`` of them in one group,
+    runs on TMA + tcgen05.  The weight-streaming kernel keeps a group's rows in one or two blocks of eight; with
+    one block it wins up to about 32 rows in all, with two it loses from the start (24 layers at the A2.7B
+    sizes, context 4,096: batch 8 4.13 against 4.86 ms a step, batch 10 6.08 against 5.66, batch 16 7.42 against
+    6.75, batch 64 14.9 against 13.5)."""
+    many = rows >= TC05_GROUPED_ROWS or (max_rows is not None and max_rows > TC05_GROUP_ROWS)
+    return _both_bf16(a, w) and many and a.shape[1] % 8 == 0 and w.shape[1] % 16 == 0
 
 
 def grouped_swiglu_linear(rt, a, w_gate_up, act, group_offsets, a_rows, rows, max_rows, tag, tiles=None):
