@@ -4,7 +4,8 @@ Which kernel runs is decided here and nowhere else:
 * 32-bit engine, or a weight kept in 32-bit: the plain CUDA-core kernel with
   true float32 multiply-adds and a fixed summation order;
 * bfloat16 activations and weights, at most SKINNY_ROWS rows (decode): the
-  weight-streaming tensor-core kernel of this library;
+  weight-streaming tensor-core kernel of this library (grouped products: see
+  ``grouped_uses_tc05``);
 * bfloat16 with more rows (prefill): a library product (cuBLAS through torch)
   with float32 accumulation and output, as the reference engine leaves its
   dense products to its tensor library.
@@ -17,7 +18,10 @@ from ..csrc import ops
 
 import os
 
-SKINNY_ROWS = 16            # dense products with at most this many rows stream the weights once
+# dense products with at most this many rows stream the weights once through the kernel's one block of eight
+# rows (the kernel takes 16 in two blocks, which is slower than the library product from 9 rows on: batch 16 at
+# the A2.7B sizes 6.75 against 6.37 ms a step)
+SKINNY_ROWS = int(os.environ.get("ESP_B200_SKINNY_ROWS", "8"))
 TC05_GROUPED_ROWS = int(os.environ.get("ESP_B200_TC05_ROWS", "128"))   # grouped products with at least this many (token, expert) rows use TMA + tcgen05
 TC05_GROUP_ROWS = int(os.environ.get("ESP_B200_TC05_GROUP_ROWS", "8"))   # ... or with a group that may have more rows than this
 # dense products with many rows: "own" = this library's TMA + tcgen05 kernel everywhere; "library" = cuBLAS
