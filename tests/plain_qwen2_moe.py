@@ -96,8 +96,12 @@ def layer_window(c: dict, i: int):
     layer; else ``use_sliding_window`` and ``max_window_layers`` (the qwen2 / qwen2_moe branch)."""
     if c.get("layer_types") is not None:
         return c["sliding_window"] if c["layer_types"][i] == "sliding_attention" else None
-    if c["use_sliding_window"] is False or c["use_sliding_window"] is None:
+    if c["use_sliding_window"] is False:
         return None
+    if c.get("model_type") not in ("qwen2", "qwen3", "qwen2_moe"):
+        # every other family the reference reads: a window, when given, holds for every layer (used here only
+        # for its dense ``mistral`` checkpoint, whose head size differs from width / heads)
+        return c["sliding_window"]
     if c["use_sliding_window"] is True and i >= c["max_window_layers"]:
         return c["sliding_window"]
     return None
@@ -137,15 +141,17 @@ def apply_rope(x, cos, sin):
 
 def attention(c, w, prefix, x, window):
     """GQA attention of one layer over a whole sequence x [T, H]
-    (crates/esp/src/infer/decoder/attention.rs:292-404): q/k/v with bias,
+    (crates/esp/src/infer/decoder/attention.rs:292-404): q/k/v with bias (where the checkpoint has one),
     rotary on q and k, scores divided by sqrt(hd) after the product, key j of
     query a masked iff j > a or (window and a - j >= window), softmax, PV,
     o_proj without bias."""
     T = x.shape[0]
     nh, nkv, hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
-    q = x @ w[prefix + "q_proj.weight"].T + w[prefix + "q_proj.bias"]
-    k = x @ w[prefix + "k_proj.weight"].T + w[prefix + "k_proj.bias"]
-    v = x @ w[prefix + "v_proj.weight"].T + w[prefix + "v_proj.bias"]
+    def project(name):      # the bias is added where the checkpoint has one (the Qwen2 families do, always)
+        y = x @ w[prefix + name + ".weight"].T
+        return y + w[prefix + name + ".bias"] if prefix + name + ".bias" in w else y
+
+    q, k, v = project("q_proj"), project("k_proj"), project("v_proj")
     q = q.reshape(T, nh, hd)
     k = k.reshape(T, nkv, hd)
     v = v.reshape(T, nkv, hd)

@@ -47,6 +47,30 @@ def test_recorded_outputs_of_the_windowed_checkpoint_pin_the_mask(dtype):
     assert [plain.layer_window(dict(c, layer_types=None), i) for i in range(2)] == [None, 3]
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_recorded_outputs_of_a_checkpoint_whose_head_size_is_not_width_over_heads(dtype):
+    """The reference's dense ``mistral`` checkpoint runs the same attention code with ``head_dim`` 12 at a
+    width of 16 with 2 heads (so that q is 24 wide and the scores are divided by sqrt(12)), one key/value head
+    for two query heads and a window of 3 on every layer.  Its recorded logits pin the explicit head size;
+    every layer is dense here and no projection has a bias."""
+    case = CASES["mistral"]
+    c, w = plain.load_model(GOLDEN / "mistral")
+    assert c["head_dim"] == 12 and c["hidden_size"] // c["num_attention_heads"] == 8
+    assert [plain.layer_window(c, i) for i in range(2)] == [3, 3]
+    logits = plain.forward_logits(c, w, case["input_ids"], dtype)
+    err = np.abs(logits[-1] - np.asarray(case["last_logits"], dtype=np.float32)).max()
+    assert err < (2e-6 if dtype is np.float32 else 5e-7), err
+    assert plain.generate(c, w, case["input_ids"], 4, dtype=dtype) == case["generated_ids"]
+    # the numbers do depend on the divisor: with sqrt(width / heads) they are missed
+    import unittest.mock as mock
+    real_sqrt = np.sqrt
+    wrong = dict(c)
+    off = None
+    with mock.patch.object(plain.np, "sqrt", lambda v, *a, **k: real_sqrt(8.0 if np.ndim(v) == 0 and float(v) == 12.0 else v, *a, **k)):
+        off = np.abs(plain.forward_logits(wrong, w, case["input_ids"], dtype)[-1] - np.asarray(case["last_logits"])).max()
+    assert off > 1e-5, off
+
+
 def test_splitmix64_known_values():
     # first outputs of splitmix64 from seed 0 (public test vector of the generator)
     r = plain.SplitMix64(0)
