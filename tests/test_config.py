@@ -149,3 +149,18 @@ def test_the_plan_carries_the_checkpoint_names_and_the_parts_spell_none():
     import pytest
     with pytest.raises(InvalidConfig, match="decay"):
         InitSpec().mean_std("decay")
+
+
+def test_which_grouped_kernel_a_step_takes():
+    """The weight-streaming kernel while no expert can have more than eight rows and the step has fewer than
+    128 (token, expert) rows; the TMA + tcgen05 kernel beyond either bound, and never for 32-bit operands."""
+    import torch
+    from esp_b200.parts import linear
+    a = torch.empty(4, 64, dtype=torch.bfloat16)
+    w = torch.empty(3, 32, 64, dtype=torch.bfloat16)
+    assert not linear.grouped_uses_tc05(a, w, 32, 8)
+    assert linear.grouped_uses_tc05(a, w, 36, 9)
+    assert linear.grouped_uses_tc05(a, w, 128, 8)
+    assert not linear.grouped_uses_tc05(a, w, 127)
+    assert not linear.grouped_uses_tc05(a.float(), w.float(), 4096, 1024)
+    assert not linear.grouped_uses_tc05(a[:, :60], w[:, :, :60], 4096, 1024)      # K no multiple of 8

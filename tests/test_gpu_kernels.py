@@ -710,6 +710,29 @@ def test_gemm_tc05_swiglu(m, inter, k):
     close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "tcgen05 swiglu")
 
 
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("max_ctas", [2, 7, 140])
+def test_gemm_tc05_on_fewer_ctas_than_sms_gives_the_same_bits(pair, max_ctas):
+    """A launch told to take at most ``max_ctas`` SMs (so that another stream's kernels find room) walks the
+    same tiles with a longer stride: equal bits, for an odd k-step count too (groups of two k steps then
+    straddle tiles)."""
+    m, inter, k = 700, 328, 3 * 64 + 8          # 4 k steps, the last one 8 wide
+    a, w = rnd(m, k, dtype=torch.bfloat16), rnd(2 * inter, k, dtype=torch.bfloat16, seed=1, scale=0.1)
+    outs = []
+    for limit in (0, max_ctas):
+        act = torch.zeros(m, inter, dtype=torch.bfloat16, device=DEV)
+        c = torch.zeros(m, 2 * inter, device=DEV)
+        st = status()
+        ops.gemm_tc05(a, w, act, st, swiglu=True, pair=pair, max_ctas=limit)
+        ops.gemm_tc05(a, w, c, st, pair=pair, max_ctas=limit)
+        assert st.item() == 0
+        outs.append((act, c))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    close(outs[1][1], a.double() @ w.double().t(), torch.float32, "tcgen05 dense on few CTAs", k=k)
+    with pytest.raises(Exception):
+        ops.gemm_tc05(a, w, outs[0][1], status(), pair=True, max_ctas=1)      # a pair needs two
+
+
 def check_tile_cover(first_rows, counts, rows, tile):
     """Every permuted row lies in exactly one tile."""
     seen = np.zeros(rows, dtype=np.int64)

@@ -240,6 +240,40 @@ def test_feed_forward_rows_cut_into_portions_change_nothing(folders_b, dtype, ch
         assert np.abs(cut - uncut).max() <= 4 * 2.0 ** -8 * np.abs(uncut).max()
 
 
+def test_shared_expert_ahead_of_the_router_changes_nothing(folders_b):
+    """Steps of many rows start the shared expert's first product on a second stream, on fewer SMs, before the
+    router runs.  A prompt of 1,700 tokens through that path (whole, and cut into portions of 800 rows so that
+    two portions take it and a last one of 100 rows does not) gives the logits of the same prompt with the
+    second stream never used: rows do not depend on where their product ran."""
+    from esp_b200.engine import StepEntry
+    from esp_b200.parts import ffn
+    eng = engine_for(folders_b["hd128"], "bfloat16", max_tokens=2048, record_routing=False)
+    rng = np.random.default_rng(17)
+    toks = random_ids(rng, 1700, 2000)
+    want = [0, 1, 767, 768, 799, 800, 1599, 1600, 1699]
+
+    def run():
+        s = eng.open()
+        out = eng.step([StepEntry(s, toks, want)]).float().cpu().numpy()
+        eng.close(s)
+        return out
+
+    assert len(toks) >= ffn.AHEAD_ROWS
+    ahead = run()
+    limit, rows = eng.rt.ffn_chunk_tokens, ffn.AHEAD_ROWS
+    try:
+        eng.rt.ffn_chunk_tokens = 800
+        portions = run()
+        ffn.AHEAD_ROWS = 10 ** 9
+        eng.rt.ffn_chunk_tokens = limit
+        in_line = run()
+    finally:
+        eng.rt.ffn_chunk_tokens, ffn.AHEAD_ROWS = limit, rows
+    assert eng.read_status() == 0
+    assert np.array_equal(ahead, in_line)
+    assert np.abs(portions - in_line).max() <= 4 * 2.0 ** -8 * np.abs(in_line).max()
+
+
 def test_a_single_token_step_reads_exactly_top_k_experts_per_sparse_layer(folders_b):
     """The engine's counters: a step of one token touches exactly k experts in every sparse layer
     (crates/esp/src/infer/decoder/architecture_tests.rs:220-236); a step of several tokens touches at most
