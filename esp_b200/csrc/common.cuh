@@ -25,6 +25,23 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// four consecutive values stored as one piece (16 bytes of float, 8 of bfloat16); p is aligned to the piece
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void store(bf16* p, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<unsigned*>(&lo);
+        v.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(p) = v;
+    }
+};
+
 // Warp sum with a fixed butterfly order: the result does not depend on which
 // other warps or blocks run beside this one.
 __device__ __forceinline__ float warp_sum(float v) {

@@ -134,7 +134,7 @@ add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, cons
             const float4 gm = reinterpret_cast<const float4*>(gamma)[q];
             const float o0 = v[i].x * inv * gm.x, o1 = v[i].y * inv * gm.y, o2 = v[i].z * inv * gm.z, o3 = v[i].w * inv * gm.w;
             TH* hr = h + (size_t)r * width + 4 * q;
-            hr[0] = from_f32<TH>(o0); hr[1] = from_f32<TH>(o1); hr[2] = from_f32<TH>(o2); hr[3] = from_f32<TH>(o3);
+            Vec4<TH>::store(hr, o0, o1, o2, o3);
             if (h32) reinterpret_cast<float4*>(h32 + (size_t)r * width)[q] = make_float4(o0, o1, o2, o3);
         }
     }

@@ -73,22 +73,6 @@ __global__ void rope_kvwrite_kernel(const float* __restrict__ qkv, const float* 
 
 // The same for full rotation (rot == hd, hd a multiple of 8) with 16-byte accesses: a thread owns four
 // consecutive pairs (i, i + hd/2) of one head of one token.
-template <typename T> struct Vec4;
-template <> struct Vec4<float> {
-    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
-        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
-    }
-};
-template <> struct Vec4<bf16> {
-    static __device__ __forceinline__ void store(bf16* p, float a, float b, float c, float d) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-        uint2 v;
-        v.x = *reinterpret_cast<unsigned*>(&lo);
-        v.y = *reinterpret_cast<unsigned*>(&hi);
-        *reinterpret_cast<uint2*>(p) = v;
-    }
-};
-
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_kvwrite_vec_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, const int* __restrict__ tok_seq,
