@@ -49,12 +49,13 @@ def cmd_generate(a) -> int:
         from .engine import StepEntry
         eng = prov.engine
         ids = list(reqs[0].prompt_ids)
-        slot = eng.open()
-        try:
-            _logits, prefill = eng.profile_step([StepEntry(slot, ids, [len(ids) - 1])])
-            _logits, decode = eng.profile_step([StepEntry(slot, [ids[-1]], [0])])
-        finally:
-            eng.close(slot)
+        for timed in (False, True):          # once untimed: the first launches load the kernels
+            slot = eng.open()
+            try:
+                _logits, prefill = eng.profile_step([StepEntry(slot, ids, [len(ids) - 1])])
+                _logits, decode = eng.profile_step([StepEntry(slot, [ids[-1]], [0])])
+            finally:
+                eng.close(slot)
         print(f"prefill of {len(ids)} tokens, by kernel:\n{prefill.table()}\n\none decode step, by kernel:\n{decode.table()}",
               file=sys.stderr)
     for i, g in enumerate(prov.generate(reqs)):
