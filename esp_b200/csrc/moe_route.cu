@@ -375,6 +375,8 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
     float* ps_all = sm_f;                                      // [8 warps][n_experts]
     int* counts = reinterpret_cast<int*>(sm_f + 8 * n_experts); // [n_experts]
     int* cursor = counts + n_experts;                           // [n_experts + 1]
+    int* pair_e = cursor + n_experts + 1;                       // [n_tokens * top_k]
+    float* pair_w = reinterpret_cast<float*>(pair_e + n_tokens * top_k);   // [n_tokens * top_k]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int e = tid; e < n_experts; e += 256) counts[e] = 0;
     __syncthreads();
@@ -427,32 +429,48 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
             if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
         }
         if (lane < top_k) {
+            const float w = my_p / denom;
             topk_ids[(size_t)n * top_k + lane] = my_e;
-            topk_w[(size_t)n * top_k + lane] = my_p / denom;
+            topk_w[(size_t)n * top_k + lane] = w;
+            pair_e[n * top_k + lane] = my_e;                      // kept in shared memory for the placement below
+            pair_w[n * top_k + lane] = w;
             atomicAdd(&counts[my_e], 1);
         }
         __syncwarp();
     }
     __syncthreads();
-    if (tid == 0) {
+    if (warp == 0) {
+        // first rows of the experts' ranges: a running sum over the counts, 32 experts at a time
         int run = 0, used = 0;
-        for (int e = 0; e < n_experts; e++) {
-            cursor[e] = run;
-            offsets[e] = run;
-            run += counts[e];
-            used += counts[e] > 0;
+        for (int e0 = 0; e0 < n_experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < n_experts ? counts[e] : 0;
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            if (e < n_experts) {
+                cursor[e] = run + incl - c;
+                offsets[e] = run + incl - c;
+            }
+            used += __popc(__ballot_sync(0xffffffffu, c > 0));
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        cursor[n_experts] = run;
-        offsets[n_experts] = run;
-        if (distinct) atomicAdd(distinct, (unsigned long long)used);     // experts that this step reads
+        if (lane == 0) {
+            cursor[n_experts] = run;
+            offsets[n_experts] = run;
+            if (distinct) atomicAdd(distinct, (unsigned long long)used);     // experts that this step reads
+        }
     }
     __syncthreads();
     const int n_pairs = n_tokens * top_k;
     for (int i = tid; i < n_pairs; i += 256) {
-        const int e = topk_ids[i];                                // written above by this block
+        const int e = pair_e[i];
         const int row = atomicAdd(&cursor[e], 1);
         perm_token[row] = i / top_k;
-        perm_weight[row] = topk_w[i];
+        perm_weight[row] = pair_w[i];
         inverse[i] = row;
     }
 }
@@ -806,7 +824,8 @@ ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, 
     if (n_tokens <= 0) return 0;
     if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts || n_tokens > 32) return (int)cudaErrorInvalidValue;
     const size_t smem_a = (size_t)width * sizeof(float);
-    const size_t smem_b = (size_t)(8 * n_experts) * sizeof(float) + (size_t)(2 * n_experts + 1) * sizeof(int);
+    const size_t smem_b = (size_t)(8 * n_experts) * sizeof(float) + (size_t)(2 * n_experts + 1) * sizeof(int) +
+                          (size_t)n_tokens * top_k * (sizeof(int) + sizeof(float));
     if (smem_a > 48 * 1024 || smem_b > 48 * 1024) return (int)cudaErrorInvalidValue;
     const dim3 grid(n_tokens, (n_experts + 1 + 7) / 8);
 #define ESP_LOGITS(TH, TW)                                                                                        \

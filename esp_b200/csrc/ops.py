@@ -298,7 +298,8 @@ ROUTE_SMALL_TOKENS = 32
 
 
 def route_small_fits(width: int, n_experts: int) -> bool:
-    return width * 4 <= 48 * 1024 and (8 * n_experts) * 4 + (2 * n_experts + 1) * 4 <= 48 * 1024
+    # the second kernel's shared memory: probabilities of eight tokens, counts and cursors, and the step's pairs
+    return width * 4 <= 48 * 1024 and (8 * n_experts) * 4 + (2 * n_experts + 1) * 4 + ROUTE_SMALL_TOKENS * 32 * 8 <= 48 * 1024
 
 
 def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm_topk, offsets, perm_token,
