@@ -58,6 +58,34 @@ def make_folder(tmp: Path, case: str, seed: int = 1234, store: str = "bfloat16",
     return folder
 
 
+def random_config(rng: np.random.Generator) -> dict:
+    """A configuration drawn from the sizes the architecture allows: head sizes in steps of 16 from 16 to 128, one
+    to three key/value heads with one to five query heads each, widths that are and are not multiples of 8, odd
+    vocabularies, one to three layers, dense layers among them, windows from 5 to 130 positions, tying."""
+    hd = int(rng.choice([16, 32, 48, 64, 80, 128]))
+    nkv = int(rng.choice([1, 2, 3]))
+    nh = nkv * int(rng.choice([1, 2, 4, 5]))
+    layers = int(rng.choice([1, 2, 3]))
+    experts = int(rng.choice([3, 4, 7, 8, 12]))
+    window = bool(rng.integers(0, 2))
+    return {
+        "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "hidden_act": "silu",
+        "num_hidden_layers": layers, "hidden_size": int(rng.choice([64, 72, 100, 128, 136, 200])),
+        "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd,
+        "vocab_size": int(rng.choice([97, 256, 301, 512])), "rope_theta": float(rng.choice([1e4, 1e6, 5e4])),
+        "rms_norm_eps": float(rng.choice([1e-6, 1e-5])), "max_position_embeddings": 1024,
+        "intermediate_size": int(rng.choice([40, 64, 96, 136])), "num_experts": experts,
+        "num_experts_per_tok": int(rng.integers(1, min(experts, 5) + 1)), "norm_topk_prob": bool(rng.integers(0, 2)),
+        "moe_intermediate_size": int(rng.choice([16, 24, 40, 64])),
+        "shared_expert_intermediate_size": int(rng.choice([24, 32, 56, 128])),
+        "decoder_sparse_step": int(rng.choice([1, 1, 2])),
+        "mlp_only_layers": [0] if (layers > 1 and rng.integers(0, 3) == 0) else [],
+        "use_sliding_window": window, "sliding_window": int(rng.choice([5, 17, 64, 70, 130])) if window else None,
+        "max_window_layers": int(rng.integers(0, layers)) if window else 28,
+        "tie_word_embeddings": bool(rng.integers(0, 2)),
+    }
+
+
 def random_ids(rng: np.random.Generator, n: int, vocab: int) -> list:
     return [int(t) for t in rng.integers(0, vocab, size=n)]
 
