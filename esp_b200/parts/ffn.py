@@ -185,7 +185,7 @@ class MoeSwiGluShared(Part):
             rt.side_stream.wait_stream(main)
             act_s = ws.get("moe_shared_act", (n, s.shared_intermediate), rt.dtype)
             with torch.cuda.stream(rt.side_stream):
-                swiglu_linear(rt, h, self.w_shared_gate_up, act_s, "moe_shared", max_ctas=rt.sm_count - ROUTING_SMS)
+                swiglu_linear(rt, h, self.w_shared_gate_up, act_s, "moe_shared", max_ctas=max(2, rt.sm_count - ROUTING_SMS))
         if beside:
             # few rows: the shared expert depends neither on the router nor on the routing, so it runs beside
             # them and the routed experts on a second stream (in a captured step: a parallel branch of the graph)
