@@ -196,7 +196,7 @@ def prefill_numbers(nums, layers, T, ms, pk):
 
 
 def measure_shape(torch, raw, layers, batch, context, steps, warmup, pk, points=(1, 64), e2e=True, prefill=True,
-                  clocks=None):
+                  clocks=None, prefill_tokens=2048):
     """Builds the model with random weights and measures prefill, decode at ``batch``, the same through the
     entry point, and decode at ``points``.  Returns a dict of results; the engine is freed before returning."""
     import gc
@@ -212,11 +212,11 @@ def measure_shape(torch, raw, layers, batch, context, steps, warmup, pk, points=
     vocab = raw["vocab_size"]
     biggest = max([batch, *points])
     engine = Engine.from_random(cfg, seed=0, init=InitSpec(0.02, 0.02, 0.0), dtype="bfloat16",
-                                max_tokens=biggest * (context + 64), max_slots=biggest + 2)
+                                max_tokens=max(biggest * (context + 64), prefill_tokens + 64), max_slots=biggest + 2)
     torch.cuda.synchronize()
     out = {}
     rng = np.random.default_rng(1)
-    T = 2048
+    T = prefill_tokens
 
     def prefill_once():
         s = engine.open()
@@ -399,6 +399,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement (for profiling decode)")
+    ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the prompt whose prefill is timed")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the 32-bit cuttings check at the headline sizes and the Qwen2-57B-A14B shape")
     ap.add_argument("--dense-products", action="store_true",
@@ -427,7 +428,8 @@ def main() -> int:
         a.layers = full_layers
     clocks = ClockSampler()
     m = measure_shape(torch, raw, a.layers, a.batch, a.context, a.steps, a.warmup, pk,
-                      points=() if a.no_points else (1, 64), e2e=not a.no_e2e, prefill=not a.no_prefill, clocks=clocks)
+                      points=() if a.no_points else (1, 64), e2e=not a.no_e2e, prefill=not a.no_prefill, clocks=clocks,
+                      prefill_tokens=a.prefill_tokens)
 
     extras = {}
     if not a.no_extras and a.shape == "a2.7b":
