@@ -521,6 +521,7 @@ TC05_TILE_ROWS = 256
 # A2.7B sizes, 2,048 tokens: grouped gate/up 143.5 -> 133.8 us, grouped down 86.9 -> 82.8 us, dense fused SwiGLU
 # 78.4 -> 74.7 us, dense plain 42.3 -> 43.9 us; results are equal bit for bit.
 TC05_PAIR = os.environ.get("ESP_B200_TC05_PAIR", "all")
+TC05_PAIR_ROWS_PER_GROUP = 32          # grouped products with fewer rows per group than this run on single CTAs
 
 
 def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=None, tile_rows=None, pair=None,
@@ -548,6 +549,11 @@ def gemm_tc05(a, w, c, status, swiglu=False, row_scale=None, tiles=None, rows=No
     tile_rows = TC05_TILE_ROWS if tile_rows is None else tile_rows
     if pair is None:
         pair = TC05_PAIR == "all" or TC05_PAIR == ("grouped" if grouped else "dense")
+        # narrow token tiles gain nothing from sharing them between two CTAs, and one MMA thread per CTA issues
+        # more per SM than one per pair: a prompt of 256 tokens (17 rows an expert) 7.45 -> 6.91 ms on single
+        # CTAs, one of 1,024 tokens (68 rows an expert) 8.11 -> 8.55 ms
+        if grouped and m < TC05_PAIR_ROWS_PER_GROUP * groups:
+            pair = False
     code = _fn("tc05", "esp_gemm_tc05")(
         a.data_ptr(), m, w.data_ptr(), groups, wn, _ptr(row_scale, torch.float32, "row_scale"), c.data_ptr(),
         c.stride(0), _ptr(tiles[0], torch.int32) if grouped else None,
