@@ -182,6 +182,25 @@ def test_medium_models_cuttings_agree_with_decode_steps_replayed_from_graphs(fol
             check_against_plain(folder, dtype, reqs, rec, f"medium {name}, all experts, graphs, {what}")
 
 
+@pytest.mark.parametrize("name", ["hd128", "hd64"])
+def test_the_same_steps_twice_give_the_same_bits_in_bfloat16(folders_b, name):
+    """Nothing in a step depends on the order in which blocks happen to run (the permutation places an expert's
+    rows with atomics, the attention's last block combines, the shared expert runs on a second stream): the
+    same batches run twice, eagerly and from captured graphs, give identical logits."""
+    eng = engine_for(folders_b[name], "bfloat16", max_tokens=cache_for_one_batch(name), record_routing=False)
+    reqs = requests_b(name, seed=6)
+    steps = cuttings_b(name, reqs)["unequal batches"]
+    runs = []
+    for _ in range(3):
+        rec = Recorder(eng.plan.vocab)
+        run_steps(eng, steps, rec)
+        runs.append(rec)
+    for rid, toks in reqs.items():
+        first = runs[0].logits_of(rid, range(len(toks)))
+        for other in runs[1:]:
+            assert np.array_equal(first, other.logits_of(rid, range(len(toks)))), f"{name}, {rid}: two runs differ"
+
+
 def test_window_pages_are_trimmed_and_reused_at_head_size_64(folders_b):
     """All layers windowed (100 keys): a prompt longer than two pages, a second portion after the window has
     passed whole pages, single tokens across positions 256 and 512, then another request in a cache so small
