@@ -345,6 +345,53 @@ def fp32_cuttings(torch, raw, layers, n_prompts=16, longest=1024, decoded=64, se
     return out
 
 
+def decode_timeline(torch, raw, layers, batch, context):
+    """When each kernel of a captured decode step starts and how long it runs (CUPTI through torch.profiler):
+    the step as the device sees it, with kernels of the two streams side by side and dependent launches
+    resident before their predecessors end.  Prints a table; the times are microseconds from the step's first
+    kernel."""
+    import numpy as np
+    from torch.profiler import ProfilerActivity, profile
+    from esp_b200.config import config_from_dict
+    from esp_b200.engine import Engine, StepEntry
+    from esp_b200.weights import InitSpec
+
+    cfg = config_from_dict(dict(raw, num_hidden_layers=layers))
+    engine = Engine.from_random(cfg, seed=0, init=InitSpec(0.02, 0.02, 0.0), dtype="bfloat16",
+                                max_tokens=batch * (context + 64), max_slots=batch + 2)
+    rng = np.random.default_rng(1)
+    vocab = raw["vocab_size"]
+    slots = [engine.open() for _ in range(batch)]
+    for s in slots:
+        engine.step([StepEntry(s, rng.integers(0, vocab, context - 26).tolist(), [])])
+    temps, tops = [0.0] * batch, [None] * batch
+
+    def one():
+        toks = rng.integers(0, vocab, batch).tolist()
+        engine.step_and_pick([StepEntry(s, [t], [0]) for s, t in zip(slots, toks)], temps, tops)
+
+    for _ in range(6):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            one()
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "Memcpy" not in e.name),
+                    key=lambda e: e.time_range.start)
+    first = [i for i, e in enumerate(events) if "embed_gather" in e.name]
+    step = events[first[-1]:] if first else events
+    t0 = step[0].time_range.start
+    done = t0
+    print(f"{'start':>9} {'runs':>8} {'after the last end':>19}  kernel")
+    for e in step:
+        name = e.name.replace("(anonymous namespace)::", "").replace("void ", "")
+        print(f"{e.time_range.start - t0:9.1f} {e.time_range.end - e.time_range.start:8.1f} "
+              f"{max(0.0, e.time_range.end - max(done, e.time_range.start)):19.1f}  {name[:72]}")
+        done = max(done, e.time_range.end)
+    print(f"step: {done - t0:.1f} us, {len(step)} kernels, {layers} layers")
+
+
 def dense_products(torch, raw, tokens=2048):
     """Times the plain dense products of a prefill step (q/k/v, o, shared down) and the fused shared gate/up
     through this library's TMA + tcgen05 kernel (one CTA per tile, and pairs of CTAs) and through cuBLAS."""
@@ -402,6 +449,8 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the prompt whose prefill is timed")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the 32-bit cuttings check at the headline sizes and the Qwen2-57B-A14B shape")
+    ap.add_argument("--timeline", action="store_true",
+                    help="only print when each kernel of one captured decode step starts and ends (default: 2 layers)")
     ap.add_argument("--dense-products", action="store_true",
                     help="only time the dense products of a 2,048-token prefill, own kernel against cuBLAS, and print them")
     a = ap.parse_args()
@@ -422,6 +471,9 @@ def main() -> int:
     raw, shape_name = SHAPES[a.shape]
     if a.dense_products:
         print(json.dumps({"model": shape_name, **dense_products(torch, raw)}))
+        return 0
+    if a.timeline:
+        decode_timeline(torch, raw, a.layers or 2, a.batch, a.context)
         return 0
     full_layers = raw["num_hidden_layers"]
     if a.layers is None:

@@ -335,6 +335,12 @@ int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
     constexpr int SLOTS = 12;      // measured: 8 and 16 were slower at batch 8, 24 slower at batch 1
     // a warp takes a tile all by itself only with several waves of tiles (measured: batch 1 gains 4 % over a
     // limit of 12, batch 8 and 64 are the same)
+    // one wave: with a warp per tile the launch has about as many blocks as the device holds at once (three per
+    // SM), so no second, partly filled wave follows (the down-projection of 32 (token, expert) rows: 512 blocks
+    // of which three quarters have an expert; batch 8 4.11 -> 4.03 ms a step)
+    const long long blocks1 = (long long)((tiles + WARPS - 1) / WARPS) * (p.group_offsets ? (groups < p.M ? groups : p.M) : 1);
+    if (p.group_offsets && blocks1 >= 148 * 2 && blocks1 <= 148 * ESP_SKINNY_BLOCKS + 148 / 2)
+        return launch_variant<NBLK, MODE, TC, 1>(p, groups, tiles, stream);
     if (spread >= 148 * 48) return launch_variant<NBLK, MODE, TC, 1>(p, groups, tiles, stream);
     if (spread * 2 >= 148 * SLOTS) return launch_variant<NBLK, MODE, TC, 2>(p, groups, tiles, stream);
     if (spread * 4 >= 148 * SLOTS) return launch_variant<NBLK, MODE, TC, 4>(p, groups, tiles, stream);
