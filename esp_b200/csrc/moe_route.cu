@@ -346,15 +346,19 @@ __global__ void __launch_bounds__(256)
 router_logits_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, const TW* __restrict__ w_gate,
                      float* __restrict__ logits, int width, int n_experts) {
     pdl_trigger();
-    pdl_wait();
     extern __shared__ float hs[];
     const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rows = n_experts + (w_gate ? 1 : 0);
+    const int e = blockIdx.y * 8 + warp;
+    const TW* wr = e < n_experts ? w_router + (size_t)e * width : w_gate;
+    // the warp's weight row does not depend on the kernel before: it is asked into L2 while that one finishes
+    if (e < rows)
+        for (int b = lane * 128; b < width * (int)sizeof(TW); b += 32 * 128)
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(reinterpret_cast<const char*>(wr) + b));
+    pdl_wait();
     for (int i = tid; i < width; i += 256) hs[i] = to_f32(h[(size_t)n * width + i]);
     __syncthreads();
-    const int e = blockIdx.y * 8 + warp;
     if (e >= rows) return;
-    const TW* wr = e < n_experts ? w_router + (size_t)e * width : w_gate;
     float s[1];
     lane_dots<1>(hs, width, wr, width, lane, s);
     const float v = warp_sum(s[0]);
@@ -695,7 +699,9 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
                                const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
                                int top_k, float eps, int write_x) {
     pdl_trigger();
-    pdl_wait();
+    // The kernel before this one in the stream made the experts' rows or the shared expert's row; the routing, the
+    // gate and the residual row were complete long before it started, so they are read before the wait, while
+    // that kernel finishes.
     __shared__ int order[MAX_TOPK];
     __shared__ float scratch[33];
     const int r = blockIdx.x;
@@ -711,10 +717,16 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
         }
         for (int j = 0; j < top_k; j++) order[j] = inverse[t * top_k + order[j]];
     }
-    __syncthreads();
     const float g = gate ? gate[t] : 0.f;
     const int pieces = width / 4;
     float4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < pieces) v[i] = reinterpret_cast<float4*>(x + t * width)[q];
+    }
+    __syncthreads();
+    pdl_wait();
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -732,7 +744,7 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
                 const float4 e = reinterpret_cast<const float4*>(shared + t * width)[q];
                 acc.x += g * e.x; acc.y += g * e.y; acc.z += g * e.z; acc.w += g * e.w;
             }
-            float4 xv = reinterpret_cast<float4*>(x + t * width)[q];
+            float4 xv = v[i];
             xv.x += acc.x; xv.y += acc.y; xv.z += acc.z; xv.w += acc.w;
             if (write_x) reinterpret_cast<float4*>(x + t * width)[q] = xv;
             v[i] = xv;
