@@ -89,10 +89,9 @@ __global__ void __launch_bounds__(THREADS)
 attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                      const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv,
-                      int window, int n_splits, int* __restrict__ status) {
+                      const int* __restrict__ seq_past, const int* __restrict__ block_table, int table_stride, int n_pages,
+                      int page, int nh, int nkv, int window, int n_splits, int* __restrict__ status) {
     pdl_trigger();
-    pdl_wait();
     constexpr int ITEM = PAGE_KEYS * HD;
     constexpr int NBW = HD / 32;                   // 8-column blocks of the head that one warp accumulates
     constexpr int PLD = PAGE_KEYS + 8;             // row stride of the probabilities (bfloat16)
@@ -123,22 +122,6 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         for (int r = 0; r < RING; r++) mbar_init(&full_bar[r], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    // the query fragments of the block's heads (rows beyond ``heads`` are zero)
-    unsigned qa[HD / 16][4];
-    {
-        const bf16* q0 = q + ((size_t)n * nh + h0 + g8) * HD;
-        const bf16* q1 = q + ((size_t)n * nh + h0 + g8 + 8) * HD;
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; kk++) {
-            const int c = kk * 16 + tg * 2;
-            qa[kk][0] = g8 < heads ? *reinterpret_cast<const unsigned*>(q0 + c) : 0u;
-            qa[kk][1] = g8 + 8 < heads ? *reinterpret_cast<const unsigned*>(q1 + c) : 0u;
-            qa[kk][2] = g8 < heads ? *reinterpret_cast<const unsigned*>(q0 + c + 8) : 0u;
-            qa[kk][3] = g8 + 8 < heads ? *reinterpret_cast<const unsigned*>(q1 + c + 8) : 0u;
-        }
-    }
-    __syncthreads();
-
     auto issue = [&](int item) {
         const int slot = item % RING;
         int pg = block_table[(size_t)seq * table_stride + first_page + item / 2];
@@ -156,8 +139,32 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             mbar_arrive(&full_bar[slot]);
         }
     };
+    // Keys and values that were cached before this step do not depend on the kernel before this one (which
+    // writes the step's new keys and values): a block all of whose positions are old asks for its first pages
+    // at once and only then waits for that kernel, whose queries it needs.  ``seq_past`` (may be null): per
+    // sequence, the positions cached before the step.
+    const bool early = seq_past != nullptr && j1 < seq_past[seq];
     int issued = 0;
-    if (tid == 0) {
+    if (early && tid == 0) {
+        for (; issued < min(RING, n_items); issued++) issue(issued);
+    }
+    pdl_wait();
+    // the query fragments of the block's heads (rows beyond ``heads`` are zero)
+    unsigned qa[HD / 16][4];
+    {
+        const bf16* q0 = q + ((size_t)n * nh + h0 + g8) * HD;
+        const bf16* q1 = q + ((size_t)n * nh + h0 + g8 + 8) * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++) {
+            const int c = kk * 16 + tg * 2;
+            qa[kk][0] = g8 < heads ? *reinterpret_cast<const unsigned*>(q0 + c) : 0u;
+            qa[kk][1] = g8 + 8 < heads ? *reinterpret_cast<const unsigned*>(q1 + c) : 0u;
+            qa[kk][2] = g8 < heads ? *reinterpret_cast<const unsigned*>(q0 + c + 8) : 0u;
+            qa[kk][3] = g8 + 8 < heads ? *reinterpret_cast<const unsigned*>(q1 + c + 8) : 0u;
+        }
+    }
+    __syncthreads();
+    if (!early && tid == 0) {
         for (; issued < min(RING, n_items); issued++) issue(issued);
     }
 
@@ -340,7 +347,7 @@ int make_cache_map(CUtensorMap* map, const void* base, unsigned long long rows, 
 
 template <int HD, int SPLIT>
 int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
-                     const int* tok_seq, const int* tok_pos, const int* table, int stride, int n_pages, int page,
+                     const int* tok_seq, const int* tok_pos, const int* seq_past, const int* table, int stride, int n_pages, int page,
                      int n_tokens, int nh, int nkv, int window, int n_splits, int* status, cudaStream_t stream) {
     CUtensorMap map_k, map_v;
     const unsigned long long rows = (unsigned long long)n_pages * nkv * PAGE_KEYS;
@@ -360,21 +367,21 @@ int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, flo
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + MMA_HEADS - 1) / MMA_HEADS), n_splits);
     esp_launch_pdl(ESP_PDL_ATTENTION, attn_split_mma_kernel<HD, SPLIT>, dim3(grid), dim3(THREADS), dyn, stream, map_k, map_v, q, out, po, pml, counters, tok_seq, tok_pos,
-                                                                     table, stride, n_pages, page, nh, nkv, window, n_splits,
+                                                                     seq_past, table, stride, n_pages, page, nh, nkv, window, n_splits,
                                                                      status);
     return esp_launch_status();
 }
 
 template <int HD>
 int dispatch(int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
-             const int* tok_seq, const int* tok_pos, const int* table, int stride, int n_pages, int page, int n_tokens, int nh,
+             const int* tok_seq, const int* tok_pos, const int* seq_past, const int* table, int stride, int n_pages, int page, int n_tokens, int nh,
              int nkv, int window, int n_splits, int* status, cudaStream_t stream) {
     if (split == 128)
-        return launch_split_mma<HD, 128>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages, page,
+        return launch_split_mma<HD, 128>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page,
                                          n_tokens, nh, nkv, window, n_splits, status, stream);
-    return split == 256 ? launch_split_mma<HD, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
+    return split == 256 ? launch_split_mma<HD, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages,
                                                      page, n_tokens, nh, nkv, window, n_splits, status, stream)
-                        : launch_split_mma<HD, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, table, stride, n_pages,
+                        : launch_split_mma<HD, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages,
                                                      page, n_tokens, nh, nkv, window, n_splits, status, stream);
 }
 }  // namespace
@@ -383,17 +390,19 @@ int dispatch(int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, 
 // counters int [n_tokens * head groups], all zero when the call starts (the kernel leaves them zero);
 // split: key positions per block, 128, 256 or 512 (the caller picks: short splits when there are few rows, so
 // that every SM still gets blocks); n_splits >= ceil(longest sequence / split).  Head sizes 64, 128, 192, 256; pages of 64 positions or any
-// size; any head counts with nh % nkv == 0.
+// size; any head counts with nh % nkv == 0.  ``seq_past`` (may be null): per sequence of the step, the positions
+// that were cached before it; with it, blocks whose keys are all older start their loads without waiting for the
+// kernel before this one.
 ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,
-                            float* part_ml, int* counters, const int* tok_seq, const int* tok_pos, const int* block_table,
-                            int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int window,
-                            int split, int n_splits, int* status, cudaStream_t stream) {
+                            float* part_ml, int* counters, const int* tok_seq, const int* tok_pos, const int* seq_past,
+                            const int* block_table, int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv,
+                            int hd, int window, int split, int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || (split != 128 && split != 256 && split != 512) ||
         page != PAGE_KEYS)
         return (int)cudaErrorInvalidValue;
 #define ESP_HD(HD) return dispatch<HD>(split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
-                                       part_ml, counters, tok_seq, tok_pos, block_table, table_stride, n_pages, page, n_tokens, nh,   \
+                                       part_ml, counters, tok_seq, tok_pos, seq_past, block_table, table_stride, n_pages, page, n_tokens, nh,   \
                                        nkv, window, n_splits, status, stream)
     switch (hd) {
         case 64: ESP_HD(64);
@@ -450,6 +459,6 @@ extern "C" int esp_attn_decode_noalloc(const void* q, const void* k_cache, const
     float* part_o = noalloc_scratch_of_device[device];
     float* part_ml = part_o + (size_t)n_tokens * nh * n_splits * hd;
     int* counters = reinterpret_cast<int*>(noalloc_scratch_of_device[device] + esp_attn_decode_noalloc_capacity());
-    return esp_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, block_table, table_stride,
+    return esp_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, nullptr, block_table, table_stride,
                            n_pages, page, n_tokens, nh, nkv, hd, window, split, n_splits, status, stream);
 }

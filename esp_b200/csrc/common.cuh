@@ -102,7 +102,7 @@ static inline int esp_launch_status() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-#define ESP_PDL_DEFAULT_MASK 9
+#define ESP_PDL_DEFAULT_MASK 13
 // classes of kernels, so that the attribute can be tried class by class: ESP_B200_PDL is a bit mask
 enum : int { ESP_PDL_DENSE = 1, ESP_PDL_GROUPED = 2, ESP_PDL_ATTENTION = 4, ESP_PDL_SMALL = 8 };
 static inline bool esp_pdl_enabled(int kind) {

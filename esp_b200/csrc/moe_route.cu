@@ -697,11 +697,13 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
                                const int* __restrict__ inverse, const float* __restrict__ gate,
                                const float* __restrict__ shared, float* __restrict__ x, const float* __restrict__ gamma,
                                const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
-                               int top_k, float eps, int write_x) {
+                               int top_k, float eps, int write_x, int early) {
     pdl_trigger();
     // The kernel before this one in the stream made the experts' rows or the shared expert's row; the routing, the
-    // gate and the residual row were complete long before it started, so they are read before the wait, while
-    // that kernel finishes.
+    // gate and the residual row were complete before it started (the experts' products are ordinary launches: each
+    // starts when its predecessor has ended), so they are read before the wait, while that kernel finishes.
+    // ``early`` 0: the experts' products are dependent launches too, and everything waits.
+    if (!early) pdl_wait();
     __shared__ int order[MAX_TOPK];
     __shared__ float scratch[33];
     const int r = blockIdx.x;
@@ -897,12 +899,13 @@ ESP_API int esp_moe_combine_add_rmsnorm(const float* expert_out, const int* topk
     // step (the 32-bit path relies on it).  Many rows rounded to bfloat16: four pieces per thread, smaller blocks,
     // more rows in flight per SM.
     if (width / 4 <= 1024 && !(h_is_bf16 && n_rows >= 256)) threads = (width / 4 + 31) / 32 * 32;
+    const int early = esp_pdl_enabled(ESP_PDL_GROUPED) ? 0 : 1;
     if (h_is_bf16)
         esp_launch_pdl(ESP_PDL_SMALL, moe_combine_add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, expert_out, topk_ids, inverse, gate, shared, x, gamma,
-                                                                            rows, (bf16*)h, h32, width, top_k, eps, write_x);
+                                                                            rows, (bf16*)h, h32, width, top_k, eps, write_x, early);
     else
         esp_launch_pdl(ESP_PDL_SMALL, moe_combine_add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, expert_out, topk_ids, inverse, gate, shared, x,
                                                                              gamma, rows, (float*)h, h32, width, top_k, eps,
-                                                                             write_x);
+                                                                             write_x, early);
     return esp_launch_status();
 }

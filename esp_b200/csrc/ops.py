@@ -47,8 +47,8 @@ _SIGNATURES = {
     "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_attn_prefill_tc05": [P, c_longlong, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               P, P],
-    "esp_attn_decode": [P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                        P, P],
+    "esp_attn_decode": [P, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                        c_int, P, P],
 }
 
 _bound: dict = {}
@@ -444,11 +444,13 @@ ATTN_DECODE_COUNTERS = 65536
 
 
 def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, block_table, page, nh, nkv, hd,
-                window, split, n_splits, status):
+                window, split, n_splits, status, seq_past=None):
     """Split-key attention for few token rows (bfloat16; head sizes 64, 128, 192, 256).  ``split``: key
-    positions per block (256 or 512); n_splits >= ceil(positions / split).  part_o float32
+    positions per block (128, 256 or 512); n_splits >= ceil(positions / split).  part_o float32
     [N, nh, n_splits, hd] and part_ml float32 [N, nh, n_splits, 2] are scratch; ``counters``: int32, at least
-    N * nh words, all zero (the kernel leaves them zero)."""
+    N * nh words, all zero (the kernel leaves them zero).  ``seq_past`` (int32 per sequence of the step: the
+    positions cached before it): blocks whose keys are all older then load them without waiting for the
+    kernel before this one, which writes the step's new keys and values."""
     if counters.numel() < q.shape[0] * nh:
         raise Backend("attn_decode: too few counters for this many rows and heads")
     if split not in (128, 256, 512):
@@ -461,7 +463,8 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, to
     _check(_fn("bf16", "esp_attn_decode")(
         _ptr(q, torch.bfloat16, "q"), _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
         _ptr(out, torch.bfloat16), _ptr(part_o, torch.float32), _ptr(part_ml, torch.float32),
-        _ptr(counters, torch.int32), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
+        _ptr(counters, torch.int32), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(seq_past, torch.int32),
+        _ptr(block_table, torch.int32), block_table.shape[1],
         k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), split, n_splits, _ptr(status, torch.int32),
         _stream()), "attn_decode")
 

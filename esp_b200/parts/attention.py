@@ -163,7 +163,8 @@ class Attention(Part):
             if getattr(rt, "attn_counters", None) is None:
                 rt.attn_counters = torch.zeros(ops.ATTN_DECODE_COUNTERS, dtype=torch.int32, device=rt.device)
             ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, rt.attn_counters, ctx.tok_seq, ctx.tok_pos, table, layer.page,
-                            s.num_heads, s.num_kv_heads, s.head_dim, s.window, split, n_splits, rt.status)
+                            s.num_heads, s.num_kv_heads, s.head_dim, s.window, split, n_splits, rt.status,
+                            seq_past=ctx.seq_past if layer.writes else None)
         elif kind == "tc05":
             ops.attn_prefill_tc05(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past,
                                   table, layer.page, s.num_heads, s.num_kv_heads, s.head_dim, s.window, rt.status)
