@@ -21,10 +21,25 @@ def _folder(tmp_path, seed):
     return raw, folder, rng
 
 
-@pytest.mark.parametrize("seed", range(24, 36))
-def test_drawn_configuration_against_plain(tmp_path, seed):
+def _folder_with(tmp_path, seed, **overrides):
+    from esp_b200.config import config_from_dict
+    from esp_b200.weights import InitSpec, write_model_folder
+    rng = np.random.default_rng(seed)
+    raw = dict(random_config(rng), **overrides)
+    folder = tmp_path / f"drawn_{seed}"
+    write_model_folder(config_from_dict(raw), seed, folder, "bfloat16", InitSpec(0.05, 0.03, 0.02))
+    return raw, folder, rng
+
+
+@pytest.mark.parametrize("seed, head_dim", [(24, None), (25, None), (26, None), (27, None), (28, None), (29, None),
+                                            (30, None), (31, None), (32, None), (33, None), (34, None), (35, None),
+                                            (7000, 96), (7001, 112), (7002, 144), (7003, 192), (7004, 256)])
+def test_drawn_configuration_against_plain(tmp_path, seed, head_dim):
+    """``head_dim`` given: the drawn configuration with that head size (every multiple of 16 up to 256 runs: the
+    split-key kernel takes 64, 128, 192 and 256, the tensor-memory prefill 64 and 128, the mma.sync prefill up to
+    128, the plain kernel the rest)."""
     from esp_b200.engine import Engine
-    raw, folder, rng = _folder(tmp_path, seed)
+    raw, folder, rng = _folder_with(tmp_path, seed, **({"head_dim": head_dim} if head_dim else {}))
     lens = [int(x) for x in rng.integers(1, 260, size=3)] + [int(rng.integers(260, 700))]
     reqs = {f"r{i}": random_ids(rng, n, raw["vocab_size"]) for i, n in enumerate(lens)}
     c, w = plain.load_model(folder)
