@@ -102,9 +102,9 @@ static inline int esp_launch_status() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-#define ESP_PDL_DEFAULT_MASK 13
+#define ESP_PDL_DEFAULT_MASK 29
 // classes of kernels, so that the attribute can be tried class by class: ESP_B200_PDL is a bit mask
-enum : int { ESP_PDL_DENSE = 1, ESP_PDL_GROUPED = 2, ESP_PDL_ATTENTION = 4, ESP_PDL_SMALL = 8 };
+enum : int { ESP_PDL_DENSE = 1, ESP_PDL_GROUPED = 2, ESP_PDL_ATTENTION = 4, ESP_PDL_SMALL = 8, ESP_PDL_GROUPED_AFTER = 16 };
 static inline bool esp_pdl_enabled(int kind) {
     static int mask = -1;
     if (mask < 0) {

@@ -39,6 +39,7 @@ struct SkinnyParams {
     long long ldc;
     int M, N, K;
     int groups;                     // grouped form: how many groups there are (the grid's y may be smaller)
+    int offsets_ready;              // grouped form: the offsets were complete before the kernel before this one started
     // ROPE form only: N counts pairs (i, i + hd/2) over the nh + 2 nkv heads of the packed projection
     const float* bias;              // [(nh + 2 nkv) * hd] or null
     const int* tok_seq;
@@ -122,9 +123,12 @@ gemm_skinny_kernel(SkinnyParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
     int m_begin = 0, m_end = p.M;
     const bf16* W = p.W;
-    pdl_trigger();
+    // The next kernel may be set up as soon as every block has said so.  A dense product says so at once; a grouped
+    // one only when its weights have been streamed, so that a dependent launch takes SM room from its last blocks,
+    // not from the waves that have yet to start.
+    if (!p.group_offsets) pdl_trigger();
     if (p.group_offsets) {
-        pdl_wait();                                                   // which group a block takes was written by the kernel before
+        if (!p.offsets_ready) pdl_wait();                             // which group a block takes was written by the kernel before
         int group = blockIdx.y;
         if ((int)gridDim.y < p.groups) {
             // fewer rows than groups (a decode step of one sequence names a few experts of many): the grid has
@@ -198,6 +202,10 @@ gemm_skinny_kernel(SkinnyParams p) {
             if (ok_b) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wb_ptr + k));
         }
         pdl_wait();
+    } else if (p.offsets_ready) {
+        // a grouped product whose groups were known before its predecessor started (the experts' second product):
+        // group, weights' first pieces and all, before the wait; only the rows below are the predecessor's
+        pdl_wait();
     }
 
     for (int m0 = m_begin; m0 < m_end; m0 += 8 * NBLK) {
@@ -238,6 +246,7 @@ gemm_skinny_kernel(SkinnyParams p) {
                 }
             }
         }
+        if (p.group_offsets && m0 + 8 * NBLK >= m_end) pdl_trigger();   // the weights are in: see the top
         if constexpr (KS == 1) {
             // this warp owns its tile: results go out straight from the accumulators
 #pragma unroll
@@ -323,7 +332,8 @@ int launch_variant(const SkinnyParams& p, int groups, int tiles, cudaStream_t st
     }
     constexpr int TILES = WARPS / KS;
     dim3 grid((tiles + TILES - 1) / TILES, p.group_offsets && p.M < groups ? p.M : groups);   // every group that has rows starts below M
-    esp_launch_pdl(p.group_offsets ? ESP_PDL_GROUPED : ESP_PDL_DENSE, gemm_skinny_kernel<NBLK, MODE, TC, KS>, grid, dim3(WARPS * 32), smem, stream, p);
+    esp_launch_pdl(p.group_offsets ? (p.offsets_ready ? ESP_PDL_GROUPED_AFTER : ESP_PDL_GROUPED) : ESP_PDL_DENSE,
+                   gemm_skinny_kernel<NBLK, MODE, TC, KS>, grid, dim3(WARPS * 32), smem, stream, p);
     return esp_launch_status();
 }
 
@@ -353,10 +363,11 @@ int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
 // size and W holds 2N rows per group.  c_dtype: 0 float, 1 bfloat16.
 ESP_API int esp_gemm_skinny(const void* A, long long lda, const int* a_rows, const void* W, long long w_group_stride,
                             const float* row_scale, void* C, int c_dtype, long long ldc, const int* group_offsets,
-                            int groups, int M, int N, int K, int max_rows, int swiglu, cudaStream_t stream) {
+                            int groups, int M, int N, int K, int max_rows, int swiglu, int offsets_ready, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K % 8 != 0 || lda % 8 != 0 || groups > 65535) return (int)cudaErrorInvalidValue;
     SkinnyParams p{};
+    p.offsets_ready = group_offsets && offsets_ready ? 1 : 0;
     p.W = (const bf16*)W; p.w_group_stride = w_group_stride; p.A = (const bf16*)A; p.lda = lda; p.a_rows = a_rows;
     p.group_offsets = group_offsets; p.row_scale = row_scale; p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
     p.groups = groups;

@@ -41,7 +41,7 @@ _SIGNATURES = {
     "esp_pick_tokens": [P, c_int, c_int, P, P, P, P, P, P],
     "esp_moe_combine_add_rmsnorm": [P, P, P, P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, c_int, P],
     "esp_gemm_skinny": [P, c_longlong, P, P, c_longlong, P, P, c_int, c_longlong, P, c_int, c_int, c_int, c_int, c_int,
-                        c_int, P],
+                        c_int, c_int, P],
     "esp_qkv_rope_skinny": [P, c_longlong, P, P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_int, c_int, c_int, P, P],
     "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
@@ -378,11 +378,14 @@ def skinny_fits(k: int) -> bool:
     return k % 8 == 0 and 8 * (k + 32) * 2 + 8 * 512 <= SKINNY_MAX_SMEM
 
 
-def gemm_skinny(a, w, c, swiglu=False, row_scale=None, a_rows=None, group_offsets=None, rows=None, max_rows=None):
+def gemm_skinny(a, w, c, swiglu=False, row_scale=None, a_rows=None, group_offsets=None, rows=None, max_rows=None,
+                offsets_ready=False):
     """Weight-streaming product for few rows; bfloat16 a and w.  Plain: c[m] =
     scale[m] * a[row(m)] @ w[g].T with w [N,K] or [G,N,K].  swiglu: w holds
     [gate rows; up rows] ([2I,K] or [G,2I,K]) and c[m, j] = silu(gate_j) * up_j
-    ([rows, I]).  ``max_rows``: upper bound of the rows of one group."""
+    ([rows, I]).  ``max_rows``: upper bound of the rows of one group.  ``offsets_ready``: the group offsets (and
+    ``row_scale``) were complete before the kernel that runs right before this one started, so this one may
+    find its group and ask for its weights while that kernel still runs (only ``a`` is waited for)."""
     grouped = group_offsets is not None
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise Backend("gemm_skinny takes bfloat16 operands")
@@ -402,7 +405,8 @@ def gemm_skinny(a, w, c, swiglu=False, row_scale=None, a_rows=None, group_offset
     code = _fn("bf16", "esp_gemm_skinny")(
         a.data_ptr(), a.stride(0), _ptr(a_rows, torch.int32, "a_rows"), w.data_ptr(), wn * k,
         _ptr(row_scale, torch.float32, "row_scale"), c.data_ptr(), _is_bf16(c), c.stride(0),
-        _ptr(group_offsets, torch.int32, "group_offsets"), groups, m, n, k, max_rows, 1 if swiglu else 0, _stream())
+        _ptr(group_offsets, torch.int32, "group_offsets"), groups, m, n, k, max_rows, 1 if swiglu else 0,
+        1 if offsets_ready else 0, _stream())
     _check(code, "gemm_skinny")
 
 

@@ -96,13 +96,15 @@ def grouped_swiglu_linear(rt, a, w_gate_up, act, group_offsets, a_rows, rows, ma
     return act
 
 
-def grouped_linear(rt, a, w, out, group_offsets, row_scale, rows, max_rows, tiles=None):
-    """out[r] = row_scale[r] * a[r] @ w[g].T for the rows of every group (w [G,N,K])."""
+def grouped_linear(rt, a, w, out, group_offsets, row_scale, rows, max_rows, tiles=None, offsets_ready=False):
+    """out[r] = row_scale[r] * a[r] @ w[g].T for the rows of every group (w [G,N,K]).  ``offsets_ready``: the
+    kernel that ran right before this call did not write ``group_offsets`` or ``row_scale`` (it made ``a``)."""
     if tiles is not None:
         ops.gemm_tc05(a, w, out, rt.status, row_scale=row_scale, tiles=tiles)
         return out
     if _both_bf16(a, w) and ops.skinny_fits(a.shape[1]):
-        ops.gemm_skinny(a, w, out, row_scale=row_scale, group_offsets=group_offsets, rows=rows, max_rows=max_rows)
+        ops.gemm_skinny(a, w, out, row_scale=row_scale, group_offsets=group_offsets, rows=rows, max_rows=max_rows,
+                        offsets_ready=offsets_ready)
     else:
         ops.gemm_simt(a, w, out, row_scale=row_scale, group_offsets=group_offsets, rows=rows)
     return out
