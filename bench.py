@@ -345,11 +345,12 @@ def fp32_cuttings(torch, raw, layers, n_prompts=16, longest=1024, decoded=64, se
     return out
 
 
-def decode_timeline(torch, raw, layers, batch, context):
+def decode_timeline(torch, raw, layers, batch, context, prefill_tokens=0):
     """When each kernel of a captured decode step starts and how long it runs (CUPTI through torch.profiler):
     the step as the device sees it, with kernels of the two streams side by side and dependent launches
     resident before their predecessors end.  Prints a table; the times are microseconds from the step's first
-    kernel."""
+    kernel.  ``prefill_tokens`` > 0: the same for the prefill of one prompt of that length (launched kernel
+    by kernel from the host, so the gaps between kernels show the host's share)."""
     import numpy as np
     from torch.profiler import ProfilerActivity, profile
     from esp_b200.config import config_from_dict
@@ -358,17 +359,23 @@ def decode_timeline(torch, raw, layers, batch, context):
 
     cfg = config_from_dict(dict(raw, num_hidden_layers=layers))
     engine = Engine.from_random(cfg, seed=0, init=InitSpec(0.02, 0.02, 0.0), dtype="bfloat16",
-                                max_tokens=batch * (context + 64), max_slots=batch + 2)
+                                max_tokens=max(batch * (context + 64), prefill_tokens + 64), max_slots=batch + 2)
     rng = np.random.default_rng(1)
     vocab = raw["vocab_size"]
-    slots = [engine.open() for _ in range(batch)]
-    for s in slots:
-        engine.step([StepEntry(s, rng.integers(0, vocab, context - 26).tolist(), [])])
-    temps, tops = [0.0] * batch, [None] * batch
+    if prefill_tokens:
+        def one():
+            s = engine.open()
+            engine.step([StepEntry(s, rng.integers(0, vocab, prefill_tokens).tolist(), [prefill_tokens - 1])])
+            engine.close(s)
+    else:
+        slots = [engine.open() for _ in range(batch)]
+        for s in slots:
+            engine.step([StepEntry(s, rng.integers(0, vocab, context - 26).tolist(), [])])
+        temps, tops = [0.0] * batch, [None] * batch
 
-    def one():
-        toks = rng.integers(0, vocab, batch).tolist()
-        engine.step_and_pick([StepEntry(s, [t], [0]) for s, t in zip(slots, toks)], temps, tops)
+        def one():
+            toks = rng.integers(0, vocab, batch).tolist()
+            engine.step_and_pick([StepEntry(s, [t], [0]) for s, t in zip(slots, toks)], temps, tops)
 
     for _ in range(6):
         one()
@@ -449,8 +456,9 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the prompt whose prefill is timed")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the 32-bit cuttings check at the headline sizes and the Qwen2-57B-A14B shape")
-    ap.add_argument("--timeline", action="store_true",
-                    help="only print when each kernel of one captured decode step starts and ends (default: 2 layers)")
+    ap.add_argument("--timeline", nargs="?", const="decode", choices=["decode", "prefill"], default=None,
+                    help="only print when each kernel of one captured decode step (or, with 'prefill', of the prefill "
+                         "of --prefill-tokens tokens) starts and ends (default: 2 layers)")
     ap.add_argument("--dense-products", action="store_true",
                     help="only time the dense products of a 2,048-token prefill, own kernel against cuBLAS, and print them")
     a = ap.parse_args()
@@ -473,7 +481,8 @@ def main() -> int:
         print(json.dumps({"model": shape_name, **dense_products(torch, raw)}))
         return 0
     if a.timeline:
-        decode_timeline(torch, raw, a.layers or 2, a.batch, a.context)
+        decode_timeline(torch, raw, a.layers or 2, a.batch, a.context,
+                        a.prefill_tokens if a.timeline == "prefill" else 0)
         return 0
     full_layers = raw["num_hidden_layers"]
     if a.layers is None:

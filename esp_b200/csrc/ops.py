@@ -68,7 +68,18 @@ def _fn(library: str, name: str):
     return f
 
 
+_device_index = None
+
+
 def _stream() -> int:
+    """The current stream's handle.  Asked for at every launch, so it takes the short way (the full
+    ``torch.cuda.current_stream()`` costs several microseconds a call, a quarter of an eager step's host time)."""
+    global _device_index
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:
+        return raw(_device_index)
     return torch.cuda.current_stream().cuda_stream
 
 

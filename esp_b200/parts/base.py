@@ -152,10 +152,14 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: dict = {}
+        self._views: dict = {}       # (name, dtype, shape) -> the view handed out last time (a step asks for the same ones)
         self.frozen = False
         self.generation = 0          # bumped whenever a buffer moves; captured graphs check it
 
     def get(self, name: str, shape: tuple, dtype) -> torch.Tensor:
+        seen = self._views.get((name, dtype, shape))
+        if seen is not None:
+            return seen
         count = 1
         for s in shape:
             count *= int(s)
@@ -167,7 +171,11 @@ class Workspace:
             buf = torch.empty(max(count, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.generation += 1
-        return buf[:count].view(*shape)
+            self._views = {k: v for k, v in self._views.items() if (k[0], k[1]) != key}    # views of the old buffer
+        view = buf[:count].view(*shape)
+        if len(self._views) < 4096:
+            self._views[(name, dtype, shape)] = view
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
