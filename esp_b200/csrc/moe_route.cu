@@ -7,6 +7,7 @@
 namespace {
 constexpr int ROUTER_THREADS = 512;
 constexpr int MAX_TOPK = 32;
+constexpr int ROUTE_SMALL_MAX = 64;          // tokens of a step that the two-launch router takes (an expert's rows stay one tile)
 
 // A lane's share of dot(hs[t], w) for TPB token rows at once: 4 consecutive
 // weights at a time (8-byte loads of bfloat16, 16-byte of float), lanes
@@ -372,7 +373,8 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
                    float* __restrict__ gate, float* __restrict__ probs_out, int n_tokens, int n_experts, int top_k,
                    int norm_topk, int has_gate, int* __restrict__ offsets, int* __restrict__ perm_token,
                    float* __restrict__ perm_weight, int* __restrict__ inverse, int* __restrict__ status,
-                   unsigned long long* __restrict__ distinct) {
+                   unsigned long long* __restrict__ distinct, int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                   int* __restrict__ tile_count, int* __restrict__ n_tiles) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm_f[];
@@ -459,12 +461,22 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
                 cursor[e] = run + incl - c;
                 offsets[e] = run + incl - c;
             }
-            used += __popc(__ballot_sync(0xffffffffu, c > 0));
+            const unsigned with_rows = __ballot_sync(0xffffffffu, c > 0);
+            // the row tiles of the grouped tensor-core products: a token names an expert once, so an expert has
+            // at most as many rows as the step has tokens (at most ROUTE_SMALL_MAX) and is one tile
+            if (tile_group && c > 0) {
+                const int t = used + __popc(with_rows & ((1u << lane) - 1));
+                tile_group[t] = e;
+                tile_row0[t] = run + incl - c;
+                tile_count[t] = c;
+            }
+            used += __popc(with_rows);
             run += __shfl_sync(0xffffffffu, incl, 31);
         }
         if (lane == 0) {
             cursor[n_experts] = run;
             offsets[n_experts] = run;
+            if (n_tiles) *n_tiles = used;
             if (distinct) atomicAdd(distinct, (unsigned long long)used);     // experts that this step reads
         }
     }
@@ -828,15 +840,19 @@ ESP_API int esp_router_topk(const void* h, int h_is_bf16, const void* w_router, 
     return esp_launch_status();
 }
 
-// Router and permutation for a step of few tokens (at most 32) in two launches.  ``logits`` is scratch
-// [n_tokens, n_experts + 1] float.
+// Router and permutation for a step of few tokens (at most ROUTE_SMALL_MAX) in two launches.  ``logits`` is scratch
+// [n_tokens, n_experts + 1] float.  tile_group / tile_row0 / tile_count / n_tiles (may be null): the list of row
+// tiles for the grouped tensor-core products, as esp_moe_permute makes it (here: one tile per expert with rows).
 ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, const void* w_gate, int w_is_bf16,
                             float* logits, int* topk_ids, float* topk_w, float* gate, float* probs_out, int n_tokens,
                             int width, int n_experts, int top_k, int norm_topk, int* offsets, int* perm_token,
-                            float* perm_weight, int* inverse, int* status, unsigned long long* distinct,
-                            cudaStream_t stream) {
+                            float* perm_weight, int* inverse, int* status, unsigned long long* distinct, int* tile_group,
+                            int* tile_row0, int* tile_count, int* n_tiles, int max_tiles, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts || n_tokens > 32) return (int)cudaErrorInvalidValue;
+    if (top_k > MAX_TOPK || top_k <= 0 || top_k > n_experts || n_tokens > ROUTE_SMALL_MAX) return (int)cudaErrorInvalidValue;
+    // the tile list (all four or none): one tile per expert with rows
+    if (tile_group && (!tile_row0 || !tile_count || !n_tiles || max_tiles < (n_experts < n_tokens * top_k ? n_experts : n_tokens * top_k)))
+        return (int)cudaErrorInvalidValue;
     const size_t smem_a = (size_t)width * sizeof(float);
     const size_t smem_b = (size_t)(8 * n_experts) * sizeof(float) + (size_t)(2 * n_experts + 1) * sizeof(int) +
                           (size_t)n_tokens * top_k * (sizeof(int) + sizeof(float));
@@ -852,7 +868,7 @@ ESP_API int esp_route_small(const void* h, int h_is_bf16, const void* w_router, 
 #undef ESP_LOGITS
     esp_launch_pdl(ESP_PDL_SMALL, route_small_kernel, dim3(1), dim3(256), smem_b, stream, logits, topk_ids, topk_w, gate, probs_out, n_tokens, n_experts, top_k,
                                                    norm_topk, w_gate ? 1 : 0, offsets, perm_token, perm_weight, inverse,
-                                                   status, distinct);
+                                                   status, distinct, tile_group, tile_row0, tile_count, n_tiles);
     return esp_launch_status();
 }
 

@@ -33,7 +33,8 @@ _SIGNATURES = {
     "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
-    "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P],
+    "esp_route_small": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P,
+                        c_int, P],
     "esp_gemm_tc05": [P, c_longlong, P, c_int, c_int, P, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                       c_int, c_int, P, P],
     "esp_wait_probe": [c_int, P, P],
@@ -305,7 +306,7 @@ def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, s
         _ptr(status, torch.int32), _stream()), "router_topk")
 
 
-ROUTE_SMALL_TOKENS = 32
+ROUTE_SMALL_TOKENS = 64
 
 
 def route_small_fits(width: int, n_experts: int) -> bool:
@@ -314,10 +315,11 @@ def route_small_fits(width: int, n_experts: int) -> bool:
 
 
 def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm_topk, offsets, perm_token,
-                perm_weight, inverse, status, probs_out=None, distinct=None):
+                perm_weight, inverse, status, probs_out=None, distinct=None, tiles=None):
     """Router and permutation for at most ROUTE_SMALL_TOKENS tokens: logits over many blocks, then one
     block for softmax, top-k and the permutation.  ``logits``: float32 scratch [N, E + 1].  ``distinct``:
-    an int64 tensor of one element to which the number of experts with at least one token is added."""
+    an int64 tensor of one element to which the number of experts with at least one token is added.
+    ``tiles``: as for moe_permute (the row tiles of the grouped tensor-core products; one per expert with rows)."""
     n, width = h.shape
     n_experts = w_router.shape[0]
     if n > ROUTE_SMALL_TOKENS or top_k > 32 or not route_small_fits(width, n_experts):
@@ -327,7 +329,10 @@ def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm
         _ptr(logits, torch.float32), _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32),
         _ptr(gate, torch.float32), _ptr(probs_out, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
         _ptr(offsets, torch.int32), _ptr(perm_token, torch.int32), _ptr(perm_weight, torch.float32),
-        _ptr(inverse, torch.int32), _ptr(status, torch.int32), _ptr(distinct, torch.int64), _stream()), "route_small")
+        _ptr(inverse, torch.int32), _ptr(status, torch.int32), _ptr(distinct, torch.int64),
+        _ptr(tiles[0], torch.int32) if tiles else None, _ptr(tiles[1], torch.int32) if tiles else None,
+        _ptr(tiles[2], torch.int32) if tiles else None, _ptr(tiles[3], torch.int32) if tiles else None,
+        tiles[0].shape[0] if tiles else 0, _stream()), "route_small")
 
 
 def moe_permute(topk_ids, topk_w, n_experts, offsets, perm_token, perm_weight, inverse, status, tiles=None,

@@ -194,19 +194,22 @@ class MoeSwiGluShared(Part):
             rt.side_stream.wait_stream(main)
             with torch.cuda.stream(rt.side_stream):
                 _swiglu_mlp(rt, h, self.w_shared_gate_up, self.w_shared_down, shared, "moe_shared")
-        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E) and not grouped_uses_tc05(h, self.w_gate_up, n * k, n):
-            # few tokens: router and permutation in two short launches
+        uses_tc05 = grouped_uses_tc05(h, self.w_gate_up, n * k, n) and Im % 8 == 0
+        if uses_tc05:
+            max_tiles = (n * k + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
+            tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32),
+                     ws.get("moe_tile_row0", (max_tiles,), torch.int32),
+                     ws.get("moe_tile_count", (max_tiles,), torch.int32), ws.get("moe_n_tiles", (1,), torch.int32))
+        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E):
+            # few tokens: router and permutation (and the tile list, when the tensor-core products follow) in two
+            # short launches
             logits = ws.get("moe_logits", (n, E + 1), torch.float32)
             ops.route_small(router_in, self.w_router, self.w_shared_gate, logits, ids, wts, gate, k, s.norm_topk,
-                            offsets, perm_token, perm_weight, inverse, rt.status, probs, distinct=self.expert_reads)
+                            offsets, perm_token, perm_weight, inverse, rt.status, probs, distinct=self.expert_reads,
+                            tiles=tiles)
         else:
             ops.router_topk(router_in, self.w_router, self.w_shared_gate, ids, wts, gate, k, s.norm_topk, rt.status,
                             probs, logits=ws.get("moe_logits", (n, E + 1), torch.float32))
-            if grouped_uses_tc05(h, self.w_gate_up, n * k, n) and Im % 8 == 0:
-                max_tiles = (n * k + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
-                tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32),
-                         ws.get("moe_tile_row0", (max_tiles,), torch.int32),
-                         ws.get("moe_tile_count", (max_tiles,), torch.int32), ws.get("moe_n_tiles", (1,), torch.int32))
             ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles,
                             distinct=self.expert_reads)
         if rt.record_routing:

@@ -223,7 +223,7 @@ def test_profile_of_a_step_names_the_kernels_and_changes_nothing(folders, capsys
     eng.close(s)
     assert torch.equal(got.cpu(), want)
     kinds = {w for w, _n, _us in prof.rows()}
-    assert {"embed_gather", "add_rmsnorm", "rope_kvwrite", "moe_permute"} <= kinds and all(us >= 0 for _w, _n, us in prof.rows())
+    assert {"embed_gather", "add_rmsnorm", "rope_kvwrite", "route_small"} <= kinds and all(us >= 0 for _w, _n, us in prof.rows())
     assert eng.use_graphs and eng.rt.side_stream is not None
     rc = main(["generate", "--model", str(folders["A"]), "--dtype", "float32", "--prompt-ids", ",".join(map(str, p[:6])),
                "--max-tokens", "3", "--profile"])

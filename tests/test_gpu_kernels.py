@@ -251,7 +251,8 @@ def test_router_topk(h_dt, w_dt, norm):
 
 
 @pytest.mark.parametrize("w_dt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n, e, k, norm", [(1, 10, 3, False), (8, 60, 4, False), (32, 7, 7, True), (13, 64, 8, True)])
+@pytest.mark.parametrize("n, e, k, norm", [(1, 10, 3, False), (8, 60, 4, False), (32, 7, 7, True), (13, 64, 8, True),
+                                           (64, 60, 4, False), (50, 12, 3, True)])
 def test_route_small_equals_router_and_permutation(w_dt, n, e, k, norm):
     """The two-launch path for few tokens gives what router_topk + moe_permute give."""
     width = 200
@@ -275,6 +276,16 @@ def test_route_small_equals_router_and_permutation(w_dt, n, e, k, norm):
     close(probs_b, probs_a, torch.float32, "probabilities")
     ids_np, off = ids_b.cpu().numpy(), offsets.cpu().numpy()
     assert list(off) == list(np.concatenate([[0], np.cumsum(np.bincount(ids_np.reshape(-1), minlength=e))]))
+    # with the tile list of the grouped tensor-core products: what moe_permute lists for the same choices
+    tiles_a = (i32(n * k + e), i32(n * k + e), i32(n * k + e), i32(1))
+    tiles_b = (i32(n * k + e), i32(n * k + e), i32(n * k + e), i32(1))
+    ops.moe_permute(ids_b, w_b, e, i32(e + 1), i32(n * k), f32(n * k), i32(n, k), st, tiles=tiles_a)
+    ops.route_small(h, wr, wg, f32(n, e + 1), i32(n, k), f32(n, k), f32(n), k, norm, i32(e + 1), i32(n * k), f32(n * k),
+                    i32(n, k), st, tiles=tiles_b)
+    n_t = int(tiles_a[3].item())
+    assert st.item() == 0 and int(tiles_b[3].item()) == n_t == int((np.bincount(ids_np.reshape(-1), minlength=e) > 0).sum())
+    for x, y in zip(tiles_a[:3], tiles_b[:3]):
+        assert torch.equal(x[:n_t], y[:n_t])
     inv, pt, pw = inverse.cpu().numpy(), perm_token.cpu().numpy(), perm_weight.cpu().numpy()
     assert sorted(inv.reshape(-1)) == list(range(n * k))
     for t in range(n):
