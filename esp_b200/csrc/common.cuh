@@ -102,9 +102,12 @@ static inline int esp_launch_status() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-#define ESP_PDL_DEFAULT_MASK 29
-// classes of kernels, so that the attribute can be tried class by class: ESP_B200_PDL is a bit mask
-enum : int { ESP_PDL_DENSE = 1, ESP_PDL_GROUPED = 2, ESP_PDL_ATTENTION = 4, ESP_PDL_SMALL = 8, ESP_PDL_GROUPED_AFTER = 16 };
+#define ESP_PDL_DEFAULT_MASK 61
+// classes of kernels, so that the attribute can be tried class by class: ESP_B200_PDL is a bit mask.  GROUPED: every
+// grouped product (off: it holds SM room while it waits for the routing); GROUPED_AFTER: a second grouped product
+// whose offsets were complete before the first one started; GROUPED_FITS: a short grouped product (gemm_skinny.cu).
+enum : int { ESP_PDL_DENSE = 1, ESP_PDL_GROUPED = 2, ESP_PDL_ATTENTION = 4, ESP_PDL_SMALL = 8, ESP_PDL_GROUPED_AFTER = 16,
+              ESP_PDL_GROUPED_FITS = 32 };
 static inline bool esp_pdl_enabled(int kind) {
     static int mask = -1;
     if (mask < 0) {

@@ -333,8 +333,15 @@ int launch_variant(const SkinnyParams& p, int groups, int tiles, cudaStream_t st
     }
     constexpr int TILES = WARPS / KS;
     dim3 grid((tiles + TILES - 1) / TILES, p.group_offsets && p.M < groups ? p.M : groups);   // every group that has rows starts below M
-    esp_launch_pdl(p.group_offsets ? (p.offsets_ready ? ESP_PDL_GROUPED_AFTER : ESP_PDL_GROUPED) : ESP_PDL_DENSE,
-                   gemm_skinny_kernel<NBLK, MODE, TC, KS>, grid, dim3(WARPS * 32), smem, stream, p);
+    // A grouped product set up early holds SM room while it waits for the routing, room that the shared expert's
+    // products on the second stream want: measured, it costs 1 to 5 % of a step of 3 to 8 tokens.  A short one (a few
+    // rows, a grid that fits the device at once, at most 128 MB of weights) gains by it: 3 % of the step at one and
+    // two tokens with 46 MB an expert set; with 293 MB (eight experts of 2560 x 3584) it lost 1.5 %.
+    const long long weight_bytes = (long long)p.M * (MODE == MODE_SWIGLU ? 2 : 1) * p.N * p.K * (long long)sizeof(bf16);
+    const bool fits = p.M <= 8 && (long long)grid.x * grid.y <= 148 * ESP_SKINNY_BLOCKS && weight_bytes <= (128ll << 20);
+    const int kind = !p.group_offsets ? ESP_PDL_DENSE : p.offsets_ready ? ESP_PDL_GROUPED_AFTER
+                     : fits && esp_pdl_enabled(ESP_PDL_GROUPED_FITS) ? ESP_PDL_GROUPED_FITS : ESP_PDL_GROUPED;
+    esp_launch_pdl(kind, gemm_skinny_kernel<NBLK, MODE, TC, KS>, grid, dim3(WARPS * 32), smem, stream, p);
     return esp_launch_status();
 }
 

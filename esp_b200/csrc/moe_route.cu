@@ -711,10 +711,10 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
                                const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
                                int top_k, float eps, int write_x, int early) {
     pdl_trigger();
-    // The kernel before this one in the stream made the experts' rows or the shared expert's row; the routing, the
-    // gate and the residual row were complete before it started (the experts' products are ordinary launches: each
-    // starts when its predecessor has ended), so they are read before the wait, while that kernel finishes.
-    // ``early`` 0: the experts' products are dependent launches too, and everything waits.
+    // The kernel before this one in the stream made the experts' rows or the shared expert's row.  It lets this one
+    // be set up only behind its own wait (the grouped product gives its signal when its weights are in), and by then
+    // the kernels before it have ended: the routing, the gate and the residual row are complete and are read before
+    // the wait, while that kernel finishes.  ``early`` 0 (every grouped product a dependent launch): everything waits.
     if (!early) pdl_wait();
     __shared__ int order[MAX_TOPK];
     __shared__ float scratch[33];
