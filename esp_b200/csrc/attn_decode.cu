@@ -303,20 +303,51 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int i = tid; i < heads * HD; i += THREADS) {
-        const int g = i / HD, d = i - g * HD;
+    // The row's splits: a warp takes a head at a time.  The weight exp(m - max) and the sum of every split are worked
+    // out once, a lane each, into the page buffers (free by now); then each lane adds up its columns over the splits
+    // in ascending order, several loads in flight, so a result does not depend on how the work is shared out.
+    constexpr int WCH = RING * ITEM * (int)sizeof(bf16) / ((THREADS / 32) * 2 * (int)sizeof(float));   // splits a pass
+    constexpr int NV = HD / 64;                             // pairs of columns per lane: 64 j + 2 lane, + 1
+    float* w_w = reinterpret_cast<float*>(ring) + (size_t)warp * 2 * WCH;
+    float* l_w = w_w + WCH;
+    for (int g = warp; g < heads; g += THREADS / 32) {
         const float* ml = part_ml + ((size_t)n * nh + h0 + g) * n_splits * 2;
         const float* po = part_o + ((size_t)n * nh + h0 + g) * n_splits * HD;
         float mx = -INFINITY;
-        for (int sp = s0; sp <= s1; sp++) mx = fmaxf(mx, __ldcg(ml + 2 * sp));
-        float denom = 0.f, num = 0.f;
-        for (int sp = s0; sp <= s1; sp++) {
-            const float m_sp = __ldcg(ml + 2 * sp);
-            const float w = m_sp == -INFINITY ? 0.f : expf(m_sp - mx);
-            denom += __ldcg(ml + 2 * sp + 1) * w;
-            num += __ldcg(po + (size_t)sp * HD + d) * w;
+        for (int sp = s0 + lane; sp <= s1; sp += 32) mx = fmaxf(mx, __ldcg(ml + 2 * sp));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        float denom = 0.f, num[NV][2];
+#pragma unroll
+        for (int j = 0; j < NV; j++) num[j][0] = num[j][1] = 0.f;
+        for (int c0 = s0; c0 <= s1; c0 += WCH) {
+            const int cn = min(WCH, s1 + 1 - c0);
+            __syncwarp();                                  // the pass (or head) before this one has been read
+            for (int i = lane; i < cn; i += 32) {
+                const float m_sp = __ldcg(ml + 2 * (c0 + i));
+                w_w[i] = m_sp == -INFINITY ? 0.f : expf(m_sp - mx);
+                l_w[i] = __ldcg(ml + 2 * (c0 + i) + 1);
+            }
+            __syncwarp();
+            const float* pc = po + (size_t)c0 * HD + lane * 2;
+#pragma unroll 8
+            for (int i = 0; i < cn; i++) {
+                const float w = w_w[i];
+                denom += l_w[i] * w;
+#pragma unroll
+                for (int j = 0; j < NV; j++) {
+                    const float2 v = __ldcg(reinterpret_cast<const float2*>(pc + (size_t)i * HD + j * 64));
+                    num[j][0] += v.x * w;
+                    num[j][1] += v.y * w;
+                }
+            }
         }
-        out[((size_t)n * nh + h0 + g) * HD + d] = __float2bfloat16_rn(denom > 0.f ? num / denom : 0.f);
+        bf16* orow = out + ((size_t)n * nh + h0 + g) * HD + lane * 2;
+#pragma unroll
+        for (int j = 0; j < NV; j++)
+            *reinterpret_cast<__nv_bfloat162*>(orow + j * 64) =
+                __nv_bfloat162(__float2bfloat16_rn(denom > 0.f ? num[j][0] / denom : 0.f),
+                               __float2bfloat16_rn(denom > 0.f ? num[j][1] / denom : 0.f));
     }
 }
 

@@ -454,7 +454,8 @@ def attn_decode_split(n_rows: int, nkv_blocks: int, positions: int) -> int:
     """Key positions per block: 128 or 256 while that still gives few blocks (so that every SM has work at
     batch 1), 512 once there are plenty (fewer partial results to combine).  128 only up to 4,096 positions:
     measured at batch 1, it gains 1 % there (16 key/value heads) and loses 7 % at 8,192 positions with 4
-    key/value heads, where a row's 64 partial results cost more to combine than the shorter blocks save."""
+    key/value heads, where a row's 64 partial results cost more to combine than the shorter blocks save (and
+    still 6 to 12 % at 8,000 to 32,000 positions with the combine's weights worked out once a split)."""
     if positions <= 4096 and n_rows * nkv_blocks * ((positions + 127) // 128) <= 1024:
         return 128
     return 256 if n_rows * nkv_blocks * ((positions + 255) // 256) <= 1024 else 512
