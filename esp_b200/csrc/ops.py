@@ -450,15 +450,20 @@ def qkv_rope_skinny(a, w_qkv, bias, tok_seq, tok_pos, cos, sin, q_out, k_cache, 
         _ptr(status, torch.int32), _stream()), "qkv_rope_skinny")
 
 
-def attn_decode_split(n_rows: int, nkv_blocks: int, positions: int) -> int:
-    """Key positions per block: 128 or 256 while that still gives few blocks (so that every SM has work at
-    batch 1), 512 once there are plenty (fewer partial results to combine).  128 only up to 4,096 positions:
-    measured at batch 1, it gains 1 % there (16 key/value heads) and loses 7 % at 8,192 positions with 4
-    key/value heads, where a row's 64 partial results cost more to combine than the shorter blocks save (and
-    still 6 to 12 % at 8,000 to 32,000 positions with the combine's weights worked out once a split)."""
-    if positions <= 4096 and n_rows * nkv_blocks * ((positions + 127) // 128) <= 1024:
+# blocks of the split-key kernel that one SM holds at a time, by head size (registers: 72 / 122 / 160 / 162 a thread)
+ATTN_DECODE_BLOCKS_PER_SM = {64: 7, 128: 4, 192: 3, 256: 3}
+
+
+def attn_decode_split(n_rows: int, nkv_blocks: int, positions: int, head_dim: int = 128, sm_count: int = 148) -> int:
+    """Key positions per block: the shortest of 128, 256 and 512 whose blocks the device still holds all at once
+    (every SM has work at batch 1, and no second, partly filled round of blocks follows), 512 beyond that
+    (fewer partial results to combine).  Measured with 16 key/value heads of 128 at 4,096 positions: against a
+    limit of 1,024 blocks, batch 2 gains 3.5 %, batch 3 1.5 %, batch 4 0 to 2 %.  128 only up to 4,096
+    positions: it gains 1 % there at batch 1 and loses 7 % at 8,192 positions with 4 key/value heads."""
+    room = sm_count * ATTN_DECODE_BLOCKS_PER_SM.get(head_dim, 3)
+    if positions <= 4096 and n_rows * nkv_blocks * ((positions + 127) // 128) <= room:
         return 128
-    return 256 if n_rows * nkv_blocks * ((positions + 255) // 256) <= 1024 else 512
+    return 256 if n_rows * nkv_blocks * ((positions + 255) // 256) <= room else 512
 
 
 ATTN_DECODE_COUNTERS = 65536
