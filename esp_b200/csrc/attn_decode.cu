@@ -410,16 +410,19 @@ int dispatch(int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, 
     if (split == 128)
         return launch_split_mma<HD, 128>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page,
                                          n_tokens, nh, nkv, window, n_splits, status, stream);
-    return split == 256 ? launch_split_mma<HD, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages,
+    if (split == 256)
+        return launch_split_mma<HD, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page,
+                                         n_tokens, nh, nkv, window, n_splits, status, stream);
+    return split == 512 ? launch_split_mma<HD, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages,
                                                      page, n_tokens, nh, nkv, window, n_splits, status, stream)
-                        : launch_split_mma<HD, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages,
-                                                     page, n_tokens, nh, nkv, window, n_splits, status, stream);
+                        : launch_split_mma<HD, 1024>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages,
+                                                      page, n_tokens, nh, nkv, window, n_splits, status, stream);
 }
 }  // namespace
 
 // Scratch: part_o float [n_tokens, nh, n_splits, hd], part_ml float [n_tokens, nh, n_splits, 2];
 // counters int [n_tokens * head groups], all zero when the call starts (the kernel leaves them zero);
-// split: key positions per block, 128, 256 or 512 (the caller picks: short splits when there are few rows, so
+// split: key positions per block, 128, 256, 512 or 1024 (the caller picks: short splits when there are few rows, so
 // that every SM still gets blocks); n_splits >= ceil(longest sequence / split).  Head sizes 64, 128, 192, 256; pages of 64 positions or any
 // size; any head counts with nh % nkv == 0.  ``seq_past`` (may be null): per sequence of the step, the positions
 // that were cached before it; with it, blocks whose keys are all older start their loads without waiting for the
@@ -429,7 +432,7 @@ ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_ca
                             const int* block_table, int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv,
                             int hd, int window, int split, int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || (split != 128 && split != 256 && split != 512) ||
+    if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || (split != 128 && split != 256 && split != 512 && split != 1024) ||
         page != PAGE_KEYS)
         return (int)cudaErrorInvalidValue;
 #define ESP_HD(HD) return dispatch<HD>(split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \

@@ -456,14 +456,19 @@ ATTN_DECODE_BLOCKS_PER_SM = {64: 7, 128: 4, 192: 3, 256: 3}
 
 def attn_decode_split(n_rows: int, nkv_blocks: int, positions: int, head_dim: int = 128, sm_count: int = 148) -> int:
     """Key positions per block: the shortest of 128, 256 and 512 whose blocks the device still holds all at once
-    (every SM has work at batch 1, and no second, partly filled round of blocks follows), 512 beyond that
-    (fewer partial results to combine).  Measured with 16 key/value heads of 128 at 4,096 positions: against a
-    limit of 1,024 blocks, batch 2 gains 3.5 %, batch 3 1.5 %, batch 4 0 to 2 %.  128 only up to 4,096
-    positions: it gains 1 % there at batch 1 and loses 7 % at 8,192 positions with 4 key/value heads."""
+    (every SM has work at batch 1, and no second, partly filled round of blocks follows); 1,024 when there are
+    more blocks than that (long blocks: fewer starts, ends and partial results).  Measured with 16 key/value heads
+    of 128 at 4,096 positions: holding to one round instead of a limit of 1,024 blocks, batch 2 gains 3.5 %, batch 3
+    1.5 %; 1,024 instead of 512 positions a block, batch 8 gains 1 to 2 %, batch 16 2.5 %, batch 64 1.5 %, batch 8 at
+    8,000 positions 5 %.  128 only up to 4,096 positions: it gains 1 % there at batch 1 and loses 7 % at 8,192
+    positions with 4 key/value heads."""
     room = sm_count * ATTN_DECODE_BLOCKS_PER_SM.get(head_dim, 3)
     if positions <= 4096 and n_rows * nkv_blocks * ((positions + 127) // 128) <= room:
         return 128
-    return 256 if n_rows * nkv_blocks * ((positions + 255) // 256) <= room else 512
+    for split in (256, 512):
+        if n_rows * nkv_blocks * ((positions + split - 1) // split) <= room:
+            return split
+    return 1024
 
 
 ATTN_DECODE_COUNTERS = 65536
@@ -472,15 +477,15 @@ ATTN_DECODE_COUNTERS = 65536
 def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, block_table, page, nh, nkv, hd,
                 window, split, n_splits, status, seq_past=None):
     """Split-key attention for few token rows (bfloat16; head sizes 64, 128, 192, 256).  ``split``: key
-    positions per block (128, 256 or 512); n_splits >= ceil(positions / split).  part_o float32
+    positions per block (128, 256, 512 or 1024); n_splits >= ceil(positions / split).  part_o float32
     [N, nh, n_splits, hd] and part_ml float32 [N, nh, n_splits, 2] are scratch; ``counters``: int32, at least
     N * nh words, all zero (the kernel leaves them zero).  ``seq_past`` (int32 per sequence of the step: the
     positions cached before it): blocks whose keys are all older then load them without waiting for the
     kernel before this one, which writes the step's new keys and values."""
     if counters.numel() < q.shape[0] * nh:
         raise Backend("attn_decode: too few counters for this many rows and heads")
-    if split not in (128, 256, 512):
-        raise Backend(f"attn_decode: split {split} is not 128, 256 or 512")
+    if split not in (128, 256, 512, 1024):
+        raise Backend(f"attn_decode: split {split} is not 128, 256, 512 or 1024")
     if hd not in (64, 128, 192, 256):
         raise Backend(f"attn_decode: head size {hd} is not one of 64, 128, 192, 256")
     n = q.shape[0]

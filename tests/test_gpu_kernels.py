@@ -593,7 +593,7 @@ def test_gemm_skinny_grouped_fewer_rows_than_groups(counts_at):
     assert torch.all(c[total:] == 7.0) and torch.all(act[total:] == 7.0)
 
 
-@pytest.mark.parametrize("split", [128, 256, 512])
+@pytest.mark.parametrize("split", [128, 256, 512, 1024])
 @pytest.mark.parametrize("nh, nkv, hd, window", [(4, 4, 128, None), (6, 2, 64, None), (7, 1, 128, 100), (8, 1, 192, None),
                                                  (4, 2, 256, 300), (16, 16, 128, 65)])
 def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window, split):
@@ -636,6 +636,48 @@ def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window, split):
     for i, (s, p, target) in enumerate(queries):
         ref = attention_reference(qd[i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(), p, window, group)
         close(out[i].view(nh, hd), ref, dtype, f"query {i} (sequence {s}, position {p}, target key {target})")
+
+
+@pytest.mark.parametrize("split", [256, 1024])
+@pytest.mark.parametrize("nh, nkv, hd, window", [(7, 1, 128, None), (4, 4, 128, 1500), (6, 2, 64, None), (2, 1, 256, 1030)])
+def test_attn_decode_over_many_splits_of_a_long_sequence(nh, nkv, hd, window, split):
+    """2,500 positions in scattered pages: keys that matter at the boundaries of the 1,024-position splits, at the
+    window's edge and at both ends; the combine of the row's splits (up to ten here, seven heads to a block in the
+    first case) against the float64 reference."""
+    torch.manual_seed(5)
+    dtype = torch.bfloat16
+    length, group = 2500, nh // nkv
+    pages = (length + 63) // 64
+    order = torch.randperm(pages + 3).tolist()
+    tables = [order[:pages]]
+    ks, vs = [torch.randn(length, nkv, hd) * 0.3], [torch.randn(length, nkv, hd)]
+    last = length - 1
+    w = window or 10 ** 9
+    targets = sorted({0, 1023, 1024, 1025, 2047, 2048, 2304, max(0, last - w + 1), max(0, last - w), last})
+    queries = [(0, last, t) for t in targets] + [(0, 1024, 1023), (0, 1024, 1024), (0, 1023, 0), (0, 2048, 1024)]
+    q = torch.randn(len(queries), nh, hd) * 0.3
+    for i, (s, p, target) in enumerate(queries):
+        for h in range(nh):
+            ks[s][target, h // group] = ks[s][target, h // group] / ks[s][target, h // group].norm() * 6.0
+            q[i, h] = ks[s][target, h // group] * (np.sqrt(hd) * 3.0 / 6.0)
+    qd = q.to(dtype)
+    kc, vc = paged(ks, vs, tables, pages + 3, nkv, hd, dtype)
+    table = torch.tensor(tables, dtype=torch.int32, device=DEV)
+    n = len(queries)
+    out = torch.empty(n, nh * hd, dtype=dtype, device=DEV)
+    n_splits = (length + split - 1) // split
+    part_o = torch.full((n, nh, n_splits, hd), float("nan"), device=DEV)
+    part_ml = torch.full((n, nh, n_splits, 2), float("nan"), device=DEV)
+    st = status()
+    counters = torch.zeros(n * nh, dtype=torch.int32, device=DEV)
+    ops.attn_decode(qd.reshape(n, nh * hd).to(DEV), kc, vc, out, part_o, part_ml, counters,
+                    torch.zeros(n, dtype=torch.int32, device=DEV),
+                    torch.tensor([p for _, p, _ in queries], dtype=torch.int32, device=DEV), table, 64, nh, nkv, hd,
+                    window, split, n_splits, st)
+    assert st.item() == 0 and not counters.any(), "the counters must be left at zero"
+    for i, (s, p, target) in enumerate(queries):
+        ref = attention_reference(qd[i].float(), ks[s].to(dtype).float(), vs[s].to(dtype).float(), p, window, group)
+        close(out[i].view(nh, hd), ref, dtype, f"query {i} (position {p}, target key {target})")
 
 
 @pytest.mark.parametrize("nh, nkv, hd, window", [(4, 4, 128, None), (6, 2, 64, None), (4, 1, 24, 16), (2, 1, 128, 100),
