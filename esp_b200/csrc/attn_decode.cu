@@ -1,8 +1,8 @@
 // Decode attention over the paged bfloat16 cache (pages of 64 positions), split over the keys.
 //
 // One block = one token row, one key/value head with the query heads that share
-// it, and one split of SPLIT consecutive key positions aligned to absolute
-// multiples of SPLIT.  The block streams its pages' keys and values once from
+// it, and one split of ``split_keys`` consecutive key positions aligned to absolute
+// multiples of that number.  The block streams its pages' keys and values once from
 // HBM by TMA, keeps scores, softmax and sums in float, and writes an
 // unnormalised partial result (running maximum, sum, weighted values) to
 // scratch.  The last block of a row to finish combines the row's splits in
@@ -47,7 +47,7 @@ __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
 constexpr int PAGE_KEYS = 64, RING = 2;
 
 // One block = one token row, one key/value head with the (up to 16) query heads that share it, and one split
-// of SPLIT key positions, i.e. SPLIT / 64 pages.  The pages' keys and values are fetched by TMA into a ring
+// of split_keys key positions, i.e. split_keys / 64 pages.  The pages' keys and values are fetched by TMA into a ring
 // of RING shared-memory buffers while earlier pages are being used.  Both products run on the tensor cores
 // (mma.sync m16n8k16) with the block's heads as the 16-row operand, so a page costs the same whether one
 // head or sixteen read it.  Scores: warp w takes keys 16w..16w+15 of the page, key fragments by ldmatrix.
@@ -84,13 +84,13 @@ __device__ __forceinline__ const bf16* tile_at(const bf16* tile, int r, int d) {
     return tile + (d >> 6) * (PAGE_KEYS * 64) + r * 64 + ((((d & 63) >> 3) ^ (r & 7)) << 3);
 }
 
-template <int HD, int SPLIT>
+template <int HD>
 __global__ void __launch_bounds__(THREADS)
 attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ seq_past, const int* __restrict__ block_table, int table_stride, int n_pages,
-                      int page, int nh, int nkv, int window, int n_splits, int* __restrict__ status) {
+                      int page, int nh, int nkv, int window, int split_keys, int n_splits, int* __restrict__ status) {
     pdl_trigger();
     constexpr int ITEM = PAGE_KEYS * HD;
     constexpr int NBW = HD / 32;                   // 8-column blocks of the head that one warp accumulates
@@ -110,7 +110,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const int heads = min(MMA_HEADS, (kvh + 1) * group - h0);
     const int pos = tok_pos[n], seq = tok_seq[n];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int j0 = max(lo, split * SPLIT), j1 = min(pos, split * SPLIT + SPLIT - 1);
+    const int j0 = max(lo, split * split_keys), j1 = min(pos, split * split_keys + split_keys - 1);
     if (j0 > j1) return;
     const int first_page = j0 / PAGE_KEYS, n_pg = j1 / PAGE_KEYS - first_page + 1, n_items = 2 * n_pg;
 
@@ -293,7 +293,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     __shared__ int is_last;
     __threadfence();
     __syncthreads();
-    const int s0 = lo / SPLIT, s1 = pos / SPLIT;
+    const int s0 = lo / split_keys, s1 = pos / split_keys;
     if (tid == 0) {
         int* c = counters + (size_t)n * gridDim.y + blockIdx.y;
         const int done = atomicAdd(c, 1);
@@ -376,8 +376,8 @@ int make_cache_map(CUtensorMap* map, const void* base, unsigned long long rows, 
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int HD, int SPLIT>
-int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
+template <int HD>
+int launch_split_mma(int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
                      const int* tok_seq, const int* tok_pos, const int* seq_past, const int* table, int stride, int n_pages, int page,
                      int n_tokens, int nh, int nkv, int window, int n_splits, int* status, cudaStream_t stream) {
     CUtensorMap map_k, map_v;
@@ -391,38 +391,21 @@ int launch_split_mma(const bf16* q, const bf16* k, const bf16* v, bf16* out, flo
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
     if (!raised[device]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel<HD, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+        cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
         if (e != cudaSuccess) return (int)e;
         raised[device] = true;
     }
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + MMA_HEADS - 1) / MMA_HEADS), n_splits);
-    esp_launch_pdl(ESP_PDL_ATTENTION, attn_split_mma_kernel<HD, SPLIT>, dim3(grid), dim3(THREADS), dyn, stream, map_k, map_v, q, out, po, pml, counters, tok_seq, tok_pos,
-                                                                     seq_past, table, stride, n_pages, page, nh, nkv, window, n_splits,
-                                                                     status);
+    esp_launch_pdl(ESP_PDL_ATTENTION, attn_split_mma_kernel<HD>, dim3(grid), dim3(THREADS), dyn, stream, map_k, map_v, q, out, po, pml,
+                   counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page, nh, nkv, window, split, n_splits, status);
     return esp_launch_status();
-}
-
-template <int HD>
-int dispatch(int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
-             const int* tok_seq, const int* tok_pos, const int* seq_past, const int* table, int stride, int n_pages, int page, int n_tokens, int nh,
-             int nkv, int window, int n_splits, int* status, cudaStream_t stream) {
-    if (split == 128)
-        return launch_split_mma<HD, 128>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page,
-                                         n_tokens, nh, nkv, window, n_splits, status, stream);
-    if (split == 256)
-        return launch_split_mma<HD, 256>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page,
-                                         n_tokens, nh, nkv, window, n_splits, status, stream);
-    return split == 512 ? launch_split_mma<HD, 512>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages,
-                                                     page, n_tokens, nh, nkv, window, n_splits, status, stream)
-                        : launch_split_mma<HD, 1024>(q, k, v, out, po, pml, counters, tok_seq, tok_pos, seq_past, table, stride, n_pages,
-                                                      page, n_tokens, nh, nkv, window, n_splits, status, stream);
 }
 }  // namespace
 
 // Scratch: part_o float [n_tokens, nh, n_splits, hd], part_ml float [n_tokens, nh, n_splits, 2];
 // counters int [n_tokens * head groups], all zero when the call starts (the kernel leaves them zero);
-// split: key positions per block, 128, 256, 512 or 1024 (the caller picks: short splits when there are few rows, so
+// split: key positions per block, a multiple of 64 (the caller picks: short splits when there are few rows, so
 // that every SM still gets blocks); n_splits >= ceil(longest sequence / split).  Head sizes 64, 128, 192, 256; pages of 64 positions or any
 // size; any head counts with nh % nkv == 0.  ``seq_past`` (may be null): per sequence of the step, the positions
 // that were cached before it; with it, blocks whose keys are all older start their loads without waiting for the
@@ -432,12 +415,12 @@ ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_ca
                             const int* block_table, int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv,
                             int hd, int window, int split, int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || (split != 128 && split != 256 && split != 512 && split != 1024) ||
+    if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || split < PAGE_KEYS || split % PAGE_KEYS != 0 ||
         page != PAGE_KEYS)
         return (int)cudaErrorInvalidValue;
-#define ESP_HD(HD) return dispatch<HD>(split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
-                                       part_ml, counters, tok_seq, tok_pos, seq_past, block_table, table_stride, n_pages, page, n_tokens, nh,   \
-                                       nkv, window, n_splits, status, stream)
+#define ESP_HD(HD) return launch_split_mma<HD>(split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
+                                               part_ml, counters, tok_seq, tok_pos, seq_past, block_table, table_stride, n_pages, \
+                                               page, n_tokens, nh, nkv, window, n_splits, status, stream)
     switch (hd) {
         case 64: ESP_HD(64);
         case 128: ESP_HD(128);

@@ -17,7 +17,7 @@
 // Limits: n_tokens * nh * n_splits * (hd + 2) must not exceed esp_attn_decode_noalloc_capacity() (the
 // array less the ESP_NOALLOC_COUNTERS words kept for the kernel's counters) and n_tokens * nh must not
 // exceed ESP_NOALLOC_COUNTERS, else the call returns ESP_NOALLOC_TOO_LARGE and launches nothing.  hd is
-// 64, 128, 192 or 256 and split 128, 256, 512 or 1024, as for esp_attn_decode.
+// 64, 128, 192 or 256 and split a multiple of 64, as for esp_attn_decode.
 // Sharing: all calls on a device use the same array.  It keeps whatever the last call left there.  The
 // kernel writes every partial result it later reads, so that part needs no clearing; the counters at
 // the array's end must be zero when a call starts: they are zero when the library is loaded and each

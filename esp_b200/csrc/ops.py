@@ -8,6 +8,7 @@ these functions: without the compiled library they raise.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
@@ -454,21 +455,32 @@ def qkv_rope_skinny(a, w_qkv, bias, tok_seq, tok_pos, cos, sin, q_out, k_cache, 
 ATTN_DECODE_BLOCKS_PER_SM = {64: 7, 128: 4, 192: 3, 256: 3}
 
 
+@functools.lru_cache(maxsize=4096)
 def attn_decode_split(n_rows: int, nkv_blocks: int, positions: int, head_dim: int = 128, sm_count: int = 148) -> int:
-    """Key positions per block: the shortest of 128, 256 and 512 whose blocks the device still holds all at once
-    (every SM has work at batch 1, and no second, partly filled round of blocks follows); 1,024 when there are
-    more blocks than that (long blocks: fewer starts, ends and partial results).  Measured with 16 key/value heads
-    of 128 at 4,096 positions: holding to one round instead of a limit of 1,024 blocks, batch 2 gains 3.5 %, batch 3
-    1.5 %; 1,024 instead of 512 positions a block, batch 8 gains 1 to 2 %, batch 16 2.5 %, batch 64 1.5 %, batch 8 at
-    8,000 positions 5 %.  128 only up to 4,096 positions: it gains 1 % there at batch 1 and loses 7 % at 8,192
-    positions with 4 key/value heads."""
+    """Key positions per block (whole pages of 64), the same for every row of the step: the length with the least
+    estimated time.  The estimate, fitted to steps of 1 to 64 rows with 16 key/value heads of 128 at 4,096
+    positions and checked at 8,000 to 32,000 positions with 4: the device holds ``room`` blocks at once and needs
+    three quarters of that many to draw the full memory rate; blocks start as others end, so the time is that of
+    all blocks' pages at the full rate, plus what the last, partly filled round lacks of three quarters, plus one
+    page's time a block for its start, its partial result and its share of the combine.  It gives one round of
+    short blocks to a few rows (128 positions at batch 1, 256 at batch 2, 1,024 at batch 8), whole rows to 32 or
+    64 rows, and thirds or quarters of a row where whole rows would leave a round nearly empty (batch 24, 40, 48).
+    Against the earlier choice among 128, 256 and 512 under a limit of 1,024 blocks: batch 2 +3.5 %, 5 +6 %, 6 +5 %,
+    8 +1.5 %, 16 +4 %, 32 +4 %, 48 +2 %, 64 +4.5 %; batch 8 at 8,000 positions +5 %.  At least 128 positions, 256 beyond
+    4,096 (at batch 1, 128 gains 1 % at 4,096 positions and loses 7 % at 8,192 with 4 key/value heads)."""
     room = sm_count * ATTN_DECODE_BLOCKS_PER_SM.get(head_dim, 3)
-    if positions <= 4096 and n_rows * nkv_blocks * ((positions + 127) // 128) <= room:
-        return 128
-    for split in (256, 512):
-        if n_rows * nkv_blocks * ((positions + split - 1) // split) <= room:
-            return split
-    return 1024
+    full_rate = 0.75 * room
+    pairs = max(1, n_rows * nkv_blocks)
+    pages = max(1, (positions + 63) // 64)
+    shortest = min(pages, 2 if positions <= 4096 else 4)
+    best, best_cost = pages, None
+    for length in range(pages, shortest - 1, -1):          # longest first: it wins a tie
+        blocks = pairs * ((pages + length - 1) // length)
+        last = blocks % room
+        cost = (blocks + (full_rate - last if 0 < last < full_rate else 0.0)) * (length + 1.0)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = length, cost
+    return 64 * best
 
 
 ATTN_DECODE_COUNTERS = 65536
@@ -477,15 +489,15 @@ ATTN_DECODE_COUNTERS = 65536
 def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, block_table, page, nh, nkv, hd,
                 window, split, n_splits, status, seq_past=None):
     """Split-key attention for few token rows (bfloat16; head sizes 64, 128, 192, 256).  ``split``: key
-    positions per block (128, 256, 512 or 1024); n_splits >= ceil(positions / split).  part_o float32
+    positions per block (a multiple of 64); n_splits >= ceil(positions / split).  part_o float32
     [N, nh, n_splits, hd] and part_ml float32 [N, nh, n_splits, 2] are scratch; ``counters``: int32, at least
     N * nh words, all zero (the kernel leaves them zero).  ``seq_past`` (int32 per sequence of the step: the
     positions cached before it): blocks whose keys are all older then load them without waiting for the
     kernel before this one, which writes the step's new keys and values."""
     if counters.numel() < q.shape[0] * nh:
         raise Backend("attn_decode: too few counters for this many rows and heads")
-    if split not in (128, 256, 512, 1024):
-        raise Backend(f"attn_decode: split {split} is not 128, 256, 512 or 1024")
+    if split < 64 or split % 64:
+        raise Backend(f"attn_decode: split {split} is not a multiple of 64")
     if hd not in (64, 128, 192, 256):
         raise Backend(f"attn_decode: head size {hd} is not one of 64, 128, 192, 256")
     n = q.shape[0]

@@ -638,7 +638,7 @@ def test_attn_decode_finds_the_key_that_matters(nh, nkv, hd, window, split):
         close(out[i].view(nh, hd), ref, dtype, f"query {i} (sequence {s}, position {p}, target key {target})")
 
 
-@pytest.mark.parametrize("split", [256, 1024])
+@pytest.mark.parametrize("split", [192, 640, 1024])
 @pytest.mark.parametrize("nh, nkv, hd, window", [(7, 1, 128, None), (4, 4, 128, 1500), (6, 2, 64, None), (2, 1, 256, 1030)])
 def test_attn_decode_over_many_splits_of_a_long_sequence(nh, nkv, hd, window, split):
     """2,500 positions in scattered pages: keys that matter at the boundaries of the 1,024-position splits, at the
