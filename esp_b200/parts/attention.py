@@ -156,7 +156,9 @@ class Attention(Part):
             positions = table.shape[1] * layer.page
             group = s.num_heads // s.num_kv_heads
             kv_blocks = s.num_kv_heads * ((group + 15) // 16)
-            split = ops.attn_decode_split(n, kv_blocks, positions, s.head_dim, rt.sm_count)
+            # a windowed layer reads at most window + a page of each row, wherever in the table that lies
+            span = min(positions, s.window + layer.page) if s.window else positions
+            split = ops.attn_decode_split(n, kv_blocks, span, s.head_dim, rt.sm_count)
             n_splits = (positions + split - 1) // split
             part_o = rt.ws.get("attn_part_o", (n, s.num_heads, n_splits, s.head_dim), torch.float32)
             part_ml = rt.ws.get("attn_part_ml", (n, s.num_heads, n_splits, 2), torch.float32)

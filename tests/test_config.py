@@ -164,3 +164,18 @@ def test_which_grouped_kernel_a_step_takes():
     assert not linear.grouped_uses_tc05(a, w, 127)
     assert not linear.grouped_uses_tc05(a.float(), w.float(), 4096, 1024)
     assert not linear.grouped_uses_tc05(a[:, :60], w[:, :, :60], 4096, 1024)      # K no multiple of 8
+
+
+def test_how_many_positions_a_block_of_the_decode_attention_takes():
+    """Whole pages, never fewer than the minimum, few enough splits that one round of blocks holds them when the
+    rows are few, and the choices that were measured (16 key/value heads of 128, 4,096 positions)."""
+    from esp_b200.csrc import ops
+    room = 148 * ops.ATTN_DECODE_BLOCKS_PER_SM[128]
+    for rows, kv, positions in [(1, 16, 4096), (2, 16, 4096), (5, 16, 4096), (8, 16, 4096), (16, 16, 4096), (1, 4, 32000),
+                                (8, 4, 32000), (3, 7, 1000), (1, 1, 64), (1, 1, 65), (64, 16, 256), (7, 3, 12345)]:
+        split = ops.attn_decode_split(rows, kv, positions)
+        assert split % 64 == 0 and split >= min(128 if positions <= 4096 else 256, 64 * ((positions + 63) // 64))
+        if rows * kv * 2 <= room:
+            assert rows * kv * ((positions + split - 1) // split) <= room, (rows, kv, positions, split)
+    assert [ops.attn_decode_split(b, 16, 4096) for b in (1, 2, 4, 8, 16, 32, 48, 64)] == [128, 256, 512, 1024, 2048, 4096, 1408, 4096]
+    assert ops.attn_decode_split(1, 4, 32000) == 256 and ops.attn_decode_split(1, 16, 8000) == 256
