@@ -3,7 +3,8 @@
 The reference has no generation command; the options here carry the names and
 meanings of its request (crates/esp/src/infer/provider.rs:91-117):
 ``--max-tokens``, ``--temperature`` (0 = greedy), ``--top-p``, ``--seed``,
-``--stop``.
+``--stop``.  ``generate`` takes a model folder (``--model``) or a configuration
+whose model gets random weights from a seed (``--random-config``, ``--weights-seed``).
 """
 from __future__ import annotations
 
@@ -23,8 +24,11 @@ def cmd_generate(a) -> int:
     for ids in a.prompt_ids or []:
         reqs.append(GenerationRequest(prompt_ids=_ids(ids), max_tokens=a.max_tokens, temperature=a.temperature,
                                       top_p=a.top_p, seed=a.seed, stop=a.stop or [], stop_token_ids=a.stop_token_id or []))
+    if (a.model is None) == (a.random_config is None):
+        print("give either --model DIR or --random-config FILE (with --weights-seed)", file=sys.stderr)
+        return 2
     if a.prompt:
-        tok = load_tokenizer(a.model)
+        tok = load_tokenizer(a.model) if a.model is not None else None
         if tok is None:
             print("text prompts need tokenizer.json in the model folder (and the tokenizers package); "
                   "give --prompt-ids", file=sys.stderr)
@@ -38,12 +42,21 @@ def cmd_generate(a) -> int:
         return 2
     # the cache is sized for the requests at hand (prompt + what each may generate, in whole pages),
     # not for the most the model could ever hold
-    window = config_from_json(a.model).plan().max_positions
+    config = config_from_json(a.model if a.model is not None else a.random_config)
+    window = config.plan().max_positions
     if a.max_context is not None:
         window = min(window, a.max_context)
     cache_tokens = a.cache_tokens or cache_tokens_for([len(r.prompt_ids) for r in reqs], a.max_tokens, window, a.max_batch)
-    prov = DecoderProvider.load(a.model, dtype=a.dtype, device=a.device, max_batch=a.max_batch,
-                                max_context=a.max_context, max_tokens=cache_tokens)
+    if a.model is not None:
+        prov = DecoderProvider.load(a.model, dtype=a.dtype, device=a.device, max_batch=a.max_batch,
+                                    max_context=a.max_context, max_tokens=cache_tokens)
+    else:
+        # weights made on the device from the configuration and the seed: the same values that
+        # ``random-model`` with this seed writes into a folder
+        from .weights import InitSpec
+        prov = DecoderProvider.from_random(config, a.weights_seed, init=InitSpec(a.weight_std, a.bias_std, a.norm_std),
+                                           dtype=a.dtype, device=a.device, max_batch=a.max_batch,
+                                           max_context=a.max_context, max_tokens=cache_tokens, stored_dtype=a.store_dtype)
     if a.profile:
         # one eager prefill of the first request and one eager decode step of it, timed kernel by kernel
         from .engine import StepEntry
@@ -84,7 +97,15 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="esp_b200", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="command", required=True)
     g = sub.add_parser("generate", help="generate tokens for one or more prompts")
-    g.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    g.add_argument("--model", default=None, help="folder with config.json and model.safetensors")
+    g.add_argument("--random-config", default=None,
+                   help="instead of --model: a config.json (or a folder with one) whose model gets random weights")
+    g.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights of --random-config")
+    g.add_argument("--store-dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                   help="with --random-config: the dtype a folder of these weights would hold (as random-model)")
+    g.add_argument("--weight-std", type=float, default=0.02)
+    g.add_argument("--bias-std", type=float, default=0.0)
+    g.add_argument("--norm-std", type=float, default=0.0)
     g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     g.add_argument("--device", default="cuda:0")
     g.add_argument("--prompt-ids", action="append", help="token ids, comma or space separated; repeat for a batch")

@@ -143,11 +143,16 @@ class DecoderProvider:
 
     @classmethod
     def from_random(cls, config, seed: int = 0, init=None, dtype="bfloat16", device="cuda:0", max_batch: int = 64,
-                    max_context: Optional[int] = None, max_tokens: Optional[int] = None) -> "DecoderProvider":
+                    max_context: Optional[int] = None, max_tokens: Optional[int] = None,
+                    stored_dtype=None) -> "DecoderProvider":
+        """Random weights made on the device.  ``stored_dtype``: the dtype a model
+        folder of these weights would store them in (default: ``dtype``); with the
+        same configuration, seed, ``init`` and stored dtype the values are those
+        that ``write_model_folder`` writes."""
         from .weights import InitSpec
         fit = max_tokens is None
         max_tokens = cls._cache_tokens(config, max_batch, max_context, max_tokens)
-        engine = Engine.from_random(config, seed, init or InitSpec(), dtype=dtype, device=device,
+        engine = Engine.from_random(config, seed, init or InitSpec(), stored_dtype=stored_dtype, dtype=dtype, device=device,
                                     max_tokens=max_tokens, shrink_to_fit=fit)
         return cls(engine, None, max_batch)
 

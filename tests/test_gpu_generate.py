@@ -117,6 +117,27 @@ def test_command_line_generates(folders, capsys):
     assert out["token_ids"] == plain.generate(c, w, p, 5) and out["finish_reason"] == "length"
 
 
+def test_command_line_with_random_weights_equals_the_folder_of_the_same_seed(folders, tmp_path, capsys):
+    """``generate --random-config`` makes on the device the weights that ``random-model`` with the same seed and
+    deviations writes into a folder: the same tokens either way, and the tokens of the plain implementation."""
+    import json
+    from esp_b200.cli import main
+    config = str(folders["B"] / "config.json")
+    out = tmp_path / "written"
+    spec = ["--weights-seed", "31", "--weight-std", "0.05", "--bias-std", "0.02", "--norm-std", "0.01"]
+    assert main(["random-model", "--config", config, "--out", str(out)] + spec) == 0
+    capsys.readouterr()
+    p = prompts("B", [7, 19])
+    ask = ["--dtype", "float32", "--max-tokens", "6"] + [x for q in p for x in ("--prompt-ids", ",".join(map(str, q)))]
+    assert main(["generate", "--model", str(out)] + ask) == 0
+    from_folder = [json.loads(line)["token_ids"] for line in capsys.readouterr().out.strip().splitlines()]
+    assert main(["generate", "--random-config", config] + spec + ask) == 0
+    from_seed = [json.loads(line)["token_ids"] for line in capsys.readouterr().out.strip().splitlines()]
+    c, w = plain.load_model(out)
+    assert from_folder == from_seed == [plain.generate(c, w, q, 6) for q in p]
+    assert main(["generate"] + ask) == 2 and main(["generate", "--model", str(out), "--random-config", config] + ask) == 2
+
+
 def test_waiting_and_one_step_ahead_agree_bfloat16(folders):
     """Seeded sampling in bfloat16 with a stop token and unequal budgets: the loop that launches the next step
     before it reads this one's tokens gives the tokens of the loop that waits, and hands every slot back."""
