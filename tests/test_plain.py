@@ -71,6 +71,21 @@ def test_recorded_outputs_of_a_checkpoint_whose_head_size_is_not_width_over_head
     assert off > 1e-5, off
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_recorded_outputs_of_a_plain_dense_checkpoint(dtype):
+    """The reference's dense ``llama`` checkpoint: the same attention and feed-forward code with no bias, no
+    window, one key/value head for two query heads and a head size equal to width / heads.  With the ``qwen2`` and
+    ``mistral`` cases it shows that neither the window nor the explicit head size leaks into the case without them."""
+    case = CASES["llama"]
+    c, w = plain.load_model(GOLDEN / "llama")
+    assert [plain.layer_window(c, i) for i in range(2)] == [None, None]
+    assert not any(name.endswith("_proj.bias") for name in w)
+    logits = plain.forward_logits(c, w, case["input_ids"], dtype)
+    err = np.abs(logits[-1] - np.asarray(case["last_logits"], dtype=np.float32)).max()
+    assert err < (2e-6 if dtype is np.float32 else 5e-7), err
+    assert plain.generate(c, w, case["input_ids"], len(case["generated_ids"]), dtype=dtype) == case["generated_ids"]
+
+
 def test_splitmix64_known_values():
     # first outputs of splitmix64 from seed 0 (public test vector of the generator)
     r = plain.SplitMix64(0)
